@@ -1,0 +1,172 @@
+"""Compiles the kernel library for sm_100a with nvcc and loads it.
+
+The library is plain CUDA behind C entry points (no framework headers), so a fresh
+checkout compiles in well under a minute. It is built next to the sources in
+``csrc/_build/`` (or in a per-user temporary folder when the checkout is read-only) at
+the first call that needs a kernel, and rebuilt when a source or a flag changes. While
+nvcc runs, a line is printed to stderr every few seconds.
+"""
+from __future__ import annotations
+
+import ctypes
+import fcntl
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from typing import List, Optional
+
+CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "libllmrs_b200.so"
+# Fast math stays off: norms, softmax and rotation are checked against float32 references.
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC"]
+ABI_VERSION = 1
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _log(msg: str) -> None:
+    print(f"[llm_rs_b200 build] {msg}", file=sys.stderr, flush=True)
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+
+
+def _headers() -> List[str]:
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+
+
+def _fingerprint() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for name in sources() + _headers():
+        h.update(name.encode())
+        with open(os.path.join(CSRC_DIR, name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def find_nvcc() -> Optional[str]:
+    for base in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH"), "/usr/local/cuda"):
+        if base:
+            cand = os.path.join(base, "bin", "nvcc")
+            if os.path.isfile(cand) and os.access(cand, os.X_OK):
+                return cand
+    return shutil.which("nvcc")
+
+
+def _build_dirs() -> List[str]:
+    dirs = [os.path.join(CSRC_DIR, "_build")]
+    tmp = os.path.join(tempfile.gettempdir(), f"llm_rs_b200_build_{os.getuid()}")
+    dirs.append(tmp)
+    return dirs
+
+
+def _is_current(build_dir: str, fp: str) -> bool:
+    stamp = os.path.join(build_dir, "stamp.json")
+    lib = os.path.join(build_dir, LIB_NAME)
+    if not (os.path.isfile(stamp) and os.path.isfile(lib)):
+        return False
+    try:
+        with open(stamp) as f:
+            return json.load(f).get("fingerprint") == fp
+    except (OSError, ValueError):
+        return False
+
+
+def _writable_dir() -> str:
+    for d in _build_dirs():
+        try:
+            os.makedirs(d, exist_ok=True)
+            probe = os.path.join(d, f".probe_{os.getpid()}")
+            with open(probe, "w"):
+                pass
+            os.unlink(probe)
+            return d
+        except OSError:
+            continue
+    raise KernelBuildError(f"no writable folder for the kernel library among {_build_dirs()}")
+
+
+def _compile(build_dir: str, fp: str) -> None:
+    nvcc = find_nvcc()
+    if nvcc is None:
+        raise KernelBuildError(
+            "the CUDA kernel library is not built and nvcc was not found (looked in $CUDA_HOME, "
+            "/usr/local/cuda and PATH); this engine has no fallback without its kernels")
+    srcs = sources()
+    _log(f"compiling {len(srcs)} CUDA sources for sm_100a with {nvcc} into {build_dir}")
+    t0 = time.time()
+    procs = []
+    for name in srcs:
+        obj = os.path.join(build_dir, name[:-3] + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, name), "-o", obj]
+        procs.append((name, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    pending = list(procs)
+    last = time.time()
+    while pending:
+        for item in list(pending):
+            name, _, p = item
+            if p.poll() is not None:
+                out = p.stdout.read()
+                pending.remove(item)
+                if p.returncode != 0:
+                    for _, _, q in pending:
+                        q.kill()
+                    raise KernelBuildError(f"nvcc failed on {name}:\n{out}")
+                _log(f"compiled {name} ({time.time() - t0:.0f} s)")
+        if pending and time.time() - last > 5:
+            _log(f"still compiling: {', '.join(n for n, _, _ in pending)} ({time.time() - t0:.0f} s)")
+            last = time.time()
+        time.sleep(0.1)
+    lib_tmp = os.path.join(build_dir, f".{LIB_NAME}.{os.getpid()}")
+    cmd = [nvcc, "-shared", "-o", lib_tmp, *[o for _, o, _ in procs], "-lcudart"]
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise KernelBuildError(f"linking the kernel library failed:\n{r.stdout}")
+    os.replace(lib_tmp, os.path.join(build_dir, LIB_NAME))
+    with open(os.path.join(build_dir, "stamp.json"), "w") as f:
+        json.dump({"fingerprint": fp, "flags": NVCC_FLAGS, "sources": srcs}, f)
+    _log(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
+
+
+def build(force: bool = False) -> str:
+    """Make sure the library is built for the current sources; return its path."""
+    fp = _fingerprint()
+    if not force:
+        for d in _build_dirs():
+            if _is_current(d, fp):
+                return os.path.join(d, LIB_NAME)
+    d = _writable_dir()
+    with open(os.path.join(d, ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if force or not _is_current(d, fp):
+                _compile(d, fp)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return os.path.join(d, LIB_NAME)
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library (built first if needed). Raises if it cannot be had."""
+    global _lib
+    if _lib is None:
+        path = build()
+        lib = ctypes.CDLL(path)
+        lib.llmrs_abi_version.restype = ctypes.c_int
+        lib.llmrs_last_error.restype = ctypes.c_char_p
+        if lib.llmrs_abi_version() != ABI_VERSION:
+            raise KernelBuildError(f"{path} has ABI {lib.llmrs_abi_version()}, expected {ABI_VERSION}")
+        _lib = lib
+    return _lib

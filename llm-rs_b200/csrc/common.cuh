@@ -1,0 +1,80 @@
+// Shared helpers of the kernel library: element types, loads and stores that widen to
+// float, warp and block reductions, and the error record of the C entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LLMRS_API extern "C" __attribute__((visibility("default")))
+
+// Element types as the Python side names them.
+enum LlmrsDtype : int { LLMRS_F32 = 0, LLMRS_BF16 = 1 };
+
+// Records a message for llmrs_last_error() and returns the negative code that entry
+// points hand back when they refuse their arguments (no kernel was launched).
+int llmrs_fail(const char* fmt, ...);
+// cudaGetLastError() as the entry point's return value (0 = launched).
+int llmrs_launch_status(const char* what);
+
+#define LLMRS_REQUIRE(cond, ...)                     \
+  do {                                               \
+    if (!(cond)) return llmrs_fail(__VA_ARGS__);     \
+  } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// Element offset of (page, kv head, K|V, slot in page, 0) in one layer's cache:
+// [n_pages, n_kv_heads, 2, page_size, head_dim]. The keys of one (page, head) and its
+// values are two adjacent contiguous tiles, so one tile is one straight copy.
+__device__ __host__ __forceinline__ size_t kv_tile_offset(int page, int kvh, int which, int n_kv_heads,
+                                                           int page_size, int head_dim) {
+  return ((size_t)((size_t)page * n_kv_heads + kvh) * 2 + which) * page_size * head_dim;
+}

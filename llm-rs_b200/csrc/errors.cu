@@ -1,0 +1,29 @@
+// Error record of the C entry points.
+#include <stdarg.h>
+#include <stdio.h>
+#include "common.cuh"
+
+static thread_local char g_last_error[512] = "";
+
+int llmrs_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+int llmrs_launch_status(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+// The message of the last refusal or failed launch on this thread.
+LLMRS_API const char* llmrs_last_error() { return g_last_error; }
+
+// Version of the entry points' signatures; the Python side checks it after loading.
+LLMRS_API int llmrs_abi_version() { return 1; }

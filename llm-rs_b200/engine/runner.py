@@ -1,0 +1,270 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+``ModelRunner.step(entries)`` takes portions of prompts beside single decoded tokens, cut
+anywhere, runs only those tokens (everything earlier comes from the cache) and returns
+the float32 logits at the wanted places. The reference's ``forward_pass``
+(llm-core/src/backends/candle.rs:1096-2031) has the same role but reshapes the flat
+batch to a rectangle (candle.rs:1122-1125), so it is only right when every sequence
+brings the same number of tokens, and it cannot continue a prompt; the batch here is
+ragged: per token its id, position and request row, per request its cached length,
+number of new tokens and block tables.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..cache.manager import RELEASED
+from ..cache.storage import CacheStorage
+from ..config import load_config
+from ..parts import DecoderModel, ModelSpec, Runtime
+from ..weights import load_weights
+
+PREFILL_TILE = 16  # queries per tile of the prefill attention kernel
+
+
+class StepError(RuntimeError):
+    pass
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens and the places among them whose
+    logits are wanted."""
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepContext:
+    """Everything a part may read about the current step. Device tensors are int32."""
+
+    def __init__(self, runner: "ModelRunner"):
+        self._runner = runner
+        self.act_dtype = runner.act_dtype
+        self.n_tokens = self.n_requests = self.n_want = 0
+        self.n_prefill_tiles = self.n_decode = self.max_decode_kv_len = 0
+        self.token_ids = self.positions = self.token_req = None
+        self.q_start = self.n_new = self.cached_len = self.slot_ids = None
+        self.want_rows = self.prefill_tiles = self.decode_reqs = None
+        self.block_tables: List[Optional[torch.Tensor]] = []
+        # Host copies, for parts that plan their work on the host.
+        self.host_n_new: List[int] = []
+        self.host_cached_len: List[int] = []
+        self.host_q_start: List[int] = []
+        self.host_slot_ids: List[int] = []
+        self.request_ids: List[Hashable] = []
+
+    def layer_cache(self, s: int):
+        return self._runner.storage.layer_cache(s, self.block_tables)
+
+    def scratch(self, name: str, n_floats: int) -> torch.Tensor:
+        """Float32 workspace that lives across steps (grown when a step needs more)."""
+        return self._runner._scratch(name, n_floats)
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+class ModelRunner:
+    """A model on the device with its cache; owns the step function."""
+
+    def __init__(self, spec: ModelSpec, tensors: Dict[str, torch.Tensor], act_dtype: torch.dtype, device,
+                 max_tokens: int, page_size: int = 16, max_requests: int = 64):
+        if not torch.cuda.is_available():
+            raise StepError("no CUDA device: this engine runs on the GPU only")
+        self.device = torch.device(device)
+        self.act_dtype = act_dtype
+        self.spec = spec
+        self.page_size = page_size
+        self.max_requests = max_requests
+        n_pages = max(1, -(-max_tokens // page_size))
+        self.max_positions = min(spec.max_positions, n_pages * page_size)
+        self.model = DecoderModel(spec)
+        self.model.bind(tensors, Runtime(self.device, act_dtype, self.max_positions))
+        needs = self.model.cache_needs()
+        self.storage = CacheStorage(needs, spec.run_order, page_size, n_pages, max_requests, act_dtype, self.device)
+        self.manager = CacheManager(self.storage.groups, page_size, max_requests)
+        self._scratch_bufs: Dict[str, torch.Tensor] = {}
+        self._meta_host = [None, None]
+        self._meta_events = [None, None]
+        self._meta_flip = 0
+        self.steps_run = 0
+
+    # -- construction ----------------------------------------------------------------
+    @classmethod
+    def from_model_dir(cls, model_dir: str, dtype: torch.dtype = torch.bfloat16, device="cuda:0", **kw):
+        entry, cfg = load_config(model_dir)
+        spec = entry.build_spec(cfg)
+        dev = torch.device(device)
+        tensors = load_weights(model_dir, DecoderModel(spec).weight_specs(), dtype, dev)
+        return cls(spec, tensors, dtype, dev, **kw)
+
+    # -- helpers ---------------------------------------------------------------------
+    def _scratch(self, name: str, n_floats: int) -> torch.Tensor:
+        buf = self._scratch_bufs.get(name)
+        if buf is None or buf.numel() < n_floats:
+            buf = torch.empty((max(n_floats, 1),), dtype=torch.float32, device=self.device)
+            self._scratch_bufs[name] = buf
+        return buf
+
+    def release(self, request_id: Hashable) -> None:
+        """The request is finished: its pages and its slot go back."""
+        self.manager.release(request_id)
+
+    def live_requests(self) -> List[Hashable]:
+        return list(self.manager.requests)
+
+    # -- the step --------------------------------------------------------------------
+    def _plan(self, entries: Sequence[StepEntry]):
+        """Check the entries, admit new requests and reserve their pages. Either all of
+        it succeeds or nothing is left changed."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if len(e.tokens) < 1:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.spec.vocab_size:
+                    raise StepError(f"token id {t} of request {e.request_id!r} is outside the vocabulary "
+                                    f"of {self.spec.vocab_size}")
+            for w in e.want:
+                if not 0 <= int(w) < len(e.tokens):
+                    raise StepError(f"request {e.request_id!r} wants place {w} of {len(e.tokens)} tokens")
+        admitted, reserved = [], []
+        try:
+            for e in entries:
+                if e.request_id not in self.manager.requests:
+                    rec = self.manager.admit(e.request_id)
+                    admitted.append(e.request_id)
+                    self.storage.reset_slot(rec.slot)
+                rec = self.manager.record(e.request_id)
+                if rec.cached_len + len(e.tokens) > self.max_positions:
+                    raise StepError(
+                        f"request {e.request_id!r} would reach {rec.cached_len + len(e.tokens)} tokens; the limit "
+                        f"is {self.max_positions} (max_position_embeddings and the cache pool)")
+                self.manager.reserve(e.request_id, len(e.tokens))
+                reserved.append(e.request_id)
+        except Exception:
+            for rid in reserved:
+                self.manager.cancel(rid)
+            for rid in admitted:
+                self.manager.release(rid)
+            raise
+        return admitted
+
+    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        ctx = StepContext(self)
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        recs = [self.manager.record(e.request_id) for e in entries]
+        token_ids = np.empty(T, np.int32)
+        positions = np.empty(T, np.int32)
+        token_req = np.empty(T, np.int32)
+        q_start = np.empty(R, np.int32)
+        n_new = np.empty(R, np.int32)
+        cached = np.empty(R, np.int32)
+        slots = np.empty(R, np.int32)
+        want_rows: List[int] = []
+        tiles: List[int] = []
+        dec: List[int] = []
+        at = 0
+        max_dec_kv = 0
+        for r, (e, rec) in enumerate(zip(entries, recs)):
+            n = len(e.tokens)
+            token_ids[at:at + n] = np.asarray(e.tokens, dtype=np.int64)
+            positions[at:at + n] = np.arange(rec.cached_len, rec.cached_len + n)
+            token_req[at:at + n] = r
+            q_start[r], n_new[r], cached[r], slots[r] = at, n, rec.cached_len, rec.slot
+            want_rows.extend(at + int(w) for w in e.want)
+            if n == 1:
+                dec.append(r)
+                max_dec_kv = max(max_dec_kv, rec.cached_len + 1)
+            else:
+                for off in range(0, n, PREFILL_TILE):
+                    tiles.extend((r, off))
+            at += n
+        tables = []
+        for g in range(len(self.manager.groups)):
+            width = _round_up(max(len(rec.tables[g]) for rec in recs), 8)
+            tab = np.full((R, width), RELEASED, np.int32)
+            for r, rec in enumerate(recs):
+                tab[r, :len(rec.tables[g])] = rec.tables[g]
+            tables.append(tab)
+
+        parts = [token_ids, positions, token_req, q_start, n_new, cached, slots,
+                 np.asarray(want_rows, np.int32), np.asarray(tiles, np.int32), np.asarray(dec, np.int32),
+                 *[t.reshape(-1) for t in tables]]
+        offsets, total = [], 0
+        for p in parts:
+            offsets.append(total)
+            total += _round_up(max(p.size, 1), 4)
+        flip = self._meta_flip
+        self._meta_flip ^= 1
+        if self._meta_host[flip] is None or self._meta_host[flip].numel() < total:
+            self._meta_host[flip] = torch.empty((_round_up(total, 4096),), dtype=torch.int32).pin_memory()
+            self._meta_events[flip] = None
+        if self._meta_events[flip] is not None:
+            self._meta_events[flip].synchronize()  # the copy that last read this buffer is done
+        host = self._meta_host[flip]
+        host_np = host.numpy()
+        for p, off in zip(parts, offsets):
+            host_np[off:off + p.size] = p
+        dev = torch.empty((total,), dtype=torch.int32, device=self.device)
+        dev.copy_(host[:total], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._meta_events[flip] = ev
+
+        def view(i, size):
+            return dev[offsets[i]:offsets[i] + size]
+        ctx.n_tokens, ctx.n_requests, ctx.n_want = T, R, len(want_rows)
+        ctx.token_ids, ctx.positions, ctx.token_req = view(0, T), view(1, T), view(2, T)
+        ctx.q_start, ctx.n_new, ctx.cached_len, ctx.slot_ids = view(3, R), view(4, R), view(5, R), view(6, R)
+        ctx.want_rows = view(7, len(want_rows))
+        ctx.n_prefill_tiles = len(tiles) // 2
+        ctx.prefill_tiles = view(8, len(tiles)).view(-1, 2) if tiles else view(8, 0)
+        ctx.n_decode = len(dec)
+        ctx.decode_reqs = view(9, len(dec))
+        ctx.max_decode_kv_len = max_dec_kv
+        ctx.block_tables = [view(10 + g, tables[g].size).view(R, -1) for g in range(len(tables))]
+        ctx.host_n_new = [int(x) for x in n_new]
+        ctx.host_cached_len = [int(x) for x in cached]
+        ctx.host_q_start = [int(x) for x in q_start]
+        ctx.host_slot_ids = [int(x) for x in slots]
+        ctx.request_ids = [e.request_id for e in entries]
+        return ctx
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch. Returns float32 logits ``[wanted, vocab]`` on the device, in the
+        order of the entries and of each entry's ``want`` (None if nothing is wanted).
+
+        A request id that is not live is admitted. Raises ``OutOfPages`` (and leaves
+        every request as it was) when the pool cannot hold the step's tokens.
+        """
+        entries = list(entries)
+        admitted = self._plan(entries)
+        try:
+            with torch.cuda.device(self.device):
+                ctx = self._build_context(entries)
+                logits = self.model.forward(ctx)
+        except Exception:
+            for e in entries:
+                self.manager.cancel(e.request_id)
+            for rid in admitted:
+                self.manager.release(rid)
+            raise
+        for e in entries:
+            self.manager.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,285 @@
+"""Python face of the CUDA kernel library: each function checks its tensors and launches
+one kernel (or one kernel and its combine step) on the current CUDA stream.
+
+There is no CPU path: a tensor that is not on a CUDA device is refused, and a missing
+library is an error (``csrc.build.KernelBuildError``), never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+launch_count = 0  # kernels launched through this module since import (read by the benchmark)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _lib():
+    return _build.library()
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(rc: int, what: str, launches: int = 1) -> None:
+    global launch_count
+    if rc != 0:
+        msg = _lib().llmrs_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{what} failed (code {rc}): {msg}")
+    launch_count += launches
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be on a CUDA device (this engine has no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+def _row_stride(t: torch.Tensor, name: str) -> int:
+    """Stride between rows of a 2-D view whose rows are dense."""
+    if t.dim() != 2 or (t.size(1) > 1 and t.stride(1) != 1):
+        raise KernelError(f"{name} must be 2-D with dense rows, got sizes {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` widened to float32 (the residual stream's type)."""
+    _need(table, "table")
+    _need(ids, "ids", torch.int32)
+    vocab, hidden = table.shape
+    n = ids.numel()
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32)
+    _check(_lib().llmrs_embedding(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), n, hidden, vocab,
+                                  _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                act_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta`` (when given), then ``out = h / sqrt(mean(h^2) + eps) * weight``.
+
+    ``h`` is the float32 residual stream and is updated in place. With ``rows`` (int32
+    indices) only those rows are normed, into ``out[i]``, and ``h`` is left as it is.
+    """
+    _need(h, "h", torch.float32)
+    _need(weight, "weight", torch.float32)
+    hidden = h.size(-1)
+    if weight.numel() != hidden:
+        raise KernelError(f"norm weight has {weight.numel()} elements, rows have {hidden}")
+    if delta is not None:
+        _need(delta, "delta", act_dtype)
+        if delta.shape != h.shape:
+            raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+    n_rows = h.size(0) if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if out is None:
+        out = torch.empty((n_rows, hidden), dtype=act_dtype, device=h.device)
+    _need(out, "out", act_dtype)
+    _check(_lib().llmrs_add_rmsnorm(_ptr(h), _ptr(delta), _ptr(weight), _ptr(out), _ptr(rows), n_rows, hidden,
+                                    ctypes.c_float(eps), dtype_code(act_dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """``h += delta`` in float32, in place."""
+    _need(h, "h", torch.float32)
+    _need(delta, "delta")
+    if delta.shape != h.shape:
+        raise KernelError(f"delta {tuple(delta.shape)} does not match h {tuple(h.shape)}")
+    _check(_lib().llmrs_residual_add(_ptr(h), _ptr(delta), ctypes.c_longlong(h.numel()), dtype_code(delta.dtype),
+                                     _stream()), "residual_add")
+    return h
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]`` for ``gate_up`` of width 2I."""
+    _need(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, "out", gate_up.dtype)
+    _check(_lib().llmrs_silu_mul(_ptr(gate_up), _ptr(out), n, inter, dtype_code(gate_up.dtype), _stream()), "silu_mul")
+    return out
+
+
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """True float32 ``x @ w.T (+ bias)`` with ``w`` of shape [N, K] (FFMA, no TF32)."""
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(w, "w", torch.float32)
+    M, K = x.shape
+    N = w.size(0)
+    if w.size(1) != K:
+        raise KernelError(f"x has {K} columns, w has {w.size(1)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _need(out, "out", torch.float32, contiguous=False)
+    _check(_lib().llmrs_gemm_f32(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(bias), _ptr(out),
+                                 ctypes.c_longlong(_row_stride(out, "out")), M, N, K, _stream()), "gemm_f32")
+    return out
+
+
+def qk_norm_rope_kvwrite(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+                         q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                         cos_sin: Optional[torch.Tensor], positions: torch.Tensor, token_req: torch.Tensor,
+                         block_table: torch.Tensor, cache: Optional[torch.Tensor], n_q_heads: int, n_kv_heads: int,
+                         head_dim: int, rotary_dim: int, page_size: int, eps: float) -> None:
+    """Per-head norm and rotation of ``q`` (in place) and ``k``; ``k`` and ``v`` go to their pages.
+
+    ``q``, ``k``, ``v`` are 2-D views with dense rows (slices of one projection output
+    are fine). ``k`` = ``v`` = None: this layer reads another layer's cache and writes none.
+    ``cos_sin`` is [positions, rotary_dim/2, 2] float32, or None for no rotation.
+    ``cache`` is one layer's [n_pages, n_kv_heads, 2, page_size, head_dim].
+    """
+    _need(q, "q", contiguous=False)
+    dt = q.dtype
+    n = q.size(0)
+    for name, t in (("k", k), ("v", v)):
+        if t is not None:
+            _need(t, name, dt, contiguous=False)
+    if (k is None) != (v is None):
+        raise KernelError("k and v must both be given or both be None")
+    if k is not None:
+        _need(cache, "cache", dt)
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("cos_sin", cos_sin)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    if cos_sin is not None and cos_sin.size(1) * 2 != rotary_dim:
+        raise KernelError(f"cos_sin table is for rotary_dim {cos_sin.size(1) * 2}, asked {rotary_dim}")
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    _check(_lib().llmrs_qk_norm_rope_kvwrite(
+        _ptr(q), ctypes.c_longlong(_row_stride(q, "q")),
+        _ptr(k), ctypes.c_longlong(_row_stride(k, "k") if k is not None else 0),
+        _ptr(v), ctypes.c_longlong(_row_stride(v, "v") if v is not None else 0),
+        _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin), _ptr(positions), _ptr(token_req), _ptr(block_table),
+        block_table.size(1), _ptr(cache), n, n_q_heads, n_kv_heads, head_dim,
+        rotary_dim if cos_sin is not None else 0, page_size, ctypes.c_float(eps), dtype_code(dt), _stream()),
+        "qk_norm_rope_kvwrite")
+
+
+def attn_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor, n_tiles: int,
+                 q_start: torch.Tensor, n_new: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor,
+                 n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> None:
+    """Causal attention of prompt portions over the paged cache (their own keys are already written).
+
+    ``tiles`` is int32 [n_tiles, 2]: (request row, offset of the tile's first query in
+    the request's new tokens); a tile covers 16 queries.
+    """
+    _need(q, "q", contiguous=False)
+    _need(out, "out", q.dtype, contiguous=False)
+    _need(cache, "cache", q.dtype)
+    for name, t in (("tiles", tiles), ("q_start", q_start), ("n_new", n_new), ("cached_len", cached_len),
+                    ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    _check(_lib().llmrs_attn_prefill(
+        _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
+        _ptr(cache), _ptr(tiles), n_tiles, _ptr(q_start), _ptr(n_new), _ptr(cached_len), _ptr(block_table),
+        block_table.size(1), n_q_heads, n_kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
+        dtype_code(q.dtype), _stream()), "attn_prefill")
+
+
+def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_splits: int) -> int:
+    return int(_lib_ll("llmrs_attn_decode_scratch_floats")(n_dec, n_q_heads, head_dim, max_splits))
+
+
+def _lib_ll(name: str):
+    fn = getattr(_lib(), name)
+    fn.restype = ctypes.c_longlong
+    return fn
+
+
+def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_reqs: torch.Tensor, n_dec: int,
+                q_start: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor, scratch: torch.Tensor,
+                max_splits: int, split_keys: int, n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
+                window: int, scale: float) -> None:
+    """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
+    the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace."""
+    _need(q, "q", contiguous=False)
+    _need(out, "out", q.dtype, contiguous=False)
+    _need(cache, "cache", q.dtype)
+    _need(scratch, "scratch", torch.float32)
+    for name, t in (("dec_reqs", dec_reqs), ("q_start", q_start), ("cached_len", cached_len),
+                    ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    need = attn_decode_scratch_floats(n_dec, n_q_heads, head_dim, max_splits)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode scratch holds {scratch.numel()} floats, {need} needed")
+    _check(_lib().llmrs_attn_decode(
+        _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
+        _ptr(cache), _ptr(dec_reqs), n_dec, _ptr(q_start), _ptr(cached_len), _ptr(block_table), block_table.size(1),
+        _ptr(scratch), max_splits, split_keys, n_q_heads, n_kv_heads, head_dim, page_size, window,
+        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode", launches=2)
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Index of the first maximum of each row of float32 ``logits``."""
+    _need(logits, "logits", torch.float32)
+    n, vocab = logits.shape
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32)
+    _check(_lib().llmrs_argmax(_ptr(logits), n, vocab, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor],
+           top_p: Optional[torch.Tensor], penalty: Optional[torch.Tensor], hist_tokens: Optional[torch.Tensor],
+           hist_offsets: Optional[torch.Tensor], seeds: torch.Tensor, request_ids: torch.Tensor,
+           gen_index: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Choose one token per row; ``logits`` (float32) are overwritten. See csrc/sampling.cu."""
+    _need(logits, "logits", torch.float32)
+    n, vocab = logits.shape
+    _need(temperature, "temperature", torch.float32)
+    for name, t, dt in (("top_k", top_k, torch.int32), ("top_p", top_p, torch.float32),
+                        ("penalty", penalty, torch.float32), ("hist_tokens", hist_tokens, torch.int32),
+                        ("hist_offsets", hist_offsets, torch.int32), ("seeds", seeds, torch.int64),
+                        ("request_ids", request_ids, torch.int64), ("gen_index", gen_index, torch.int32)):
+        if t is not None:
+            _need(t, name, dt)
+    if out is None:
+        out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(_lib().llmrs_sample(_ptr(logits), n, vocab, _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(penalty),
+                               _ptr(hist_tokens), _ptr(hist_offsets), _ptr(seeds), _ptr(request_ids),
+                               _ptr(gen_index), _ptr(out), _stream()), "sample")
+    return out
+
+
+def philox_uniform(seed: int, request_id: int, index: int) -> float:
+    """The uniform number in [0, 1) that the sampler draws for (seed, request, index); host code."""
+    fn = _lib().llmrs_philox_uniform
+    fn.restype = ctypes.c_float
+    return float(fn(ctypes.c_ulonglong(seed & (2**64 - 1)), ctypes.c_ulonglong(request_id & (2**64 - 1)),
+                    ctypes.c_uint(index)))

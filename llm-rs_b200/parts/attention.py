@@ -1,0 +1,113 @@
+"""Grouped-query attention over the paged cache."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import ops
+from .base import Mixer, Runtime
+from .linear import Linear
+from .registry import build, register
+from .spec import CacheNeed, PartSpec, WeightSpec
+
+
+@register("mixer", "gqa_attention")
+class GQAttention(Mixer):
+    """Attention with ``n_heads`` query heads sharing ``n_kv_heads`` key/value heads.
+
+    In order (llm-core/src/graph/builder.rs:97-243): q, k, v projections (bias only when
+    ``bias``) -> per-head RMSNorm of q and k over ``head_dim`` with a shared weight when
+    ``qk_norm`` (builder.rs:123-153; its eps is the parameter ``qk_norm_eps``, where the
+    reference fixes 1e-6, builder.rs:130,144) -> position encoding -> new keys and values
+    into the cache -> softmax(q k^T * scale) v over the keys the query may see (causal;
+    the last ``window`` keys when ``window`` > 0; llm-core/src/backends/candle.rs:1587-1640)
+    -> output projection. ``scale`` defaults to 1/sqrt(head_dim) (candle.rs:1608).
+
+    The q/k/v weights are concatenated at load so that one product makes all three.
+    """
+
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 position: PartSpec, qk_norm: bool = True, qk_norm_eps: float = 1e-6, bias: bool = False,
+                 window: int = 0, scale: Optional[float] = None, split_keys: int = 256, prefix: str = ""):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
+        if head_dim % 16:
+            raise ValueError(f"head_dim {head_dim} must be a multiple of 16 for the attention kernels")
+        self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
+        self.qk_norm, self.qk_norm_eps, self.bias, self.window = qk_norm, float(qk_norm_eps), bias, int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.split_keys = int(split_keys)
+        self.prefix = prefix
+        self.position = build("position", position, prefix=prefix)
+        self.q_width, self.kv_width = n_heads * head_dim, n_kv_heads * head_dim
+
+    # -- weights ---------------------------------------------------------------------
+    def weight_specs(self):
+        p, H = self.prefix, self.hidden_size
+        specs = [WeightSpec(p + "q_proj.weight", (self.q_width, H)),
+                 WeightSpec(p + "k_proj.weight", (self.kv_width, H)),
+                 WeightSpec(p + "v_proj.weight", (self.kv_width, H)),
+                 WeightSpec(p + "o_proj.weight", (H, self.q_width))]
+        if self.bias:
+            specs += [WeightSpec(p + "q_proj.bias", (self.q_width,), role="bias"),
+                      WeightSpec(p + "k_proj.bias", (self.kv_width,), role="bias"),
+                      WeightSpec(p + "v_proj.bias", (self.kv_width,), role="bias"),
+                      WeightSpec(p + "o_proj.bias", (H,), role="bias", optional=True)]
+        if self.qk_norm:
+            specs += [WeightSpec(p + "q_norm.weight", (self.head_dim,), role="norm"),
+                      WeightSpec(p + "k_norm.weight", (self.head_dim,), role="norm")]
+        return specs + self.position.weight_specs()
+
+    def bind(self, tensors, runtime: Runtime):
+        p = self.prefix
+        self.act_dtype = runtime.act_dtype
+        ws = [tensors[p + f"{n}_proj.weight"] for n in "qkv"]
+        dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
+        wqkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
+        bqkv = None
+        if self.bias:
+            bqkv = torch.cat([tensors[p + f"{n}_proj.bias"].to(dt) for n in "qkv"], dim=0).contiguous()
+        self.qkv_proj = Linear(wqkv, bqkv, runtime.act_dtype)
+        # The query rows alone, for run-order entries that read another entry's cache.
+        self.q_proj = Linear(wqkv[: self.q_width], None if bqkv is None else bqkv[: self.q_width], runtime.act_dtype)
+        self.o_proj = Linear(tensors[p + "o_proj.weight"], tensors.get(p + "o_proj.bias"), runtime.act_dtype)
+        self.q_norm_w = self.k_norm_w = None
+        if self.qk_norm:
+            self.q_norm_w = tensors[p + "q_norm.weight"].to(torch.float32).contiguous()
+            self.k_norm_w = tensors[p + "k_norm.weight"].to(torch.float32).contiguous()
+        self.position.bind(tensors, runtime)
+
+    # -- cache -----------------------------------------------------------------------
+    def cache_need(self):
+        return CacheNeed("window" if self.window > 0 else "full", self.n_kv_heads, self.head_dim, self.window)
+
+    # -- step ------------------------------------------------------------------------
+    def forward(self, x, ctx, cache):
+        nq, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
+        table = cache.block_table
+        if cache.owns:
+            qkv = self.qkv_proj.forward(x)
+            q = qkv[:, : self.q_width]
+            k = qkv[:, self.q_width: self.q_width + self.kv_width]
+            v = qkv[:, self.q_width + self.kv_width:]
+        else:
+            q, k, v = self.q_proj.forward(x), None, None
+        cos_sin = self.position.rotation_table()
+        if cos_sin is None:
+            self.position.apply_unfused(q, k, ctx.positions)
+        ops.qk_norm_rope_kvwrite(q, k, v, self.q_norm_w, self.k_norm_w, cos_sin, ctx.positions, ctx.token_req,
+                                 table, cache.kv if cache.owns else None, nq, nkv, d, self.position.rotary_dim,
+                                 cache.page_size, self.qk_norm_eps)
+        out = torch.empty((ctx.n_tokens, self.q_width), dtype=q.dtype, device=q.device)
+        if ctx.n_prefill_tiles:
+            ops.attn_prefill(q, out, cache.kv, ctx.prefill_tiles, ctx.n_prefill_tiles, ctx.q_start, ctx.n_new,
+                             ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale)
+        if ctx.n_decode:
+            max_splits = max(1, -(-ctx.max_decode_kv_len // self.split_keys))
+            scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(ctx.n_decode, nq, d, max_splits))
+            ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
+                            scratch, max_splits, self.split_keys, nq, nkv, d, cache.page_size, self.window,
+                            self.scale)
+        return self.o_proj.forward(out)

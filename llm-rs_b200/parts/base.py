@@ -1,0 +1,101 @@
+"""Interfaces of the parts a layer is put together from.
+
+Every part gets its sizes and constants as constructor parameters (from
+``PartSpec.params``) plus ``prefix``, the string put before its weight names. No part
+knows which model it is in.
+
+Life of a part:  construct -> ``weight_specs()`` tells the loader which tensors it wants
+-> ``bind(tensors, runtime)`` receives them on the device -> ``forward(...)`` per step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from .spec import CacheNeed, StateNeed, WeightSpec
+
+
+@dataclass
+class Runtime:
+    """What ``bind`` needs to know about the engine a part runs in."""
+    device: torch.device
+    act_dtype: torch.dtype          # bfloat16 or float32: type of activations and of the cache
+    max_positions: int              # positions 0 .. max_positions-1 can occur
+
+
+class Part:
+    prefix: str = ""
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return []
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        """Take the tensors named in ``weight_specs`` (already on ``runtime.device``)."""
+
+
+class Norm(Part):
+    """``forward(h, delta)``: ``h += delta`` (float32 residual stream, in place; ``delta``
+    may be None) and return the normed rows in the activation type. With ``rows`` only
+    those rows are normed and ``h`` stays untouched."""
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Turns token positions into something a mixer applies to queries and keys.
+
+    ``rotation_table()``: a float32 [positions, rotary_dim/2, 2] table of (cos, sin) that
+    the fused norm+rotation kernel applies in the rotate-half pairing, or None.
+    ``apply_unfused(q, k, positions)``: for encodings that are no such rotation; changes
+    q and k ([tokens, heads*head_dim] views) in place before the fused kernel runs
+    without a table.
+    """
+    rotary_dim: int = 0
+
+    def rotation_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def apply_unfused(self, q, k, positions) -> None:
+        return None
+
+
+class Mixer(Part):
+    """Mixes information between the tokens of a request (attention here).
+
+    ``cache_need()``  pages this mixer wants for a run-order entry (None: no pages)
+    ``state_need()``  fixed-size per-request state it wants (None: none)
+    ``forward(x, ctx, cache)``  x: [tokens, hidden] activations; ctx: the step's
+        ``StepContext``; cache: the ``LayerCache`` of this run-order entry. Returns
+        [tokens, hidden] in the activation type.
+    """
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, x, ctx, cache):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """``forward(x, ctx)``: [tokens, hidden] -> [tokens, hidden], token by token."""
+
+    def forward(self, x, ctx):
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arranges a mixer and a feed-forward around the residual stream.
+
+    ``forward(h, pending, ctx, cache) -> (h, pending)``: ``h`` is the float32 residual
+    stream; ``pending`` is a branch output that has not been added to ``h`` yet (None at
+    the first layer), so that the sum can be fused with the next norm.
+    """
+
+    def forward(self, h, pending, ctx, cache):
+        raise NotImplementedError

@@ -1,0 +1,39 @@
+"""Small configurations of the architecture for the tests. They differ in every size and
+option: layers, width, head counts and groups, head size, feed-forward width, vocabulary,
+rope base, eps, tied or untied head, bias, window, unrotated layers, page size."""
+import os
+
+import torch
+
+TINY_A = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+    intermediate_size=128, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=True, attention_bias=False, max_position_embeddings=512, hidden_act="silu",
+    eos_token_id=255)
+TINY_B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=3, hidden_size=96, num_attention_heads=8, num_key_value_heads=2, head_dim=32,
+    intermediate_size=224, vocab_size=384, rope_theta=1000000.0, rms_norm_eps=1e-5,
+    tie_word_embeddings=False, attention_bias=False, max_position_embeddings=1024, hidden_act="silu",
+    eos_token_id=[382, 383])
+TINY_C = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=4, hidden_size=80, num_attention_heads=6, num_key_value_heads=3, head_dim=48,
+    intermediate_size=176, vocab_size=333, rope_theta=500000.0, rms_norm_eps=3e-6,
+    tie_word_embeddings=False, attention_bias=True, max_position_embeddings=640, hidden_act="silu",
+    use_sliding_window=True, sliding_window=24, max_window_layers=2, no_rope_layers=[False, False, False, True],
+    eos_token_id=1)
+
+# name -> (config.json, seed, sigma of matrices, page size)
+TINY = {"A": (TINY_A, 0, 0.02, 16), "B": (TINY_B, 1, 0.03, 8), "C": (TINY_C, 5, 0.05, 16)}
+
+
+def write_tiny_model(name: str, folder: str, sigma_scale: float = 1.0, norm_dtype=None) -> str:
+    """Write the tiny model ``name`` into ``folder`` with the package's random-weights mode."""
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.weights import write_random_model
+    raw, seed, sigma, _ = TINY[name]
+    cfg = Qwen3Config.from_dict(raw)
+    return write_random_model(os.path.join(folder, f"tiny_{name}"), cfg, seed=seed, sigma=sigma * sigma_scale,
+                              norm_jitter=0.1, dtype=torch.bfloat16, norm_dtype=norm_dtype)
