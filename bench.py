@@ -1,0 +1,322 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second and prefill throughput
+at the layer sizes of Qwen3-8B with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C]
+
+A "step" is one decode step of the whole batch. The default is batch 8 at a context of
+4,096 tokens per request. One JSON line is printed:
+
+  value          decoded tokens per second, timed on the device with CUDA events around K
+                 steps of the step function (given tokens, no host round trip per step)
+  e2e            the same through ``Engine.step()``: every step copies that step's index
+                 arrays from pinned host memory and reads the sampled tokens back
+  prefill        one prompt of 2,048 tokens: tokens/s, milliseconds, fraction of the
+                 bf16 peak (flops of the step / time / peak)
+  roofline       decode: bytes the step must read (every weight once, the cache of the
+                 live requests) / time, against the measured HBM copy bandwidth
+  points         decode tokens per second at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file when present, else 6.65 TB/s and
+1.59 PFLOP/s. Only N = 1 is supported: the engine is a single-GPU engine.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+    rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, attention_bias=False,
+    max_position_embeddings=40960, hidden_act="silu", eos_token_id=151645)
+FULL_LAYERS = 36
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(path) as f:
+            m = json.load(f)
+        out["hbm_gbs"] = float(m.get("hbm_gbs", out["hbm_gbs"]))
+        out["bf16_tflops"] = float(m.get("bf16_tflops", out["bf16_tflops"]))
+        if "bf16_tflops_sustained" in m:
+            out["bf16_tflops_sustained"] = float(m["bf16_tflops_sustained"])
+        out["source"] = "measured"
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            cols = [c.strip() for c in line.split(",")]
+            if len(cols) < 7:
+                continue
+            try:
+                sm.append(float(cols[0]))
+                mx.append(float(cols[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, cols[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_bytes_per_decode_step(cfg, n_layers, batch, context, kv_bytes=2, w_bytes=2):
+    """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = ((nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I) * w_bytes + (2 * H + 2 * d) * 4
+    weights = n_layers * per_layer + V * H * w_bytes + H * 4 + batch * H * w_bytes
+    cache = batch * context * 2 * nkv * d * kv_bytes * n_layers
+    return weights + cache
+
+
+def prefill_flops(cfg, n_layers, tokens):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer_params = (nq + 2 * nkv) * d * H + H * nq * d + 3 * H * I
+    linear = 2.0 * tokens * n_layers * per_layer_params + 2.0 * V * H  # head on the last position only
+    attention = 2.0 * tokens * tokens * nq * d * n_layers              # causal: half of 4*T^2*d per head
+    return linear + attention
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than 36 only where memory or time needs it")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "mashriram/llm-rs is a Rust workspace (cargo, candle, cubecl); no Rust toolchain or "
+                          "vendored crates offline, pip cannot install it"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    W = max(3, args.warmup)
+    K = max(1, args.steps)
+
+    import numpy as np
+    import torch
+    import llm_rs_b200
+    from llm_rs_b200 import ops
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import Engine, EngineConfig, ModelRunner, StepEntry
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel
+    from llm_rs_b200.sampling import SamplingParams
+    from llm_rs_b200.weights import random_tensors
+
+    torch.cuda.set_device(0)
+    pk = peaks()
+    raw = dict(QWEN3_8B, num_hidden_layers=args.layers)
+    cfg = Qwen3Config.from_dict(raw)
+    spec = build_spec(cfg)
+    page = 16
+    ctx = args.context
+    max_batch = args.batch if args.no_points else max(args.batch, 64)
+    pool_tokens = max_batch * (ctx + 64) + PREFILL_TOKENS + 64
+    t0 = time.time()
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=2, sigma=0.02, dtype=torch.bfloat16,
+                             device="cuda:0")
+    runner = ModelRunner(spec, tensors, torch.bfloat16, "cuda:0", max_tokens=pool_tokens, page_size=page,
+                         max_requests=max_batch + 1)
+    del tensors
+    torch.cuda.empty_cache()
+    # Keys and values of the context are random numbers: the decode step reads the same bytes
+    # whatever they hold, and random values keep the softmax from degenerating.
+    for kv in runner.storage.kv:
+        for i in range(kv.size(0)):
+            kv[i].normal_(0.0, 1.0)
+    runner.use_graphs = True
+    print(f"[bench] model on device in {time.time() - t0:.1f} s, "
+          f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated", file=sys.stderr, flush=True)
+    rng = np.random.default_rng(0)
+    V = cfg.vocab_size
+
+    def fill_context(ids, n_tokens):
+        """Give each request ``n_tokens`` of (random) cached context without running a prefill."""
+        for rid in ids:
+            runner.manager.admit(rid)
+            runner.manager.reserve(rid, n_tokens)
+            runner.manager.commit(rid, n_tokens)
+
+    def timed_decode(batch, steps, warmup, sampler=None):
+        ids = [f"d{batch}_{i}" for i in range(batch)]
+        fill_context(ids, ctx - warmup - steps)
+        toks = rng.integers(0, V, (warmup + steps, batch)).tolist()
+        out = torch.empty((batch,), dtype=torch.int32, device="cuda:0")
+        for s in range(warmup):
+            logits = runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+            ops.argmax(logits, out)
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count
+        if sampler:
+            sampler.start()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for s in range(warmup, warmup + steps):
+            logits = runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
+            ops.argmax(logits, out)
+        end.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if sampler else None
+        ms = start.elapsed_time(end) / steps
+        for rid in ids:
+            runner.release(rid)
+        return ms, clocks, ops.launch_count - launches0
+
+    # Kernels of ours in one captured decode step (a replay launches all of them again).
+    def kernels_per_decode_step(batch):
+        ids = [f"k{i}" for i in range(batch)]
+        fill_context(ids, 64)
+        runner.use_graphs = False
+        n0 = ops.launch_count
+        runner.step([StepEntry(r, [1], [0]) for r in ids])
+        n = ops.launch_count - n0
+        runner.use_graphs = True
+        for rid in ids:
+            runner.release(rid)
+        return n
+
+    per_step_kernels = kernels_per_decode_step(args.batch)
+    ms, clocks, eager_launches = timed_decode(args.batch, K, W, ClockSampler())
+    value = args.batch / (ms / 1e3)
+    step_bytes = model_bytes_per_decode_step(raw, args.layers, args.batch, ctx)
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    result = {
+        "metric": "Qwen3-8B bf16 decode tok/s @ batch 8, context 4096 (random weights)",
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights (seed 2), uniform-random token ids, random cache contents",
+        "impl": "ours",
+        "config": {
+            "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": cfg.hidden_size,
+            "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
+            "seq_len": ctx, "page_size": page, "kv_dtype": "bf16", "parallelism": "single GPU",
+            "cuda_graphs": True, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "peaks": pk["source"]},
+        "clocks": clocks,
+        # One replay of a captured step launches every kernel of the step; argmax is launched eagerly.
+        "gpu_launches": per_step_kernels * K + eager_launches,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
+    }
+
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            try:
+                ms_b, _, _ = timed_decode(b, max(8, K // 2), W)
+                points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 2)
+            except Exception as e:  # a point that fails must not lose the headline
+                points[f"decode_b{b}"] = None
+                print(f"[bench] decode at batch {b} failed: {e}", file=sys.stderr)
+        result["points"] = points
+
+    if not args.no_prefill:
+        try:
+            prompt = rng.integers(0, V, PREFILL_TOKENS).tolist()
+            times = []
+            for it in range(4):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+                end.record()
+                torch.cuda.synchronize()
+                runner.release("p")
+                if it >= 1:
+                    times.append(start.elapsed_time(end))
+            pms = statistics.median(times)
+            fl = prefill_flops(raw, args.layers, PREFILL_TOKENS)
+            result["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS,
+                                 "ms": round(pms, 3),
+                                 "frac": round(fl / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
+        except Exception as e:
+            result["prefill"] = None
+            print(f"[bench] prefill failed: {e}", file=sys.stderr)
+
+    if not args.no_e2e:
+        try:
+            engine = Engine(EngineConfig(model_path="", block_pool_size=pool_tokens // page, page_size=page,
+                                         max_requests=max_batch + 1, max_tokens_per_step=2048, prefill_chunk=512),
+                            runner=runner)
+            sp = SamplingParams(temperature=0.0, max_new_tokens=W + K + 1, ignore_eos=True)
+            plen = ctx - W - K - 1
+            rids = [engine.add_request(rng.integers(0, V, plen).tolist(), sp) for _ in range(args.batch)]
+            while any(engine.requests[r].remaining > 1 or not engine.requests[r].output for r in rids):
+                engine.step()   # prefill of the prompts, not timed
+            for _ in range(W):
+                engine.step()
+            torch.cuda.synchronize()
+            h2d0 = runner.h2d_bytes
+            t_start = time.perf_counter()
+            got = 0
+            for _ in range(K):
+                got += sum(1 for _, tok, _ in engine.step() if tok is not None)
+            torch.cuda.synchronize()
+            dt = time.perf_counter() - t_start
+            result["e2e"] = {"value": round(got / dt, 2), "unit": "tokens/s",
+                             "h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // K,
+                             "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(dt / K * 1e3, 4)}
+            while engine.has_work():
+                engine.step()
+        except Exception as e:
+            result["e2e"] = None
+            print(f"[bench] e2e failed: {e}", file=sys.stderr)
+
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

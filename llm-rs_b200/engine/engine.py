@@ -1,0 +1,176 @@
+"""The engine a user talks to: requests in, tokens out.
+
+Python entry point in the manner of the reference's C API (llm-ffi/src/lib.rs:39-167:
+create_engine, send_request, poll_token, destroy_engine) and of its scheduler's step
+(llm-scheduler/src/scheduler.rs:51: a list of (sequence id, token, finished) per step),
+on token ids: the reference's FFI "tokenizes" by character code (lib.rs:102) and this
+engine depends on no tokenizer.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .runner import ModelRunner, StepEntry
+from .scheduler import Output, Request, Scheduled, Scheduler
+
+
+@dataclass
+class EngineConfig:
+    """``model_path`` and ``block_pool_size`` are the reference's two fields
+    (llm-ffi/src/lib.rs:10-15; pool default 1024 pages as llm-cli/src/main.rs:23); the
+    rest configures what the reference fixes in code or does not have."""
+    model_path: str
+    block_pool_size: int = 1024          # pages in the cache pool
+    page_size: int = 16                  # llm-core/src/backends/candle.rs:827
+    dtype: str = "bfloat16"              # "bfloat16" or "float32"
+    device: str = "cuda:0"
+    max_requests: int = 64               # live requests (state slots)
+    max_tokens_per_step: int = 2048
+    prefill_chunk: int = 512
+    cuda_graphs: bool = True
+
+
+class Engine:
+    def __init__(self, config: EngineConfig, runner: Optional[ModelRunner] = None):
+        self.config = config
+        dtype = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+                 "fp32": torch.float32}[config.dtype]
+        self.runner = runner or ModelRunner.from_model_dir(
+            config.model_path, dtype=dtype, device=config.device,
+            max_tokens=config.block_pool_size * config.page_size, page_size=config.page_size,
+            max_requests=config.max_requests)
+        self.runner.use_graphs = config.cuda_graphs
+        self.scheduler = Scheduler(
+            self.runner.manager, self.runner.max_positions, self.runner.spec.eos_token_ids,
+            max_tokens_per_step=config.max_tokens_per_step, prefill_chunk=config.prefill_chunk,
+            max_requests_per_step=config.max_requests)
+        self.sampler = Sampler(self.runner.device)
+        self._ids = itertools.count(1)
+        self.requests: Dict[int, Request] = {}
+        self._events: Dict[int, List[Output]] = {}
+
+    # -- requests --------------------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
+        """Queue a request; returns its id (ids start at 1; 0 is the reference's failure value)."""
+        params = params or SamplingParams()
+        vocab = self.runner.spec.vocab_size
+        for t in prompt_token_ids:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+        rid = next(self._ids)
+        req = Request(rid, [int(t) for t in prompt_token_ids], params)
+        self.scheduler.add_request(req)
+        self.requests[rid] = req
+        self._events[rid] = []
+        return rid
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # -- one step --------------------------------------------------------------------
+    def step(self) -> List[Tuple[int, Optional[int], bool]]:
+        """Run one scheduler step. Returns ``(request id, token, finished)`` for every
+        request that got a token or ended in it."""
+        batch = self.scheduler.schedule()
+        sampled: Dict[int, int] = {}
+        if batch:
+            entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
+                       for s in batch]
+            try:
+                logits = self.runner.step(entries)
+                rows = [(s.request.params, s.request.request_id, len(s.request.output), s.request.tokens())
+                        for s in batch if s.sample]
+                if rows:
+                    tokens = self.sampler.sample(logits, rows).cpu().tolist()
+                    sampled = {r[1]: t for r, t in zip(rows, tokens)}
+            except Exception:
+                outs = self.scheduler.abort_all()
+                for o in outs:
+                    self._events.setdefault(o.request_id, []).append(o)
+                raise
+        outs = self.scheduler.update(batch, sampled)
+        for o in outs:
+            self._events.setdefault(o.request_id, []).append(o)
+        return [(o.request_id, o.token, o.finished) for o in outs]
+
+    # -- conveniences ----------------------------------------------------------------
+    def poll(self, request_id: int) -> Output:
+        """The next event of one request, stepping the engine until there is one
+        (the blocking ``poll_token`` of llm-ffi/src/lib.rs:127-158)."""
+        if request_id not in self._events:
+            raise KeyError(f"unknown request {request_id}")
+        while not self._events[request_id]:
+            if not self.has_work():
+                raise RuntimeError(f"request {request_id} has no further events")
+            self.step()
+        return self._events[request_id].pop(0)
+
+    def generate(self, prompts: Sequence[Sequence[int]], params=None) -> List[List[int]]:
+        """Generate for a batch of prompts (token ids in, token ids out)."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        while self.has_work():
+            self.step()
+        out = []
+        for rid in ids:
+            out.append(list(self.requests[rid].output))
+            self.forget(rid)
+        return out
+
+    def finish_reason(self, request_id: int) -> Optional[str]:
+        return self.requests[request_id].finish_reason
+
+    def forget(self, request_id: int) -> None:
+        """Drop the record of a finished request."""
+        self.requests.pop(request_id, None)
+        self._events.pop(request_id, None)
+
+
+# -- the reference's five verbs ------------------------------------------------------------
+@dataclass
+class ChatRequest:
+    """llm-ffi/src/lib.rs:17-23, with token ids where the reference has a prompt string.
+    top_k 40 and repetition_penalty 1.1 are what the reference's ``send_request`` fixes
+    (lib.rs:110-111); here they are fields with neutral defaults."""
+    prompt: Sequence[int]
+    temperature: float = 0.0
+    top_p: float = 1.0
+    max_tokens: int = 50
+    top_k: int = 0
+    repetition_penalty: float = 1.0
+    seed: int = 0
+
+
+@dataclass
+class GenerationResult:
+    """llm-ffi/src/lib.rs:25-29 without the text field (no tokenizer here)."""
+    token: int
+    is_eos: bool
+    reason: Optional[str] = None
+
+
+def create_engine(config: EngineConfig) -> Engine:
+    return Engine(config)
+
+
+def send_request(engine: Engine, request: ChatRequest) -> int:
+    return engine.add_request(request.prompt, SamplingParams(
+        temperature=request.temperature, top_p=request.top_p, top_k=request.top_k,
+        repetition_penalty=request.repetition_penalty, max_new_tokens=request.max_tokens, seed=request.seed))
+
+
+def poll_token(engine: Engine, request_id: int) -> GenerationResult:
+    o = engine.poll(request_id)
+    return GenerationResult(token=-1 if o.token is None else o.token, is_eos=o.finished, reason=o.reason)
+
+
+def destroy_engine(engine: Engine) -> None:
+    for rid in list(engine.runner.manager.requests):
+        engine.runner.release(rid)
+    engine.requests.clear()

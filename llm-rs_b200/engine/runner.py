@@ -45,6 +45,7 @@ class StepContext:
 
     def __init__(self, runner: "ModelRunner"):
         self._runner = runner
+        self._scratch_bufs = runner._scratch_bufs
         self.act_dtype = runner.act_dtype
         self.n_tokens = self.n_requests = self.n_want = 0
         self.n_prefill_tiles = self.n_decode = self.max_decode_kv_len = 0
@@ -63,8 +64,9 @@ class StepContext:
         return self._runner.storage.layer_cache(s, self.block_tables)
 
     def scratch(self, name: str, n_floats: int) -> torch.Tensor:
-        """Float32 workspace that lives across steps (grown when a step needs more)."""
-        return self._runner._scratch(name, n_floats)
+        """Float32 workspace that lives across steps (grown when a step needs more). A step
+        that is captured in a CUDA graph has workspace of its own, which never moves."""
+        return self._runner._scratch(self._scratch_bufs, name, n_floats)
 
 
 def _round_up(n: int, m: int) -> int:
@@ -95,6 +97,14 @@ class ModelRunner:
         self._meta_events = [None, None]
         self._meta_flip = 0
         self.steps_run = 0
+        self.h2d_bytes = 0  # bytes of index arrays copied to the device so far
+        # Steps that only decode (one token per request) are captured in CUDA graphs and
+        # replayed: one launch instead of some ten per layer.
+        self.use_graphs = False
+        # A mixer that plans work on the host per step sets ``graph_safe = False``.
+        self._graph_safe = all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks
+                               if hasattr(b, "mixer"))
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
 
     # -- construction ----------------------------------------------------------------
     @classmethod
@@ -106,11 +116,11 @@ class ModelRunner:
         return cls(spec, tensors, dtype, dev, **kw)
 
     # -- helpers ---------------------------------------------------------------------
-    def _scratch(self, name: str, n_floats: int) -> torch.Tensor:
-        buf = self._scratch_bufs.get(name)
+    def _scratch(self, bufs: Dict[str, torch.Tensor], name: str, n_floats: int) -> torch.Tensor:
+        buf = bufs.get(name)
         if buf is None or buf.numel() < n_floats:
             buf = torch.empty((max(n_floats, 1),), dtype=torch.float32, device=self.device)
-            self._scratch_bufs[name] = buf
+            bufs[name] = buf
         return buf
 
     def release(self, request_id: Hashable) -> None:
@@ -162,7 +172,11 @@ class ModelRunner:
             raise
         return admitted
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], table_round: int = 8,
+                       graph: Optional["_DecodeGraph"] = None) -> StepContext:
+        """Pack the step's index arrays, copy them to the device in one transfer and
+        return the context that views them. With ``graph`` the arrays go into that
+        graph's own buffer (same layout every time) and its context is returned."""
         ctx = StepContext(self)
         R = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -195,7 +209,7 @@ class ModelRunner:
             at += n
         tables = []
         for g in range(len(self.manager.groups)):
-            width = _round_up(max(len(rec.tables[g]) for rec in recs), 8)
+            width = _round_up(max(len(rec.tables[g]) for rec in recs), table_round)
             tab = np.full((R, width), RELEASED, np.int32)
             for r, rec in enumerate(recs):
                 tab[r, :len(rec.tables[g])] = rec.tables[g]
@@ -219,11 +233,25 @@ class ModelRunner:
         host_np = host.numpy()
         for p, off in zip(parts, offsets):
             host_np[off:off + p.size] = p
-        dev = torch.empty((total,), dtype=torch.int32, device=self.device)
+        if graph is not None:
+            if graph.meta is None:
+                graph.meta = torch.empty((total,), dtype=torch.int32, device=self.device)
+            dev = graph.meta
+            if dev.numel() != total:
+                raise StepError("a captured step's layout changed")
+        else:
+            dev = torch.empty((total,), dtype=torch.int32, device=self.device)
         dev.copy_(host[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
         ev = torch.cuda.Event()
         ev.record()
         self._meta_events[flip] = ev
+        host_lists = dict(host_n_new=[int(x) for x in n_new], host_cached_len=[int(x) for x in cached],
+                          host_q_start=[int(x) for x in q_start], host_slot_ids=[int(x) for x in slots],
+                          request_ids=[e.request_id for e in entries])
+        if graph is not None and graph.ctx is not None:
+            graph.ctx.__dict__.update(host_lists)
+            return graph.ctx  # its device views already point into graph.meta
 
         def view(i, size):
             return dev[offsets[i]:offsets[i] + size]
@@ -236,12 +264,13 @@ class ModelRunner:
         ctx.n_decode = len(dec)
         ctx.decode_reqs = view(9, len(dec))
         ctx.max_decode_kv_len = max_dec_kv
+        if graph is not None:
+            # Captured launch sizes must hold for every step that replays the graph.
+            ctx.max_decode_kv_len = max(t.shape[1] for t in tables) * self.page_size if tables else max_dec_kv
+            ctx._scratch_bufs = graph.scratch
+            graph.ctx = ctx
         ctx.block_tables = [view(10 + g, tables[g].size).view(R, -1) for g in range(len(tables))]
-        ctx.host_n_new = [int(x) for x in n_new]
-        ctx.host_cached_len = [int(x) for x in cached]
-        ctx.host_q_start = [int(x) for x in q_start]
-        ctx.host_slot_ids = [int(x) for x in slots]
-        ctx.request_ids = [e.request_id for e in entries]
+        ctx.__dict__.update(host_lists)
         return ctx
 
     @torch.no_grad()
@@ -256,8 +285,11 @@ class ModelRunner:
         admitted = self._plan(entries)
         try:
             with torch.cuda.device(self.device):
-                ctx = self._build_context(entries)
-                logits = self.model.forward(ctx)
+                if self.use_graphs and self._graph_safe and all(len(e.tokens) == 1 for e in entries):
+                    logits = self._graph_step(entries)
+                else:
+                    ctx = self._build_context(entries)
+                    logits = self.model.forward(ctx)
         except Exception:
             for e in entries:
                 self.manager.cancel(e.request_id)
@@ -268,3 +300,38 @@ class ModelRunner:
             self.manager.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    # -- captured decode steps ---------------------------------------------------------
+    def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        recs = [self.manager.record(e.request_id) for e in entries]
+        widths = tuple(_round_up(max(len(rec.tables[g]) for rec in recs), GRAPH_TABLE_ROUND)
+                       for g in range(len(self.manager.groups)))
+        key = (len(entries), tuple(len(e.want) for e in entries), widths)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = _DecodeGraph()
+            ctx = self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            self.model.forward(ctx)  # warm-up: sizes the workspace; rewrites the same keys and values
+            torch.cuda.current_stream().synchronize()
+            graph.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph.graph):
+                graph.logits = self.model.forward(ctx)
+            self._graphs[key] = graph
+        else:
+            self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+        graph.graph.replay()
+        return graph.logits
+
+
+GRAPH_TABLE_ROUND = 64  # block-table width of a captured step, in pages
+
+
+class _DecodeGraph:
+    """A captured decode step: its index buffer, its context, its workspace and its output."""
+
+    def __init__(self):
+        self.meta: Optional[torch.Tensor] = None
+        self.ctx: Optional[StepContext] = None
+        self.scratch: Dict[str, torch.Tensor] = {}
+        self.graph = None
+        self.logits: Optional[torch.Tensor] = None

@@ -246,3 +246,17 @@ def greedy_generate(config: dict, w, prompt: Sequence[int], n_new: int) -> List[
         out.append(nxt)
         ids.append(nxt)
     return out
+
+
+def greedy_gap(config: dict, w, prompt: Sequence[int], generated: Sequence[int]) -> float:
+    """How far the tokens someone else generated greedily are from this implementation's
+    choice: the largest (max logit - logit of the generated token) along the sequence.
+    0 means the same tokens; a reduced-precision engine may pick another token only where
+    two logits are closer than its rounding."""
+    ids = list(prompt) + list(generated)
+    logits = forward(config, w, ids[:-1])
+    worst = 0.0
+    for i, tok in enumerate(generated):
+        row = logits[len(prompt) - 1 + i]
+        worst = max(worst, float(row.max() - row[tok]))
+    return worst
