@@ -1,0 +1,174 @@
+"""The scheduler's decisions against a fake step function (CPU): admission, token budget,
+portions, finishing, what happens when pages run out."""
+import pytest
+
+from llm_rs_b200.cache import CacheManager, GroupSpec
+from llm_rs_b200.engine import Request, Scheduler
+from llm_rs_b200.parts import CacheNeed
+from llm_rs_b200.sampling import SamplingParams
+
+
+def make(n_pages=16, page=4, slots=4, budget=16, chunk=8, eos=(99,), max_positions=64):
+    m = CacheManager([GroupSpec(CacheNeed("full", 1, 16), [0], n_pages)], page, slots)
+    return m, Scheduler(m, max_positions, eos, max_tokens_per_step=budget, prefill_chunk=chunk,
+                        max_requests_per_step=slots)
+
+
+def run_step(m, s, token_of=lambda req: 7):
+    """What the engine does around the real step function, with a fake one."""
+    batch = s.schedule()
+    for b in batch:
+        if b.request.request_id not in m.requests:
+            m.admit(b.request.request_id)
+        m.reserve(b.request.request_id, len(b.tokens))
+    for b in batch:
+        m.commit(b.request.request_id, len(b.tokens))
+    sampled = {b.request.request_id: token_of(b.request) for b in batch if b.sample}
+    outs = s.update(batch, sampled)
+    m.check_invariants()
+    return batch, outs
+
+
+def req(i, n, max_new=4, **kw):
+    return Request(i, list(range(1, n + 1)), SamplingParams(temperature=0.0, max_new_tokens=max_new, **kw))
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    m, s = make(budget=16, chunk=8)
+    s.add_request(req(1, 20))
+    sizes = []
+    while s.has_work():
+        batch, outs = run_step(m, s)
+        sizes.append([len(b.tokens) for b in batch])
+    assert sizes[:3] == [[8], [8], [4]]          # chunks of at most prefill_chunk
+    assert sizes[3:] == [[1], [1], [1]]          # then one token a step until max_new_tokens
+    assert not m.requests and m.free_pages() == 16
+
+
+def test_decode_first_then_portions_in_arrival_order():
+    m, s = make(budget=10, chunk=8, n_pages=32)
+    s.add_request(req(1, 3))
+    run_step(m, s)                                # request 1 is now decoding
+    s.add_request(req(2, 12))
+    s.add_request(req(3, 5))
+    batch, _ = run_step(m, s)
+    assert [(b.request.request_id, len(b.tokens), b.sample) for b in batch] == [(1, 1, True), (2, 8, False), (3, 1, False)]
+    batch, _ = run_step(m, s)
+    assert [(b.request.request_id, len(b.tokens), b.sample) for b in batch] == [(1, 1, True), (2, 4, True), (3, 4, True)]
+
+
+def test_sample_only_when_the_prompt_is_complete_and_outputs():
+    m, s = make()
+    s.add_request(req(1, 10, max_new=2))
+    batch, outs = run_step(m, s)
+    assert [b.sample for b in batch] == [False] and outs == []
+    batch, outs = run_step(m, s)
+    assert [b.sample for b in batch] == [True]
+    assert [(o.request_id, o.token, o.finished) for o in outs] == [(1, 7, False)]
+    batch, outs = run_step(m, s)
+    assert [(o.token, o.finished, o.reason) for o in outs] == [(7, True, "length")]
+
+
+def test_eos_finishes_and_is_emitted_unless_ignored():
+    m, s = make()
+    s.add_request(req(1, 3, max_new=10))
+    s.add_request(req(2, 3, max_new=3, ignore_eos=True))
+    outs = []
+    while s.has_work():
+        outs += run_step(m, s, token_of=lambda r: 99)[1]
+    one = [(o.token, o.finished, o.reason) for o in outs if o.request_id == 1]
+    two = [(o.token, o.finished, o.reason) for o in outs if o.request_id == 2]
+    assert one == [(99, True, "stop")]
+    assert two == [(99, False, None), (99, False, None), (99, True, "length")]
+
+
+def test_context_limit_finishes():
+    m, s = make(max_positions=8, n_pages=8)
+    s.add_request(req(1, 6, max_new=50))
+    outs = []
+    while s.has_work():
+        outs += run_step(m, s)[1]
+    assert len(outs) == 2 and outs[-1].reason == "length"      # 6 + 2 = 8 positions
+    with pytest.raises(ValueError, match="no room"):
+        s.add_request(req(2, 8))
+    with pytest.raises(ValueError, match="at least one"):
+        s.add_request(Request(3, [], SamplingParams()))
+
+
+def test_admission_waits_behind_the_head_of_the_queue():
+    m, s = make(n_pages=4, page=4, budget=64, chunk=64)        # 16 tokens of cache
+    s.add_request(req(1, 10, max_new=3))
+    s.add_request(req(2, 9, max_new=2))                          # does not fit beside request 1
+    s.add_request(req(3, 2, max_new=2))                          # would fit, but waits behind 2
+    batch, _ = run_step(m, s)
+    assert [b.request.request_id for b in batch] == [1]
+    assert [r.request_id for r in s.waiting] == [2, 3]
+    done = []
+    while s.has_work():
+        done += [o.request_id for o in run_step(m, s)[1] if o.finished]
+    assert done == [1, 2, 3]
+    assert s.stats["preemptions"] == 0
+
+
+def test_out_of_pages_preempts_the_last_admitted_and_recomputes():
+    m, s = make(n_pages=4, page=4, budget=64, chunk=64, slots=3)
+    s.add_request(req(1, 7, max_new=6))
+    s.add_request(req(2, 7, max_new=6))
+    outs = []
+    steps = 0
+    while s.has_work():
+        batch, o = run_step(m, s)
+        outs += o
+        steps += 1
+        assert steps < 100
+    # 16 tokens of cache cannot hold 2 x (7 + 6): request 2 was sent back and came again.
+    assert s.stats["preemptions"] >= 1
+    by = {1: [], 2: []}
+    for o in outs:
+        by[o.request_id].append(o)
+    assert [len(v) for v in by.values()] == [6, 6]              # nothing dropped, nothing emitted twice
+    assert by[1][-1].reason == by[2][-1].reason == "length"
+    assert not m.requests and m.free_pages() == 4
+
+
+def test_preempted_request_recomputes_prompt_plus_generated():
+    m, s = make(n_pages=3, page=4, budget=64, chunk=64)
+    s.add_request(req(1, 4, max_new=8))
+    s.add_request(req(2, 4, max_new=8))
+    seen = []
+    while s.has_work():
+        batch, _ = run_step(m, s)
+        seen += [(b.request.request_id, len(b.tokens), b.request.preemptions) for b in batch]
+    again = [n for rid, n, p in seen if rid == 2 and p >= 1 and n > 1]
+    assert again and again[0] > 4            # came back with its prompt AND what it had generated
+
+
+def test_request_that_can_never_fit_ends_with_an_error():
+    m, s = make(n_pages=2, page=4, budget=64, chunk=64)        # 8 tokens of cache
+    s.add_request(req(1, 12))
+    s.add_request(req(2, 3, max_new=2))
+    outs = []
+    while s.has_work():
+        outs += run_step(m, s)[1]
+    assert [(o.request_id, o.reason) for o in outs if o.finished] == [(1, "error_too_long"), (2, "length")]
+
+
+def test_lone_request_that_outgrows_the_pool_ends_with_an_error():
+    m, s = make(n_pages=2, page=4, budget=64, chunk=64)
+    s.add_request(req(1, 6, max_new=10))
+    outs = []
+    while s.has_work():
+        outs += run_step(m, s)[1]
+    assert outs[-1].reason == "error_too_long" and outs[-1].token is None
+    assert [o.token for o in outs[:-1]] == [7, 7, 7]             # tokens 7, 8 and the one at position 8 fails
+    assert not m.requests and m.free_pages() == 2
+
+
+def test_abort_frees_everything():
+    m, s = make()
+    s.add_request(req(1, 5))
+    s.add_request(req(2, 5))
+    run_step(m, s)
+    outs = s.abort_all()
+    assert sorted(o.request_id for o in outs) == [1, 2] and all(o.finished for o in outs)
+    assert not m.requests and m.free_pages() == 16
