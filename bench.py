@@ -131,6 +131,8 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself "
+                    "(for a profiler's launch list)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -176,7 +178,7 @@ def main():
     for kv in runner.storage.kv:
         for i in range(kv.size(0)):
             kv[i].normal_(0.0, 1.0)
-    runner.use_graphs = True
+    runner.use_graphs = not args.no_graphs
     print(f"[bench] model on device in {time.time() - t0:.1f} s, "
           f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated", file=sys.stderr, flush=True)
     rng = np.random.default_rng(0)
@@ -222,7 +224,7 @@ def main():
         n0 = ops.launch_count
         runner.step([StepEntry(r, [1], [0]) for r in ids])
         n = ops.launch_count - n0
-        runner.use_graphs = True
+        runner.use_graphs = not args.no_graphs
         for rid in ids:
             runner.release(rid)
         return n
@@ -243,11 +245,11 @@ def main():
             "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
             "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
             "seq_len": ctx, "page_size": page, "kv_dtype": "bf16", "parallelism": "single GPU",
-            "cuda_graphs": True, "l2": "inputs larger than L2 (weights 15 GB per step)",
+            "cuda_graphs": not args.no_graphs, "l2": "inputs larger than L2 (weights 15 GB per step)",
             "peaks": pk["source"]},
         "clocks": clocks,
         # One replay of a captured step launches every kernel of the step; argmax is launched eagerly.
-        "gpu_launches": per_step_kernels * K + eager_launches,
+        "gpu_launches": (per_step_kernels * K if not args.no_graphs else 0) + eager_launches,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
     }
