@@ -1,8 +1,9 @@
 // Attention over the paged cache, for every element type and head size (head_dim in
 // steps of 16, any number of heads and groups).
 //
-//   prefill: a tile of 16 query tokens of one request against all keys it may see
-//            (earlier portions from the cache plus its own causal part), online softmax.
+//   prefill: 16 query tokens of one request against all keys they may see (earlier
+//            portions from the cache plus their own causal part), online softmax. The
+//            tile list names tiles of 64 queries; grid.z picks the quarter.
 //   decode:  one query token per request; the keys are cut into splits of a fixed
 //            number that run as separate blocks and are merged by a combine kernel.
 //
@@ -13,10 +14,25 @@
 // softmax over keys, product with values).
 #include "common.cuh"
 
+// Tensor-core kernels for bfloat16 with head_dim <= 128 (attention_mma.cu).
+int llmrs_attn_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* cache,
+                           const int* tiles, int n_tiles, const int* q_start, const int* n_new,
+                           const int* cached_len, const int* block_table, int table_stride, int n_q_heads,
+                           int n_kv_heads, int d, int page_size, int window, float scale, cudaStream_t stream);
+int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
+                                const int* q_start, const int* cached_len, const int* block_table, int table_stride,
+                                float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
+                                int page_size, int window, float scale, cudaStream_t stream);
+
+// 1: bfloat16 also takes the generic kernels (tests compare the two implementations).
+static int g_generic_only = 0;
+LLMRS_API void llmrs_attention_generic_only(int on) { g_generic_only = on; }
+
 // ---------------------------------------------------------------------------------
 // Prefill
 // ---------------------------------------------------------------------------------
 constexpr int PF_BQ = 16;        // query rows per block
+constexpr int PF_TILE = 64;      // query rows per entry of the tile list
 constexpr int PF_BK = 32;        // keys per iteration
 constexpr int PF_THREADS = 256;  // 16 threads per query row
 constexpr int PF_MAX_DCHUNK = 16;  // head_dim / 16 <= 16  => head_dim <= 256
@@ -36,7 +52,8 @@ attn_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__
 
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (n_q_heads / n_kv_heads);
-  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
+  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1] + blockIdx.z * PF_BQ;
+  if (q_off >= n_new[req]) return;
   const int rows = min(PF_BQ, n_new[req] - q_off);
   const int cached = cached_len[req];
   const int tok0 = q_start[req] + q_off;
@@ -145,8 +162,12 @@ LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, l
                 "attn_prefill: head_dim %d must be a multiple of 16 between 16 and %d", d, 16 * PF_MAX_DCHUNK);
   if (n_tiles == 0) return 0;
   const size_t smem = (size_t)(PF_BQ * d + PF_BK * (d + 1) + PF_BK * d + PF_BQ * PF_BK) * sizeof(float);
-  dim3 grid(n_tiles, n_q_heads);
+  dim3 grid(n_tiles, n_q_heads, PF_TILE / PF_BQ);
   cudaError_t e;
+  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only)
+    return llmrs_attn_prefill_mma(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new, cached_len,
+                                  block_table, table_stride, n_q_heads, n_kv_heads, d, page_size, window, scale,
+                                  stream);
   if (dtype == LLMRS_F32) {
     e = cudaFuncSetAttribute(attn_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llmrs_fail("attn_prefill: shared memory %zu: %s", smem, cudaGetErrorString(e));
@@ -412,6 +433,17 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
     return launch_decode<float, 4>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,
                                    block_table, table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads,
                                    d, page_size, window, scale, stream);
+  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only) {
+    int rc = llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
+                                         table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
+                                         page_size, window, scale, stream);
+    if (rc) return rc;
+    dim3 cgrid(n_dec, n_q_heads);
+    attn_decode_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, stream>>>(
+        scratch, (__nv_bfloat16*)out, out_stride, dec_reqs, q_start, cached_len, max_splits, split_keys, n_q_heads, d,
+        window);
+    return llmrs_launch_status("attn_decode_combine");
+  }
   if (dtype == LLMRS_BF16)
     return launch_decode<__nv_bfloat16, 8>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,
                                            block_table, table_stride, scratch, max_splits, split_keys, n_q_heads,

@@ -1,0 +1,470 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16 with
+// float32 accumulation), for head sizes 16..128 in steps of 16. Same contracts and the
+// same math as the generic kernels in attention.cu (scores, softmax and the weighted sum
+// accumulate in float32; causal mask with an optional window), which stay in use for
+// float32 and for larger heads.
+//
+//   decode:  a block owns (request, key head, split of the keys). The query heads that
+//            share the key head are the rows of one 16-row tile, so one pass over the
+//            keys serves them all. Each of the 4 warps streams its own 16-key tiles
+//            through a 3-stage cp.async pipeline; the warps' partial results are merged
+//            in shared memory and written as one (max, sum, weighted values) record per
+//            head, which the combine kernel of attention.cu merges across splits.
+//   prefill: a block owns (64 query tokens of one request, query head); 4 warps of 16
+//            rows; keys and values come in tiles of 64 through a double buffer.
+#include "common.cuh"
+#include "mma_util.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------------
+// Decode
+// ---------------------------------------------------------------------------------
+constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_STAGES = 3, DM_TILE = 16;
+
+template <int DCH>
+__global__ void __launch_bounds__(DM_THREADS)
+attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ cache,
+                             const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
+                             const int* __restrict__ cached_len, const int* __restrict__ block_table,
+                             int table_stride, float* __restrict__ part, int max_splits, int split_keys,
+                             int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
+  constexpr int D = 16 * DCH;
+  constexpr int ROW = D + 8;               // 16 bytes of padding: ldmatrix rows fall into distinct banks
+  constexpr int CH = D / 8;                // 16-byte chunks per row
+  constexpr int TILE_ELEMS = DM_TILE * ROW;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+
+  const int G = n_q_heads / n_kv_heads;
+  const int hgroups = (G + 15) / 16;
+  const int di = blockIdx.x;
+  const int kvh = blockIdx.y / hgroups;
+  const int g0 = (blockIdx.y % hgroups) * 16;
+  const int ng = min(16, G - g0);
+  const int split = blockIdx.z;
+  const int req = dec_reqs[di];
+  const int kv_len = cached_len[req] + 1;
+  const int kv_lo = window > 0 ? max(0, kv_len - window) : 0;
+  const int k_begin = max(split * split_keys, kv_lo);
+  const int k_end = min((split + 1) * split_keys, kv_len);
+  if (k_begin >= k_end) return;
+  const int* table = block_table + (size_t)req * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  const int tile_first = k_begin / DM_TILE, tile_last = (k_end - 1) / DM_TILE;
+  const int n_tiles = tile_last - tile_first + 1;
+  const int n_my = n_tiles > warp ? (n_tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
+
+  bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * DM_STAGES * 2 * TILE_ELEMS;
+
+  // Query rows as A fragments: row gq is head g0+gq, row gq+8 is head g0+gq+8; absent heads are zero.
+  uint32_t qf[DCH][4];
+  {
+    const bf16* qt = q + (size_t)q_start[req] * q_stride + (size_t)(kvh * G + g0) * D;
+#pragma unroll
+    for (int kc = 0; kc < DCH; ++kc) {
+      const int col = kc * 16 + tq * 2;
+      qf[kc][0] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col) : 0u;
+      qf[kc][1] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col) : 0u;
+      qf[kc][2] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col + 8) : 0u;
+      qf[kc][3] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col + 8) : 0u;
+    }
+  }
+
+  auto load_tile = [&](int i, int stage) {
+    const int t = tile_first + warp + i * DM_WARPS;
+    bf16* Ks = wbase + (size_t)stage * 2 * TILE_ELEMS;
+    bf16* Vs = Ks + TILE_ELEMS;
+#pragma unroll 4
+    for (int c = lane; c < DM_TILE * CH; c += 32) {
+      const int row = c / CH, ch = c - row * CH;
+      const int key = t * DM_TILE + row;
+      const bool valid = key >= k_begin && key < k_end;
+      const bf16* src = cache;
+      if (valid) {
+        const int page = table[key / page_size];
+        src = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) + (size_t)(key % page_size) * D + ch * 8;
+      }
+      cp_async_16(Ks + row * ROW + ch * 8, src, valid ? 16 : 0);
+      cp_async_16(Vs + row * ROW + ch * 8, valid ? src + (size_t)page_size * D : src, valid ? 16 : 0);
+    }
+  };
+
+  float o[2 * DCH][4];
+#pragma unroll
+  for (int n = 0; n < 2 * DCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  const float sl2 = scale * LOG2E;
+
+#pragma unroll
+  for (int s = 0; s < DM_STAGES - 1; ++s) {
+    if (s < n_my) load_tile(s, s);
+    cp_async_commit();
+  }
+  for (int i = 0; i < n_my; ++i) {
+    cp_async_wait<DM_STAGES - 2>();
+    __syncwarp();
+    if (i + DM_STAGES - 1 < n_my) load_tile(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
+    cp_async_commit();
+
+    const bf16* Ks = wbase + (size_t)(i % DM_STAGES) * 2 * TILE_ELEMS;
+    const bf16* Vs = Ks + TILE_ELEMS;
+    const int key0 = (tile_first + warp + i * DM_WARPS) * DM_TILE;
+
+    // Scores of the 16 head rows against 16 keys: two 16x8 tiles.
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kc = 0; kc < DCH; ++kc) {
+      uint32_t b[4];
+      // matrix j = lane/8: keys (j/2)*8.., head-dim columns kc*16 + (j%2)*8..
+      const int j = lane >> 3;
+      ldmatrix_x4(b, Ks + ((j >> 1) * 8 + (lane & 7)) * ROW + kc * 16 + (j & 1) * 8);
+      mma_bf16_16816(s[0], qf[kc], b[0], b[1]);
+      mma_bf16_16816(s[1], qf[kc], b[2], b[3]);
+    }
+    // Mask, scale into the log2 domain, online softmax per row.
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + n * 8 + tq * 2 + (e & 1);
+        const bool seen = key >= k_begin && key < k_end;
+        s[n][e] = seen ? s[n][e] * sl2 : -INFINITY;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+      }
+    uint32_t pf[4];
+    float corr[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_row[r], mx[r]);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = exp2f(m_row[r] - m_use);
+      m_row[r] = m_new;
+      float sum = 0.f;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float p = exp2f(s[n][r * 2 + e] - m_use);
+          s[n][r * 2 + e] = p;
+          sum += p;
+        }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l_row[r] = l_row[r] * corr[r] + sum;
+    }
+    pf[0] = pack_bf16(s[0][0], s[0][1]);
+    pf[1] = pack_bf16(s[0][2], s[0][3]);
+    pf[2] = pack_bf16(s[1][0], s[1][1]);
+    pf[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int n = 0; n < 2 * DCH; ++n) {
+      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+    // Weighted sum of values: B fragments are 8x8 blocks of V read transposed.
+#pragma unroll
+    for (int nc = 0; nc < DCH; ++nc) {
+      uint32_t b[4];
+      // matrix j = lane/8: keys (j%2)*8.., head-dim columns (2*nc + j/2)*8..
+      const int j = lane >> 3;
+      ldmatrix_x4_trans(b, Vs + ((j & 1) * 8 + (lane & 7)) * ROW + (2 * nc + (j >> 1)) * 8);
+      mma_bf16_16816(o[2 * nc], pf, b[0], b[1]);
+      mma_bf16_16816(o[2 * nc + 1], pf, b[2], b[3]);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // Merge the warps: every warp leaves (m, l, o) of its rows in shared memory.
+  float* Om = reinterpret_cast<float*>(smem_raw);           // [warps][16][D]
+  float* Mm = Om + DM_WARPS * 16 * D;                       // [warps][16]
+  float* Lm = Mm + DM_WARPS * 16;
+#pragma unroll
+  for (int n = 0; n < 2 * DCH; ++n) {
+    const int col = n * 8 + tq * 2;
+    float* r0 = Om + ((size_t)warp * 16 + gq) * D + col;
+    float* r1 = Om + ((size_t)warp * 16 + gq + 8) * D + col;
+    r0[0] = o[n][0]; r0[1] = o[n][1]; r1[0] = o[n][2]; r1[1] = o[n][3];
+  }
+  if (tq == 0) {
+    Mm[warp * 16 + gq] = m_row[0]; Mm[warp * 16 + gq + 8] = m_row[1];
+    Lm[warp * 16 + gq] = l_row[0]; Lm[warp * 16 + gq + 8] = l_row[1];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng * D; i += DM_THREADS) {
+    const int g = i / D, e = i - g * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) M = fmaxf(M, Mm[w * 16 + g]);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < DM_WARPS; ++w) {
+      const float mw = Mm[w * 16 + g];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      L += Lm[w * 16 + g] * f;
+      acc += Om[((size_t)w * 16 + g) * D + e] * f;
+    }
+    const int head = kvh * G + g0 + g;
+    float* pp = part + ((size_t)((size_t)di * n_q_heads + head) * max_splits + split) * (D + 2);
+    pp[2 + e] = acc;
+    // The combine kernel works with natural logarithms: hand it the maximum in that domain.
+    if (e == 0) { pp[0] = M / LOG2E; pp[1] = L; }
+  }
+}
+
+template <int DCH>
+static int launch_decode_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
+                             const int* q_start, const int* cached_len, const int* block_table, int table_stride,
+                             float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
+                             int page_size, int window, float scale, cudaStream_t stream) {
+  constexpr int D = 16 * DCH;
+  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
+  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16) * sizeof(float);
+  const size_t smem = pipe > merge ? pipe : merge;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  const int G = n_q_heads / n_kv_heads;
+  dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
+  attn_decode_split_mma_kernel<DCH><<<grid, DM_THREADS, smem, stream>>>(
+      (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,
+      max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale);
+  return llmrs_launch_status("attn_decode_split_mma");
+}
+
+// The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).
+// Writes the same per-split records as the generic split kernel.
+int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
+                                const int* q_start, const int* cached_len, const int* block_table, int table_stride,
+                                float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
+                                int page_size, int window, float scale, cudaStream_t stream) {
+#define LLMRS_DM_CASE(N)                                                                                          \
+  case N:                                                                                                          \
+    return launch_decode_mma<N>(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table, table_stride, \
+                                scratch, max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, stream)
+  switch (d / 16) {
+    LLMRS_DM_CASE(1); LLMRS_DM_CASE(2); LLMRS_DM_CASE(3); LLMRS_DM_CASE(4);
+    LLMRS_DM_CASE(5); LLMRS_DM_CASE(6); LLMRS_DM_CASE(7); LLMRS_DM_CASE(8);
+  }
+#undef LLMRS_DM_CASE
+  return llmrs_fail("attn_decode_mma: head_dim %d is not supported", d);
+}
+
+// ---------------------------------------------------------------------------------
+// Prefill
+// ---------------------------------------------------------------------------------
+constexpr int PM_BQ = 64, PM_BK = 64, PM_WARPS = 4, PM_THREADS = PM_WARPS * 32;
+
+template <int DCH>
+__global__ void __launch_bounds__(PM_THREADS)
+attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
+                        const bf16* __restrict__ cache, const int* __restrict__ tiles,
+                        const int* __restrict__ q_start, const int* __restrict__ n_new,
+                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
+                        int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
+  constexpr int D = 16 * DCH;
+  constexpr int ROW = D + 8;
+  constexpr int CH = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [64][ROW]
+  bf16* KV = Qs + PM_BQ * ROW;                      // 2 stages x (K [64][ROW], V [64][ROW])
+
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (n_q_heads / n_kv_heads);
+  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
+  const int rows = min(PM_BQ, n_new[req] - q_off);
+  const int tok0 = q_start[req] + q_off;
+  const int pos0 = cached_len[req] + q_off;
+  const int kv_hi = pos0 + rows;
+  int kv_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  kv_lo = (kv_lo / PM_BK) * PM_BK;
+  const int key_floor = window > 0 ? max(0, pos0 - window + 1) : 0;   // no row reads a key below this
+  const int* table = block_table + (size_t)req * table_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  for (int c = threadIdx.x; c < PM_BQ * CH; c += PM_THREADS) {
+    const int row = c / CH, ch = c - row * CH;
+    const bool valid = row < rows;
+    const bf16* src = valid ? q + (size_t)(tok0 + row) * q_stride + (size_t)head * D + ch * 8 : q;
+    cp_async_16(Qs + row * ROW + ch * 8, src, valid ? 16 : 0);
+  }
+  auto load_kv = [&](int kb, int stage) {
+    bf16* Ks = KV + (size_t)stage * 2 * PM_BK * ROW;
+    bf16* Vs = Ks + PM_BK * ROW;
+    for (int c = threadIdx.x; c < PM_BK * CH; c += PM_THREADS) {
+      const int row = c / CH, ch = c - row * CH;
+      const int key = kb + row;
+      const bool valid = key >= key_floor && key < kv_hi;
+      const bf16* src = cache;
+      if (valid) {
+        const int page = table[key / page_size];
+        src = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) + (size_t)(key % page_size) * D + ch * 8;
+      }
+      cp_async_16(Ks + row * ROW + ch * 8, src, valid ? 16 : 0);
+      cp_async_16(Vs + row * ROW + ch * 8, valid ? src + (size_t)page_size * D : src, valid ? 16 : 0);
+    }
+  };
+  load_kv(kv_lo, 0);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  uint32_t qf[DCH][4];
+  {
+    const int j = lane >> 3;  // matrix j: rows (j%2)*8.., columns kc*16 + (j/2)*8..
+#pragma unroll
+    for (int kc = 0; kc < DCH; ++kc)
+      ldmatrix_x4(qf[kc], Qs + (warp * 16 + (j & 1) * 8 + (lane & 7)) * ROW + kc * 16 + (j >> 1) * 8);
+  }
+  float o[2 * DCH][4];
+#pragma unroll
+  for (int n = 0; n < 2 * DCH; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
+  const float sl2 = scale * LOG2E;
+  const int pos_r[2] = {pos0 + warp * 16 + gq, pos0 + warp * 16 + gq + 8};
+
+  int stage = 0;
+  for (int kb = kv_lo; kb < kv_hi; kb += PM_BK, stage ^= 1) {
+    // Tile kb is in `stage` (waited for below or before the loop); fetch the next one.
+    if (kb + PM_BK < kv_hi) load_kv(kb + PM_BK, stage ^ 1);
+    cp_async_commit();
+    const bf16* Ks = KV + (size_t)stage * 2 * PM_BK * ROW;
+    const bf16* Vs = Ks + PM_BK * ROW;
+    // A warp whose rows all lie before this tile of keys has nothing to add.
+    const bool active = kb <= pos0 + warp * 16 + 15;
+    if (active) {
+      float s[PM_BK / 8][4];
+#pragma unroll
+      for (int n = 0; n < PM_BK / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+      for (int kc = 0; kc < DCH; ++kc) {
+        const int j = lane >> 3;
+#pragma unroll
+        for (int np = 0; np < PM_BK / 16; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4(b, Ks + (np * 16 + (j >> 1) * 8 + (lane & 7)) * ROW + kc * 16 + (j & 1) * 8);
+          mma_bf16_16816(s[2 * np], qf[kc], b[0], b[1]);
+          mma_bf16_16816(s[2 * np + 1], qf[kc], b[2], b[3]);
+        }
+      }
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < PM_BK / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kb + n * 8 + tq * 2 + (e & 1);
+          const int p = pos_r[e >> 1];
+          const bool seen = key <= p && (window <= 0 || key > p - window);
+          s[n][e] = seen ? s[n][e] * sl2 : -INFINITY;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+        }
+      float corr[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m_row[r], mx[r]);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        corr[r] = exp2f(m_row[r] - m_use);
+        m_row[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < PM_BK / 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float p = exp2f(s[n][r * 2 + e] - m_use);
+            s[n][r * 2 + e] = p;
+            sum += p;
+          }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_row[r] = l_row[r] * corr[r] + sum;
+      }
+#pragma unroll
+      for (int n = 0; n < 2 * DCH; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
+#pragma unroll
+      for (int kc = 0; kc < PM_BK / 16; ++kc) {
+        uint32_t pf[4];
+        pf[0] = pack_bf16(s[2 * kc][0], s[2 * kc][1]);
+        pf[1] = pack_bf16(s[2 * kc][2], s[2 * kc][3]);
+        pf[2] = pack_bf16(s[2 * kc + 1][0], s[2 * kc + 1][1]);
+        pf[3] = pack_bf16(s[2 * kc + 1][2], s[2 * kc + 1][3]);
+        const int j = lane >> 3;
+#pragma unroll
+        for (int nc = 0; nc < DCH; ++nc) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, Vs + (kc * 16 + (j & 1) * 8 + (lane & 7)) * ROW + (2 * nc + (j >> 1)) * 8);
+          mma_bf16_16816(o[2 * nc], pf, b[0], b[1]);
+          mma_bf16_16816(o[2 * nc + 1], pf, b[2], b[3]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = warp * 16 + gq + r * 8;
+    if (row < rows) {
+      const float inv = l_row[r] > 0.f ? 1.0f / l_row[r] : 0.f;
+      bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * D;
+#pragma unroll
+      for (int n = 0; n < 2 * DCH; ++n) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(o[n][r * 2] * inv, o[n][r * 2 + 1] * inv);
+        *reinterpret_cast<__nv_bfloat162*>(orow + n * 8 + tq * 2) = v;
+      }
+    }
+  }
+}
+
+template <int DCH>
+static int launch_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* cache,
+                              const int* tiles, int n_tiles, const int* q_start, const int* n_new,
+                              const int* cached_len, const int* block_table, int table_stride, int n_q_heads,
+                              int n_kv_heads, int page_size, int window, float scale, cudaStream_t stream) {
+  constexpr int D = 16 * DCH;
+  const size_t smem = (size_t)(PM_BQ + 4 * PM_BK) * (D + 8) * sizeof(bf16);
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_prefill_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
+  dim3 grid(n_tiles, n_q_heads);
+  attn_prefill_mma_kernel<DCH><<<grid, PM_THREADS, smem, stream>>>(
+      (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, tiles, q_start, n_new, cached_len,
+      block_table, table_stride, n_q_heads, n_kv_heads, page_size, window, scale);
+  return llmrs_launch_status("attn_prefill_mma");
+}
+
+// Prefill attention on the tensor cores (bfloat16, head_dim <= 128); tiles of 64 queries.
+int llmrs_attn_prefill_mma(const void* q, long long q_stride, void* out, long long out_stride, const void* cache,
+                           const int* tiles, int n_tiles, const int* q_start, const int* n_new,
+                           const int* cached_len, const int* block_table, int table_stride, int n_q_heads,
+                           int n_kv_heads, int d, int page_size, int window, float scale, cudaStream_t stream) {
+#define LLMRS_PM_CASE(N)                                                                                         \
+  case N:                                                                                                         \
+    return launch_prefill_mma<N>(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new, cached_len, \
+                                 block_table, table_stride, n_q_heads, n_kv_heads, page_size, window, scale, stream)
+  switch (d / 16) {
+    LLMRS_PM_CASE(1); LLMRS_PM_CASE(2); LLMRS_PM_CASE(3); LLMRS_PM_CASE(4);
+    LLMRS_PM_CASE(5); LLMRS_PM_CASE(6); LLMRS_PM_CASE(7); LLMRS_PM_CASE(8);
+  }
+#undef LLMRS_PM_CASE
+  return llmrs_fail("attn_prefill_mma: head_dim %d is not supported", d);
+}

@@ -24,7 +24,7 @@ from ..config import load_config
 from ..parts import DecoderModel, ModelSpec, Runtime
 from ..weights import load_weights
 
-PREFILL_TILE = 16  # queries per tile of the prefill attention kernel
+PREFILL_TILE = 64  # queries per entry of the prefill attention kernels' tile list
 
 
 class StepError(RuntimeError):

@@ -196,7 +196,7 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles:
     """Causal attention of prompt portions over the paged cache (their own keys are already written).
 
     ``tiles`` is int32 [n_tiles, 2]: (request row, offset of the tile's first query in
-    the request's new tokens); a tile covers 16 queries.
+    the request's new tokens); a tile covers 64 queries.
     """
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
@@ -283,3 +283,10 @@ def philox_uniform(seed: int, request_id: int, index: int) -> float:
     fn.restype = ctypes.c_float
     return float(fn(ctypes.c_ulonglong(seed & (2**64 - 1)), ctypes.c_ulonglong(request_id & (2**64 - 1)),
                     ctypes.c_uint(index)))
+
+
+def attention_generic_only(on: bool) -> None:
+    """Make bfloat16 attention take the generic kernels too (tests compare both implementations)."""
+    fn = _lib().llmrs_attention_generic_only
+    fn.restype = None
+    fn(1 if on else 0)

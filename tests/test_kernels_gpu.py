@@ -1,0 +1,386 @@
+"""Each CUDA kernel alone against a plain float32/float64 PyTorch restatement of the same
+operation, at sizes other than the engine's test models (head sizes in steps of 16, odd
+head counts and groups, widths and vocabularies that are no power of two)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _ops():
+    from llm_rs_b200 import ops
+    return ops
+
+
+def _tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+# -- element-wise --------------------------------------------------------------------------
+@pytest.mark.parametrize("table_dtype", [torch.float32, torch.bfloat16])
+def test_embedding(table_dtype):
+    ops = _ops()
+    table = torch.randn(301, 72, device=DEV).to(table_dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = ops.embedding(table, ids)
+    assert out.dtype == torch.float32 and torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [48, 1000, 4096, 5120])
+def test_add_rmsnorm(dtype, hidden):
+    ops = _ops()
+    torch.manual_seed(hidden)
+    h = torch.randn(7, hidden, device=DEV) * 3
+    delta = torch.randn(7, hidden, device=DEV).to(dtype)
+    w = 1 + 0.1 * torch.randn(hidden, device=DEV)
+    eps = 3e-6
+    want_h = h.double() + delta.double()
+    want_y = P.rms_norm(want_h, w.double(), eps)
+    h2 = h.clone()
+    y = ops.add_rmsnorm(h2, delta, w, eps, dtype)
+    assert torch.allclose(h2.double(), want_h, atol=1e-6)
+    assert torch.allclose(y.double(), want_y, **_tol(dtype))
+    # without a delta, and with a row gather that leaves h alone
+    h3 = h.clone()
+    y0 = ops.add_rmsnorm(h3, None, w, eps, dtype)
+    assert torch.equal(h3, h) and torch.allclose(y0.double(), P.rms_norm(h.double(), w.double(), eps), **_tol(dtype))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    h4 = h.clone()
+    yr = ops.add_rmsnorm(h4, delta, w, eps, dtype, rows=rows)
+    assert torch.equal(h4, h) and torch.allclose(yr.double(), want_y[rows.long()], **_tol(dtype))
+
+
+def test_rmsnorm_eps_matters():
+    ops = _ops()
+    h = torch.full((1, 64), 1e-3, device=DEV)
+    w = torch.ones(64, device=DEV)
+    a = ops.add_rmsnorm(h.clone(), None, w, 1e-6, torch.float32)
+    b = ops.add_rmsnorm(h.clone(), None, w, 1e-5, torch.float32)
+    assert abs(float(a[0, 0]) - 1e-3 / math.sqrt(1e-6 + 1e-6)) < 1e-4
+    assert abs(float(b[0, 0]) - 1e-3 / math.sqrt(1e-6 + 1e-5)) < 1e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul_and_residual_add(dtype):
+    ops = _ops()
+    gu = (torch.randn(5, 2 * 176, device=DEV) * 4).to(dtype)
+    g, u = gu[:, :176].double(), gu[:, 176:].double()
+    assert torch.allclose(ops.silu_mul(gu).double(), g * torch.sigmoid(g) * u, **_tol(dtype))
+    h = torch.randn(5, 88, device=DEV)
+    d = torch.randn(5, 88, device=DEV).to(dtype)
+    want = h.double() + d.double()
+    assert torch.allclose(ops.residual_add(h, d).double(), want, atol=1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 96, 80), (5, 333, 176), (70, 130, 17), (129, 64, 257)])
+def test_gemm_f32_is_true_float32(M, N, K):
+    ops = _ops()
+    torch.manual_seed(M)
+    x, w, b = torch.randn(M, K, device=DEV), torch.randn(N, K, device=DEV), torch.randn(N, device=DEV)
+    want = x.double() @ w.double().t() + b.double()
+    got = ops.gemm_f32(x, w, b)
+    # TF32 (10 bits of mantissa) would miss this by a factor of a thousand.
+    assert float((got.double() - want).abs().max()) < 1e-4 * math.sqrt(K)
+    assert float((got.double() - want).abs().max() / want.abs().max()) < 1e-5
+    # One row alone gives the same bits as the row inside the batch.
+    if M > 1:
+        assert torch.equal(ops.gemm_f32(x[3:4].contiguous(), w, b)[0], got[3])
+
+
+# -- norm + rotation + cache write ---------------------------------------------------------
+def _paged_setup(lens, new, n_kv, d, page, dtype, seed=0):
+    """Random cache with scattered pages; returns tensors for kernels and dense copies for the reference."""
+    g = torch.Generator().manual_seed(seed)
+    n_req = len(lens)
+    pages_per = [-(-(l + n) // page) for l, n in zip(lens, new)]
+    n_pages = sum(pages_per) + 5
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((n_req, max(pages_per) + 1), -1, dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_per):
+        table[r, :n] = torch.tensor(perm[at:at + n], dtype=torch.int32)
+        at += n
+    cache = torch.randn((n_pages, n_kv, 2, page, d), generator=g).to(dtype)
+    return table, cache
+
+
+def _dense_kv(cache, table, r, length, page):
+    """[length, n_kv, d] keys and values of request r gathered from its pages."""
+    ks, vs = [], []
+    for pos in range(length):
+        pg = int(table[r, pos // page])
+        ks.append(cache[pg, :, 0, pos % page])
+        vs.append(cache[pg, :, 1, pos % page])
+    return torch.stack(ks).double(), torch.stack(vs).double()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(6, 3, 48, 48, 8), (5, 1, 16, 8, 16), (8, 2, 128, 128, 16), (2, 2, 80, 0, 4)])
+def test_qk_norm_rope_kvwrite(dtype, nq, nkv, d, rot, page):
+    ops = _ops()
+    torch.manual_seed(d)
+    lens, new = [5, 0, 37], [3, 9, 1]
+    table, cache = _paged_setup(lens, new, nkv, d, page, dtype)
+    T = sum(new)
+    qkv = torch.randn(T, (nq + 2 * nkv) * d).to(dtype)
+    qn, kn = 1 + 0.2 * torch.randn(d), 1 + 0.2 * torch.randn(d)
+    eps, theta = 1e-5, 12345.0
+    positions = torch.tensor([l + i for l, n in zip(lens, new) for i in range(n)], dtype=torch.int32)
+    token_req = torch.tensor([r for r, n in enumerate(new) for _ in range(n)], dtype=torch.int32)
+    cos_sin = None
+    if rot:
+        ang = P.rope_angles(range(64), rot, theta, torch.float64)
+        cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float().contiguous().to(DEV)
+    # reference
+    q = qkv[:, :nq * d].double().reshape(T, nq, d)
+    k = qkv[:, nq * d:(nq + nkv) * d].double().reshape(T, nkv, d)
+    v = qkv[:, (nq + nkv) * d:].double().reshape(T, nkv, d)
+    q, k = P.rms_norm(q, qn.double(), eps), P.rms_norm(k, kn.double(), eps)
+    if rot:
+        a = P.rope_angles(positions.tolist(), rot, theta, torch.float64)
+        q = torch.cat([P.rotate_half(q[..., :rot], a), q[..., rot:]], -1)
+        k = torch.cat([P.rotate_half(k[..., :rot], a), k[..., rot:]], -1)
+    dq, dc = qkv.to(DEV), cache.to(DEV)
+    before = dc.clone()
+    ops.qk_norm_rope_kvwrite(dq[:, :nq * d], dq[:, nq * d:(nq + nkv) * d], dq[:, (nq + nkv) * d:], qn.to(DEV),
+                             kn.to(DEV), cos_sin, positions.to(DEV), token_req.to(DEV), table.to(DEV), dc, nq, nkv,
+                             d, rot, page, eps)
+    tol = _tol(dtype)
+    assert torch.allclose(dq[:, :nq * d].double().cpu().reshape(T, nq, d), q, **tol)
+    written = torch.zeros(dc.shape, dtype=torch.bool)
+    for t in range(T):
+        pos, r = int(positions[t]), int(token_req[t])
+        pg = int(table[r, pos // page])
+        assert torch.allclose(dc[pg, :, 0, pos % page].double().cpu(), k[t], **tol)
+        assert torch.allclose(dc[pg, :, 1, pos % page].double().cpu(), v[t], **tol)
+        written[pg, :, :, pos % page] = True
+    assert torch.equal(dc.cpu()[~written], before.cpu()[~written]), "a slot of another token was touched"
+
+
+# -- attention ------------------------------------------------------------------------------
+def _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, scale):
+    """Plain attention per request over the gathered keys: [T, nq*d] float64."""
+    outs, at = [], 0
+    for r, (l, n) in enumerate(zip(lens, new)):
+        K, V = _dense_kv(cache, table, r, l + n, page)
+        qq = q[at:at + n].double().reshape(n, nq, d)
+        G = nq // nkv
+        kk, vv = K.repeat_interleave(G, 1), V.repeat_interleave(G, 1)
+        s = torch.einsum("qhd,khd->hqk", qq, kk) * scale
+        qi = torch.arange(l, l + n)[:, None]
+        ki = torch.arange(l + n)[None, :]
+        hidden = ki > qi
+        if window > 0:
+            hidden = hidden | (ki <= qi - window)
+        p = torch.softmax(s.masked_fill(hidden[None], float("-inf")), -1)
+        outs.append(torch.einsum("hqk,khd->qhd", p, vv).reshape(n, nq * d))
+        at += n
+    return torch.cat(outs)
+
+
+def _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale, split_keys=64):
+    ops = _ops()
+    T = sum(new)
+    dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+    out = torch.zeros(T, nq * d, dtype=q.dtype, device=DEV)
+    q_start = torch.tensor(np.cumsum([0] + new[:-1]), dtype=torch.int32, device=DEV)
+    n_new = torch.tensor(new, dtype=torch.int32, device=DEV)
+    cached = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    tiles = [(r, off) for r, n in enumerate(new) if n > 1 for off in range(0, n, 64)]
+    dec = [r for r, n in enumerate(new) if n == 1]
+    if tiles:
+        tt = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+        ops.attn_prefill(dq, out, dc, tt, len(tiles), q_start, n_new, cached, dt, nq, nkv, d, page, window, scale)
+    if dec:
+        max_splits = -(-max(lens[r] + 1 for r in dec) // split_keys)
+        scratch = torch.full((ops.attn_decode_scratch_floats(len(dec), nq, d, max_splits),), float("nan"), device=DEV)
+        ops.attn_decode(dq, out, dc, torch.tensor(dec, dtype=torch.int32, device=DEV), len(dec), q_start, cached, dt,
+                        scratch, max_splits, split_keys, nq, nkv, d, page, window, scale)
+    torch.cuda.synchronize()
+    return out.double().cpu()
+
+
+SHAPES = [  # nq, nkv, d, page
+    (4, 2, 16, 16), (6, 3, 48, 8), (8, 1, 64, 16), (5, 5, 80, 4), (32, 8, 128, 16), (3, 1, 96, 32), (40, 2, 32, 16),
+    (2, 1, 160, 16), (4, 2, 256, 16)]
+
+
+@pytest.mark.parametrize("impl", ["auto", "generic"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 37])
+@pytest.mark.parametrize("nq,nkv,d,page", SHAPES)
+def test_attention_prefill_and_decode(nq, nkv, d, page, window, dtype, impl):
+    """A mixed step: long portions, a two-token portion, single decode tokens, with and without earlier context."""
+    if impl == "generic" and dtype == torch.float32:
+        pytest.skip("float32 always takes the generic kernels")
+    ops = _ops()
+    lens = [0, 70, 129, 300, 3, 0, 64]
+    new = [150, 65, 2, 1, 1, 1, 16]
+    torch.manual_seed(nq * d + window)
+    table, cache = _paged_setup(lens, new, nkv, d, page, dtype, seed=d)
+    q = (torch.randn(sum(new), nq * d) * 1.5).to(dtype)
+    scale = 0.7 / math.sqrt(d)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, scale)
+    ops.attention_generic_only(impl == "generic")
+    try:
+        got = _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale)
+    finally:
+        ops.attention_generic_only(False)
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2.5e-2, rtol=2e-2)
+    bad = ~torch.isclose(got, want, **tol)
+    assert not bad.any(), f"{int(bad.sum())} elements differ; worst {float((got - want).abs().max()):.3e} " \
+                          f"first at {bad.nonzero()[0].tolist()}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 257, 1000, 1999])
+def test_one_far_key_among_thousands(dtype, far):
+    """Random scores would hide a key that is skipped or read from the wrong page: here one
+    key far back carries nearly all the weight, so the output must be that key's value."""
+    nq, nkv, d, page = 8, 2, 64, 16
+    n_ctx = 2000
+    lens, new = [n_ctx, n_ctx - 40], [1, 40]          # a decode token and a portion, same context
+    torch.manual_seed(far)
+    table, cache = _paged_setup(lens, new, nkv, d, page, dtype, seed=far)
+    cache = cache * 0.05
+    q = torch.randn(sum(new), nq * d) * 0.05
+    # Request 0 / 1: the key at position `far` matches the queries strongly.
+    spike = torch.randn(nkv, d)
+    spike = spike / spike.norm(dim=-1, keepdim=True) * 6
+    for r in range(2):
+        cache[int(table[r, far // page]), :, 0, far % page] = spike.to(dtype)
+    q = q.reshape(-1, nq, d)
+    q += spike.repeat_interleave(nq // nkv, 0)[None] * 1.0
+    q = q.reshape(-1, nq * d).to(dtype)
+    scale = 1.0
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, 0, scale)
+    got = _run_attention(q, cache, table, lens, new, nq, nkv, d, page, 0, scale, split_keys=256)
+    # The far key's value dominates: check against it and against the full reference.
+    K, V = _dense_kv(cache, table, 0, n_ctx + 1, page)
+    dom = V[far].repeat_interleave(nq // nkv, 0).reshape(-1)
+    assert float((want[0] - dom).abs().max()) < 0.05
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    assert float((got - want).abs().max()) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_edge(dtype):
+    """Two keys carry the weight: the last one inside the window and the first one outside it."""
+    nq, nkv, d, page, window = 4, 2, 32, 8, 24
+    lens, new = [100, 60], [1, 41]
+    torch.manual_seed(1)
+    table, cache = _paged_setup(lens, new, nkv, d, page, dtype, seed=3)
+    cache = cache * 0.05
+    spike = torch.randn(nkv, d)
+    spike = spike / spike.norm(dim=-1, keepdim=True) * 6
+    q = (torch.randn(sum(new), nq, d) * 0.05 + spike.repeat_interleave(2, 0)[None]).reshape(-1, nq * d).to(dtype)
+    # For the decode token at position 100 the window holds keys 77..100: spike both 77 and 76.
+    for pos in (76, 77):
+        cache[int(table[0, pos // page]), :, 0, pos % page] = spike.to(dtype)
+        cache[int(table[0, pos // page]), :, 1, pos % page] = (1.0 if pos == 77 else -1.0)
+    # For the portion (positions 60..100) spike keys 50 and 51: query 73 sees 50 (73-24+1), query 74 does not.
+    for pos in (50, 51):
+        cache[int(table[1, pos // page]), :, 0, pos % page] = spike.to(dtype)
+        cache[int(table[1, pos // page]), :, 1, pos % page] = (1.0 if pos == 51 else -1.0)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, 1.0)
+    got = _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, 1.0, split_keys=32)
+    assert float(want[0].mean()) > 0.9              # only key 77 (value +1) is inside
+    assert abs(float(want[1 + 13].mean())) < 0.2    # query at 73: keys 50 (-1) and 51 (+1) both inside
+    assert float(want[1 + 14].mean()) > 0.9         # query at 74: only key 51
+    assert float((got - want).abs().max()) < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+# -- sampling -------------------------------------------------------------------------------
+def test_argmax_first_maximum_wins():
+    ops = _ops()
+    x = torch.randn(6, 1531, device=DEV)
+    x[2, 77] = x[2, 900] = 50.0
+    x[4, 1530] = 60.0
+    got = ops.argmax(x).cpu().tolist()
+    want = [int(np.argmax(r)) for r in x.cpu().numpy()]
+    assert got == want and got[2] == 77 and got[4] == 1530
+
+
+def test_philox_matches_the_plain_implementation():
+    ops = _ops()
+    for seed, rid, idx in [(0, 0, 0), (7, 3, 11), (2**40 + 5, 2**33 + 1, 4000), (2**63 + 9, 1, 2)]:
+        assert ops.philox_uniform(seed, rid, idx) == pytest.approx(P.uniform(seed, rid, idx), abs=0)
+
+
+def _sample(logits, rows):
+    from llm_rs_b200.sampling import Sampler
+    return Sampler(DEV).sample(logits.clone(), rows).cpu().tolist()
+
+
+def test_sampler_greedy_temperature_and_penalty():
+    from llm_rs_b200.sampling import SamplingParams
+    torch.manual_seed(0)
+    V = 1531
+    logits = torch.randn(5, V, device=DEV) * 2
+    host = logits.cpu().numpy()
+    hist = [int(np.argmax(host[1])), 3, 3]
+    rows = [(SamplingParams(temperature=0.0), 1, 0, []),
+            (SamplingParams(temperature=0.0, repetition_penalty=3.0), 2, 0, hist),
+            (SamplingParams(temperature=0.8, seed=5), 3, 0, []),
+            (SamplingParams(temperature=0.8, seed=5), 3, 1, []),
+            (SamplingParams(temperature=1.3, seed=6, repetition_penalty=1.5), 4, 2, [1, 2, 3])]
+    got = _sample(logits, rows)
+    for r, (p, rid, idx, h) in enumerate(rows):
+        want = P.sample(host[r], p.temperature, p.top_k, p.top_p, p.repetition_penalty, h, p.seed, rid, idx)
+        if p.temperature <= 1e-5:
+            assert got[r] == want
+        else:
+            _assert_draw(host[r], p, h, rid, idx, got[r])
+    assert got[1] != hist[0]                  # the penalised maximum lost
+    # A row's token does not depend on what else is in the batch.
+    assert _sample(logits[2:4], rows[2:4]) == got[2:4]
+    assert _sample(logits[3:4], rows[3:4]) == got[3:4]
+
+
+def _assert_draw(row, p, history, rid, idx, token):
+    """The token's slice of the cumulative distribution holds the Philox draw (up to float32 rounding)."""
+    probs = P.kept_probabilities(row, p.temperature, p.top_k, p.top_p, p.repetition_penalty, history)
+    assert probs[token] > 0, "a token that was cut off was drawn"
+    cum = np.cumsum(probs)
+    u = P.uniform(p.seed, rid, idx)
+    lo, hi = (cum[token - 1] if token else 0.0), cum[token]
+    assert lo - 1e-4 <= u <= hi + 1e-4, (lo, u, hi)
+
+
+@pytest.mark.parametrize("top_k,top_p", [(5, 1.0), (0, 0.6), (40, 0.9), (1, 1.0), (0, 0.05)])
+def test_sampler_top_k_top_p(top_k, top_p):
+    from llm_rs_b200.sampling import SamplingParams
+    torch.manual_seed(1)
+    V = 3001
+    logits = torch.randn(1, V, device=DEV) * 3
+    host = logits.cpu().numpy()[0]
+    p = SamplingParams(temperature=0.9, top_k=top_k, top_p=top_p, seed=11)
+    probs = P.kept_probabilities(host, 0.9, top_k, top_p)
+    seen = set()
+    for idx in range(200):
+        tok = _sample(logits, [(p, 9, idx, [])])[0]
+        _assert_draw(host, p, [], 9, idx, tok)
+        seen.add(tok)
+    kept = set(np.nonzero(probs)[0].tolist())
+    assert seen <= kept
+    if len(kept) <= 5:
+        assert seen == kept                    # every kept token shows up in 200 draws
+
+
+def test_sampler_follows_the_distribution():
+    from llm_rs_b200.sampling import SamplingParams
+    logits = torch.tensor([[0.0, 1.0, 2.0, -1.0] + [-30.0] * 200], device=DEV)
+    p = SamplingParams(temperature=1.0, seed=3)
+    n = 2000
+    rows = [(p, 1, i, []) for i in range(n)]
+    toks = _sample(logits.repeat(n, 1), rows)
+    want = torch.softmax(logits[0].double().cpu(), 0).numpy()
+    for t in range(4):
+        assert abs(toks.count(t) / n - want[t]) < 0.04
