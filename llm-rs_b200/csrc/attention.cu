@@ -400,9 +400,13 @@ static int launch_decode(const void* q, long long q_stride, void* out, long long
   const size_t smem = ((size_t)DC_HG * d + (size_t)DC_HG * split_keys + (size_t)n_sub * DC_HG * d) * sizeof(float);
   LLMRS_REQUIRE(smem <= 200 * 1024, "attn_decode: %zu bytes of shared memory needed (split of %d keys)", smem,
                 split_keys);
-  cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<T, VEC>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return llmrs_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  static size_t configured = 0;  // per instantiation; raised only when a launch needs more
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<T, VEC>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = smem;
+  }
   dim3 grid(n_dec, n_kv_heads * groups_per_kv, max_splits);
   attn_decode_split_kernel<T, VEC><<<grid, DC_THREADS, smem, stream>>>(
       (const T*)q, q_stride, (const T*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,

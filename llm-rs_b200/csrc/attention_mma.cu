@@ -74,10 +74,36 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     }
   }
 
+  // When a page holds whole 16-key tiles, a tile is one contiguous run of rows in one
+  // page: lane j keeps the page of the warp's j-th tile (of the current 32), so the
+  // copies need neither a table look-up nor a division on their way out.
+  const bool page_tiles = page_size % DM_TILE == 0;
+  int my_pages = 0, pages_base = -1;
   auto load_tile = [&](int i, int stage) {
     const int t = tile_first + warp + i * DM_WARPS;
     bf16* Ks = wbase + (size_t)stage * 2 * TILE_ELEMS;
     bf16* Vs = Ks + TILE_ELEMS;
+    if (page_tiles) {
+      if ((i >> 5) != pages_base) {
+        pages_base = i >> 5;
+        const int ti = tile_first + warp + ((pages_base << 5) + lane) * DM_WARPS;
+        my_pages = ti <= tile_last ? table[(ti * DM_TILE) / page_size] : 0;
+      }
+      const int page = __shfl_sync(0xffffffffu, my_pages, i & 31);
+      const bf16* kbase = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) +
+                          (size_t)((t * DM_TILE) % page_size) * D;
+      const bf16* vbase = kbase + (size_t)page_size * D;
+      const int key0 = t * DM_TILE;
+      const bool whole = key0 >= k_begin && key0 + DM_TILE <= k_end;
+#pragma unroll 4
+      for (int c = lane; c < DM_TILE * CH; c += 32) {
+        const int row = c / CH, ch = c - row * CH;
+        const bool valid = whole || (key0 + row >= k_begin && key0 + row < k_end);
+        cp_async_16(Ks + row * ROW + ch * 8, valid ? kbase + c * 8 : cache, valid ? 16 : 0);
+        cp_async_16(Vs + row * ROW + ch * 8, valid ? vbase + c * 8 : cache, valid ? 16 : 0);
+      }
+      return;
+    }
 #pragma unroll 4
     for (int c = lane; c < DM_TILE * CH; c += 32) {
       const int row = c / CH, ch = c - row * CH;

@@ -83,16 +83,102 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TA* __restrict__
   }
 }
 
+// The same, for rows whose length is a multiple of 4 and at most 4 * NORM_THREADS * CHUNKS:
+// every thread loads all of its values (16 bytes at a time) before anything is stored,
+// so the loads of a row are in flight together instead of one behind the other.
+template <typename TA> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+
+template <typename TA, int CHUNKS>
+__global__ void __launch_bounds__(NORM_THREADS)
+add_rmsnorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ delta, const float* __restrict__ weight,
+                       TA* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float red[33];
+  const int i = blockIdx.x;
+  const int src = rows ? rows[i] : i;
+  float* hr = h + (size_t)src * hidden;
+  const TA* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  float4 v[CHUNKS];
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int c = (k * NORM_THREADS + threadIdx.x) * 4;
+    v[k] = c < hidden ? Vec4<float>::load(hr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (dr) {
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+      const int c = (k * NORM_THREADS + threadIdx.x) * 4;
+      if (c < hidden) {
+        const float4 d = Vec4<TA>::load(dr + c);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+      }
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int c = (k * NORM_THREADS + threadIdx.x) * 4;
+    ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    if (!rows && dr && c < hidden) Vec4<float>::store(hr + c, v[k]);
+  }
+  const float total = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  TA* yr = y + (size_t)i * hidden;
+#pragma unroll
+  for (int k = 0; k < CHUNKS; ++k) {
+    const int c = (k * NORM_THREADS + threadIdx.x) * 4;
+    if (c < hidden) {
+      const float4 w = Vec4<float>::load(weight + c);
+      Vec4<TA>::store(yr + c, make_float4(v[k].x * inv * w.x, v[k].y * inv * w.y, v[k].z * inv * w.z,
+                                          v[k].w * inv * w.w));
+    }
+  }
+}
+
+template <typename TA>
+static void launch_add_rmsnorm(float* h, const TA* delta, const float* weight, TA* y, const int* rows, int n_rows,
+                               int hidden, float eps, cudaStream_t stream) {
+  const int per_chunk = 4 * NORM_THREADS;
+  if (hidden % 4 == 0 && hidden <= 8 * per_chunk) {
+    if (hidden <= per_chunk)
+      add_rmsnorm_vec_kernel<TA, 1><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+    else if (hidden <= 2 * per_chunk)
+      add_rmsnorm_vec_kernel<TA, 2><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+    else if (hidden <= 4 * per_chunk)
+      add_rmsnorm_vec_kernel<TA, 4><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+    else
+      add_rmsnorm_vec_kernel<TA, 8><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+  } else {
+    add_rmsnorm_kernel<TA><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+  }
+}
+
 LLMRS_API int llmrs_add_rmsnorm(float* h, const void* delta, const float* weight, void* y, const int* rows,
                                 int n_rows, int hidden, float eps, int act_dtype, cudaStream_t stream) {
   LLMRS_REQUIRE(n_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes");
   if (n_rows == 0) return 0;
   if (act_dtype == LLMRS_F32)
-    add_rmsnorm_kernel<float><<<n_rows, NORM_THREADS, 0, stream>>>(h, (const float*)delta, weight, (float*)y, rows,
-                                                                    hidden, eps);
+    launch_add_rmsnorm<float>(h, (const float*)delta, weight, (float*)y, rows, n_rows, hidden, eps, stream);
   else if (act_dtype == LLMRS_BF16)
-    add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, NORM_THREADS, 0, stream>>>(
-        h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)y, rows, hidden, eps);
+    launch_add_rmsnorm<__nv_bfloat16>(h, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)y, rows, n_rows,
+                                      hidden, eps, stream);
   else
     return llmrs_fail("add_rmsnorm: unknown activation dtype %d", act_dtype);
   return llmrs_launch_status("add_rmsnorm");
@@ -140,19 +226,57 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
   }
 }
 
+// Eight (bfloat16) or four (float32) columns per thread, 16 bytes per load, when the
+// width allows; no division per element.
+template <typename TA>
+__global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, int n_tokens) {
+  constexpr int PER = 16 / sizeof(TA);
+  const int chunks = inter / PER;
+  const size_t total = (size_t)n_tokens * chunks;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / chunks;
+    const int c = (int)(i - t * chunks) * PER;
+    const TA* gp = gu + t * 2 * inter + c;
+    float g[PER], u[PER];
+#pragma unroll
+    for (int k = 0; k < PER; k += 4) {
+      const float4 a = Vec4<TA>::load(gp + k), b = Vec4<TA>::load(gp + inter + k);
+      g[k] = a.x; g[k + 1] = a.y; g[k + 2] = a.z; g[k + 3] = a.w;
+      u[k] = b.x; u[k + 1] = b.y; u[k + 2] = b.z; u[k + 3] = b.w;
+    }
+#pragma unroll
+    for (int k = 0; k < PER; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+#pragma unroll
+    for (int k = 0; k < PER; k += 4)
+      Vec4<TA>::store(out + t * inter + c + k, make_float4(g[k], g[k + 1], g[k + 2], g[k + 3]));
+  }
+}
+
+template <typename TA>
+static void launch_silu_mul(const TA* gu, TA* out, int n_tokens, int inter, cudaStream_t stream) {
+  constexpr int PER = 16 / sizeof(TA);
+  const int threads = 256;
+  if (inter % PER == 0) {
+    const size_t total = (size_t)n_tokens * (inter / PER);
+    const size_t want = (total + threads - 1) / threads;
+    silu_mul_vec_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, n_tokens);
+  } else {
+    const size_t total = (size_t)n_tokens * inter;
+    const size_t want = (total + threads - 1) / threads;
+    silu_mul_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, total);
+  }
+}
+
 LLMRS_API int llmrs_silu_mul(const void* gu, void* out, int n_tokens, int inter, int act_dtype,
                              cudaStream_t stream) {
   LLMRS_REQUIRE(n_tokens >= 0 && inter > 0, "silu_mul: bad sizes");
-  const size_t total = (size_t)n_tokens * inter;
-  if (total == 0) return 0;
-  const int threads = 256;
-  const size_t want = (total + threads - 1) / threads;
-  const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+  if ((size_t)n_tokens * inter == 0) return 0;
   if (act_dtype == LLMRS_F32)
-    silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+    launch_silu_mul<float>((const float*)gu, (float*)out, n_tokens, inter, stream);
   else if (act_dtype == LLMRS_BF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
-                                                                    inter, total);
+    launch_silu_mul<__nv_bfloat16>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, stream);
   else
     return llmrs_fail("silu_mul: unknown activation dtype %d", act_dtype);
   return llmrs_launch_status("silu_mul");

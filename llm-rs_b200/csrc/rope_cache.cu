@@ -10,7 +10,7 @@
 // Norm and rotation run in float32 and the result is rounded once.
 #include "common.cuh"
 
-constexpr int ROPE_THREADS = 256;
+constexpr int ROPE_THREADS = 128;  // one warp per (token, head); grid.y covers the heads
 constexpr int ROPE_WARPS = ROPE_THREADS / 32;
 
 template <typename T>
@@ -35,7 +35,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
   const float* cs = cos_sin ? cos_sin + (size_t)pos * rotary_dim : nullptr;
   const int n_heads_total = n_q_heads + (k ? 2 * n_kv_heads : 0);
 
-  for (int hh = warp; hh < n_heads_total; hh += ROPE_WARPS) {
+  for (int hh = blockIdx.y * ROPE_WARPS + warp; hh < n_heads_total; hh += gridDim.y * ROPE_WARPS) {
     // Which tensor this head belongs to.
     int kind, head;
     if (hh < n_q_heads) { kind = 0; head = hh; }
@@ -94,13 +94,15 @@ LLMRS_API int llmrs_qk_norm_rope_kvwrite(void* q, long long q_stride, const void
   LLMRS_REQUIRE(d <= 1024, "qk_norm_rope_kvwrite: head_dim %d above 1024 is not supported", d);
   if (n_tokens == 0) return 0;
   const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
+  const int heads_total = n_q_heads + (k ? 2 * n_kv_heads : 0);
+  dim3 grid(n_tokens, (heads_total + ROPE_WARPS - 1) / ROPE_WARPS);
   if (dtype == LLMRS_F32)
-    qk_norm_rope_kvwrite_kernel<float><<<n_tokens, ROPE_THREADS, smem, stream>>>(
+    qk_norm_rope_kvwrite_kernel<float><<<grid, ROPE_THREADS, smem, stream>>>(
         (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, q_norm_w, k_norm_w, cos_sin,
         positions, token_req, block_table, table_stride, (float*)cache, n_q_heads, n_kv_heads, d, rotary_dim,
         page_size, eps);
   else if (dtype == LLMRS_BF16)
-    qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<n_tokens, ROPE_THREADS, smem, stream>>>(
+    qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, ROPE_THREADS, smem, stream>>>(
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm_w,
         k_norm_w, cos_sin, positions, token_req, block_table, table_stride, (__nv_bfloat16*)cache, n_q_heads,
         n_kv_heads, d, rotary_dim, page_size, eps);

@@ -13,6 +13,15 @@ from .registry import build, register
 from .spec import CacheNeed, PartSpec, WeightSpec
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[device]
+
+
 @register("mixer", "gqa_attention")
 class GQAttention(Mixer):
     """Attention with ``n_heads`` query heads sharing ``n_kv_heads`` key/value heads.
@@ -30,7 +39,7 @@ class GQAttention(Mixer):
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, qk_norm: bool = True, qk_norm_eps: float = 1e-6, bias: bool = False,
-                 window: int = 0, scale: Optional[float] = None, split_keys: int = 256, prefix: str = ""):
+                 window: int = 0, scale: Optional[float] = None, split_keys: int = 0, prefix: str = ""):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
         if head_dim % 16:
@@ -38,7 +47,7 @@ class GQAttention(Mixer):
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
         self.qk_norm, self.qk_norm_eps, self.bias, self.window = qk_norm, float(qk_norm_eps), bias, int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
-        self.split_keys = int(split_keys)
+        self.split_keys = int(split_keys)   # keys per split of decode attention; 0: chosen per step
         self.prefix = prefix
         self.position = build("position", position, prefix=prefix)
         self.q_width, self.kv_width = n_heads * head_dim, n_kv_heads * head_dim
@@ -83,6 +92,17 @@ class GQAttention(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.n_kv_heads, self.head_dim, self.window)
 
+    def _choose_split(self, n_decode: int, max_kv_len: int, q: torch.Tensor) -> int:
+        """Keys per split of decode attention: long enough that a block streams many tiles,
+        short enough that the step's blocks fill the GPU about once. The choice changes
+        results by rounding only (every split is merged in float32)."""
+        sms = _sm_count(q.device)
+        groups = self.n_kv_heads * (-(-(self.n_heads // self.n_kv_heads) // 16))
+        splits = max(1, (2 * sms) // max(1, n_decode * groups))
+        keys = -(-max(max_kv_len, 1) // splits)
+        keys = -(-keys // 64) * 64
+        return min(max(keys, 128), 1024 if q.dtype == torch.float32 or self.head_dim > 128 else 2048)
+
     # -- step ------------------------------------------------------------------------
     def forward(self, x, ctx, cache):
         nq, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
@@ -105,9 +125,10 @@ class GQAttention(Mixer):
             ops.attn_prefill(q, out, cache.kv, ctx.prefill_tiles, ctx.n_prefill_tiles, ctx.q_start, ctx.n_new,
                              ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale)
         if ctx.n_decode:
-            max_splits = max(1, -(-ctx.max_decode_kv_len // self.split_keys))
+            split_keys = self.split_keys or self._choose_split(ctx.n_decode, ctx.max_decode_kv_len, q)
+            max_splits = max(1, -(-ctx.max_decode_kv_len // split_keys))
             scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(ctx.n_decode, nq, d, max_splits))
             ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
-                            scratch, max_splits, self.split_keys, nq, nkv, d, cache.page_size, self.window,
+                            scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
                             self.scale)
         return self.o_proj.forward(out)

@@ -1,0 +1,367 @@
+"""The engine above the step function, and the generality of the parts: generation through
+the entry point, long decoding, the first tokens of a sequence, parts alone, a run order
+that names a layer twice and lets a layer read another's cache, tensors stored in 32-bit,
+and a toy mixer with state of its own that is defined here and plugged in."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+import replay_util as RU
+from tiny_configs import TINY, TINY_A, TINY_B, write_tiny_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    return str(tmp_path_factory.mktemp("models"))
+
+
+@pytest.fixture(scope="module")
+def models(folder):
+    out = {}
+    for name in TINY:
+        path = write_tiny_model(name, folder)
+        out[name] = (path, *P.load_model_dir(path))
+    return out
+
+
+# -- generation through the entry point ------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_through_the_engine(models, name, dtype, graphs):
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w = models[name]
+    rng = np.random.default_rng(7)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (3, 40, 17, 70)]
+    engine = Engine(EngineConfig(model_path=path, block_pool_size=64, page_size=TINY[name][3], dtype=dtype,
+                                 max_requests=4, max_tokens_per_step=48, prefill_chunk=32, cuda_graphs=graphs))
+    got = engine.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12, ignore_eos=True))
+    assert [len(g) for g in got] == [12] * 4
+    if dtype == "float32":
+        for p, g in zip(prompts, got):
+            assert P.greedy_gap(cfg, w, p, g) < 1e-4        # the plain implementation's own choice (or an exact tie)
+    else:
+        for p, g in zip(prompts, got):
+            assert P.greedy_gap(cfg, w, p, g) < 0.05
+    assert not engine.runner.manager.requests
+    engine.runner.manager.check_invariants()
+
+
+def test_reference_style_entry_points(models):
+    from llm_rs_b200.engine import (ChatRequest, EngineConfig, create_engine, destroy_engine, poll_token,
+                                    send_request)
+    path, cfg, w = models["A"]
+    engine = create_engine(EngineConfig(model_path=path, block_pool_size=32, dtype="float32"))
+    a = send_request(engine, ChatRequest(prompt=[5, 6, 7], temperature=0.0, max_tokens=5))
+    b = send_request(engine, ChatRequest(prompt=[9, 1], temperature=0.9, top_p=0.9, max_tokens=3, seed=4))
+    assert a != 0 and b != 0 and a != b
+    toks = []
+    while True:
+        r = poll_token(engine, a)
+        toks.append(r.token)
+        if r.is_eos:
+            break
+    eos = cfg["eos_token_id"]
+    assert len(toks) == 5 or toks[-1] == eos
+    want = P.greedy_generate(cfg, w, [5, 6, 7], len(toks))
+    assert toks == want
+    n = 0
+    while not poll_token(engine, b).is_eos:
+        n += 1
+    assert n <= 2
+    destroy_engine(engine)
+    assert not engine.runner.manager.requests
+
+
+def test_temperature_sampling_is_seeded_and_batch_independent(models):
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w = models["B"]
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (9, 40, 77)]
+    sp = [SamplingParams(temperature=0.7, seed=7, max_new_tokens=10, ignore_eos=True),
+          SamplingParams(temperature=1.0, top_k=20, top_p=0.9, repetition_penalty=1.2, seed=8, max_new_tokens=10,
+                         ignore_eos=True),
+          SamplingParams(temperature=0.0, max_new_tokens=10, ignore_eos=True)]
+
+    def run(order, budget):
+        e = Engine(EngineConfig(model_path=path, block_pool_size=128, page_size=8, dtype="float32", max_requests=4,
+                                max_tokens_per_step=budget, prefill_chunk=32))
+        ids = {}
+        for i in order:
+            # Request ids feed the draws: give each prompt the same id whatever the order.
+            e._ids = iter([i + 1])
+            ids[i] = e.add_request(prompts[i], sp[i])
+        while e.has_work():
+            e.step()
+        return [e.requests[ids[i]].output for i in range(3)]
+    a = run([0, 1, 2], 64)
+    b = run([2, 1, 0], 17)          # other order, other cuts: same tokens
+    assert a == b
+    # The first sampled token follows the plain sampler on the plain logits.
+    logits = P.forward(cfg, w, prompts[0])[-1].numpy()
+    probs = P.kept_probabilities(logits, 0.7)
+    u = P.uniform(7, 1, 0)
+    cum = np.cumsum(probs)
+    tok = a[0][0]
+    assert (cum[tok - 1] if tok else 0.0) - 1e-4 <= u <= cum[tok] + 1e-4
+
+
+def test_out_of_pages_preempts_and_still_finishes(models):
+    """A pool too small for all requests at once: the engine preempts, recomputes, and every
+    request gets exactly the tokens it would get alone."""
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w = models["A"]
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (30, 30, 30)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=24, ignore_eos=True)
+    e = Engine(EngineConfig(model_path=path, block_pool_size=8, page_size=16, dtype="float32", max_requests=4,
+                            max_tokens_per_step=64, prefill_chunk=32))     # 128 tokens of cache for 3 x 54
+    got = e.generate(prompts, sp)
+    assert e.scheduler.stats["preemptions"] >= 1
+    for p, g in zip(prompts, got):
+        assert len(g) == 24 and P.greedy_gap(cfg, w, p, g) < 1e-4
+    assert e.runner.manager.free_pages(0) == 8
+
+
+# -- long decoding, first tokens ---------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_long_decoding(models, dtype):
+    """600 tokens decoded one by one after a short prompt (many pages, many splits), against the whole sequence."""
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    path, cfg, w = models["B"]
+    toks = np.random.default_rng(5).integers(0, cfg["vocab_size"], 640).tolist()
+    ref = P.forward(cfg, w, toks).numpy()
+    runner = ModelRunner.from_model_dir(path, dtype=dtype, max_tokens=704, page_size=8, max_requests=2)
+    runner.use_graphs = True
+    runner.step([StepEntry("r", toks[:40], [])])
+    worst = 0.0
+    for i in range(40, 640):
+        row = runner.step([StepEntry("r", [toks[i]], [0])]).float().cpu().numpy()[0]
+        worst = max(worst, float(np.abs(row - ref[i]).max()))
+    tol = 1e-4 if dtype == torch.float32 else 0.02 * float(np.abs(ref).max())
+    assert worst <= tol, worst
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("name", list(TINY))
+def test_first_tokens(models, name, dtype):
+    """Sequences of 1, 2 and 3 tokens, fed whole and token by token from position 0."""
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    path, cfg, w = models[name]
+    runner = ModelRunner.from_model_dir(path, dtype=dtype, max_tokens=256, page_size=TINY[name][3], max_requests=4)
+    tol = 1e-4 if dtype == torch.float32 else 0.03
+    for n in (1, 2, 3):
+        toks = np.random.default_rng(n).integers(0, cfg["vocab_size"], n).tolist()
+        ref = P.forward(cfg, w, toks).numpy()
+        whole = runner.step([StepEntry(f"w{n}", toks, list(range(n)))]).float().cpu().numpy()
+        assert np.abs(whole - ref).max() <= tol
+        for i, t in enumerate(toks):
+            row = runner.step([StepEntry(f"s{n}", [t], [0])]).float().cpu().numpy()[0]
+            assert np.abs(row - ref[i]).max() <= tol
+        runner.release(f"w{n}")
+        runner.release(f"s{n}")
+
+
+# -- weights stored in 32-bit --------------------------------------------------------------------
+def test_tensors_stored_in_32_bit_stay_32_bit(folder):
+    """A folder whose matrices are float32: the bfloat16 engine keeps them (its products then
+    run in true float32), so it lands closer to the plain implementation than bfloat16 weights could."""
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.weights import write_random_model
+    path = write_random_model(folder + "/f32", Qwen3Config.from_dict(TINY_B), seed=3, sigma=0.03, norm_jitter=0.1,
+                              dtype=torch.float32)
+    cfg, w = P.load_model_dir(path)
+    toks = np.random.default_rng(0).integers(0, cfg["vocab_size"], 50).tolist()
+    ref = P.forward(cfg, w, toks).numpy()
+    runner = ModelRunner.from_model_dir(path, dtype=torch.bfloat16, max_tokens=128, page_size=8)
+    assert runner.model.blocks[0].feed_forward.down.weight.dtype == torch.float32
+    got = runner.step([StepEntry("a", toks, list(range(50)))]).float().cpu().numpy()
+    assert np.abs(got - ref).max() < 0.02 * np.abs(ref).max()
+    r32 = ModelRunner.from_model_dir(path, dtype=torch.float32, max_tokens=128, page_size=8)
+    got32 = r32.step([StepEntry("a", toks, list(range(50)))]).float().cpu().numpy()
+    assert np.abs(got32 - ref).max() < 1e-4
+
+
+# -- parts alone -----------------------------------------------------------------------------------
+def _runtime(dtype, max_positions=128):
+    from llm_rs_b200.parts import Runtime
+    return Runtime(torch.device(DEV), dtype, max_positions)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_part_rmsnorm_and_swiglu_alone(dtype):
+    from llm_rs_b200.parts import PartSpec, build
+    torch.manual_seed(0)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    norm = build("norm", PartSpec("rmsnorm", {"dim": 72, "eps": 2e-6, "name": "n.weight"}), prefix="x.")
+    assert [s.name for s in norm.weight_specs()] == ["x.n.weight"]
+    wn = 1 + 0.1 * torch.randn(72)
+    norm.bind({"x.n.weight": wn.to(DEV)}, _runtime(dtype))
+    h = torch.randn(5, 72, device=DEV)
+    y = norm.forward(h.clone(), None)
+    assert torch.allclose(y.double().cpu(), P.rms_norm(h.double().cpu(), wn.double(), 2e-6), **tol)
+
+    ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200}), prefix="m.")
+    ws = {s.name: (torch.randn(s.shape) * 0.1).to(dtype).to(DEV) for s in ffn.weight_specs()}
+    ffn.bind(ws, _runtime(dtype))
+    x = torch.randn(5, 72).to(dtype)
+    want = P.swiglu(x.double(), {k: v.double().cpu() for k, v in ws.items()}, "m.")
+    assert torch.allclose(ffn.forward(x.to(DEV), None).double().cpu(), want, **tol)
+
+
+def test_part_rotary_table():
+    from llm_rs_b200.parts import PartSpec, build
+    rope = build("position", PartSpec("rope_half", {"head_dim": 32, "theta": 5e5, "rotary_dim": 16}))
+    rope.bind({}, _runtime(torch.float32, 300))
+    table = rope.rotation_table().cpu().double()
+    ang = P.rope_angles(range(300), 16, 5e5, torch.float64)
+    assert table.shape == (300, 8, 2)
+    assert torch.allclose(table[..., 0], ang.cos(), atol=1e-7) and torch.allclose(table[..., 1], ang.sin(), atol=1e-7)
+    assert build("position", PartSpec("none", {"head_dim": 32})).rotation_table() is None
+
+
+# -- run order: a layer named twice, a layer that reads another's cache ----------------------------
+def _plain_with_run_order(cfg, w, toks, order):
+    """The plain forward with an explicit run order [(layer, cache_of)]: an entry that reads
+    another entry's cache attends with ITS queries over THAT entry's keys and values."""
+    h = P.embedding(w["model.embed_tokens.weight"], toks)
+    pos = list(range(len(toks)))
+    eps = cfg["rms_norm_eps"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    kv = {}
+    for s, (layer, cache_of) in enumerate(order):
+        p = f"model.layers.{layer}."
+        x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+        T = x.shape[0]
+        ang = P.rope_angles(pos, d, cfg["rope_theta"], x.dtype)
+        q = P.rotate_half(P.rms_norm(P.linear(x, w[p + "self_attn.q_proj.weight"]).reshape(T, nq, d),
+                                     w[p + "self_attn.q_norm.weight"], eps), ang)
+        if cache_of is None:
+            k = P.rotate_half(P.rms_norm(P.linear(x, w[p + "self_attn.k_proj.weight"]).reshape(T, nkv, d),
+                                         w[p + "self_attn.k_norm.weight"], eps), ang)
+            v = P.linear(x, w[p + "self_attn.v_proj.weight"]).reshape(T, nkv, d)
+            kv[s] = (k, v)
+        else:
+            k, v = kv[cache_of]
+        h = h + P.linear(P.attention(q, k, v), w[p + "self_attn.o_proj.weight"])
+        h = h + P.swiglu(P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    h = P.rms_norm(h, w["model.norm.weight"], eps)
+    return P.linear(h, w["lm_head.weight"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_run_order_with_repeated_layer_and_shared_cache(models, dtype):
+    import dataclasses
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel, RunStep
+    from llm_rs_b200.weights import load_weights
+    path, cfg, w = models["B"]
+    spec = build_spec(Qwen3Config.from_dict(cfg))
+    # layer 0, layer 1, layer 1 again (own cache), layer 2 reading entry 1's cache, layer 0 again
+    order = [(0, None), (1, None), (1, None), (2, 1), (0, None)]
+    spec = dataclasses.replace(spec, run_order=tuple(RunStep(l, c) for l, c in order))
+    tensors = load_weights(path, DecoderModel(spec).weight_specs(), dtype, torch.device(DEV))
+    runner = ModelRunner(spec, tensors, dtype, DEV, max_tokens=256, page_size=8, max_requests=2)
+    assert len(runner.storage.groups) == 1 and len(runner.storage.groups[0].entries) == 4   # four caches for five entries
+    toks = np.random.default_rng(2).integers(0, cfg["vocab_size"], 70).tolist()
+    ref = _plain_with_run_order(cfg, w, toks, order).numpy()
+    steps = RU.portions({"a": toks}, sizes=(9, 2, 30, 1, 1, 1, 5, 64))
+    got = RU.run_steps(runner, steps)
+    worst, where, n = RU.max_diff(got, {"a": ref})
+    assert n == 70
+    assert worst <= (1e-4 if dtype == torch.float32 else 0.02 * float(np.abs(ref).max())), (worst, where)
+
+
+# -- a toy mixer with state of its own, defined here ------------------------------------------------
+def test_toy_mixer_with_state_plugs_in(models):
+    """A mixer that keeps a running mean of its inputs per request (fixed-size state, no pages)
+    is registered from this file, built into a model beside attention layers, and stepped in
+    portions and mixed batches; the framework's files are not touched."""
+    import dataclasses
+    from llm_rs_b200 import ops
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import (DecoderModel, Mixer, PartSpec, StateNeed, WeightSpec, register, unregister)
+    from llm_rs_b200.weights import load_weights
+
+    @register("mixer", "toy_running_mean", replace=True)
+    class RunningMean(Mixer):
+        """out_t = W * mean(x_0..x_t) per request; state = (sum of inputs, count)."""
+        graph_safe = False          # plans on the host every step
+
+        def __init__(self, hidden_size, prefix=""):
+            self.hidden_size, self.prefix = hidden_size, prefix
+
+        def weight_specs(self):
+            return [WeightSpec(self.prefix + "mix.weight", (self.hidden_size, self.hidden_size))]
+
+        def state_need(self):
+            return StateNeed({"sum": (self.hidden_size,), "count": (1,)})
+
+        def bind(self, tensors, runtime):
+            self.w = tensors[self.prefix + "mix.weight"].float()
+            self.dtype = runtime.act_dtype
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            for r in range(ctx.n_requests):
+                a, n, slot = ctx.host_q_start[r], ctx.host_n_new[r], ctx.host_slot_ids[r]
+                xs = x[a:a + n].float()
+                run = cache.state["sum"][slot] + torch.cumsum(xs, 0)
+                cnt = cache.state["count"][slot] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)[:, None]
+                out[a:a + n] = ((run / cnt) @ self.w.t()).to(x.dtype)
+                cache.state["sum"][slot] = run[-1]
+                cache.state["count"][slot] = cnt[-1]
+            return out
+
+    try:
+        path, cfg, w = models["A"]
+        spec = build_spec(Qwen3Config.from_dict(cfg))
+        toy = dataclasses.replace(spec.layers[1], mixer=PartSpec("toy_running_mean", {"hidden_size": 64}),
+                                  mixer_scope="toy.")
+        spec = dataclasses.replace(spec, layers=(spec.layers[0], toy))
+        model = DecoderModel(spec)
+        names = [s.name for s in model.weight_specs()]
+        assert "model.layers.1.toy.mix.weight" in names and "model.layers.1.self_attn.q_proj.weight" not in names
+        # The folder has no toy weight: take the real tensors by name and add one.
+        from llm_rs_b200.weights import open_model_files
+        f = open_model_files(path)[0]
+        tensors = {n: f.tensor(n).float().to(DEV) for n in names if n in f.names()}
+        torch.manual_seed(0)
+        mixw = torch.randn(64, 64) * 0.05
+        tensors["model.layers.1.toy.mix.weight"] = mixw.to(DEV)
+        runner = ModelRunner(spec, tensors, torch.float32, DEV, max_tokens=256, page_size=16, max_requests=3)
+        assert runner.storage.state[1]["sum"].shape == (3, 64) and not runner.storage.state[0]
+        assert len(runner.storage.groups[0].entries) == 1           # only the attention layer has pages
+
+        def plain(toks):
+            h = P.embedding(w["model.embed_tokens.weight"], toks)
+            h = P.decoder_layer(h, w, 0, cfg, list(range(len(toks))), 0)
+            x = P.rms_norm(h, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+            mean = torch.cumsum(x, 0) / torch.arange(1, len(toks) + 1, dtype=torch.float64)[:, None]
+            h = h + mean @ mixw.double().t()
+            h = h + P.swiglu(P.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"]),
+                             w, "model.layers.1.mlp.")
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
+
+        rng = np.random.default_rng(4)
+        reqs = {f"r{i}": rng.integers(0, 256, n).tolist() for i, n in enumerate((50, 23, 64, 9))}
+        ref = {r: plain(t).numpy() for r, t in reqs.items()}
+        got = RU.run_steps(runner, RU.mixed(reqs, seed=1, max_live=3))
+        worst, where, n = RU.max_diff(got, ref)
+        assert n == sum(len(t) for t in reqs.values()) and worst < 1e-4, (worst, where)
+    finally:
+        unregister("mixer", "toy_running_mean")
