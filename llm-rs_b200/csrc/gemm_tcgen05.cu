@@ -1,0 +1,456 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a: operands staged
+// in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), tcgen05.mma issued by
+// one thread with the float32 accumulator in tensor memory, read back with tcgen05.ld.
+//
+//   D[a, b] = sum_k A[a, k] * B[b, k]      A: [a_rows, K], B: [b_rows, K], both K-major
+//
+// Two ways of mapping a linear layer y = x W^T onto it:
+//   mode 0 (many tokens)  A = x (tokens), B = W (features): tile 128 tokens x BN features.
+//   mode 1 (few tokens)   A = W (features), B = x (tokens): the 128 rows of the MMA are
+//                         filled by weights whatever the batch is, the tokens (16..64) are
+//                         the narrow N side. The k range is cut over the blocks of a
+//                         thread-block cluster, which add up their partial tiles through
+//                         distributed shared memory in a fixed order, so that a skinny
+//                         product still puts some hundred blocks on the GPU.
+// Epilogues: store (bfloat16 or float32), add into the float32 residual stream, or
+// SiLU(gate)*up for a weight whose rows alternate 64 gate rows and 64 up rows.
+//
+// Every block loads its own tiles (no multicast). Every wait on an mbarrier is bounded:
+// when a wait runs out the kernel records a code in *error_flag, waits (bounded) for its
+// copies in flight, frees its tensor memory and returns.
+//
+// The reference's products are library calls (llm-core/src/backends/candle.rs:1276-1340).
+#include <cuda.h>
+#include <mutex>
+
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int TC_BM = 128;        // rows of A per tile = M of the MMA
+constexpr int TC_BK = 64;         // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_THREADS = 128;
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;  // polls of a barrier before giving up (some seconds)
+
+enum TcEpilogue : int { TC_STORE = 0, TC_RESIDUAL = 1, TC_SILU_MUL = 2 };
+
+struct TcParams {
+  void* out;            // TC_STORE / TC_SILU_MUL: [tokens, ldo] of out_dtype; TC_RESIDUAL: float32 h
+  long long ldo;
+  int out_dtype;        // LLMRS_F32 or LLMRS_BF16 (TC_STORE, TC_SILU_MUL)
+  int epilogue;
+  int a_rows, b_rows;   // valid extents (tokens / features according to the mode)
+  int k_blocks;         // ceil(K / 64)
+  int* error_flag;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. False: gave up (or another thread of the block already had).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 128) {
+      __nanosleep(64);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);   // start address
+  d |= (uint64_t)1 << 16;                   // leading byte offset (unused with this swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset
+  d |= (uint64_t)1 << 46;                   // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: bf16 x bf16 -> f32, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t tc_instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// The barrier gets one arrival when every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// ---- the kernel ----------------------------------------------------------------------------
+// MODE 0: rows of the tile are tokens (A = x), columns features (B = W); one block per tile.
+// MODE 1: rows are features (A = W), columns tokens (B = x); gridDim.z = cluster size = k splits.
+template <int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const TcParams p) {
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  // Tiles need 1024-byte alignment for the 128-byte swizzle pattern.
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)STAGES * STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y;
+  const int splits = MODE == 1 ? (int)gridDim.z : 1;
+  const int split = MODE == 1 ? (int)blockIdx.z : 0;
+  const int kb0 = (int)(((long long)split * p.k_blocks) / splits);
+  const int kb1 = (int)(((long long)(split + 1) * p.k_blocks) / splits);
+  const int nkb = kb1 - kb0;
+
+  const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accum_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // Producer: one thread feeds the ring of stages by TMA.
+    int issued = 0;
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, abort_flag)) break;
+      mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+      const uint32_t a_dst = tc_smem(tiles + (size_t)s * STAGE_BYTES);
+      tma_load_2d(a_dst, &map_a, full0 + 8 * s, (kb0 + i) * TC_BK, tile_a * TC_BM);
+      tma_load_2d(a_dst + A_BYTES, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, tile_b * BN);
+      issued = i + 1;
+    }
+    if (*abort_flag) {
+      // Do not leave while copies may still land in this block's shared memory.
+      for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, abort_flag);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // MMA issuer: one thread, four k16 steps per stage.
+    constexpr uint32_t idesc = tc_instr_desc(BN);
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t a_addr = tc_smem(tiles + (size_t)s * STAGE_BYTES);
+      const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + A_BYTES);
+#pragma unroll
+      for (int k = 0; k < TC_BK / 16; ++k)
+        tc_mma(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs are done
+    }
+    tc_commit(accum_bar);
+  }
+  __syncwarp();
+  bool ok = true;
+  if (nkb > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
+  tc_fence_after();
+  __syncwarp();
+  if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+
+  const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int row = warp * 32 + lane;  // row of the tile this thread reads from tensor memory
+
+  if (MODE == 0) {
+    // Rows are tokens: each thread owns one token's BN features.
+    const int t = tile_a * TC_BM + row;
+    const bool t_ok = t < p.a_rows && ok;
+    if (p.epilogue == TC_SILU_MUL) {
+      // Columns come in groups of 128: 64 gate columns, then the 64 up columns of the same features.
+#pragma unroll 1
+      for (int g = 0; g < BN / 128; ++g) {
+#pragma unroll 1
+        for (int c = 0; c < 64; c += 8) {
+          float gv[8], uv[8];
+          tc_ld8(taddr + g * 128 + c, gv);
+          tc_ld8(taddr + g * 128 + 64 + c, uv);
+          const int f = (tile_b * BN + g * 128) / 2 + c;
+          if (t_ok && f < p.b_rows / 2) {
+            bf16* o = (bf16*)p.out + (size_t)t * p.ldo + f;
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              h2[e] = __floats2bfloat162_rn(silu_f(gv[2 * e]) * uv[2 * e], silu_f(gv[2 * e + 1]) * uv[2 * e + 1]);
+            *reinterpret_cast<uint4*>(o) = pk;
+          }
+          __syncwarp();
+        }
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 8) {
+        float v[8];
+        tc_ld8(taddr + c, v);
+        const int f = tile_b * BN + c;
+        if (!t_ok || f >= p.b_rows) {
+          // nothing to store for this thread; stay with the warp for the next tcgen05.ld
+        } else if (p.epilogue == TC_RESIDUAL) {
+          float4* hp = reinterpret_cast<float4*>((float*)p.out + (size_t)t * p.ldo + f);
+          float4 x0 = hp[0], x1 = hp[1];
+          x0.x += v[0]; x0.y += v[1]; x0.z += v[2]; x0.w += v[3];
+          x1.x += v[4]; x1.y += v[5]; x1.z += v[6]; x1.w += v[7];
+          hp[0] = x0; hp[1] = x1;
+        } else if (p.out_dtype == LLMRS_F32) {
+          float4* op = reinterpret_cast<float4*>((float*)p.out + (size_t)t * p.ldo + f);
+          op[0] = make_float4(v[0], v[1], v[2], v[3]);
+          op[1] = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+          uint4 pk;
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)t * p.ldo + f) = pk;
+        }
+        __syncwarp();
+      }
+    }
+    tc_fence_before();
+    __syncthreads();
+  } else {
+    // Rows are features, columns tokens. Partial tile -> shared memory -> sum over the
+    // cluster's blocks in rank order -> epilogue for the rows this block owns.
+    __syncthreads();  // the stages are free: every MMA has finished (accumulator barrier)
+    float* red = reinterpret_cast<float*>(tiles);  // [128][BN + 1]
+    constexpr int RS = BN + 1;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 8) {
+      float v[8];
+      if (nkb > 0 && ok) {
+        tc_ld8(taddr + c, v);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) red[row * RS + c + e] = v[e];
+    }
+    tc_fence_before();
+    if (splits > 1) cluster_sync_all(); else __syncthreads();
+
+    const uint32_t rank = splits > 1 ? cluster_rank() : 0u;
+    const int per = 64 / splits;                 // feature pairs (i, i + 64) owned by this block
+    const uint32_t red_addr = tc_smem(red);
+    const int n_tok = min(BN, p.b_rows - tile_b * BN);
+    for (int idx = tid; idx < per * n_tok; idx += TC_THREADS) {
+      const int pr = idx % per, j = idx / per;
+      const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
+      float lo = 0.f, hi = 0.f;
+      if (splits > 1) {
+        for (int r = 0; r < splits; ++r) {
+          lo += ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r);
+          hi += ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r);
+        }
+      } else {
+        lo = red[i_lo * RS + j];
+        hi = red[i_hi * RS + j];
+      }
+      const int t = tile_b * BN + j;
+      const int f_lo = tile_a * TC_BM + i_lo, f_hi = f_lo + 64;
+      if (p.epilogue == TC_SILU_MUL) {
+        const int f = tile_a * (TC_BM / 2) + i_lo;
+        if (f < p.a_rows / 2) ((bf16*)p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_f(lo) * hi);
+      } else if (p.epilogue == TC_RESIDUAL) {
+        float* h = (float*)p.out + (size_t)t * p.ldo;
+        if (f_lo < p.a_rows) h[f_lo] += lo;
+        if (f_hi < p.a_rows) h[f_hi] += hi;
+      } else if (p.out_dtype == LLMRS_F32) {
+        float* o = (float*)p.out + (size_t)t * p.ldo;
+        if (f_lo < p.a_rows) o[f_lo] = lo;
+        if (f_hi < p.a_rows) o[f_hi] = hi;
+      } else {
+        bf16* o = (bf16*)p.out + (size_t)t * p.ldo;
+        if (f_lo < p.a_rows) o[f_lo] = __float2bfloat16_rn(lo);
+        if (f_hi < p.a_rows) o[f_hi] = __float2bfloat16_rn(hi);
+      }
+    }
+    // No block may leave while another still reads its shared memory.
+    if (splits > 1) cluster_sync_all(); else __syncthreads();
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+// Tensor map of a K-major bfloat16 matrix [rows, K] with row stride ld (elements); box = 64 x box_rows.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return llmrs_fail("gemm_bf16: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return llmrs_fail("gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+template <int BN, int STAGES, int MODE>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, dim3 grid, int cluster_z,
+                     cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + (2 * STAGES + 1) * 8 + 16;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, MODE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("gemm_bf16: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = cluster_z;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, MODE>, ma, mb, p);
+  if (e != cudaSuccess) return llmrs_fail("gemm_bf16 launch: %s", cudaGetErrorString(e));
+  return llmrs_launch_status("gemm_bf16");
+}
+
+// y = x W^T for bfloat16 x [tokens, K] (row stride ldx) and W [features, K] (dense).
+//   epilogue TC_STORE:    out[tokens, features] (out_dtype), row stride ldo
+//   epilogue TC_RESIDUAL: out is the float32 residual stream, out[t, f] += y[t, f]
+//   epilogue TC_SILU_MUL: W alternates 64 gate rows and 64 up rows; out[tokens, features/2] bfloat16
+// splits: blocks of a cluster that share the k range (1, 2, 4 or 8; only when tokens <= 64).
+LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
+                              int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
+                              cudaStream_t stream) {
+  LLMRS_REQUIRE(tokens > 0 && features > 0 && K > 0, "gemm_bf16: bad sizes");
+  LLMRS_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_bf16: K = %d and the row stride %lld must be multiples of 8", K, ldx);
+  LLMRS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
+  LLMRS_REQUIRE(features % 8 == 0 && ldo % 8 == 0, "gemm_bf16: features %d and the output row stride %lld must be "
+                "multiples of 8", features, ldo);
+  LLMRS_REQUIRE(epilogue != TC_SILU_MUL || features % 128 == 0,
+                "gemm_bf16: SiLU*up needs features in groups of 128, got %d", features);
+  LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
+  TcParams p;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
+  CUtensorMap ma, mb;
+  int rc;
+  if (tokens <= 64) {
+    LLMRS_REQUIRE(splits == 1 || splits == 2 || splits == 4 || splits == 8, "gemm_bf16: splits must be 1, 2, 4 or 8");
+    const int bn = tokens <= 16 ? 16 : tokens <= 32 ? 32 : 64;
+    if ((rc = make_map(&ma, w, features, K, K, TC_BM))) return rc;
+    if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
+    p.a_rows = features; p.b_rows = tokens;
+    dim3 grid((features + TC_BM - 1) / TC_BM, 1, splits);
+    if (bn == 16) return launch_tc<16, 6, 1>(ma, mb, p, grid, splits, stream);
+    if (bn == 32) return launch_tc<32, 6, 1>(ma, mb, p, grid, splits, stream);
+    return launch_tc<64, 6, 1>(ma, mb, p, grid, splits, stream);
+  }
+  const bool wide = features >= 256 || epilogue == TC_SILU_MUL;
+  const int bn = wide ? 256 : 128;
+  LLMRS_REQUIRE(epilogue != TC_SILU_MUL || features % 256 == 0,
+                "gemm_bf16: SiLU*up over many tokens needs features in groups of 256, got %d", features);
+  if ((rc = make_map(&ma, x, tokens, K, ldx, TC_BM))) return rc;
+  if ((rc = make_map(&mb, w, features, K, K, bn))) return rc;
+  p.a_rows = tokens; p.b_rows = features;
+  dim3 grid((tokens + TC_BM - 1) / TC_BM, (features + bn - 1) / bn, 1);
+  if (bn == 256) return launch_tc<256, 4, 0>(ma, mb, p, grid, 1, stream);
+  return launch_tc<128, 6, 0>(ma, mb, p, grid, 1, stream);
+}

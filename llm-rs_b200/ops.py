@@ -290,3 +290,78 @@ def attention_generic_only(on: bool) -> None:
     fn = _lib().llmrs_attention_generic_only
     fn.restype = None
     fn(1 if on else 0)
+
+
+# -- bfloat16 products on tcgen05 ------------------------------------------------------------
+EPILOGUE = {"store": 0, "residual": 1, "silu_mul": 2}
+_tc_flags = {}
+
+
+def tc_error_flag(device) -> torch.Tensor:
+    """The int32 word the tcgen05 kernels write when one of their bounded waits ran out."""
+    dev = torch.device(device)
+    if dev not in _tc_flags:
+        _tc_flags[dev] = torch.zeros((1,), dtype=torch.int32, device=dev)
+    return _tc_flags[dev]
+
+
+def check_tc_error(device) -> None:
+    """Raise if a tcgen05 kernel gave up on a wait since the last check (synchronises)."""
+    flag = tc_error_flag(device)
+    code = int(flag.item())
+    if code:
+        flag.zero_()
+        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); its output is invalid")
+
+
+def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
+    """Blocks of a cluster that share the k range of a skinny product: enough blocks to
+    fill the GPU about twice, at least four 64-wide k blocks each."""
+    if tokens > 64:
+        return 1
+    tiles = -(-features // 128)
+    k_blocks = -(-K // 64)
+    for s in (8, 4, 2):
+        if tiles * s <= 2.2 * sms and k_blocks // s >= 4:
+            return s
+    return 1
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, epilogue: str = "store",
+              out_dtype: torch.dtype = torch.bfloat16, splits: Optional[int] = None) -> torch.Tensor:
+    """``x @ w.T`` for bfloat16 ``x`` [tokens, K] and ``w`` [features, K] on tcgen05 (see csrc/gemm_tcgen05.cu).
+
+    epilogue "store": returns [tokens, features] in ``out_dtype``. "residual": ``out`` is the
+    float32 residual stream and gets the product added. "silu_mul": ``w`` alternates 64
+    gate rows and 64 up rows; returns silu(gate) * up, [tokens, features / 2] bfloat16.
+    """
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    tokens, K = x.shape
+    features = w.size(0)
+    if w.size(1) != K:
+        raise KernelError(f"x has {K} columns, w has {w.size(1)}")
+    epi = EPILOGUE[epilogue]
+    if epilogue == "residual":
+        _need(out, "out", torch.float32)
+        if out.shape != (tokens, features):
+            raise KernelError(f"residual stream is {tuple(out.shape)}, product is {(tokens, features)}")
+        odt = torch.float32
+    else:
+        width = features // 2 if epilogue == "silu_mul" else features
+        odt = torch.bfloat16 if epilogue == "silu_mul" else out_dtype
+        if out is None:
+            out = torch.empty((tokens, width), dtype=odt, device=x.device)
+        _need(out, "out", odt)
+    if splits is None:
+        splits = tc_splits(tokens, features, K, torch.cuda.get_device_properties(x.device).multi_processor_count)
+    _check(_lib().llmrs_gemm_bf16(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
+                                  ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
+                                  splits, _ptr(tc_error_flag(x.device)), _stream()), "gemm_bf16")
+    return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2I, K]: 64 rows of gate, the 64 matching rows of up, and so on (I a multiple of 64)."""
+    I, K = gate.shape
+    return torch.stack([gate.reshape(I // 64, 64, K), up.reshape(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
