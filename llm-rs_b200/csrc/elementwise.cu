@@ -209,18 +209,22 @@ LLMRS_API int llmrs_residual_add(float* h, const void* delta, long long n, int a
 }
 
 // ---------------------------------------------------------------------------------
-// out[t, c] = silu(gu[t, c]) * gu[t, inter + c]; silu(x) = x * 1/(1+exp(-x)) in float32.
+// out[t, c] = silu(gate(t, c)) * up(t, c); silu(x) = x * 1/(1+exp(-x)) in float32.
 // (llm-core/src/backends/candle.rs:1645-1663: SiLU as x*sigmoid(x), then Mul.)
+// gu holds gate and up in alternating runs of `block` columns: column c of the output has
+// its gate at (c / block) * 2 * block + c % block and its up `block` columns further.
+// block = inter is the plain layout [gate | up].
 // ---------------------------------------------------------------------------------
 template <typename TA>
-__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, size_t total) {
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, int block, size_t total) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
     const size_t t = i / inter;
     const int c = (int)(i - t * inter);
-    const float g = to_float(gu[t * 2 * inter + c]);
-    const float u = to_float(gu[t * 2 * inter + inter + c]);
+    const size_t gcol = (size_t)(c / block) * 2 * block + c % block;
+    const float g = to_float(gu[t * 2 * inter + gcol]);
+    const float u = to_float(gu[t * 2 * inter + gcol + block]);
     const float s = g / (1.0f + expf(-g));
     out[i] = from_float<TA>(s * u);
   }
@@ -229,7 +233,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
 // Eight (bfloat16) or four (float32) columns per thread, 16 bytes per load, when the
 // width allows; no division per element.
 template <typename TA>
-__global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, int n_tokens) {
+__global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, int block,
+                                    int n_tokens) {
   constexpr int PER = 16 / sizeof(TA);
   const int chunks = inter / PER;
   const size_t total = (size_t)n_tokens * chunks;
@@ -238,11 +243,11 @@ __global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ 
   for (; i < total; i += stride) {
     const size_t t = i / chunks;
     const int c = (int)(i - t * chunks) * PER;
-    const TA* gp = gu + t * 2 * inter + c;
+    const TA* gp = gu + t * 2 * inter + (size_t)(c / block) * 2 * block + c % block;
     float g[PER], u[PER];
 #pragma unroll
     for (int k = 0; k < PER; k += 4) {
-      const float4 a = Vec4<TA>::load(gp + k), b = Vec4<TA>::load(gp + inter + k);
+      const float4 a = Vec4<TA>::load(gp + k), b = Vec4<TA>::load(gp + block + k);
       g[k] = a.x; g[k + 1] = a.y; g[k + 2] = a.z; g[k + 3] = a.w;
       u[k] = b.x; u[k + 1] = b.y; u[k + 2] = b.z; u[k + 3] = b.w;
     }
@@ -255,28 +260,30 @@ __global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ 
 }
 
 template <typename TA>
-static void launch_silu_mul(const TA* gu, TA* out, int n_tokens, int inter, cudaStream_t stream) {
+static void launch_silu_mul(const TA* gu, TA* out, int n_tokens, int inter, int block, cudaStream_t stream) {
   constexpr int PER = 16 / sizeof(TA);
   const int threads = 256;
-  if (inter % PER == 0) {
+  if (inter % PER == 0 && block % PER == 0) {
     const size_t total = (size_t)n_tokens * (inter / PER);
     const size_t want = (total + threads - 1) / threads;
-    silu_mul_vec_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, n_tokens);
+    silu_mul_vec_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, block,
+                                                                                              n_tokens);
   } else {
     const size_t total = (size_t)n_tokens * inter;
     const size_t want = (total + threads - 1) / threads;
-    silu_mul_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, total);
+    silu_mul_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, block, total);
   }
 }
 
-LLMRS_API int llmrs_silu_mul(const void* gu, void* out, int n_tokens, int inter, int act_dtype,
+LLMRS_API int llmrs_silu_mul(const void* gu, void* out, int n_tokens, int inter, int block, int act_dtype,
                              cudaStream_t stream) {
-  LLMRS_REQUIRE(n_tokens >= 0 && inter > 0, "silu_mul: bad sizes");
+  LLMRS_REQUIRE(n_tokens >= 0 && inter > 0 && block > 0 && inter % block == 0,
+                "silu_mul: bad sizes (width %d, runs of %d)", inter, block);
   if ((size_t)n_tokens * inter == 0) return 0;
   if (act_dtype == LLMRS_F32)
-    launch_silu_mul<float>((const float*)gu, (float*)out, n_tokens, inter, stream);
+    launch_silu_mul<float>((const float*)gu, (float*)out, n_tokens, inter, block, stream);
   else if (act_dtype == LLMRS_BF16)
-    launch_silu_mul<__nv_bfloat16>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, stream);
+    launch_silu_mul<__nv_bfloat16>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n_tokens, inter, block, stream);
   else
     return llmrs_fail("silu_mul: unknown activation dtype %d", act_dtype);
   return llmrs_launch_status("silu_mul");

@@ -119,15 +119,18 @@ def residual_add(h: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     return h
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]`` for ``gate_up`` of width 2I."""
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, block: int = 0) -> torch.Tensor:
+    """``out[t, c] = silu(gate(t, c)) * up(t, c)`` for ``gate_up`` of width 2I that holds gate and
+    up in alternating runs of ``block`` columns (0: the plain layout, I gate columns then I up columns)."""
     _need(gate_up, "gate_up")
     n, two_i = gate_up.shape
     inter = two_i // 2
+    block = block or inter
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     _need(out, "out", gate_up.dtype)
-    _check(_lib().llmrs_silu_mul(_ptr(gate_up), _ptr(out), n, inter, dtype_code(gate_up.dtype), _stream()), "silu_mul")
+    _check(_lib().llmrs_silu_mul(_ptr(gate_up), _ptr(out), n, inter, block, dtype_code(gate_up.dtype), _stream()),
+           "silu_mul")
     return out
 
 

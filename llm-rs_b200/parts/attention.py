@@ -34,8 +34,10 @@ class GQAttention(Mixer):
     the last ``window`` keys when ``window`` > 0; llm-core/src/backends/candle.rs:1587-1640)
     -> output projection. ``scale`` defaults to 1/sqrt(head_dim) (candle.rs:1608).
 
-    The q/k/v weights are concatenated at load so that one product makes all three.
+    The q/k/v weights are concatenated at load so that one product makes all three. The
+    output projection may add its result straight into the residual stream.
     """
+    fuses_residual = True
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, qk_norm: bool = True, qk_norm_eps: float = 1e-6, bias: bool = False,
@@ -104,7 +106,7 @@ class GQAttention(Mixer):
         return min(max(keys, 128), 1024 if q.dtype == torch.float32 or self.head_dim > 128 else 2048)
 
     # -- step ------------------------------------------------------------------------
-    def forward(self, x, ctx, cache):
+    def forward(self, x, ctx, cache, residual=None):
         nq, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
         table = cache.block_table
         if cache.owns:
@@ -131,4 +133,6 @@ class GQAttention(Mixer):
             ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
                             self.scale)
+        if residual is not None:
+            return self.o_proj.forward_into_residual(out, residual)
         return self.o_proj.forward(out)

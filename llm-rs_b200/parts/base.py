@@ -70,7 +70,10 @@ class Mixer(Part):
     ``forward(x, ctx, cache)``  x: [tokens, hidden] activations; ctx: the step's
         ``StepContext``; cache: the ``LayerCache`` of this run-order entry. Returns
         [tokens, hidden] in the activation type.
+    A part with ``fuses_residual = True`` also takes ``residual=h`` (the float32 residual
+    stream) and may add its output into it itself, returning None.
     """
+    fuses_residual = False
 
     def cache_need(self) -> Optional[CacheNeed]:
         return None
@@ -83,7 +86,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """``forward(x, ctx)``: [tokens, hidden] -> [tokens, hidden], token by token."""
+    """``forward(x, ctx)``: [tokens, hidden] -> [tokens, hidden], token by token. With
+    ``fuses_residual = True`` it also takes ``residual=h`` as a mixer does."""
+    fuses_residual = False
 
     def forward(self, x, ctx):
         raise NotImplementedError

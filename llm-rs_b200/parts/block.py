@@ -11,7 +11,8 @@ class PreNormBlock(Block):
     """``h += mixer(norm1(h)); h += feed_forward(norm2(h))``
     (llm-core/src/graph/builder.rs:74-88,223-254,322-333: norm before each branch, no
     norm on a branch's output). Each sum into ``h`` is fused with the norm that follows
-    it, so the feed-forward's output leaves the block not yet added."""
+    it, so the feed-forward's output leaves the block not yet added. A part that sets
+    ``fuses_residual`` is handed ``h`` and may add its output itself (it then returns None)."""
 
     def __init__(self, layer: LayerSpec, prefix: str = ""):
         p = layer.prefix
@@ -32,6 +33,11 @@ class PreNormBlock(Block):
 
     def forward(self, h, pending, ctx, cache):
         x = self.mixer_norm.forward(h, pending)
-        a = self.mixer.forward(x, ctx, cache)
+        if getattr(self.mixer, "fuses_residual", False):
+            a = self.mixer.forward(x, ctx, cache, residual=h)
+        else:
+            a = self.mixer.forward(x, ctx, cache)
         y = self.feed_forward_norm.forward(h, a)
+        if getattr(self.feed_forward, "fuses_residual", False):
+            return h, self.feed_forward.forward(y, ctx, residual=h)
         return h, self.feed_forward.forward(y, ctx)

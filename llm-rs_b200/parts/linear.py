@@ -1,18 +1,27 @@
 """Matrix products of the parts.
 
-bfloat16 weights go through the library product (cuBLAS via ``torch``), as the
+bfloat16 weights: steps of up to ``TC_MAX_TOKENS`` tokens (decoding) run this package's
+tcgen05 kernel (``csrc/gemm_tcgen05.cu``: weights fill the 128 rows of the MMA, the k range
+is shared by a thread-block cluster) with the residual sum or SiLU*up fused into its
+epilogue; larger steps go through the library product (cuBLAS via ``torch``), as the
 reference's projections go through its tensor library
-(llm-core/src/backends/candle.rs:1276-1340). float32 weights, the whole float32 path
-and tensors that the model folder stores in 32-bit, go through this package's own FFMA
+(llm-core/src/backends/candle.rs:1276-1340). float32 weights, the whole float32 path and
+tensors that the model folder stores in 32-bit, go through this package's own FFMA
 kernel: true 32-bit, no reduced-precision tensor-core mode.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
 
 from .. import ops
+
+# Steps with at most this many tokens take the tcgen05 kernel; 0 switches it off.
+TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "64"))
+# Also for larger steps (prefill) when set; by default those stay with the library product.
+TC_PREFILL = os.environ.get("LLMRS_TC_PREFILL", "0") == "1"
 
 
 class Linear:
@@ -24,6 +33,12 @@ class Linear:
         self.weight = weight
         self.bias = None if bias is None else bias.to(weight.dtype).contiguous()
         self.act_dtype = act_dtype
+        n, k = weight.shape
+        self.tc_ok = (weight.dtype == torch.bfloat16 and bias is None and weight.is_contiguous()
+                      and k % 8 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0)
+
+    def uses_tc(self, n_tokens: int) -> bool:
+        return self.tc_ok and n_tokens > 0 and (n_tokens <= TC_MAX_TOKENS or (TC_PREFILL and TC_MAX_TOKENS > 0))
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
@@ -32,9 +47,19 @@ class Linear:
             y = ops.gemm_f32(xf, self.weight, self.bias)
             return y if out_dtype == torch.float32 else y.to(out_dtype)
         xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
+        if self.uses_tc(xb.size(0)) and out_dtype in (torch.float32, torch.bfloat16):
+            return ops.gemm_bf16(xb, self.weight, out_dtype=out_dtype)
         if out_dtype == torch.float32:
             y = torch.mm(xb, self.weight.t(), out_dtype=torch.float32)
             if self.bias is not None:
                 y += self.bias.to(torch.float32)
             return y
         return torch.nn.functional.linear(xb, self.weight, self.bias)
+
+    def forward_into_residual(self, x: torch.Tensor, h: torch.Tensor) -> Optional[torch.Tensor]:
+        """``h += x @ weight.T`` inside the product's epilogue when the tcgen05 kernel runs
+        (returns None); otherwise the product is returned for the caller to add."""
+        if x.dtype == torch.bfloat16 and self.uses_tc(x.size(0)) and h.is_contiguous():
+            ops.gemm_bf16(x, self.weight, out=h, epilogue="residual")
+            return None
+        return self.forward(x)

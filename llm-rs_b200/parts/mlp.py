@@ -14,7 +14,13 @@ from .spec import WeightSpec
 class SwiGLU(FeedForward):
     """``down( silu(gate(x)) * up(x) )`` with silu(x) = x * sigmoid(x)
     (llm-core/src/graph/builder.rs:256-297, llm-core/src/backends/candle.rs:1645-1663).
-    gate and up are concatenated at load: one product, then one fused kernel."""
+    gate and up are concatenated at load into one weight: one product, then SiLU*up,
+    inside the product's epilogue when the tcgen05 kernel runs, else as one kernel. For
+    that epilogue the rows alternate 64 of gate and the 64 matching of up (when the
+    intermediate size is a multiple of 128); the output may be added straight into the
+    residual stream."""
+
+    fuses_residual = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
         self.hidden_size, self.intermediate_size, self.prefix = hidden_size, intermediate_size, prefix
@@ -28,8 +34,20 @@ class SwiGLU(FeedForward):
         p = self.prefix
         g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
-        self.gate_up = Linear(torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous(), None, runtime.act_dtype)
+        self.block = 0      # columns of gate and up alternate in runs of this many (0: all gate, then all up)
+        if dt == torch.bfloat16 and self.intermediate_size % 128 == 0 and self.hidden_size % 8 == 0:
+            self.block = 64
+            w = ops.interleave_gate_up(g.to(dt), u.to(dt))
+        else:
+            w = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.gate_up = Linear(w, None, runtime.act_dtype)
         self.down = Linear(tensors[p + "down_proj.weight"], None, runtime.act_dtype)
 
-    def forward(self, x, ctx):
-        return self.down.forward(ops.silu_mul(self.gate_up.forward(x)))
+    def forward(self, x, ctx, residual=None):
+        if self.block and x.dtype == torch.bfloat16 and self.gate_up.uses_tc(x.size(0)):
+            act = ops.gemm_bf16(x, self.gate_up.weight, epilogue="silu_mul")
+        else:
+            act = ops.silu_mul(self.gate_up.forward(x), block=self.block)
+        if residual is not None:
+            return self.down.forward_into_residual(act, residual)
+        return self.down.forward(act)

@@ -384,3 +384,72 @@ def test_sampler_follows_the_distribution():
     want = torch.softmax(logits[0].double().cpu(), 0).numpy()
     for t in range(4):
         assert abs(toks.count(t) / n - want[t]) < 0.04
+
+
+# -- tcgen05 matrix product ---------------------------------------------------------------------
+def _tc_case(tokens, features, K, epilogue, out_dtype, splits, ldx=None):
+    ops = _ops()
+    torch.manual_seed(tokens * 7 + features + K)
+    x = (torch.randn(tokens, ldx or K, device=DEV) * 0.5).to(torch.bfloat16)[:, :K]
+    w = (torch.randn(features, K, device=DEV) * 0.5).to(torch.bfloat16)
+    ref = x.double() @ w.double().t()
+    if epilogue == "residual":
+        h = torch.randn(tokens, features, device=DEV)
+        want = h.double() + ref
+        got = ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=splits).double()
+        tol = 1e-5 * math.sqrt(K) * float(want.abs().max())
+    elif epilogue == "silu_mul":
+        half = features // 2
+        g, u = w[:half], w[half:]
+        gg, uu = x.double() @ g.double().t(), x.double() @ u.double().t()
+        want = gg * torch.sigmoid(gg) * uu
+        got = ops.gemm_bf16(x, ops.interleave_gate_up(g, u), epilogue="silu_mul", splits=splits).double()
+        tol = 1e-2 * float(want.abs().max())
+    else:
+        want = ref
+        got = ops.gemm_bf16(x, w, out_dtype=out_dtype, splits=splits).double()
+        tol = (1e-2 if out_dtype == torch.bfloat16 else 1e-5 * math.sqrt(K)) * float(want.abs().max())
+    ops.check_tc_error(DEV)
+    err = float((got - want).abs().max())
+    assert err <= tol, f"max |diff| {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("tokens,features,K,epilogue,out_dtype,splits", [
+    (8, 128, 64, "store", torch.float32, 1), (8, 128, 512, "store", torch.float32, 2),
+    (16, 256, 1024, "store", torch.bfloat16, 4), (1, 384, 4096, "store", torch.float32, 8),
+    (17, 136, 192, "store", torch.float32, 1), (33, 512, 1000, "store", torch.bfloat16, 2),
+    (64, 1024, 2048, "residual", torch.float32, 8), (5, 264, 328, "residual", torch.float32, 4),
+    (8, 512, 256, "silu_mul", torch.bfloat16, 1), (40, 1280, 4096, "silu_mul", torch.bfloat16, 4),
+    (3, 1000, 96, "store", torch.float32, 1), (2, 151936, 128, "store", torch.float32, None)])
+def test_gemm_tcgen05_few_tokens(tokens, features, K, epilogue, out_dtype, splits):
+    """Weights on the 128 rows of the MMA, tokens on the narrow side, k shared by a cluster."""
+    _tc_case(tokens, features, K, epilogue, out_dtype, splits)
+
+
+@pytest.mark.parametrize("tokens,features,K,epilogue,out_dtype", [
+    (65, 128, 64, "store", torch.float32), (128, 256, 512, "store", torch.bfloat16),
+    (300, 392, 1000, "store", torch.float32), (200, 512, 4096, "residual", torch.float32),
+    (130, 1024, 512, "silu_mul", torch.bfloat16), (515, 768, 320, "store", torch.bfloat16)])
+def test_gemm_tcgen05_many_tokens(tokens, features, K, epilogue, out_dtype):
+    _tc_case(tokens, features, K, epilogue, out_dtype, None)
+
+
+def test_gemm_tcgen05_strided_input_and_refusals():
+    ops = _ops()
+    _tc_case(8, 256, 256, "store", torch.float32, 1, ldx=1024)
+    x = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(64, 100, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.gemm_bf16(x, w)
+    with pytest.raises(ops.KernelError, match="splits"):
+        ops.gemm_bf16(torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV),
+                      torch.zeros(64, 64, dtype=torch.bfloat16, device=DEV), splits=3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul_interleaved_layout(dtype):
+    ops = _ops()
+    gate, up = torch.randn(5, 256, device=DEV).to(dtype), torch.randn(5, 256, device=DEV).to(dtype)
+    inter = torch.stack([gate.reshape(5, 4, 64), up.reshape(5, 4, 64)], 2).reshape(5, 512).contiguous()
+    want = gate.double() * torch.sigmoid(gate.double()) * up.double()
+    assert torch.allclose(ops.silu_mul(inter, block=64).double(), want, **_tol(dtype))
