@@ -293,7 +293,7 @@ def main():
                                          max_requests=max_batch + 1, max_tokens_per_step=2048, prefill_chunk=512),
                             runner=runner)
             sp = SamplingParams(temperature=0.0, max_new_tokens=W + K + 1, ignore_eos=True)
-            plen = ctx - W - K - 1
+            plen = ctx - W - K - 2     # the last decoded token lands inside the context length
             rids = [engine.add_request(rng.integers(0, V, plen).tolist(), sp) for _ in range(args.batch)]
             while any(engine.requests[r].remaining > 1 or not engine.requests[r].output for r in rids):
                 engine.step()   # prefill of the prompts, not timed

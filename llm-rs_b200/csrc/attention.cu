@@ -357,6 +357,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part, T* __
                                            const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
                                            const int* __restrict__ cached_len, int max_splits, int split_keys,
                                            int n_q_heads, int d, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int di = blockIdx.x, head = blockIdx.y;
   const int req = dec_reqs[di];
   const int kv_len = cached_len[req] + 1;
@@ -414,8 +416,8 @@ static int launch_decode(const void* q, long long q_stride, void* out, long long
   int rc = llmrs_launch_status("attn_decode_split");
   if (rc) return rc;
   dim3 cgrid(n_dec, n_q_heads);
-  attn_decode_combine_kernel<T><<<cgrid, 128, 0, stream>>>(scratch, (T*)out, out_stride, dec_reqs, q_start,
-                                                            cached_len, max_splits, split_keys, n_q_heads, d, window);
+  llmrs_launch(attn_decode_combine_kernel<T>, cgrid, dim3(128), 0, stream, true, (const float*)scratch, (T*)out,
+               out_stride, dec_reqs, q_start, cached_len, max_splits, split_keys, n_q_heads, d, window);
   return llmrs_launch_status("attn_decode_combine");
 }
 
@@ -443,9 +445,9 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
                                          page_size, window, scale, stream);
     if (rc) return rc;
     dim3 cgrid(n_dec, n_q_heads);
-    attn_decode_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, stream>>>(
-        scratch, (__nv_bfloat16*)out, out_stride, dec_reqs, q_start, cached_len, max_splits, split_keys, n_q_heads, d,
-        window);
+    llmrs_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, true, (const float*)scratch,
+                 (__nv_bfloat16*)out, out_stride, dec_reqs, q_start, cached_len, max_splits, split_keys, n_q_heads, d,
+                 window);
     return llmrs_launch_status("attn_decode_combine");
   }
   if (dtype == LLMRS_BF16)

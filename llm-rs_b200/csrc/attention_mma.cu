@@ -36,6 +36,8 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   constexpr int CH = D / 8;                // 16-byte chunks per row
   constexpr int TILE_ELEMS = DM_TILE * ROW;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  pdl_launch_dependents();
+  pdl_wait();
 
   const int G = n_q_heads / n_kv_heads;
   const int hgroups = (G + 15) / 16;
@@ -262,7 +264,7 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   }
   const int G = n_q_heads / n_kv_heads;
   dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
-  attn_decode_split_mma_kernel<DCH><<<grid, DM_THREADS, smem, stream>>>(
+  llmrs_launch(attn_decode_split_mma_kernel<DCH>, grid, dim3(DM_THREADS), smem, stream, true,
       (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,
       max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale);
   return llmrs_launch_status("attn_decode_split_mma");

@@ -16,6 +16,38 @@ int llmrs_fail(const char* fmt, ...);
 // cudaGetLastError() as the entry point's return value (0 = launched).
 int llmrs_launch_status(const char* what);
 
+// Programmatic dependent launch. A kernel launched through llmrs_launch() with pdl = true
+// may start while the kernel before it in the stream is still running: it calls
+// pdl_launch_dependents() at its top (the kernel after it may be scheduled early in turn)
+// and pdl_wait() before its first read or write of anything an earlier kernel touches;
+// what it does before that wait (barrier set-up, loads of weights) overlaps the tail of
+// its predecessor. Without the launch attribute both calls do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// 1: kernels that support it are launched with the programmatic-serialization attribute.
+extern int g_llmrs_pdl;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t llmrs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                bool pdl, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  unsigned n = 0;
+  if (pdl && g_llmrs_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    n = 1;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 #define LLMRS_REQUIRE(cond, ...)                     \
   do {                                               \
     if (!(cond)) return llmrs_fail(__VA_ARGS__);     \

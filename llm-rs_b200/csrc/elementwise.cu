@@ -111,6 +111,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const TA* __restrict__ delta, const float* __restrict__ weight,
                        TA* __restrict__ y, const int* __restrict__ rows, int hidden, float eps) {
   __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x;
   const int src = rows ? rows[i] : i;
   float* hr = h + (size_t)src * hidden;
@@ -158,13 +160,17 @@ static void launch_add_rmsnorm(float* h, const TA* delta, const float* weight, T
   const int per_chunk = 4 * NORM_THREADS;
   if (hidden % 4 == 0 && hidden <= 8 * per_chunk) {
     if (hidden <= per_chunk)
-      add_rmsnorm_vec_kernel<TA, 1><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+      llmrs_launch(add_rmsnorm_vec_kernel<TA, 1>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, true, h, delta, weight, y, rows,
+                   hidden, eps);
     else if (hidden <= 2 * per_chunk)
-      add_rmsnorm_vec_kernel<TA, 2><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+      llmrs_launch(add_rmsnorm_vec_kernel<TA, 2>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, true, h, delta, weight, y, rows,
+                   hidden, eps);
     else if (hidden <= 4 * per_chunk)
-      add_rmsnorm_vec_kernel<TA, 4><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+      llmrs_launch(add_rmsnorm_vec_kernel<TA, 4>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, true, h, delta, weight, y, rows,
+                   hidden, eps);
     else
-      add_rmsnorm_vec_kernel<TA, 8><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
+      llmrs_launch(add_rmsnorm_vec_kernel<TA, 8>, dim3(n_rows), dim3(NORM_THREADS), 0, stream, true, h, delta, weight, y, rows,
+                   hidden, eps);
   } else {
     add_rmsnorm_kernel<TA><<<n_rows, NORM_THREADS, 0, stream>>>(h, delta, weight, y, rows, hidden, eps);
   }

@@ -25,5 +25,9 @@ int llmrs_launch_status(const char* what) {
 // The message of the last refusal or failed launch on this thread.
 LLMRS_API const char* llmrs_last_error() { return g_last_error; }
 
+int g_llmrs_pdl = 1;
+// Switch programmatic dependent launch on (1, the default) or off (0) for the kernels that support it.
+LLMRS_API void llmrs_set_pdl(int on) { g_llmrs_pdl = on; }
+
 // Version of the entry points' signatures; the Python side checks it after loading.
 LLMRS_API int llmrs_abi_version() { return 1; }

@@ -157,6 +157,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
+  pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y;
   const int splits = MODE == 1 ? (int)gridDim.z : 1;
@@ -188,9 +189,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0 && lane == 0) {
-    // Producer: one thread feeds the ring of stages by TMA.
+    // Producer: one thread feeds the ring of stages by TMA. In mode 1 the A operand is the
+    // weight, which no earlier kernel writes: its first tiles are requested before the
+    // wait on the preceding kernel, whose tail they overlap.
     int issued = 0;
-    for (int i = 0; i < nkb; ++i) {
+    const int early = MODE == 1 ? min(nkb, STAGES) : 0;
+    for (int i = 0; i < early; ++i) {
+      mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
+      tma_load_2d(tc_smem(tiles + (size_t)i * STAGE_BYTES), &map_a, full0 + 8 * i, (kb0 + i) * TC_BK, tile_a * TC_BM);
+    }
+    pdl_wait();
+    for (int i = 0; i < early; ++i)
+      tma_load_2d(tc_smem(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_b, full0 + 8 * i, (kb0 + i) * TC_BK,
+                  tile_b * BN);
+    issued = early;
+    for (int i = early; i < nkb; ++i) {
       const int s = i % STAGES;
       if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, abort_flag)) break;
       mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
@@ -226,6 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncwarp();
   if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
 
+  pdl_wait();  // the epilogue writes (and for the residual reads) what earlier kernels touch
   const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int row = warp * 32 + lane;  // row of the tile this thread reads from tensor memory
 
@@ -399,13 +413,18 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   cfg.blockDim = dim3(TC_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = cluster_z;
-  cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (g_llmrs_pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, MODE>, ma, mb, p);
   if (e != cudaSuccess) return llmrs_fail("gemm_bf16 launch: %s", cudaGetErrorString(e));
   return llmrs_launch_status("gemm_bf16");
@@ -439,9 +458,10 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
     if ((rc = make_map(&mb, x, tokens, K, ldx, bn))) return rc;
     p.a_rows = features; p.b_rows = tokens;
     dim3 grid((features + TC_BM - 1) / TC_BM, 1, splits);
+    // Stages sized so that two blocks fit on an SM: the second one's loads cover the first one's epilogue.
     if (bn == 16) return launch_tc<16, 6, 1>(ma, mb, p, grid, splits, stream);
-    if (bn == 32) return launch_tc<32, 6, 1>(ma, mb, p, grid, splits, stream);
-    return launch_tc<64, 6, 1>(ma, mb, p, grid, splits, stream);
+    if (bn == 32) return launch_tc<32, 5, 1>(ma, mb, p, grid, splits, stream);
+    return launch_tc<64, 4, 1>(ma, mb, p, grid, splits, stream);
   }
   const bool wide = features >= 256 || epilogue == TC_SILU_MUL;
   const int bn = wide ? 256 : 128;

@@ -27,6 +27,8 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     T* __restrict__ cache,                          // [n_pages, n_kv_heads, 2, page_size, d]
     int n_q_heads, int n_kv_heads, int d, int rotary_dim, int page_size, float eps) {
   extern __shared__ float smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* x = smem + warp * d;
@@ -97,12 +99,12 @@ LLMRS_API int llmrs_qk_norm_rope_kvwrite(void* q, long long q_stride, const void
   const int heads_total = n_q_heads + (k ? 2 * n_kv_heads : 0);
   dim3 grid(n_tokens, (heads_total + ROPE_WARPS - 1) / ROPE_WARPS);
   if (dtype == LLMRS_F32)
-    qk_norm_rope_kvwrite_kernel<float><<<grid, ROPE_THREADS, smem, stream>>>(
+    llmrs_launch(qk_norm_rope_kvwrite_kernel<float>, grid, dim3(ROPE_THREADS), smem, stream, true,
         (float*)q, q_stride, (const float*)k, k_stride, (const float*)v, v_stride, q_norm_w, k_norm_w, cos_sin,
         positions, token_req, block_table, table_stride, (float*)cache, n_q_heads, n_kv_heads, d, rotary_dim,
         page_size, eps);
   else if (dtype == LLMRS_BF16)
-    qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, ROPE_THREADS, smem, stream>>>(
+    llmrs_launch(qk_norm_rope_kvwrite_kernel<__nv_bfloat16>, grid, dim3(ROPE_THREADS), smem, stream, true,
         (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm_w,
         k_norm_w, cos_sin, positions, token_req, block_table, table_stride, (__nv_bfloat16*)cache, n_q_heads,
         n_kv_heads, d, rotary_dim, page_size, eps);

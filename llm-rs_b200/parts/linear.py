@@ -19,7 +19,7 @@ import torch
 from .. import ops
 
 # Steps with at most this many tokens take the tcgen05 kernel; 0 switches it off.
-TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "64"))
+TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "32"))
 # Also for larger steps (prefill) when set; by default those stay with the library product.
 TC_PREFILL = os.environ.get("LLMRS_TC_PREFILL", "0") == "1"
 
