@@ -122,7 +122,7 @@ def prefill_flops(cfg, n_layers, tokens):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than 36 only where memory or time needs it")
@@ -196,13 +196,13 @@ def main():
         fill_context(ids, ctx - warmup - steps)
         toks = rng.integers(0, V, (warmup + steps, batch)).tolist()
         out = torch.empty((batch,), dtype=torch.int32, device="cuda:0")
+        if sampler:
+            sampler.start()       # nvidia-smi needs a moment to deliver its first sample
         for s in range(warmup):
             logits = runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
             ops.argmax(logits, out)
         torch.cuda.synchronize()
         launches0 = ops.launch_count
-        if sampler:
-            sampler.start()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for s in range(warmup, warmup + steps):
@@ -292,8 +292,12 @@ def main():
             engine = Engine(EngineConfig(model_path="", block_pool_size=pool_tokens // page, page_size=page,
                                          max_requests=max_batch + 1, max_tokens_per_step=2048, prefill_chunk=512),
                             runner=runner)
-            sp = SamplingParams(temperature=0.0, max_new_tokens=W + K + 1, ignore_eos=True)
-            plen = ctx - W - K - 2     # the last decoded token lands inside the context length
+            # Prompts are prefilled four at a time, so some requests start decoding several steps
+            # before the others, and results are read one step late: give every request enough
+            # tokens to decode through the whole timed region, inside the context length.
+            spare = 2 * (-(-(ctx) // 512)) + 8
+            sp = SamplingParams(temperature=0.0, max_new_tokens=W + K + spare, ignore_eos=True)
+            plen = ctx - (W + K + spare) - 2
             rids = [engine.add_request(rng.integers(0, V, plen).tolist(), sp) for _ in range(args.batch)]
             while any(engine.requests[r].remaining > 1 or not engine.requests[r].output for r in rids):
                 engine.step()   # prefill of the prompts, not timed
@@ -301,12 +305,16 @@ def main():
                 engine.step()
             torch.cuda.synchronize()
             h2d0 = runner.h2d_bytes
+            graphs0, pre0 = len(runner._graphs), engine.scheduler.stats["preemptions"]
             t_start = time.perf_counter()
             got = 0
             for _ in range(K):
                 got += sum(1 for _, tok, _ in engine.step() if tok is not None)
             torch.cuda.synchronize()
             dt = time.perf_counter() - t_start
+            print(f"[bench] e2e: {got} tokens in {K} steps, {len(runner._graphs) - graphs0} graphs captured and "
+                  f"{engine.scheduler.stats['preemptions'] - pre0} preemptions inside the timed region",
+                  file=sys.stderr, flush=True)
             result["e2e"] = {"value": round(got / dt, 2), "unit": "tokens/s",
                              "h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // K,
                              "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(dt / K * 1e3, 4)}

@@ -38,6 +38,7 @@ class RequestRecord:
     cached_len: int = 0
     reserved_len: int = 0       # tokens that the tables cover (>= cached_len between reserve and commit)
     tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> physical page
+    edits: int = 0              # counts changes to the tables other than appending a page
 
 
 class NoFreeSlot(CacheError):
@@ -141,6 +142,7 @@ class CacheManager:
         """Undo a reservation that was not committed (pages beyond the cached length go back)."""
         rec = self.record(request_id)
         keep = pages_for(rec.cached_len, self.page_size)
+        rec.edits += 1
         for g, table in enumerate(rec.tables):
             while len(table) > keep:
                 page = table.pop()
@@ -161,6 +163,7 @@ class CacheManager:
                 if table[j] != RELEASED:
                     self.pools[g].free(table[j])
                     table[j] = RELEASED
+                    rec.edits += 1
 
     # -- views -----------------------------------------------------------------------
     def table(self, request_id: Hashable, group: int) -> List[int]:

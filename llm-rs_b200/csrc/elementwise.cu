@@ -294,3 +294,21 @@ LLMRS_API int llmrs_silu_mul(const void* gu, void* out, int n_tokens, int inter,
     return llmrs_fail("silu_mul: unknown activation dtype %d", act_dtype);
   return llmrs_launch_status("silu_mul");
 }
+
+// ---------------------------------------------------------------------------------
+// dst[dst_idx[i]] = src[src_idx[i]] for the pairs with dst_idx[i] >= 0: token ids that an
+// earlier step sampled go into this step's input without a trip through the host.
+// ---------------------------------------------------------------------------------
+__global__ void scatter_tokens_kernel(int* __restrict__ dst, const int* __restrict__ dst_idx,
+                                      const int* __restrict__ src, const int* __restrict__ src_idx, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && dst_idx[i] >= 0) dst[dst_idx[i]] = src[src_idx[i]];
+}
+
+LLMRS_API int llmrs_scatter_tokens(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n,
+                                   cudaStream_t stream) {
+  LLMRS_REQUIRE(n >= 0, "scatter_tokens: bad size");
+  if (n == 0) return 0;
+  scatter_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(dst, dst_idx, src, src_idx, n);
+  return llmrs_launch_status("scatter_tokens");
+}

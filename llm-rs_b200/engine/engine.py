@@ -33,6 +33,9 @@ class EngineConfig:
     max_tokens_per_step: int = 2048
     prefill_chunk: int = 512
     cuda_graphs: bool = True
+    # Queue the next step on the GPU before the last one's tokens are read back (they feed
+    # the next step on the device); ``step()`` then reports a step's tokens one call later.
+    async_steps: bool = True
 
 
 class Engine:
@@ -53,6 +56,9 @@ class Engine:
         self._ids = itertools.count(1)
         self.requests: Dict[int, Request] = {}
         self._events: Dict[int, List[Output]] = {}
+        self._inflight = None            # the step that is queued on the GPU and not read back yet
+        self._tok_bufs = [None, None]
+        self._tok_flip = 0
 
     # -- requests --------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -69,34 +75,79 @@ class Engine:
         self._events[rid] = []
         return rid
 
-    def has_work(self) -> bool:
-        return self.scheduler.has_work()
-
     # -- one step --------------------------------------------------------------------
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._inflight is not None
+
     def step(self) -> List[Tuple[int, Optional[int], bool]]:
         """Run one scheduler step. Returns ``(request id, token, finished)`` for every
-        request that got a token or ended in it."""
+        request whose token became known or that ended in this call. With ``async_steps``
+        the tokens of a step are reported by the NEXT call: the step is queued on the GPU,
+        then the previous step's tokens are read while it runs."""
         batch = self.scheduler.schedule()
-        sampled: Dict[int, int] = {}
+        launched = None
         if batch:
-            entries = [StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [])
-                       for s in batch]
+            prev = self._inflight
+            entries = []
+            for s in batch:
+                src = prev["row_of"][s.request.request_id] if s.pending else -1
+                entries.append(StepEntry(s.request.request_id, s.tokens, [len(s.tokens) - 1] if s.sample else [],
+                                         device_token=src))
             try:
-                logits = self.runner.step(entries)
-                rows = [(s.request.params, s.request.request_id, len(s.request.output), s.request.tokens())
-                        for s in batch if s.sample]
-                if rows:
-                    tokens = self.sampler.sample(logits, rows).cpu().tolist()
-                    sampled = {r[1]: t for r, t in zip(rows, tokens)}
+                logits = self.runner.step(entries, token_source=prev["tokens"] if prev else None)
+                sampled = [s for s in batch if s.sample]
+                tokens = host = event = None
+                if sampled:
+                    rows = [(s.request.params, s.request.request_id, len(s.request.output) + s.request.n_inflight,
+                             s.request.tokens() if s.request.params.repetition_penalty != 1.0 else ())
+                            for s in sampled]
+                    tokens = self.sampler.sample(logits, rows)
+                    host = self._token_buffer(len(sampled))
+                    host.copy_(tokens, non_blocking=True)
+                    event = torch.cuda.Event()
+                    event.record()
             except Exception:
                 outs = self.scheduler.abort_all()
                 for o in outs:
                     self._events.setdefault(o.request_id, []).append(o)
+                self._inflight = None
                 raise
-        outs = self.scheduler.update(batch, sampled)
+            self.scheduler.on_launched(batch)
+            launched = {"batch": batch, "tokens": tokens, "host": host, "event": event,
+                        "row_of": {s.request.request_id: i for i, s in enumerate(sampled)}}
+        outs: List[Output] = []
+        if self._inflight is not None:
+            outs += self._collect(self._inflight)
+        self._inflight = launched
+        # Read this step's tokens at once when the caller asked for that, or when a request
+        # needs its full history on the host for the next step (repetition penalty).
+        if launched is not None and (not self.config.async_steps or any(
+                s.request.params.repetition_penalty != 1.0 for s in batch)):
+            outs += self._collect(launched)
+            self._inflight = None
+        if launched is None and self._inflight is None:
+            outs += self.scheduler.on_result([], {})    # requests that ended without a step
         for o in outs:
             self._events.setdefault(o.request_id, []).append(o)
         return [(o.request_id, o.token, o.finished) for o in outs]
+
+    def _token_buffer(self, n: int) -> torch.Tensor:
+        """Pinned host memory for a step's sampled tokens (two buffers: one step is in flight)."""
+        self._tok_flip ^= 1
+        buf = self._tok_bufs[self._tok_flip]
+        if buf is None or buf.numel() < n:
+            buf = torch.empty((max(n, 64),), dtype=torch.int32).pin_memory()
+            self._tok_bufs[self._tok_flip] = buf
+        return buf[:n]
+
+    def _collect(self, flight) -> List[Output]:
+        """Wait for a queued step's tokens and let the scheduler account for them."""
+        sampled = {}
+        if flight["event"] is not None:
+            flight["event"].synchronize()
+            values = flight["host"].tolist()
+            sampled = {rid: values[i] for rid, i in flight["row_of"].items()}
+        return self.scheduler.on_result(flight["batch"], sampled)
 
     # -- conveniences ----------------------------------------------------------------
     def poll(self, request_id: int) -> Output:

@@ -11,6 +11,7 @@ number of new tokens and block tables.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -34,10 +35,13 @@ class StepError(RuntimeError):
 @dataclass
 class StepEntry:
     """One request's share of a step: its next tokens and the places among them whose
-    logits are wanted."""
+    logits are wanted. ``device_token`` >= 0 says that the entry's single token is not
+    known on the host yet: it is element ``device_token`` of the ``token_source`` tensor
+    given to ``step`` (what an earlier step sampled), and ``tokens`` holds a placeholder."""
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    device_token: int = -1
 
 
 class StepContext:
@@ -98,6 +102,7 @@ class ModelRunner:
         self._meta_flip = 0
         self.steps_run = 0
         self.h2d_bytes = 0  # bytes of index arrays copied to the device so far
+        self._table_rows: Dict[Hashable, list] = {}
         # Steps that only decode (one token per request) are captured in CUDA graphs and
         # replayed: one launch instead of some ten per layer.
         self.use_graphs = False
@@ -126,6 +131,27 @@ class ModelRunner:
     def release(self, request_id: Hashable) -> None:
         """The request is finished: its pages and its slot go back."""
         self.manager.release(request_id)
+        self._table_rows.pop(request_id, None)
+
+    def _table_row(self, rec, g: int) -> np.ndarray:
+        """The request's block table of group ``g`` as an int32 array, kept between steps and
+        extended when a page is appended (rebuilt after any other change to the table)."""
+        cache = self._table_rows.get(rec.request_id)
+        if cache is None or cache[0] is not rec or cache[1] != rec.edits:
+            cache = [rec, rec.edits, [np.empty(64, np.int32) for _ in rec.tables], [0] * len(rec.tables)]
+            if len(self._table_rows) > 4 * self.max_requests:
+                self._table_rows = {k: v for k, v in self._table_rows.items() if k in self.manager.requests}
+            self._table_rows[rec.request_id] = cache
+        table, have = rec.tables[g], cache[3][g]
+        arr = cache[2][g]
+        if len(table) > arr.size:
+            bigger = np.empty(max(2 * arr.size, len(table)), np.int32)
+            bigger[:have] = arr[:have]
+            cache[2][g] = arr = bigger
+        if len(table) > have:
+            arr[have:len(table)] = table[have:]
+        cache[3][g] = len(table)
+        return arr[:len(table)]
 
     def live_requests(self) -> List[Hashable]:
         return list(self.manager.requests)
@@ -143,10 +169,12 @@ class ModelRunner:
             seen.add(e.request_id)
             if len(e.tokens) < 1:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.spec.vocab_size:
-                    raise StepError(f"token id {t} of request {e.request_id!r} is outside the vocabulary "
-                                    f"of {self.spec.vocab_size}")
+            if e.device_token >= 0:
+                if len(e.tokens) != 1:
+                    raise StepError(f"request {e.request_id!r}: a token taken from the device comes alone")
+            elif min(e.tokens) < 0 or max(e.tokens) >= self.spec.vocab_size:
+                raise StepError(f"a token id of request {e.request_id!r} is outside the vocabulary "
+                                f"of {self.spec.vocab_size}")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise StepError(f"request {e.request_id!r} wants place {w} of {len(e.tokens)} tokens")
@@ -195,7 +223,7 @@ class ModelRunner:
         max_dec_kv = 0
         for r, (e, rec) in enumerate(zip(entries, recs)):
             n = len(e.tokens)
-            token_ids[at:at + n] = np.asarray(e.tokens, dtype=np.int64)
+            token_ids[at:at + n] = e.tokens
             positions[at:at + n] = np.arange(rec.cached_len, rec.cached_len + n)
             token_req[at:at + n] = r
             q_start[r], n_new[r], cached[r], slots[r] = at, n, rec.cached_len, rec.slot
@@ -212,12 +240,19 @@ class ModelRunner:
             width = _round_up(max(len(rec.tables[g]) for rec in recs), table_round)
             tab = np.full((R, width), RELEASED, np.int32)
             for r, rec in enumerate(recs):
-                tab[r, :len(rec.tables[g])] = rec.tables[g]
+                row = self._table_row(rec, g)
+                tab[r, :row.size] = row
             tables.append(tab)
+        pend_dst = np.full(R, -1, np.int32)
+        pend_src = np.zeros(R, np.int32)
+        for r, e in enumerate(entries):
+            if e.device_token >= 0:
+                pend_dst[r], pend_src[r] = q_start[r], e.device_token
+                token_ids[q_start[r]] = 0
 
         parts = [token_ids, positions, token_req, q_start, n_new, cached, slots,
                  np.asarray(want_rows, np.int32), np.asarray(tiles, np.int32), np.asarray(dec, np.int32),
-                 *[t.reshape(-1) for t in tables]]
+                 pend_dst, pend_src, *[t.reshape(-1) for t in tables]]
         offsets, total = [], 0
         for p in parts:
             offsets.append(total)
@@ -269,26 +304,32 @@ class ModelRunner:
             ctx.max_decode_kv_len = max(t.shape[1] for t in tables) * self.page_size if tables else max_dec_kv
             ctx._scratch_bufs = graph.scratch
             graph.ctx = ctx
-        ctx.block_tables = [view(10 + g, tables[g].size).view(R, -1) for g in range(len(tables))]
+        ctx.pend_dst, ctx.pend_src = view(10, R), view(11, R)
+        ctx.block_tables = [view(12 + g, tables[g].size).view(R, -1) for g in range(len(tables))]
         ctx.__dict__.update(host_lists)
         return ctx
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch. Returns float32 logits ``[wanted, vocab]`` on the device, in the
         order of the entries and of each entry's ``want`` (None if nothing is wanted).
 
         A request id that is not live is admitted. Raises ``OutOfPages`` (and leaves
         every request as it was) when the pool cannot hold the step's tokens.
+        ``token_source`` is the int32 device tensor that entries with ``device_token``
+        index (tokens sampled by a step that the host has not read back yet).
         """
         entries = list(entries)
+        if token_source is None and any(e.device_token >= 0 for e in entries):
+            raise StepError("an entry takes its token from the device but no token_source was given")
         admitted = self._plan(entries)
         try:
             with torch.cuda.device(self.device):
                 if self.use_graphs and self._graph_safe and all(len(e.tokens) == 1 for e in entries):
-                    logits = self._graph_step(entries)
+                    logits = self._graph_step(entries, token_source)
                 else:
                     ctx = self._build_context(entries)
+                    self._feed_device_tokens(ctx, entries, token_source)
                     logits = self.model.forward(ctx)
         except Exception:
             for e in entries:
@@ -302,7 +343,12 @@ class ModelRunner:
         return logits
 
     # -- captured decode steps ---------------------------------------------------------
-    def _graph_step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def _feed_device_tokens(self, ctx: StepContext, entries, token_source) -> None:
+        if token_source is not None and any(e.device_token >= 0 for e in entries):
+            from .. import ops
+            ops.scatter_tokens(ctx.token_ids, ctx.pend_dst, token_source, ctx.pend_src)
+
+    def _graph_step(self, entries: Sequence[StepEntry], token_source=None) -> Optional[torch.Tensor]:
         recs = [self.manager.record(e.request_id) for e in entries]
         widths = tuple(_round_up(max(len(rec.tables[g]) for rec in recs), GRAPH_TABLE_ROUND)
                        for g in range(len(self.manager.groups)))
@@ -311,14 +357,25 @@ class ModelRunner:
         if graph is None:
             graph = _DecodeGraph()
             ctx = self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            self._feed_device_tokens(ctx, entries, token_source)
             self.model.forward(ctx)  # warm-up: sizes the workspace; rewrites the same keys and values
             torch.cuda.current_stream().synchronize()
             graph.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph.graph):
-                graph.logits = self.model.forward(ctx)
+            # A collection that ran during the capture could destroy an older runner's graphs,
+            # which CUDA does not allow while a stream is capturing: collect now, then hold off.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph.graph):
+                    graph.logits = self.model.forward(ctx)
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self._graphs[key] = graph
         else:
-            self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            ctx = self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            self._feed_device_tokens(ctx, entries, token_source)
         graph.graph.replay()
         return graph.logits
 

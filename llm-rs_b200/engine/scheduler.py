@@ -16,6 +16,12 @@ What this scheduler does differently, and why:
     returns to the front of the waiting queue and later recomputes prompt + generated
     tokens. Nothing is dropped. A request that cannot fit although it is alone is
     finished with reason "error_too_long".
+  * a step's result may be read one step late (``on_launched`` when the step is queued on
+    the GPU, ``on_result`` when its tokens are on the host): the next step is scheduled
+    while the tokens of the last one are still unknown. A request whose next token is
+    "in flight" is scheduled with that token taken from the device; one that will end by
+    its length is not scheduled further; one that turns out to have ended at EOS has its
+    last, superfluous token dropped.
 """
 from __future__ import annotations
 
@@ -39,13 +45,28 @@ class Request:
     status: str = WAITING
     finish_reason: Optional[str] = None
     preemptions: int = 0
+    n_inflight: int = 0          # tokens sampled on the device that the host has not read yet (0 or 1)
 
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_slice(self, a: int, b: int) -> List[int]:
+        """Tokens a..b-1 of prompt + output without building the whole list."""
+        p = len(self.prompt)
+        if b <= p:
+            return self.prompt[a:b]
+        if a >= p:
+            return self.output[a - p:b - p]
+        return self.prompt[a:] + self.output[:b - p]
+
+    @property
+    def n_known(self) -> int:
+        return len(self.prompt) + len(self.output)
+
     @property
     def remaining(self) -> int:
-        return len(self.prompt) + len(self.output) - self.n_computed
+        """Tokens whose keys and values are not computed (or queued) yet, the in-flight one included."""
+        return self.n_known + self.n_inflight - self.n_computed
 
 
 @dataclass
@@ -54,6 +75,7 @@ class Scheduled:
     request: Request
     tokens: List[int]
     sample: bool                 # the last of these tokens yields the request's next token
+    pending: bool = False        # the single token is the request's in-flight one (not on the host yet)
 
 
 @dataclass
@@ -122,6 +144,8 @@ class Scheduler:
         req.status, req.finish_reason = FINISHED, reason
         if req in self.running:
             self.running.remove(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)   # it was preempted while its last token was in flight
         if req.request_id in self.manager.requests:
             self.manager.release(req.request_id)
 
@@ -133,7 +157,11 @@ class Scheduler:
             batch = self._try_schedule()
             if batch or not self.running:
                 return batch
-            # Requests are running but none could get its pages: make room from the back.
+            # Nothing to run. Either every running request only waits for tokens that are in
+            # flight, or requests are running and none could get its pages.
+            stuck = [r for r in self.running if r.remaining >= 1 and not self._ends_by_length(r)]
+            if not stuck:
+                return batch
             if len(self.running) == 1:
                 req = self.running[0]
                 self._finish(req, "error_too_long")
@@ -150,7 +178,7 @@ class Scheduler:
         i = 0
         while i < len(self.running) and budget >= 1 and len(batch) < self.max_requests_per_step:
             req = self.running[i]
-            if req.remaining != 1:
+            if req.remaining != 1 or self._ends_by_length(req):
                 i += 1
                 continue
             fits = self._fits(req, 1, free)
@@ -159,24 +187,27 @@ class Scheduler:
                 fits = self._fits(req, 1, free)
             if not fits:
                 break  # req is the last one running; schedule() decides what becomes of it
-            batch.append(Scheduled(req, [req.tokens()[-1]], True))
+            if req.n_inflight:
+                batch.append(Scheduled(req, [0], True, pending=True))
+            else:
+                batch.append(Scheduled(req, req.token_slice(req.n_known - 1, req.n_known), True))
             budget -= 1
             i += 1
 
         # 2. running requests that still have prompt left, in order of admission
         for req in self.running:
             if req.remaining > 1 and budget >= 1 and len(batch) < self.max_requests_per_step:
-                n = min(req.remaining, self.prefill_chunk, budget)
-                if self._fits(req, n, free):
-                    toks = req.tokens()[req.n_computed:req.n_computed + n]
-                    batch.append(Scheduled(req, toks, req.n_computed + n == len(req.prompt) + len(req.output)))
+                n = min(req.n_known - req.n_computed, self.prefill_chunk, budget)   # known tokens only
+                if n >= 1 and self._fits(req, n, free):
+                    toks = req.token_slice(req.n_computed, req.n_computed + n)
+                    batch.append(Scheduled(req, toks, req.n_computed + n == req.n_known and not req.n_inflight))
                     budget -= n
 
         # 3. admit from the front of the waiting queue while a slot, budget and pages last
         slots = self.manager.n_slots - len(self.manager.requests)
         while self.waiting and budget >= 1 and slots > 0 and len(batch) < self.max_requests_per_step:
             req = self.waiting[0]
-            n = min(req.remaining, self.prefill_chunk, budget)
+            n = min(req.n_known - req.n_computed, self.prefill_chunk, budget)
             if not self._fits(req, n, free):
                 if not self.running and not batch:
                     # Nothing else holds pages: this request can never start.
@@ -189,22 +220,36 @@ class Scheduler:
             req.status = RUNNING
             self.running.append(req)
             slots -= 1
-            toks = req.tokens()[req.n_computed:req.n_computed + n]
-            batch.append(Scheduled(req, toks, req.n_computed + n == len(req.prompt) + len(req.output)))
+            toks = req.token_slice(req.n_computed, req.n_computed + n)
+            batch.append(Scheduled(req, toks, req.n_computed + n == req.n_known and not req.n_inflight))
             budget -= n
         return batch
 
-    def update(self, batch: Sequence[Scheduled], sampled: Dict[int, int]) -> List[Output]:
-        """Account for a step that ran: ``sampled`` maps request id -> chosen token for
-        the entries with ``sample``. Returns what happened, finished requests freed."""
-        outputs, self._finished_early = list(self._finished_early), []
+    def _ends_by_length(self, req: Request) -> bool:
+        """True when the tokens already sampled (read or not) complete the request."""
+        n_out = len(req.output) + req.n_inflight
+        return n_out >= req.params.max_new_tokens or len(req.prompt) + n_out >= self.max_positions
+
+    def on_launched(self, batch: Sequence[Scheduled]) -> None:
+        """The step is queued on the GPU: its tokens count as computed, its samples as in flight."""
         self.stats["steps"] += 1
         for s in batch:
-            req = s.request
-            req.n_computed += len(s.tokens)
+            s.request.n_computed += len(s.tokens)
             self.stats["tokens"] += len(s.tokens)
+            if s.sample:
+                s.request.n_inflight += 1
+
+    def on_result(self, batch: Sequence[Scheduled], sampled: Dict[int, int]) -> List[Output]:
+        """The step's tokens are on the host: ``sampled`` maps request id -> chosen token for
+        the entries with ``sample``. Returns what happened, finished requests freed."""
+        outputs, self._finished_early = list(self._finished_early), []
+        for s in batch:
+            req = s.request
             if not s.sample:
                 continue
+            req.n_inflight -= 1
+            if req.status == FINISHED:
+                continue          # it had ended at EOS one step earlier: this token is one too many
             token = int(sampled[req.request_id])
             req.output.append(token)
             reason = None
@@ -218,6 +263,11 @@ class Scheduler:
                 self._finish(req, reason)
             outputs.append(Output(req.request_id, token, reason is not None, reason))
         return outputs
+
+    def update(self, batch: Sequence[Scheduled], sampled: Dict[int, int]) -> List[Output]:
+        """``on_launched`` and ``on_result`` in one call, for a caller that reads every step's tokens at once."""
+        self.on_launched(batch)
+        return self.on_result(batch, sampled)
 
     def abort_all(self, reason: str = "error_step_failed") -> List[Output]:
         """A step failed: every running request ends and frees its pages

@@ -247,6 +247,14 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
         ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode", launches=2)
 
 
+def scatter_tokens(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor, src_idx: torch.Tensor) -> None:
+    """``dst[dst_idx[i]] = src[src_idx[i]]`` where ``dst_idx[i] >= 0`` (all int32, on the device)."""
+    for name, t in (("dst", dst), ("dst_idx", dst_idx), ("src", src), ("src_idx", src_idx)):
+        _need(t, name, torch.int32)
+    _check(_lib().llmrs_scatter_tokens(_ptr(dst), _ptr(dst_idx), _ptr(src), _ptr(src_idx), dst_idx.numel(),
+                                       _stream()), "scatter_tokens")
+
+
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Index of the first maximum of each row of float32 ``logits``."""
     _need(logits, "logits", torch.float32)

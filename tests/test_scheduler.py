@@ -172,3 +172,65 @@ def test_abort_frees_everything():
     outs = s.abort_all()
     assert sorted(o.request_id for o in outs) == [1, 2] and all(o.finished for o in outs)
     assert not m.requests and m.free_pages() == 16
+
+
+def run_async(m, s, token_of, max_steps=200):
+    """The engine's pipelined loop with a fake step function: a step's tokens are handed to
+    the scheduler only after the NEXT step has been scheduled and 'launched'."""
+    outs, flight, steps = [], None, 0
+    while s.has_work() or flight is not None:
+        batch = s.schedule()
+        for b in batch:
+            if b.request.request_id not in m.requests:
+                m.admit(b.request.request_id)
+            m.reserve(b.request.request_id, len(b.tokens))
+            m.commit(b.request.request_id, len(b.tokens))
+            if b.pending:
+                assert b.request.n_inflight == 1 and len(b.tokens) == 1
+        s.on_launched(batch)
+        m.check_invariants()
+        launched = (batch, {b.request.request_id: token_of(b.request) for b in batch if b.sample}) if batch else None
+        if flight is not None:
+            outs += s.on_result(*flight)
+        flight = launched
+        if launched is None and flight is None:
+            outs += s.on_result([], {})
+        steps += 1
+        assert steps < max_steps
+    return outs
+
+
+def test_pipelined_results_one_step_late():
+    m, s = make(n_pages=32)
+    s.add_request(req(1, 5, max_new=4))
+    s.add_request(req(2, 3, max_new=6))
+    outs = run_async(m, s, lambda r: 7)
+    by = {1: [o for o in outs if o.request_id == 1], 2: [o for o in outs if o.request_id == 2]}
+    assert [len(v) for v in by.values()] == [4, 6]           # exactly max_new_tokens each: no step wasted on length
+    assert by[1][-1].reason == by[2][-1].reason == "length"
+    assert s.stats["tokens"] == 5 + 3 + 3 + 5                 # prompts + one decode token per generated token but the last
+    assert not m.requests and m.free_pages() == 32
+
+
+def test_pipelined_eos_drops_the_token_that_was_one_too_many():
+    m, s = make(n_pages=32)
+    s.add_request(req(1, 4, max_new=20))
+    n = {"calls": 0}
+
+    def token_of(r):
+        n["calls"] += 1
+        return 99 if n["calls"] == 3 else 7                   # the third sampled token is EOS
+    outs = run_async(m, s, token_of)
+    assert [(o.token, o.finished, o.reason) for o in outs] == [(7, False, None), (7, False, None), (99, True, "stop")]
+    assert n["calls"] == 4                                    # one more step had been queued before EOS was seen
+    assert not m.requests and m.free_pages() == 32
+
+
+def test_pipelined_preemption_keeps_every_token():
+    m, s = make(n_pages=4, page=4, budget=64, chunk=64, slots=3)
+    s.add_request(req(1, 7, max_new=6))
+    s.add_request(req(2, 7, max_new=6))
+    outs = run_async(m, s, lambda r: 7)
+    assert s.stats["preemptions"] >= 1
+    assert sorted(o.request_id for o in outs if o.token is not None) == [1] * 6 + [2] * 6
+    assert not m.requests and m.free_pages() == 4
