@@ -96,11 +96,23 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
                           (size_t)((t * DM_TILE) % page_size) * D;
       const bf16* vbase = kbase + (size_t)page_size * D;
       const int key0 = t * DM_TILE;
-      const bool whole = key0 >= k_begin && key0 + DM_TILE <= k_end;
+      if (key0 >= k_begin && key0 + DM_TILE <= k_end) {
+        // Whole tile inside the split: 16 rows of K are one contiguous run, so are the 16 rows of V.
+#pragma unroll
+        for (int j = 0; j < (DM_TILE * CH + 31) / 32; ++j) {
+          const int c = lane + 32 * j;
+          if ((DM_TILE * CH) % 32 == 0 || c < DM_TILE * CH) {
+            const int row = c / CH, ch = c - row * CH;
+            cp_async_16(Ks + row * ROW + ch * 8, kbase + c * 8, 16);
+            cp_async_16(Vs + row * ROW + ch * 8, vbase + c * 8, 16);
+          }
+        }
+        return;
+      }
 #pragma unroll 4
       for (int c = lane; c < DM_TILE * CH; c += 32) {
         const int row = c / CH, ch = c - row * CH;
-        const bool valid = whole || (key0 + row >= k_begin && key0 + row < k_end);
+        const bool valid = key0 + row >= k_begin && key0 + row < k_end;
         cp_async_16(Ks + row * ROW + ch * 8, valid ? kbase + c * 8 : cache, valid ? 16 : 0);
         cp_async_16(Vs + row * ROW + ch * 8, valid ? vbase + c * 8 : cache, valid ? 16 : 0);
       }
@@ -153,14 +165,16 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       mma_bf16_16816(s[0], qf[kc], b[0], b[1]);
       mma_bf16_16816(s[1], qf[kc], b[2], b[3]);
     }
-    // Mask, scale into the log2 domain, online softmax per row.
+    // Mask (only a tile on the split's edge has keys to hide), scale into the log2 domain,
+    // online softmax per row.
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool edge = key0 < k_begin || key0 + DM_TILE > k_end;
 #pragma unroll
     for (int n = 0; n < 2; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + n * 8 + tq * 2 + (e & 1);
-        const bool seen = key >= k_begin && key < k_end;
+        const bool seen = !edge || (key >= k_begin && key < k_end);
         s[n][e] = seen ? s[n][e] * sl2 : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
       }
@@ -191,9 +205,12 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     pf[1] = pack_bf16(s[0][2], s[0][3]);
     pf[2] = pack_bf16(s[1][0], s[1][1]);
     pf[3] = pack_bf16(s[1][2], s[1][3]);
+    // The running maximum seldom moves after the first tiles: rescale only when some row's did.
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int n = 0; n < 2 * DCH; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      for (int n = 0; n < 2 * DCH; ++n) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0]; o[n][2] *= corr[1]; o[n][3] *= corr[1];
+      }
     }
     // Weighted sum of values: B fragments are 8x8 blocks of V read transposed.
 #pragma unroll
