@@ -22,7 +22,8 @@ int llmrs_attn_prefill_mma(const void* q, long long q_stride, void* out, long lo
 int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
-                                int page_size, int window, float scale, cudaStream_t stream);
+                                int page_size, int window, float scale, void* out, long long out_stride,
+                                int* counters, cudaStream_t stream);
 
 // 1: bfloat16 also takes the generic kernels (tests compare the two implementations).
 static int g_generic_only = 0;
@@ -164,7 +165,7 @@ LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, l
   const size_t smem = (size_t)(PF_BQ * d + PF_BK * (d + 1) + PF_BK * d + PF_BQ * PF_BK) * sizeof(float);
   dim3 grid(n_tiles, n_q_heads, PF_TILE / PF_BQ);
   cudaError_t e;
-  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only)
+  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only && scale > 0.f)
     return llmrs_attn_prefill_mma(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new, cached_len,
                                   block_table, table_stride, n_q_heads, n_kv_heads, d, page_size, window, scale,
                                   stream);
@@ -384,7 +385,7 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part, T* __
   }
 }
 
-// Number of floats of scratch that llmrs_attn_decode needs.
+// Number of floats of scratch that llmrs_attn_decode needs (the splits' records).
 LLMRS_API long long llmrs_attn_decode_scratch_floats(int n_dec, int n_q_heads, int d, int max_splits) {
   return (long long)n_dec * n_q_heads * max_splits * (long long)dc_part_stride(d);
 }
@@ -423,12 +424,15 @@ static int launch_decode(const void* q, long long q_stride, void* out, long long
 
 // Decode attention for the requests listed in dec_reqs (one new token each, whose key
 // and value are already written). `max_splits` * `split_keys` must cover the longest
-// request; `scratch` holds llmrs_attn_decode_scratch_floats() floats.
+// request; `scratch` holds llmrs_attn_decode_scratch_floats() floats. `counters` is either
+// null (the splits are merged by a second kernel) or n_dec * n_q_heads ints that are zero
+// when the call starts: the tensor-core kernel then merges the splits itself, in the
+// block that finishes last, and leaves the counters at zero.
 LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                 const void* cache, const int* dec_reqs, int n_dec, const int* q_start,
                                 const int* cached_len, const int* block_table, int table_stride, float* scratch,
-                                int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
-                                int page_size, int window, float scale, int dtype, cudaStream_t stream) {
+                                int* counters, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
+                                int d, int page_size, int window, float scale, int dtype, cudaStream_t stream) {
   LLMRS_REQUIRE(n_dec >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && max_splits > 0 && split_keys > 0,
                 "attn_decode: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "attn_decode: %d query heads are no multiple of %d key heads",
@@ -439,16 +443,21 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
     return launch_decode<float, 4>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,
                                    block_table, table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads,
                                    d, page_size, window, scale, stream);
-  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only) {
-    int rc = llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
-                                         table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
-                                         page_size, window, scale, stream);
-    if (rc) return rc;
-    dim3 cgrid(n_dec, n_q_heads);
-    llmrs_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, true, (const float*)scratch,
-                 (__nv_bfloat16*)out, out_stride, dec_reqs, q_start, cached_len, max_splits, split_keys, n_q_heads, d,
-                 window);
-    return llmrs_launch_status("attn_decode_combine");
+  if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only && scale > 0.f) {
+    if (counters == nullptr) {
+      int rc = llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
+                                           table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
+                                           page_size, window, scale, out, out_stride, nullptr, stream);
+      if (rc) return rc;
+      dim3 cgrid(n_dec, n_q_heads);
+      llmrs_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, true,
+                   (const float*)scratch, (__nv_bfloat16*)out, out_stride, dec_reqs, q_start, cached_len, max_splits,
+                   split_keys, n_q_heads, d, window);
+      return llmrs_launch_status("attn_decode_combine");
+    }
+    return llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
+                                       table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
+                                       page_size, window, scale, out, out_stride, counters, stream);
   }
   if (dtype == LLMRS_BF16)
     return launch_decode<__nv_bfloat16, 8>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,

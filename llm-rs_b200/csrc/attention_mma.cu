@@ -19,6 +19,14 @@ typedef __nv_bfloat16 bf16;
 
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x on the special-function unit (2 ulp; 2^-inf = 0). The softmax works in the log2 domain:
+// exp(s * scale - m) = 2^(s * scale * log2(e) - m'), one FMA and one ex2 per score.
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---------------------------------------------------------------------------------
 // Decode
 // ---------------------------------------------------------------------------------
@@ -30,7 +38,8 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
                              const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
                              const int* __restrict__ cached_len, const int* __restrict__ block_table,
                              int table_stride, float* __restrict__ part, int max_splits, int split_keys,
-                             int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
+                             int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                             bf16* __restrict__ out, long long out_stride, int* __restrict__ counters) {
   constexpr int D = 16 * DCH;
   constexpr int ROW = D + 8;               // 16 bytes of padding: ldmatrix rows fall into distinct banks
   constexpr int CH = D / 8;                // 16-byte chunks per row
@@ -175,7 +184,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + n * 8 + tq * 2 + (e & 1);
         const bool seen = !edge || (key >= k_begin && key < k_end);
-        s[n][e] = seen ? s[n][e] * sl2 : -INFINITY;
+        s[n][e] = seen ? s[n][e] : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
       }
     uint32_t pf[4];
@@ -184,16 +193,16 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m_row[r], mx[r]);
+      const float m_new = fmaxf(m_row[r], mx[r] * sl2);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      corr[r] = exp2f(m_row[r] - m_use);
+      corr[r] = ex2(m_row[r] - m_use);
       m_row[r] = m_new;
       float sum = 0.f;
 #pragma unroll
       for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float p = exp2f(s[n][r * 2 + e] - m_use);
+          const float p = ex2(fmaf(s[n][r * 2 + e], sl2, -m_use));
           s[n][r * 2 + e] = p;
           sum += p;
         }
@@ -251,15 +260,48 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
 #pragma unroll
     for (int w = 0; w < DM_WARPS; ++w) {
       const float mw = Mm[w * 16 + g];
-      const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+      const float f = mw == -INFINITY ? 0.f : ex2(mw - M);
       L += Lm[w * 16 + g] * f;
       acc += Om[((size_t)w * 16 + g) * D + e] * f;
     }
     const int head = kvh * G + g0 + g;
     float* pp = part + ((size_t)((size_t)di * n_q_heads + head) * max_splits + split) * (D + 2);
     pp[2 + e] = acc;
-    // The combine kernel works with natural logarithms: hand it the maximum in that domain.
+    // The combine step works with natural logarithms: hand it the maximum in that domain.
     if (e == 0) { pp[0] = M / LOG2E; pp[1] = L; }
+  }
+  if (counters == nullptr) return;   // a separate kernel merges the splits
+
+  // The block that finishes last for its (request, head group) merges the splits itself:
+  // a counter per group is raised by every block after its records are visible, and put
+  // back to zero by the one that sees the full count.
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  const int s_first = kv_lo / split_keys, s_last = (kv_len - 1) / split_keys;
+  if (threadIdx.x == 0) {
+    int* c = counters + (size_t)di * gridDim.y + blockIdx.y;
+    const int seen = atomicAdd(c, 1);
+    is_last = seen == s_last - s_first;
+    if (is_last) *c = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < ng * D; i += DM_THREADS) {
+    const int g = i / D, e = i - g * D;
+    const int head = kvh * G + g0 + g;
+    const float* base = part + ((size_t)((size_t)di * n_q_heads + head) * max_splits) * (D + 2);
+    float m = -INFINITY;
+    for (int sp = s_first; sp <= s_last; ++sp) m = fmaxf(m, __ldcg(base + (size_t)sp * (D + 2)));
+    float l = 0.f, a = 0.f;
+    for (int sp = s_first; sp <= s_last; ++sp) {
+      const float* pp = base + (size_t)sp * (D + 2);
+      const float f = expf(__ldcg(pp) - m);
+      l += __ldcg(pp + 1) * f;
+      a += __ldcg(pp + 2 + e) * f;
+    }
+    out[(size_t)q_start[req] * out_stride + (size_t)head * D + e] = __float2bfloat16_rn(a / l);
   }
 }
 
@@ -267,7 +309,8 @@ template <int DCH>
 static int launch_decode_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                              const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                              float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
-                             int page_size, int window, float scale, cudaStream_t stream) {
+                             int page_size, int window, float scale, void* out, long long out_stride, int* counters,
+                             cudaStream_t stream) {
   constexpr int D = 16 * DCH;
   const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
   const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16) * sizeof(float);
@@ -283,20 +326,24 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
   llmrs_launch(attn_decode_split_mma_kernel<DCH>, grid, dim3(DM_THREADS), smem, stream, true,
       (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,
-      max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale);
+      max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out, out_stride, counters);
   return llmrs_launch_status("attn_decode_split_mma");
 }
 
 // The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).
-// Writes the same per-split records as the generic split kernel.
+// Writes the same per-split records as the generic split kernel. With `counters` (zeroed ints, one per
+// request and head group; the kernel leaves them zero) the last block of each group also merges the
+// splits into `out`; with counters == nullptr the caller runs the combine kernel.
 int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
-                                int page_size, int window, float scale, cudaStream_t stream) {
+                                int page_size, int window, float scale, void* out, long long out_stride,
+                                int* counters, cudaStream_t stream) {
 #define LLMRS_DM_CASE(N)                                                                                          \
   case N:                                                                                                          \
     return launch_decode_mma<N>(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table, table_stride, \
-                                scratch, max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, stream)
+                                scratch, max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, out, \
+                                out_stride, counters, stream)
   switch (d / 16) {
     LLMRS_DM_CASE(1); LLMRS_DM_CASE(2); LLMRS_DM_CASE(3); LLMRS_DM_CASE(4);
     LLMRS_DM_CASE(5); LLMRS_DM_CASE(6); LLMRS_DM_CASE(7); LLMRS_DM_CASE(8);
@@ -311,7 +358,7 @@ int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* c
 constexpr int PM_BQ = 64, PM_BK = 64, PM_WARPS = 4, PM_THREADS = PM_WARPS * 32;
 
 template <int DCH>
-__global__ void __launch_bounds__(PM_THREADS)
+__global__ void __launch_bounds__(PM_THREADS, 3)
 attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         const bf16* __restrict__ cache, const int* __restrict__ tiles,
                         const int* __restrict__ q_start, const int* __restrict__ n_new,
@@ -321,8 +368,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   constexpr int ROW = D + 8;
   constexpr int CH = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  bf16* Qs = reinterpret_cast<bf16*>(smem_raw);     // [64][ROW]
-  bf16* KV = Qs + PM_BQ * ROW;                      // 2 stages x (K [64][ROW], V [64][ROW])
+  bf16* KV = reinterpret_cast<bf16*>(smem_raw);     // 2 stages x (K [64][ROW], V [64][ROW])
 
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (n_q_heads / n_kv_heads);
@@ -338,12 +384,6 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gq = lane >> 2, tq = lane & 3;
 
-  for (int c = threadIdx.x; c < PM_BQ * CH; c += PM_THREADS) {
-    const int row = c / CH, ch = c - row * CH;
-    const bool valid = row < rows;
-    const bf16* src = valid ? q + (size_t)(tok0 + row) * q_stride + (size_t)head * D + ch * 8 : q;
-    cp_async_16(Qs + row * ROW + ch * 8, src, valid ? 16 : 0);
-  }
   auto load_kv = [&](int kb, int stage) {
     bf16* Ks = KV + (size_t)stage * 2 * PM_BK * ROW;
     bf16* Vs = Ks + PM_BK * ROW;
@@ -365,12 +405,20 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   cp_async_wait<0>();
   __syncthreads();
 
+  // Query rows of this warp as A fragments, straight from global memory (read once).
   uint32_t qf[DCH][4];
   {
-    const int j = lane >> 3;  // matrix j: rows (j%2)*8.., columns kc*16 + (j/2)*8..
+    const int r0 = warp * 16 + gq, r1 = r0 + 8;
+    const bf16* q0 = q + (size_t)(tok0 + r0) * q_stride + (size_t)head * D;
+    const bf16* q1 = q + (size_t)(tok0 + r1) * q_stride + (size_t)head * D;
 #pragma unroll
-    for (int kc = 0; kc < DCH; ++kc)
-      ldmatrix_x4(qf[kc], Qs + (warp * 16 + (j & 1) * 8 + (lane & 7)) * ROW + kc * 16 + (j >> 1) * 8);
+    for (int kc = 0; kc < DCH; ++kc) {
+      const int col = kc * 16 + tq * 2;
+      qf[kc][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+      qf[kc][1] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+      qf[kc][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+      qf[kc][3] = r1 < rows ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+    }
   }
   float o[2 * DCH][4];
 #pragma unroll
@@ -403,32 +451,42 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
           mma_bf16_16816(s[2 * np + 1], qf[kc], b[2], b[3]);
         }
       }
+      // Only a tile that touches the diagonal (or the window's far edge) has scores to hide.
+      const int pw = pos0 + warp * 16;
+      const bool need_mask = kb + PM_BK - 1 > pw || (window > 0 && kb <= pw + 15 - window);
       float mx[2] = {-INFINITY, -INFINITY};
+      if (need_mask) {
 #pragma unroll
-      for (int n = 0; n < PM_BK / 8; ++n)
+        for (int n = 0; n < PM_BK / 8; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kb + n * 8 + tq * 2 + (e & 1);
-          const int p = pos_r[e >> 1];
-          const bool seen = key <= p && (window <= 0 || key > p - window);
-          s[n][e] = seen ? s[n][e] * sl2 : -INFINITY;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
-        }
+          for (int e = 0; e < 4; ++e) {
+            const int key = kb + n * 8 + tq * 2 + (e & 1);
+            const int p = pos_r[e >> 1];
+            const bool seen = key <= p && (window <= 0 || key > p - window);
+            s[n][e] = seen ? s[n][e] : -INFINITY;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < PM_BK / 8; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+      }
       float corr[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m_row[r], mx[r]);
+        const float m_new = fmaxf(m_row[r], mx[r] * sl2);
         const float m_use = m_new == -INFINITY ? 0.f : m_new;
-        corr[r] = exp2f(m_row[r] - m_use);
+        corr[r] = ex2(m_row[r] - m_use);
         m_row[r] = m_new;
         float sum = 0.f;
 #pragma unroll
         for (int n = 0; n < PM_BK / 8; ++n)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const float p = exp2f(s[n][r * 2 + e] - m_use);
+            const float p = ex2(fmaf(s[n][r * 2 + e], sl2, -m_use));
             s[n][r * 2 + e] = p;
             sum += p;
           }
@@ -482,7 +540,7 @@ static int launch_prefill_mma(const void* q, long long q_stride, void* out, long
                               const int* cached_len, const int* block_table, int table_stride, int n_q_heads,
                               int n_kv_heads, int page_size, int window, float scale, cudaStream_t stream) {
   constexpr int D = 16 * DCH;
-  const size_t smem = (size_t)(PM_BQ + 4 * PM_BK) * (D + 8) * sizeof(bf16);
+  const size_t smem = (size_t)(4 * PM_BK) * (D + 8) * sizeof(bf16);
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,

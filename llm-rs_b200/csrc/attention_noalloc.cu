@@ -12,8 +12,8 @@
 extern "C" int llmrs_attn_decode(const void* q, long long q_stride, void* out, long long out_stride,
                                  const void* cache, const int* dec_reqs, int n_dec, const int* q_start,
                                  const int* cached_len, const int* block_table, int table_stride, float* scratch,
-                                 int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
-                                 int page_size, int window, float scale, int dtype, cudaStream_t stream);
+                                 int* counters, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
+                                 int d, int page_size, int window, float scale, int dtype, cudaStream_t stream);
 extern "C" long long llmrs_attn_decode_scratch_floats(int n_dec, int n_q_heads, int d, int max_splits);
 
 // 8 MiB per GPU, held from library load to process exit. In host code this name is only
@@ -61,6 +61,6 @@ LLMRS_API int llmrs_attn_decode_static_scratch(const void* q, long long q_stride
   const int rc = static_scratch_address(&scratch);
   if (rc) return rc;
   return llmrs_attn_decode(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
-                           table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d, page_size, window,
-                           scale, dtype, stream);
+                           table_stride, scratch, /*counters=*/nullptr, max_splits, split_keys, n_q_heads, n_kv_heads, d,
+                           page_size, window, scale, dtype, stream);
 }

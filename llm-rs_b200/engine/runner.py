@@ -124,7 +124,8 @@ class ModelRunner:
     def _scratch(self, bufs: Dict[str, torch.Tensor], name: str, n_floats: int) -> torch.Tensor:
         buf = bufs.get(name)
         if buf is None or buf.numel() < n_floats:
-            buf = torch.empty((max(n_floats, 1),), dtype=torch.float32, device=self.device)
+            # Zeroed: kernels that keep arrival counters in their workspace expect them at zero.
+            buf = torch.zeros((max(n_floats, 1),), dtype=torch.float32, device=self.device)
             bufs[name] = buf
         return buf
 

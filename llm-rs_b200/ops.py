@@ -227,9 +227,12 @@ def _lib_ll(name: str):
 def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_reqs: torch.Tensor, n_dec: int,
                 q_start: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor, scratch: torch.Tensor,
                 max_splits: int, split_keys: int, n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
-                window: int, scale: float) -> None:
+                window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
     """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
-    the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace."""
+    the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace of
+    ``attn_decode_scratch_floats`` elements. With ``counters`` (int32, at least n_dec * n_q_heads,
+    all zero; the call leaves them zero) the tensor-core kernel merges the splits itself instead
+    of a second kernel doing it."""
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -240,11 +243,15 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
     need = attn_decode_scratch_floats(n_dec, n_q_heads, head_dim, max_splits)
     if scratch.numel() < need:
         raise KernelError(f"attn_decode scratch holds {scratch.numel()} floats, {need} needed")
+    if counters is not None:
+        _need(counters, "counters", torch.int32)
+        if counters.numel() < n_dec * n_q_heads:
+            raise KernelError(f"attn_decode counters hold {counters.numel()} ints, {n_dec * n_q_heads} needed")
     _check(_lib().llmrs_attn_decode(
         _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
         _ptr(cache), _ptr(dec_reqs), n_dec, _ptr(q_start), _ptr(cached_len), _ptr(block_table), block_table.size(1),
-        _ptr(scratch), max_splits, split_keys, n_q_heads, n_kv_heads, head_dim, page_size, window,
-        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode", launches=2)
+        _ptr(scratch), _ptr(counters), max_splits, split_keys, n_q_heads, n_kv_heads, head_dim, page_size, window,
+        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode", launches=1 if counters is not None else 2)
 
 
 def scatter_tokens(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor, src_idx: torch.Tensor) -> None:

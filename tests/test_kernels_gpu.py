@@ -185,7 +185,7 @@ def _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, s
     return torch.cat(outs)
 
 
-def _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale, split_keys=64):
+def _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale, split_keys=64, fused_merge=True):
     ops = _ops()
     T = sum(new)
     dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
@@ -200,9 +200,13 @@ def _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale, 
         ops.attn_prefill(dq, out, dc, tt, len(tiles), q_start, n_new, cached, dt, nq, nkv, d, page, window, scale)
     if dec:
         max_splits = -(-max(lens[r] + 1 for r in dec) // split_keys)
+        # Records start as NaN: every one that is read must have been written.
         scratch = torch.full((ops.attn_decode_scratch_floats(len(dec), nq, d, max_splits),), float("nan"), device=DEV)
+        counters = torch.zeros(len(dec) * nq, dtype=torch.int32, device=DEV) if fused_merge else None
         ops.attn_decode(dq, out, dc, torch.tensor(dec, dtype=torch.int32, device=DEV), len(dec), q_start, cached, dt,
-                        scratch, max_splits, split_keys, nq, nkv, d, page, window, scale)
+                        scratch, max_splits, split_keys, nq, nkv, d, page, window, scale, counters=counters)
+        if counters is not None:
+            assert int(counters.abs().sum()) == 0, "the kernel must leave its counters at zero"
     torch.cuda.synchronize()
     return out.double().cpu()
 
@@ -212,13 +216,13 @@ SHAPES = [  # nq, nkv, d, page
     (2, 1, 160, 16), (4, 2, 256, 16)]
 
 
-@pytest.mark.parametrize("impl", ["auto", "generic"])
+@pytest.mark.parametrize("impl", ["auto", "generic", "auto-two-kernels"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [0, 37])
 @pytest.mark.parametrize("nq,nkv,d,page", SHAPES)
 def test_attention_prefill_and_decode(nq, nkv, d, page, window, dtype, impl):
     """A mixed step: long portions, a two-token portion, single decode tokens, with and without earlier context."""
-    if impl == "generic" and dtype == torch.float32:
+    if impl != "auto" and dtype == torch.float32:
         pytest.skip("float32 always takes the generic kernels")
     ops = _ops()
     lens = [0, 70, 129, 300, 3, 0, 64]
@@ -230,7 +234,8 @@ def test_attention_prefill_and_decode(nq, nkv, d, page, window, dtype, impl):
     want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, scale)
     ops.attention_generic_only(impl == "generic")
     try:
-        got = _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale)
+        got = _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale,
+                             fused_merge=impl != "auto-two-kernels")
     finally:
         ops.attention_generic_only(False)
     tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=2.5e-2, rtol=2e-2)
