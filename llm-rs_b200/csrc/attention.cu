@@ -25,6 +25,13 @@ int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* c
                                 int page_size, int window, float scale, void* out, long long out_stride,
                                 int* counters, cudaStream_t stream);
 
+bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const void* cache, int d, int page_size,
+                                     float scale);
+int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
+                          const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
+                          const int* n_new, const int* cached_len, const int* block_table, int table_stride,
+                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale, cudaStream_t stream);
+
 // 1: bfloat16 also takes the generic kernels (tests compare the two implementations).
 static int g_generic_only = 0;
 LLMRS_API void llmrs_attention_generic_only(int on) { g_generic_only = on; }
@@ -151,11 +158,15 @@ attn_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__
   }
 }
 
+// `n_tokens` rows of q and out; `n_pages` pages in `cache`. `prefer_tc` = 1 asks for the tcgen05
+// kernel (128-query blocks; worth it when the portions are long) where it applies: bfloat16,
+// head_dim 128, pages of a multiple of 16 keys.
 LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, long long out_stride,
                                  const void* cache, const int* tiles, int n_tiles, const int* q_start,
                                  const int* n_new, const int* cached_len, const int* block_table,
                                  int table_stride, int n_q_heads, int n_kv_heads, int d, int page_size,
-                                 int window, float scale, int dtype, cudaStream_t stream) {
+                                 int window, float scale, int dtype, int n_tokens, int n_pages, int prefer_tc,
+                                 cudaStream_t stream) {
   LLMRS_REQUIRE(n_tiles >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0, "attn_prefill: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "attn_prefill: %d query heads are no multiple of %d key heads",
                 n_q_heads, n_kv_heads);
@@ -165,6 +176,12 @@ LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, l
   const size_t smem = (size_t)(PF_BQ * d + PF_BK * (d + 1) + PF_BK * d + PF_BQ * PF_BK) * sizeof(float);
   dim3 grid(n_tiles, n_q_heads, PF_TILE / PF_BQ);
   cudaError_t e;
+  if (dtype == LLMRS_BF16 && prefer_tc && !g_generic_only &&
+      llmrs_attn_prefill_tc_supported(q, q_stride, cache, d, page_size, scale))
+    return llmrs_attn_prefill_tc(q, q_stride, n_tokens, out, out_stride, cache,
+                                 (long long)n_pages * n_kv_heads * 2 * page_size, tiles, n_tiles, q_start, n_new,
+                                 cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size, window, scale,
+                                 stream);
   if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only && scale > 0.f)
     return llmrs_attn_prefill_mma(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new, cached_len,
                                   block_table, table_stride, n_q_heads, n_kv_heads, d, page_size, window, scale,

@@ -1,0 +1,513 @@
+// Prefill attention on tcgen05 for head_dim 128, bfloat16, pages of a multiple of 16 keys.
+//
+// A block owns 128 query tokens of one request and one query head; its thread r owns
+// query row r, which is lane r of tensor memory, so the softmax needs no exchange
+// between threads. Per tile of 64 keys:
+//   S = Q K^T   tcgen05.mma, 128x64x128, Q and K in shared memory (TMA, 128-byte swizzle),
+//               S in tensor memory (64 columns of float32);
+//   softmax     every thread reads its row of S (tcgen05.ld), masks it if the tile touches
+//               the diagonal or the window's edge, and writes P = 2^(s*c - m) as bfloat16
+//               into shared memory in the layout the MMA expects. The reference maximum m
+//               of a row only moves when the row's maximum grew by more than 8 (a factor
+//               256): then, and only then, the row of O in tensor memory is rescaled
+//               (tcgen05.ld, multiply, tcgen05.st);
+//   O += P V    tcgen05.mma, 128x128x64; V is used as it lies in its pages (keys x head_dim,
+//               MN-major operand).
+// A fifth warp issues the TMA copies (one 16-key box per page and half of the head) and the
+// MMAs, so the softmax threads never wait for issue work. K, V and S are double-buffered:
+// while the threads work on the softmax of tile j the tensor cores already compute S of
+// tile j+1, and the copies of tiles j+1 / j+2 are under way. The roles meet at mbarriers
+// only. Two blocks share an SM. Blocks with the longest rows of keys are scheduled first.
+//
+// Same contract and math as attn_prefill_kernel in attention.cu (scores, softmax and the
+// weighted sum accumulate in float32; llm-core/src/backends/candle.rs:1587-1640). Every
+// wait is bounded; a block that gives up sets the error flag, waits for its copies and
+// frees its tensor memory.
+#include <cuda.h>
+#include <mutex>
+
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+namespace {
+
+constexpr int AT_BQ = 128, AT_BK = 64, AT_D = 128, AT_THREADS = 128;
+constexpr uint32_t AT_WAIT_LIMIT = 1u << 22;
+constexpr float AT_LOG2E = 1.4426950408889634f;
+constexpr uint32_t Q_BYTES = AT_BQ * AT_D * 2, K_BYTES = AT_BK * AT_D * 2, V_BYTES = K_BYTES, P_BYTES = AT_BQ * AT_BK * 2;
+constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;   // S twice (64 columns each), then O
+
+__device__ int g_attn_tc_error = 0;
+
+__device__ __forceinline__ uint32_t sm(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar) { asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar)); }
+__device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < AT_WAIT_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (it > 128) {
+      __nanosleep(32);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle. K-major operands: lbo unused (1),
+// sbo = 1024 (8 rows of 128 bytes). MN-major operands: lbo = distance between blocks of 64
+// elements along MN, sbo = distance between groups of 8 rows along K.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// bf16 x bf16 -> f32, M = 128, N = n; b_mn: the B operand is MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void mma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive float32 columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void bar_init_n(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. Lane 0 of warp 4
+// feeds them: it issues every TMA copy and every MMA. Nobody meets
+// at a block-wide barrier inside the loop; the roles talk through mbarriers:
+//   q, k[2], v[2]  bytes of the TMA copies have landed
+//   s[2]           S of a tile is in tensor memory (tcgen05.commit)
+//   pv             O += P V of a tile is done (tcgen05.commit): P, O and that V buffer are free
+//   p              all 128 softmax threads have written P of a tile (and are done with its S)
+__global__ void __launch_bounds__(AT_THREADS + 32)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                       bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
+                       const int* __restrict__ q_start, const int* __restrict__ n_new,
+                       const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
+                       int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
+  unsigned char* Qs = base;                 // 2 halves of [128 rows][64 dims]
+  unsigned char* Ks = Qs + Q_BYTES;         // 2 stages x 2 halves of [64 keys][64 dims]
+  unsigned char* Vs = Ks + 2 * K_BYTES;     // 2 stages x 2 halves of [64 keys][64 dims]
+  unsigned char* Ps = Vs + 2 * V_BYTES;     // [128 rows][64 keys]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);   // q, k0, k1, v0, v1, s0, s1, pv, p, vfree0, vfree1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // Pages of the coming tiles, read from the block table three tiles ahead by four softmax
+  // threads (the issuing thread never waits for global memory): tile t's four pages sit in
+  // ring slot t % 4 (-1: no copy). The issuing thread sees them through barrier p.
+  volatile int* page_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Later tiles of a prompt see more keys: run them first so that the long blocks do not end the kernel alone.
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
+  if (q_off % AT_BQ != 0) return;           // the list names tiles of 64 queries; a block takes two
+  if ((sm(base) & 1023u) != 0) {            // never seen; without the alignment the operands would be garbage
+    if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 2);
+    return;
+  }
+  const int kvh = head / (n_q_heads / n_kv_heads);
+  const int rows = min(AT_BQ, n_new[req] - q_off);
+  const int tok0 = q_start[req] + q_off;
+  const int pos0 = cached_len[req] + q_off;
+  const int kv_hi = pos0 + rows;
+  const int key_floor = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kv_lo = (key_floor / AT_BK) * AT_BK;
+  const int n_tiles = (kv_hi - kv_lo + AT_BK - 1) / AT_BK;
+  const int* table = block_table + (size_t)req * table_stride;
+
+  const uint32_t bar_q = sm(bars), bar_k = sm(bars + 1), bar_v = sm(bars + 3), bar_s = sm(bars + 5), bar_pv = sm(bars + 7),
+                 bar_p = sm(bars + 8), bar_vfree = sm(bars + 9);
+  if (tid == 0) {
+    for (int i = 0; i < 8; ++i) bar_init(sm(bars + i));
+    bar_init_n(bar_p, AT_THREADS);
+    bar_init(bar_vfree);
+    bar_init(bar_vfree + 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  auto fetch_pages = [&](int t, int i) {     // page of keys kv_lo + 64 t + 16 i .. + 15, or -1
+    const int key = kv_lo + t * AT_BK + 16 * i;
+    page_ring[(t & 3) * 4 + i] = (t < n_tiles && key < kv_hi && key + 15 >= key_floor) ? table[key / page_size] : -1;
+  };
+  if (tid < 12) fetch_pages(tid >> 2, tid & 3);
+  // Rows of K and V that no copy fills (keys past the end) must not hold NaN patterns.
+  for (uint32_t i = tid * 16; i < 2 * K_BYTES + 2 * V_BYTES; i += (AT_THREADS + 32) * 16)
+    *reinterpret_cast<uint4*>(Ks + i) = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
+
+  // Copies of tile t: per page of 16 keys, two boxes (the halves of head_dim).
+  auto load_kv = [&](int which, int t, unsigned char* dst, uint32_t bar) {
+    int pages[AT_BK / 16];
+    uint32_t bytes = 0;
+#pragma unroll
+    for (int i = 0; i < AT_BK / 16; ++i) {
+      pages[i] = page_ring[(t & 3) * 4 + i];
+      if (pages[i] >= 0) bytes += 2 * 16 * 128;
+    }
+    bar_expect(bar, bytes);
+#pragma unroll
+    for (int i = 0; i < AT_BK / 16; ++i) {
+      if (pages[i] >= 0) {
+        const int key = kv_lo + t * AT_BK + 16 * i;
+        const int row = ((pages[i] * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
+        tma_2d(sm(dst) + i * 2048, &map_kv, bar, 0, row);
+        tma_2d(sm(dst) + 8192 + i * 2048, &map_kv, bar, 64, row);
+      }
+    }
+  };
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- K copies and every MMA --------------------------------------------------------
+      auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2
+        const uint32_t kbuf = sm(Ks) + (t & 1) * K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AT_D / 16; ++kk) {
+          const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
+          const uint64_t a = smem_desc(sm(Qs) + half * 16384 + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = smem_desc(kbuf + half * 8192 + (kk % 4) * 32, 16, 1024);
+          mma(tmem + S_COL + (t & 1) * AT_BK, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        commit(bar_s + 8 * (t & 1));
+      };
+      bar_expect(bar_q, Q_BYTES);
+      tma_2d(sm(Qs), &map_q, bar_q, head * AT_D, tok0);
+      tma_2d(sm(Qs) + 16384, &map_q, bar_q, head * AT_D + 64, tok0);
+      load_kv(0, 0, Ks, bar_k);
+      load_kv(1, 0, Vs, bar_v);
+      if (n_tiles > 1) {
+        load_kv(0, 1, Ks + K_BYTES, bar_k + 8);
+        load_kv(1, 1, Vs + V_BYTES, bar_v + 8);
+      }
+      bool ok = bar_wait(bar_q, 0, abort_flag) && bar_wait(bar_k, 0, abort_flag);
+      if (ok) {
+        fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        // S of the next tile: its K has landed, and the softmax threads are done with that S
+        // buffer (they said so with P of tile j-1, which was waited for before O += P V of j-1).
+        if (j + 1 < n_tiles) {
+          ok = bar_wait(bar_k + 8 * (b ^ 1), ((j + 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          fence_after();
+          issue_s(j + 1);
+          // V of the next tile into the buffer that O += P V of tile j-1 has released.
+          if (j >= 1) {
+            ok = bar_wait(bar_vfree + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag);
+            if (!ok) break;
+            load_kv(1, j + 1, Vs + (b ^ 1) * V_BYTES, bar_v + 8 * (b ^ 1));
+          }
+        }
+        // K buffer b is free once S_j is done.
+        if (j + 2 < n_tiles) {
+          ok = bar_wait(bar_s + 8 * b, (j >> 1) & 1, abort_flag);
+          if (!ok) break;
+          load_kv(0, j + 2, Ks + b * K_BYTES, bar_k + 8 * b);
+        }
+        // O += P V of tile j: P is written, V has landed.
+        ok = bar_wait(bar_p, j & 1, abort_flag) && bar_wait(bar_v + 8 * b, (j >> 1) & 1, abort_flag);
+        if (!ok) break;
+        fence_after();
+        const uint32_t vbuf = sm(Vs) + b * V_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < AT_BK / 16; ++kk) {
+          const uint64_t a = smem_desc(sm(Ps) + kk * 32, 16, 1024);
+          const uint64_t bd = smem_desc(vbuf + kk * 2048, 8192, 1024);
+          mma(tmem + O_COL, a, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        commit(bar_pv);
+        commit(bar_vfree + 8 * b);    // the same completion, counted per V buffer (its phases cannot run ahead of the loader)
+      }
+    }
+  } else {
+    // ---- softmax threads ------------------------------------------------------------------
+    const int row = tid;                      // this thread's query row = its lane of tensor memory
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int my_pos = pos0 + row;
+    const float sl2 = scale * AT_LOG2E;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int kb = kv_lo + j * AT_BK;
+      const int b = j & 1;
+      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * b, (j >> 1) & 1, abort_flag));
+      if (!ok) break;
+      fence_after();
+      if (tid >= 32 && tid < 36) fetch_pages(j + 3, tid - 32);   // published by this tile's arrival on barrier p
+      // This thread's 64 scores -> probabilities (kept in registers until the P buffer is free).
+      float s[AT_BK];
+      {
+        float t0[32], t1[32];
+        tmem_ld32(lane_addr + S_COL + b * AT_BK, t0);
+        tmem_ld32(lane_addr + S_COL + b * AT_BK + 32, t1);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) { s[c] = t0[c]; s[32 + c] = t1[c]; }
+      }
+      const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < AT_BK; ++c) {
+          const int key = kb + c;
+          const bool seen = key <= my_pos && (window <= 0 || key > my_pos - window);
+          s[c] = seen ? s[c] : -INFINITY;
+        }
+      }
+      // Four running maxima (and sums below): a chain of 64 dependent operations would be the
+      // longest thing this thread does.
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < AT_BK; c += 4) {
+        mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+        mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // The reference maximum moves only when the row's maximum outgrew it by a factor 256.
+      const float m_tile = mx * sl2;
+      float factor = 1.f;
+      bool moved = false;
+      if (m_tile > m_ref + 8.f) {   // also the first tile with a visible key (m_ref = -inf)
+        factor = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_tile);
+        m_ref = m_tile;
+        moved = j > 0;
+        l_sum *= factor;
+      }
+      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+      uint4 pk[AT_BK / 8];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < AT_BK / 8; ++ch) {
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[ch]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = ex2(fmaf(s[ch * 8 + 2 * e], sl2, -m_use));
+          const float p1 = ex2(fmaf(s[ch * 8 + 2 * e + 1], sl2, -m_use));
+          sum4[e] += p0 + p1;
+          h2[e] = __floats2bfloat162_rn(p0, p1);
+        }
+      }
+      l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // O += P V of the previous tile is done: its P and O are free.
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, bar_wait(bar_pv, (j - 1) & 1, abort_flag));
+        if (!ok) break;
+        fence_after();
+      }
+      // Rescale O where a row's reference moved (rare after the first tiles; the loads and stores
+      // of tensor memory are warp-wide, so the warp decides together), then hand P over: row r is
+      // 128 bytes, its 16-byte chunk c sits at c ^ (r % 8).
+      if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll 1
+        for (int c = 0; c < AT_D; c += 32) {
+          float o[32];
+          tmem_ld32(lane_addr + O_COL + c, o);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] *= factor;
+          tmem_st32(lane_addr + O_COL + c, o);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      }
+#pragma unroll
+      for (int ch = 0; ch < AT_BK / 8; ++ch)
+        *reinterpret_cast<uint4*>(Ps + row * 128 + ((ch ^ (row & 7)) * 16)) = pk[ch];
+      fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P written by threads, read by the MMA
+      bar_arrive(bar_p);
+    }
+    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_pv, (n_tiles - 1) & 1, abort_flag));
+    fence_after();
+    if (ok) {
+      // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
+      const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+      bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * AT_D;
+#pragma unroll 1
+      for (int c = 0; c < AT_D; c += 32) {
+        float o[32];
+        tmem_ld32(lane_addr + O_COL + c, o);
+        if (row < rows) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) h2[q] = __floats2bfloat162_rn(o[e + 2 * q] * inv, o[e + 2 * q + 1] * inv);
+            *reinterpret_cast<uint4*>(orow + c + e) = pk;
+          }
+        }
+        __syncwarp();
+      }
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (*abort_flag && tid == AT_THREADS) {
+    atomicExch(&g_attn_tc_error, 1);
+    // Copies may still be on their way into this block's shared memory.
+    bar_wait(bar_q, 0, abort_flag);
+    for (int i = 0; i < 2; ++i)
+      for (int ph = 0; ph < 2; ++ph) { bar_wait(bar_k + 8 * i, ph, abort_flag); bar_wait(bar_v + 8 * i, ph, abort_flag); }
+  }
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  });
+  return fn;
+}
+
+int make_map(CUtensorMap* map, const void* basep, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return llmrs_fail("attn_prefill_tc: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(basep), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return llmrs_fail("attn_prefill_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+}  // namespace
+
+// 1 if a block of the tcgen05 prefill kernel gave up on a wait since the last call (clears the flag).
+LLMRS_API int llmrs_attention_tc_error() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_attn_tc_error, &zero, sizeof(int));
+  return v;
+}
+
+// True when llmrs_attn_prefill_tc can take this problem.
+bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const void* cache, int d, int page_size,
+                                     float scale) {
+  return d == AT_D && page_size % 16 == 0 && scale > 0.f && q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0 &&
+         ((uintptr_t)cache & 15) == 0 && encode_tiled() != nullptr;
+}
+
+// Prefill attention on tcgen05 (see the head of this file). `n_tokens` is the number of rows of q,
+// `cache_rows` = n_pages * n_kv_heads * 2 * page_size the number of head_dim-wide rows of the cache.
+int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
+                          const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
+                          const int* n_new, const int* cached_len, const int* block_table, int table_stride,
+                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                          cudaStream_t stream) {
+  CUtensorMap map_q, map_kv;
+  int rc;
+  if ((rc = make_map(&map_q, q, n_tokens, (long long)n_q_heads * AT_D, q_stride, AT_BQ))) return rc;
+  if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, 16))) return rc;
+  const size_t smem = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + 11 * 8 + 8 + 16 * 4;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_prefill_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid(n_tiles, n_q_heads);
+  attn_prefill_tc_kernel<<<grid, AT_THREADS + 32, smem, stream>>>(map_q, map_kv, (bf16*)out, out_stride, tiles, q_start,
+                                                              n_new, cached_len, block_table, table_stride, n_q_heads,
+                                                              n_kv_heads, page_size, window, scale);
+  return llmrs_launch_status("attn_prefill_tc");
+}

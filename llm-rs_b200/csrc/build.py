@@ -25,7 +25,7 @@ LIB_NAME = "libllmrs_b200.so"
 # Fast math stays off: norms, softmax and rotation are checked against float32 references.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _lib: Optional[ctypes.CDLL] = None
 

@@ -53,6 +53,7 @@ class StepContext:
         self.act_dtype = runner.act_dtype
         self.n_tokens = self.n_requests = self.n_want = 0
         self.n_prefill_tiles = self.n_decode = self.max_decode_kv_len = 0
+        self.long_portions = False
         self.token_ids = self.positions = self.token_req = None
         self.q_start = self.n_new = self.cached_len = self.slot_ids = None
         self.want_rows = self.prefill_tiles = self.decode_reqs = None
@@ -296,6 +297,9 @@ class ModelRunner:
         ctx.q_start, ctx.n_new, ctx.cached_len, ctx.slot_ids = view(3, R), view(4, R), view(5, R), view(6, R)
         ctx.want_rows = view(7, len(want_rows))
         ctx.n_prefill_tiles = len(tiles) // 2
+        # Blocks of 128 queries pay off when the portions fill them at least half on average.
+        blocks = sum(-(-int(n) // 128) for n in n_new if n > 1)
+        ctx.long_portions = blocks > 0 and sum(int(n) for n in n_new if n > 1) >= 64 * blocks
         ctx.prefill_tiles = view(8, len(tiles)).view(-1, 2) if tiles else view(8, 0)
         ctx.n_decode = len(dec)
         ctx.decode_reqs = view(9, len(dec))

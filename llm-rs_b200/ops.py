@@ -195,8 +195,10 @@ def qk_norm_rope_kvwrite(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional
 
 def attn_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles: torch.Tensor, n_tiles: int,
                  q_start: torch.Tensor, n_new: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor,
-                 n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float) -> None:
+                 n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                 prefer_tc: bool = False) -> None:
     """Causal attention of prompt portions over the paged cache (their own keys are already written).
+    ``prefer_tc`` asks for the tcgen05 kernel (blocks of 128 queries) where it applies.
 
     ``tiles`` is int32 [n_tiles, 2]: (request row, offset of the tile's first query in
     the request's new tokens); a tile covers 64 queries.
@@ -211,7 +213,7 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles:
         _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
         _ptr(cache), _ptr(tiles), n_tiles, _ptr(q_start), _ptr(n_new), _ptr(cached_len), _ptr(block_table),
         block_table.size(1), n_q_heads, n_kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
-        dtype_code(q.dtype), _stream()), "attn_prefill")
+        dtype_code(q.dtype), q.size(0), cache.size(0), 1 if prefer_tc else 0, _stream()), "attn_prefill")
 
 
 def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_splits: int) -> int:
@@ -383,3 +385,13 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """[2I, K]: 64 rows of gate, the 64 matching rows of up, and so on (I a multiple of 64)."""
     I, K = gate.shape
     return torch.stack([gate.reshape(I // 64, 64, K), up.reshape(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def check_attention_error() -> None:
+    """Raise if an attention kernel gave up on one of its bounded waits since the last check (synchronises)."""
+    lib = _lib()
+    for name in ("llmrs_attention_tc_error",):
+        fn = getattr(lib, name)
+        fn.restype = ctypes.c_int
+        if fn() > 0:
+            raise KernelError(f"an attention kernel gave up waiting on a barrier ({name}); its output is invalid")

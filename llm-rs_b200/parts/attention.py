@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -14,6 +15,8 @@ from .spec import CacheNeed, PartSpec, WeightSpec
 
 
 _SM_COUNT = {}
+# The tcgen05 prefill kernel for long portions (head_dim 128); LLMRS_ATTN_TC=0 keeps the mma.sync kernel.
+_ATTN_TC = os.environ.get("LLMRS_ATTN_TC", "1") != "0"
 
 
 def _sm_count(device) -> int:
@@ -125,7 +128,8 @@ class GQAttention(Mixer):
         out = torch.empty((ctx.n_tokens, self.q_width), dtype=q.dtype, device=q.device)
         if ctx.n_prefill_tiles:
             ops.attn_prefill(q, out, cache.kv, ctx.prefill_tiles, ctx.n_prefill_tiles, ctx.q_start, ctx.n_new,
-                             ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale)
+                             ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale,
+                             prefer_tc=ctx.long_portions and _ATTN_TC)
         if ctx.n_decode:
             split_keys = self.split_keys or self._choose_split(ctx.n_decode, ctx.max_decode_kv_len, q)
             max_splits = max(1, -(-ctx.max_decode_kv_len // split_keys))

@@ -458,3 +458,56 @@ def test_silu_mul_interleaved_layout(dtype):
     inter = torch.stack([gate.reshape(5, 4, 64), up.reshape(5, 4, 64)], 2).reshape(5, 512).contiguous()
     want = gate.double() * torch.sigmoid(gate.double()) * up.double()
     assert torch.allclose(ops.silu_mul(inter, block=64).double(), want, **_tol(dtype))
+
+
+# -- tcgen05 prefill attention (head_dim 128) ------------------------------------------------------
+@pytest.mark.parametrize("lens,new,nq,nkv,page,window", [
+    ([0], [128], 1, 1, 16, 0), ([0], [64], 2, 1, 16, 0), ([0], [300], 4, 2, 16, 0),
+    ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 16, 0), ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 32, 37),
+    ([1000], [1000], 4, 1, 16, 0), ([0, 500], [1100, 700], 8, 8, 16, 200), ([5], [257], 6, 3, 48, 129)])
+def test_attention_prefill_tcgen05(lens, new, nq, nkv, page, window):
+    """Blocks of 128 queries on tcgen05 against the plain attention: partial blocks, several requests,
+    earlier context, windows that start inside a tile, pages larger than a 16-key box."""
+    ops = _ops()
+    d = 128
+    torch.manual_seed(len(lens) * 31 + window)
+    table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=page + window)
+    q = torch.randn(sum(new), nq * d).to(torch.bfloat16)
+    scale = 1 / math.sqrt(d)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, window, scale)
+    dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+    q_start = torch.tensor(np.cumsum([0] + new[:-1]), dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([(r, off) for r, n in enumerate(new) for off in range(0, n, 64)], dtype=torch.int32, device=DEV)
+    out = torch.full((sum(new), nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.attn_prefill(dq, out, dc, tiles, tiles.size(0), q_start, torch.tensor(new, dtype=torch.int32, device=DEV),
+                     torch.tensor(lens, dtype=torch.int32, device=DEV), dt, nq, nkv, d, page, window, scale,
+                     prefer_tc=True)
+    torch.cuda.synchronize()
+    ops.check_attention_error()
+    got = out.double().cpu()
+    assert torch.isfinite(got).all(), "a row was not written"
+    assert float((got - want).abs().max()) < 2.5e-2
+
+
+def test_attention_prefill_tcgen05_far_key():
+    """One key 1,900 positions back carries the weight: the lazily rescaled maximum and the page boxes must find it."""
+    ops = _ops()
+    nq, nkv, d, page = 4, 2, 128, 16
+    lens, new = [1800], [200]
+    for far in (0, 63, 64, 1000, 1799, 1800, 1927):
+        torch.manual_seed(far)
+        table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=far)
+        cache = cache * 0.05
+        spike = torch.randn(nkv, d)
+        spike = spike / spike.norm(dim=-1, keepdim=True) * 6
+        cache[int(table[0, far // page]), :, 0, far % page] = spike.to(torch.bfloat16)
+        q = (torch.randn(sum(new), nq, d) * 0.05 + spike.repeat_interleave(2, 0)[None]).reshape(-1, nq * d).to(torch.bfloat16)
+        want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, 0, 1.0)
+        dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+        tiles = torch.tensor([(0, off) for off in range(0, 200, 64)], dtype=torch.int32, device=DEV)
+        out = torch.zeros(200, nq * d, dtype=torch.bfloat16, device=DEV)
+        z = torch.zeros(1, dtype=torch.int32, device=DEV)
+        ops.attn_prefill(dq, out, dc, tiles, 4, z, torch.tensor(new, dtype=torch.int32, device=DEV),
+                         torch.tensor(lens, dtype=torch.int32, device=DEV), dt, nq, nkv, d, page, 0, 1.0, prefer_tc=True)
+        torch.cuda.synchronize()
+        assert float((out.double().cpu() - want).abs().max()) < 2e-2, far
