@@ -144,8 +144,8 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. Lane 0 of warp 4
-// feeds them: it issues every TMA copy and every MMA. Nobody meets
+// Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. Warp 4 feeds
+// them: its lanes 0-7 issue the TMA copies of a tile side by side, its lane 0 every MMA. Nobody meets
 // at a block-wide barrier inside the loop; the roles talk through mbarriers:
 //   q, k[2], v[2]  bytes of the TMA copies have landed
 //   s[2]           S of a tile is in tensor memory (tcgen05.commit)
@@ -220,31 +220,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
 
-  // Copies of tile t: per page of 16 keys, two boxes (the halves of head_dim).
+  // Copies of tile t, issued by the whole issuing warp at once: per page of 16 keys two boxes
+  // (the halves of head_dim), one box per lane (lanes 0-7), so that eight copies cost the warp
+  // one instruction slot instead of eight in a row.
   auto load_kv = [&](int which, int t, unsigned char* dst, uint32_t bar) {
-    int pages[AT_BK / 16];
-    uint32_t bytes = 0;
-#pragma unroll
-    for (int i = 0; i < AT_BK / 16; ++i) {
-      pages[i] = page_ring[(t & 3) * 4 + i];
-      if (pages[i] >= 0) bytes += 2 * 16 * 128;
+    const int i = (lane >> 1) & 3, h = lane & 1;
+    const int page = page_ring[(t & 3) * 4 + i];
+    const unsigned live = __ballot_sync(0xffffffffu, lane < 8 && page >= 0);
+    if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * 16 * 128);
+    __syncwarp();
+    if (lane < 8 && page >= 0) {
+      const int key = kv_lo + t * AT_BK + 16 * i;
+      const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
+      tma_2d(sm(dst) + h * 8192 + i * 2048, &map_kv, bar, h * 64, row);
     }
-    bar_expect(bar, bytes);
-#pragma unroll
-    for (int i = 0; i < AT_BK / 16; ++i) {
-      if (pages[i] >= 0) {
-        const int key = kv_lo + t * AT_BK + 16 * i;
-        const int row = ((pages[i] * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
-        tma_2d(sm(dst) + i * 2048, &map_kv, bar, 0, row);
-        tma_2d(sm(dst) + 8192 + i * 2048, &map_kv, bar, 64, row);
-      }
-    }
+    __syncwarp();
   };
 
   if (warp == 4) {
-    if (lane == 0) {
-      // ---- K copies and every MMA --------------------------------------------------------
-      auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2
+    // ---- the issuing warp: all lanes walk the loop together; lane 0 issues the MMAs -----------
+    auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2
+      if (lane == 0) {
         const uint32_t kbuf = sm(Ks) + (t & 1) * K_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_D / 16; ++kk) {
@@ -254,47 +250,56 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mma(tmem + S_COL + (t & 1) * AT_BK, a, bd, idesc_s, kk > 0 ? 1u : 0u);
         }
         commit(bar_s + 8 * (t & 1));
-      };
+      }
+      __syncwarp();
+    };
+    auto wait_all = [&](uint32_t bar, uint32_t parity) {
+      return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
+    };
+    if (lane == 0) {
       bar_expect(bar_q, Q_BYTES);
       tma_2d(sm(Qs), &map_q, bar_q, head * AT_D, tok0);
       tma_2d(sm(Qs) + 16384, &map_q, bar_q, head * AT_D + 64, tok0);
-      load_kv(0, 0, Ks, bar_k);
-      load_kv(1, 0, Vs, bar_v);
-      if (n_tiles > 1) {
-        load_kv(0, 1, Ks + K_BYTES, bar_k + 8);
-        load_kv(1, 1, Vs + V_BYTES, bar_v + 8);
-      }
-      bool ok = bar_wait(bar_q, 0, abort_flag) && bar_wait(bar_k, 0, abort_flag);
-      if (ok) {
-        fence_after();
-        issue_s(0);
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1;
-        // S of the next tile: its K has landed, and the softmax threads are done with that S
-        // buffer (they said so with P of tile j-1, which was waited for before O += P V of j-1).
-        if (j + 1 < n_tiles) {
-          ok = bar_wait(bar_k + 8 * (b ^ 1), ((j + 1) >> 1) & 1, abort_flag);
-          if (!ok) break;
-          fence_after();
-          issue_s(j + 1);
-          // V of the next tile into the buffer that O += P V of tile j-1 has released.
-          if (j >= 1) {
-            ok = bar_wait(bar_vfree + 8 * (b ^ 1), ((j - 1) >> 1) & 1, abort_flag);
-            if (!ok) break;
-            load_kv(1, j + 1, Vs + (b ^ 1) * V_BYTES, bar_v + 8 * (b ^ 1));
-          }
-        }
-        // K buffer b is free once S_j is done.
-        if (j + 2 < n_tiles) {
-          ok = bar_wait(bar_s + 8 * b, (j >> 1) & 1, abort_flag);
-          if (!ok) break;
-          load_kv(0, j + 2, Ks + b * K_BYTES, bar_k + 8 * b);
-        }
-        // O += P V of tile j: P is written, V has landed.
-        ok = bar_wait(bar_p, j & 1, abort_flag) && bar_wait(bar_v + 8 * b, (j >> 1) & 1, abort_flag);
+    }
+    __syncwarp();
+    load_kv(0, 0, Ks, bar_k);
+    load_kv(1, 0, Vs, bar_v);
+    if (n_tiles > 1) {
+      load_kv(0, 1, Ks + K_BYTES, bar_k + 8);
+      load_kv(1, 1, Vs + V_BYTES, bar_v + 8);
+    }
+    bool ok = wait_all(bar_q, 0) && wait_all(bar_k, 0);
+    if (ok) {
+      fence_after();
+      issue_s(0);
+    }
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      // S of the next tile: its K has landed, and the softmax threads are done with that S
+      // buffer (they said so with P of tile j-1, which was waited for before O += P V of j-1).
+      if (j + 1 < n_tiles) {
+        ok = wait_all(bar_k + 8 * (b ^ 1), ((j + 1) >> 1) & 1);
         if (!ok) break;
         fence_after();
+        issue_s(j + 1);
+        // V of the next tile into the buffer that O += P V of tile j-1 has released.
+        if (j >= 1) {
+          ok = wait_all(bar_vfree + 8 * (b ^ 1), ((j - 1) >> 1) & 1);
+          if (!ok) break;
+          load_kv(1, j + 1, Vs + (b ^ 1) * V_BYTES, bar_v + 8 * (b ^ 1));
+        }
+      }
+      // K buffer b is free once S_j is done.
+      if (j + 2 < n_tiles) {
+        ok = wait_all(bar_s + 8 * b, (j >> 1) & 1);
+        if (!ok) break;
+        load_kv(0, j + 2, Ks + b * K_BYTES, bar_k + 8 * b);
+      }
+      // O += P V of tile j: P is written, V has landed.
+      ok = wait_all(bar_p, j & 1) && wait_all(bar_v + 8 * b, (j >> 1) & 1);
+      if (!ok) break;
+      fence_after();
+      if (lane == 0) {
         const uint32_t vbuf = sm(Vs) + b * V_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_BK / 16; ++kk) {
@@ -305,6 +310,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         commit(bar_pv);
         commit(bar_vfree + 8 * b);    // the same completion, counted per V buffer (its phases cannot run ahead of the loader)
       }
+      __syncwarp();
     }
   } else {
     // ---- softmax threads ------------------------------------------------------------------
