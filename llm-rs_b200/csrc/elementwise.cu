@@ -242,14 +242,12 @@ template <typename TA>
 __global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter, int block,
                                     int n_tokens) {
   constexpr int PER = 16 / sizeof(TA);
-  const int chunks = inter / PER;
-  const size_t total = (size_t)n_tokens * chunks;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (; i < total; i += stride) {
-    const size_t t = i / chunks;
-    const int c = (int)(i - t * chunks) * PER;
-    const TA* gp = gu + t * 2 * inter + (size_t)(c / block) * 2 * block + c % block;
+  // One token per blockIdx.y, one 16-byte run of outputs per thread: no division by the row length.
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * PER;
+  if (c >= inter) return;
+  const int blk = c / block, r = c - blk * block;
+  for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {
+    const TA* gp = gu + (size_t)t * 2 * inter + (size_t)blk * 2 * block + r;
     float g[PER], u[PER];
 #pragma unroll
     for (int k = 0; k < PER; k += 4) {
@@ -261,7 +259,7 @@ __global__ void silu_mul_vec_kernel(const TA* __restrict__ gu, TA* __restrict__ 
     for (int k = 0; k < PER; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
 #pragma unroll
     for (int k = 0; k < PER; k += 4)
-      Vec4<TA>::store(out + t * inter + c + k, make_float4(g[k], g[k + 1], g[k + 2], g[k + 3]));
+      Vec4<TA>::store(out + (size_t)t * inter + c + k, make_float4(g[k], g[k + 1], g[k + 2], g[k + 3]));
   }
 }
 
@@ -270,10 +268,8 @@ static void launch_silu_mul(const TA* gu, TA* out, int n_tokens, int inter, int 
   constexpr int PER = 16 / sizeof(TA);
   const int threads = 256;
   if (inter % PER == 0 && block % PER == 0) {
-    const size_t total = (size_t)n_tokens * (inter / PER);
-    const size_t want = (total + threads - 1) / threads;
-    silu_mul_vec_kernel<TA><<<(int)(want < 148 * 16 ? want : 148 * 16), threads, 0, stream>>>(gu, out, inter, block,
-                                                                                              n_tokens);
+    dim3 grid((inter / PER + threads - 1) / threads, n_tokens < 65535 ? n_tokens : 65535);
+    silu_mul_vec_kernel<TA><<<grid, threads, 0, stream>>>(gu, out, inter, block, n_tokens);
   } else {
     const size_t total = (size_t)n_tokens * inter;
     const size_t want = (total + threads - 1) / threads;
