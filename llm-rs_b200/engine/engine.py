@@ -59,6 +59,7 @@ class Engine:
         self._inflight = None            # the step that is queued on the GPU and not read back yet
         self._tok_bufs = [None, None]
         self._tok_flip = 0
+        self._steps_since_check = 0
 
     # -- requests --------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -147,7 +148,18 @@ class Engine:
             flight["event"].synchronize()
             values = flight["host"].tolist()
             sampled = {rid: values[i] for rid, i in flight["row_of"].items()}
+        self._steps_since_check += 1
+        if self._steps_since_check >= 256:
+            self.check_kernels()
         return self.scheduler.on_result(flight["batch"], sampled)
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel with bounded waits (tcgen05 GEMM or attention) gave up on one since
+        the last check; its step's output would be invalid. Runs every 256 steps and on demand."""
+        from .. import ops
+        self._steps_since_check = 0
+        ops.check_tc_error(self.runner.device)
+        ops.check_attention_error()
 
     # -- conveniences ----------------------------------------------------------------
     def poll(self, request_id: int) -> Output:
