@@ -11,14 +11,21 @@ length is advanced by ``commit`` after it (the reference grows a table by one pa
 a step, llm-scheduler/src/scheduler.rs:161-167). Pages go back when a request is
 released, and, in a window group, as soon as the window has passed them. Beside the
 pages each live request holds one slot for fixed-size state.
+
+The bookkeeping itself is C++ (``csrc/host/cache_manager.cpp``); this class holds its
+handle, maps the caller's request ids (anything hashable) to the library's numbers and
+turns its statuses into exceptions.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from ctypes import byref, c_int, c_int32, c_int64, c_void_p
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence
 
+from .. import host
 from ..parts.spec import CacheNeed
-from .pool import CacheError, OutOfPages, PagePool
+from .pool import CacheError, NoFreeSlot, OutOfPages, check  # noqa: F401  (re-exported)
 
 RELEASED = -1  # table entry of a page that a window has passed
 
@@ -31,18 +38,56 @@ class GroupSpec:
     n_pages: int
 
 
-@dataclass
 class RequestRecord:
-    request_id: Hashable
-    slot: int
-    cached_len: int = 0
-    reserved_len: int = 0       # tokens that the tables cover (>= cached_len between reserve and commit)
-    tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> physical page
-    edits: int = 0              # counts changes to the tables other than appending a page
+    """A live request as the manager sees it; the numbers are read from the library."""
+
+    def __init__(self, manager: "CacheManager", request_id: Hashable, number: int, slot: int):
+        self._manager = manager
+        self.request_id = request_id
+        self.number = number        # the request's id inside the host library
+        self.slot = slot
+
+    def _info(self):
+        info, edits = (c_int * 3)(), c_int64()
+        m = self._manager
+        check(m._lib.llmrs_cm_info(m._handle, self.number, info, byref(edits)), m._names)
+        return info[1], info[2], edits.value
+
+    @property
+    def cached_len(self) -> int:
+        return self._info()[0]
+
+    @property
+    def reserved_len(self) -> int:
+        """Tokens that the tables cover (>= cached_len between reserve and commit)."""
+        return self._info()[1]
+
+    @property
+    def edits(self) -> int:
+        """Counts changes to the tables other than appending a page."""
+        return self._info()[2]
+
+    @property
+    def tables(self) -> List[List[int]]:
+        """Per group: logical page -> physical page."""
+        return [self._manager.table(self.request_id, g) for g in range(len(self._manager.groups))]
 
 
-class NoFreeSlot(CacheError):
-    pass
+class _PoolView:
+    """Counts of one group's pool inside the manager."""
+
+    def __init__(self, manager: "CacheManager", group: int):
+        self._manager, self._group = manager, group
+        self.capacity = manager.groups[group].n_pages
+
+    def free_pages(self) -> int:
+        m = self._manager
+        free, cap = c_int(), c_int()
+        check(m._lib.llmrs_cm_pool_counts(m._handle, self._group, byref(free), byref(cap)))
+        return free.value
+
+    def used_pages(self) -> int:
+        return self.capacity - self.free_pages()
 
 
 def pages_for(n_tokens: int, page_size: int) -> int:
@@ -55,23 +100,40 @@ class CacheManager:
             raise ValueError("page_size must be positive")
         self.groups = list(groups)
         self.page_size = page_size
-        self.pools = [PagePool(g.n_pages) for g in self.groups]
         self.n_slots = n_slots
-        self._free_slots = list(range(n_slots - 1, -1, -1))
+        self._lib = host.lib()
+        self._handle = c_void_p()
+        G = len(self.groups)
+        n_pages = (c_int * max(G, 1))(*[g.n_pages for g in self.groups])
+        windows = (c_int * max(G, 1))(*[g.need.window if g.need.kind == "window" and g.need.window > 0 else 0
+                                        for g in self.groups])
+        check(self._lib.llmrs_cm_create(n_pages, windows, G, page_size, n_slots, byref(self._handle)))
+        self.pools = [_PoolView(self, g) for g in range(G)]
         self.requests: Dict[Hashable, RequestRecord] = {}
+        self._names: Dict[int, Hashable] = {}
+        self._next_number = 0
+        self._need_buf = (c_int * max(G, 1))()
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.llmrs_cm_destroy(self._handle)
+            self._handle = None
 
     # -- requests --------------------------------------------------------------------
     def admit(self, request_id: Hashable) -> RequestRecord:
         if request_id in self.requests:
             raise CacheError(f"request {request_id!r} is already live")
-        if not self._free_slots:
-            raise NoFreeSlot(f"all {self.n_slots} request slots are taken")
-        rec = RequestRecord(request_id, self._free_slots.pop(), tables=[[] for _ in self.groups])
+        number = self._next_number
+        slot = c_int()
+        check(self._lib.llmrs_cm_admit(self._handle, number, byref(slot)), self._names)
+        self._next_number += 1
+        rec = RequestRecord(self, request_id, number, slot.value)
         self.requests[request_id] = rec
+        self._names[number] = request_id
         return rec
 
     def has_free_slot(self) -> bool:
-        return bool(self._free_slots)
+        return len(self.requests) < self.n_slots
 
     def record(self, request_id: Hashable) -> RequestRecord:
         try:
@@ -82,37 +144,19 @@ class CacheManager:
     def release(self, request_id: Hashable) -> None:
         """Give back every page and the slot of a request."""
         rec = self.record(request_id)
-        for g, table in enumerate(rec.tables):
-            for page in table:
-                if page != RELEASED:
-                    self.pools[g].free(page)
-        self._free_slots.append(rec.slot)
+        check(self._lib.llmrs_cm_release(self._handle, rec.number), self._names)
         del self.requests[request_id]
+        del self._names[rec.number]
 
     # -- pages -----------------------------------------------------------------------
-    def _first_needed_page(self, g: int, first_query_pos: int) -> int:
-        """Logical page of the oldest key that a query at ``first_query_pos`` reads."""
-        need = self.groups[g].need
-        if need.kind != "window" or need.window <= 0:
-            return 0
-        return max(0, first_query_pos - need.window + 1) // self.page_size
-
     def pages_needed(self, request_id: Optional[Hashable], n_new: int, cached_len: Optional[int] = None) -> List[int]:
         """Pages per group that ``reserve(request_id, n_new)`` would take from the pools.
         For a request that is not live yet pass ``request_id=None`` and its ``cached_len`` (0)."""
-        if request_id is not None:
-            rec = self.record(request_id)
-            have, base = [len(t) for t in rec.tables], rec.cached_len
-        else:
-            have, base = [0] * len(self.groups), cached_len or 0
-        total = pages_for(base + n_new, self.page_size)
-        out = []
-        for g in range(len(self.groups)):
-            first = self._first_needed_page(g, base)
-            # Logical pages below `first` are never read: they need no physical page even
-            # if they were never allocated (a window group joined late by a long portion).
-            out.append(max(0, total - max(have[g], first)))
-        return out
+        live = request_id is not None
+        number = self.record(request_id).number if live else 0
+        check(self._lib.llmrs_cm_pages_needed(self._handle, int(live), number, n_new, cached_len or 0,
+                                              self._need_buf), self._names)
+        return list(self._need_buf[:len(self.groups)])
 
     def can_reserve(self, request_id: Optional[Hashable], n_new: int, cached_len: Optional[int] = None) -> bool:
         need = self.pages_needed(request_id, n_new, cached_len)
@@ -121,77 +165,34 @@ class CacheManager:
     def reserve(self, request_id: Hashable, n_new: int) -> None:
         """Cover positions cached_len .. cached_len+n_new-1 with pages in every group.
         Raises ``OutOfPages`` and changes nothing if any pool is short."""
-        rec = self.record(request_id)
-        if n_new < 1:
-            raise CacheError("a step must bring at least one token for a request")
-        if rec.reserved_len != rec.cached_len:
-            raise CacheError(f"request {request_id!r} has an uncommitted reservation")
-        need = self.pages_needed(request_id, n_new)
-        for g, n in enumerate(need):
-            if n > self.pools[g].free_pages():
-                raise OutOfPages(
-                    f"request {request_id!r} needs {n} pages in group {g}, {self.pools[g].free_pages()} free")
-        total = pages_for(rec.cached_len + n_new, self.page_size)
-        for g, table in enumerate(rec.tables):
-            first = self._first_needed_page(g, rec.cached_len)
-            while len(table) < total:
-                table.append(RELEASED if len(table) < first else self.pools[g].allocate())
-        rec.reserved_len = rec.cached_len + n_new
+        check(self._lib.llmrs_cm_reserve(self._handle, self.record(request_id).number, n_new), self._names)
 
     def cancel(self, request_id: Hashable) -> None:
         """Undo a reservation that was not committed (pages beyond the cached length go back)."""
-        rec = self.record(request_id)
-        keep = pages_for(rec.cached_len, self.page_size)
-        rec.edits += 1
-        for g, table in enumerate(rec.tables):
-            while len(table) > keep:
-                page = table.pop()
-                if page != RELEASED:
-                    self.pools[g].free(page)
-        rec.reserved_len = rec.cached_len
+        check(self._lib.llmrs_cm_cancel(self._handle, self.record(request_id).number), self._names)
 
     def commit(self, request_id: Hashable, n_new: int) -> None:
         """The step ran: the new tokens are cached. Pages a window has passed go back."""
-        rec = self.record(request_id)
-        if rec.cached_len + n_new != rec.reserved_len:
-            raise CacheError(
-                f"commit of {n_new} tokens does not match the reservation of request {request_id!r}")
-        rec.cached_len = rec.reserved_len
-        for g, table in enumerate(rec.tables):
-            first = min(self._first_needed_page(g, rec.cached_len), len(table))
-            for j in range(first):
-                if table[j] != RELEASED:
-                    self.pools[g].free(table[j])
-                    table[j] = RELEASED
-                    rec.edits += 1
+        check(self._lib.llmrs_cm_commit(self._handle, self.record(request_id).number, n_new), self._names)
 
     # -- views -----------------------------------------------------------------------
     def table(self, request_id: Hashable, group: int) -> List[int]:
-        return self.record(request_id).tables[group]
+        rec = self.record(request_id)
+        length = c_int()
+        cap = 64
+        while True:
+            buf = (c_int32 * cap)()
+            check(self._lib.llmrs_cm_table(self._handle, rec.number, group, buf, cap, byref(length)), self._names)
+            if length.value <= cap:
+                return list(buf[:length.value])
+            cap = length.value
 
     def free_pages(self, group: int = 0) -> int:
         return self.pools[group].free_pages()
 
     def check_invariants(self) -> None:
-        """Every page is either free or held by exactly as many tables as its count says."""
-        for g, pool in enumerate(self.pools):
-            held: Dict[int, int] = {}
-            for rec in self.requests.values():
-                for page in rec.tables[g]:
-                    if page != RELEASED:
-                        held[page] = held.get(page, 0) + 1
-            free = list(pool._free)
-            if len(set(free)) != len(free):
-                raise CacheError(f"group {g}: a page is on the free list twice")
-            if set(free) & set(held):
-                raise CacheError(f"group {g}: a page is both free and held")
-            if len(free) + len(held) != pool.capacity:
-                raise CacheError(f"group {g}: {pool.capacity - len(free) - len(held)} pages are lost")
-            for page, n in held.items():
-                if pool.ref_count(page) != n:
-                    raise CacheError(f"group {g}: page {page} is held {n} times, count says {pool.ref_count(page)}")
-        slots = [r.slot for r in self.requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
-            raise CacheError("a request slot is held twice")
-        if len(slots) + len(self._free_slots) != self.n_slots:
-            raise CacheError("a request slot is lost")
+        """Every page is either free or held by exactly as many tables as its count says; no
+        request slot is lost or held twice; the library and this class know the same requests."""
+        check(self._lib.llmrs_cm_check_invariants(self._handle), self._names)
+        if {r.number for r in self.requests.values()} != set(self._names):
+            raise CacheError("the request map and the library disagree")

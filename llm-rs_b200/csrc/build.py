@@ -1,4 +1,6 @@
-"""Compiles the kernel library for sm_100a with nvcc and loads it.
+"""Compiles the kernel library for sm_100a with nvcc, and the host library (cache
+bookkeeping and step packing, plain C++ under ``csrc/host/``) with the C++ compiler, and
+loads them.
 
 The library is plain CUDA behind C entry points (no framework headers), so a fresh
 checkout compiles in well under a minute. It is built next to the sources in
@@ -26,8 +28,13 @@ LIB_NAME = "libllmrs_b200.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 ABI_VERSION = 2
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+HOST_LIB_NAME = "libllmrs_b200_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
+HOST_ABI_VERSION = 1
 
 _lib: Optional[ctypes.CDLL] = None
+_host_lib: Optional[ctypes.CDLL] = None
 
 
 class KernelBuildError(RuntimeError):
@@ -72,9 +79,9 @@ def _build_dirs() -> List[str]:
     return dirs
 
 
-def _is_current(build_dir: str, fp: str) -> bool:
-    stamp = os.path.join(build_dir, "stamp.json")
-    lib = os.path.join(build_dir, LIB_NAME)
+def _is_current(build_dir: str, fp: str, stamp_name: str = "stamp.json", lib_name: str = LIB_NAME) -> bool:
+    stamp = os.path.join(build_dir, stamp_name)
+    lib = os.path.join(build_dir, lib_name)
     if not (os.path.isfile(stamp) and os.path.isfile(lib)):
         return False
     try:
@@ -170,3 +177,76 @@ def library() -> ctypes.CDLL:
             raise KernelBuildError(f"{path} has ABI {lib.llmrs_abi_version()}, expected {ABI_VERSION}")
         _lib = lib
     return _lib
+
+
+# -- the host library ------------------------------------------------------------------
+def host_sources() -> List[str]:
+    return sorted(f for f in os.listdir(HOST_DIR) if f.endswith(".cpp"))
+
+
+def _host_fingerprint() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(HOST_FLAGS).encode())
+    for name in sorted(os.listdir(HOST_DIR)):
+        if name.endswith((".cpp", ".hpp", ".h")):
+            h.update(name.encode())
+            with open(os.path.join(HOST_DIR, name), "rb") as f:
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def find_cxx() -> Optional[List[str]]:
+    """The command that compiles C++: $CXX, g++, c++ or clang++ (nvcc needs one of them too)."""
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        if cand and shutil.which(cand):
+            return [shutil.which(cand)]
+    return None
+
+
+def _compile_host(build_dir: str, fp: str) -> None:
+    cxx = find_cxx()
+    if cxx is None:
+        raise KernelBuildError("the host library is not built and no C++ compiler was found ($CXX, g++, c++, clang++)")
+    srcs = [os.path.join(HOST_DIR, n) for n in host_sources()]
+    lib_tmp = os.path.join(build_dir, f".{HOST_LIB_NAME}.{os.getpid()}")
+    cmd = [*cxx, *HOST_FLAGS, "-shared", "-I", HOST_DIR, *srcs, "-o", lib_tmp]
+    t0 = time.time()
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise KernelBuildError(f"compiling the host library failed:\n{r.stdout}")
+    os.replace(lib_tmp, os.path.join(build_dir, HOST_LIB_NAME))
+    with open(os.path.join(build_dir, "host_stamp.json"), "w") as f:
+        json.dump({"fingerprint": fp, "flags": HOST_FLAGS, "sources": host_sources()}, f)
+    _log(f"built {HOST_LIB_NAME} in {time.time() - t0:.0f} s")
+
+
+def build_host(force: bool = False) -> str:
+    """Make sure the host library is built for the current sources; return its path."""
+    fp = _host_fingerprint()
+    if not force:
+        for d in _build_dirs():
+            if _is_current(d, fp, "host_stamp.json", HOST_LIB_NAME):
+                return os.path.join(d, HOST_LIB_NAME)
+    d = _writable_dir()
+    with open(os.path.join(d, ".host_lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if force or not _is_current(d, fp, "host_stamp.json", HOST_LIB_NAME):
+                _compile_host(d, fp)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return os.path.join(d, HOST_LIB_NAME)
+
+
+def host_library() -> ctypes.CDLL:
+    """The loaded host library (built first if needed)."""
+    global _host_lib
+    if _host_lib is None:
+        path = build_host()
+        lib = ctypes.CDLL(path)
+        lib.llmrs_host_abi_version.restype = ctypes.c_int
+        lib.llmrs_host_last_error.restype = ctypes.c_char_p
+        if lib.llmrs_host_abi_version() != HOST_ABI_VERSION:
+            raise KernelBuildError(f"{path} has ABI {lib.llmrs_host_abi_version()}, expected {HOST_ABI_VERSION}")
+        _host_lib = lib
+    return _host_lib

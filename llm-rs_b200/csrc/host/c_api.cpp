@@ -1,0 +1,135 @@
+#include "llmrs_host.h"
+
+#include <exception>
+#include <string>
+
+#include "cache_manager.hpp"
+
+using namespace llmrs_host;
+
+namespace {
+thread_local std::string g_error;
+
+template <typename F>
+int guarded(F&& body) {
+    try {
+        body();
+        return kOk;
+    } catch (const Failure& f) {
+        g_error = f.message;
+        return f.status;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return kBadArgument;
+    }
+}
+
+template <typename T>
+T* as(void* handle, const char* what) {
+    if (handle == nullptr) throw Failure{kBadArgument, std::string("null ") + what + " handle"};
+    return static_cast<T*>(handle);
+}
+}  // namespace
+
+extern "C" {
+
+int llmrs_host_abi_version(void) { return 1; }
+const char* llmrs_host_last_error(void) { return g_error.c_str(); }
+
+int llmrs_pool_create(int capacity, void** pool) {
+    return guarded([&] { *pool = new PagePool(capacity); });
+}
+void llmrs_pool_destroy(void* pool) { delete static_cast<PagePool*>(pool); }
+int llmrs_pool_allocate(void* pool, int32_t* page) {
+    return guarded([&] { *page = as<PagePool>(pool, "pool")->allocate(); });
+}
+int llmrs_pool_free(void* pool, int32_t page, int* went_back) {
+    return guarded([&] { *went_back = as<PagePool>(pool, "pool")->free(page) ? 1 : 0; });
+}
+int llmrs_pool_increment_ref(void* pool, int32_t page) {
+    return guarded([&] { as<PagePool>(pool, "pool")->increment_ref(page); });
+}
+int llmrs_pool_ref_count(void* pool, int32_t page, int* count) {
+    return guarded([&] { *count = as<PagePool>(pool, "pool")->ref_count(page); });
+}
+int llmrs_pool_counts(void* pool, int* free_pages, int* capacity) {
+    return guarded([&] {
+        auto* p = as<PagePool>(pool, "pool");
+        *free_pages = p->free_pages();
+        *capacity = p->capacity();
+    });
+}
+
+int llmrs_cm_create(const int* n_pages, const int* windows, int n_groups, int page_size, int n_slots, void** cm) {
+    return guarded([&] { *cm = new CacheManager(n_pages, windows, n_groups, page_size, n_slots); });
+}
+void llmrs_cm_destroy(void* cm) { delete static_cast<CacheManager*>(cm); }
+int llmrs_cm_admit(void* cm, int64_t id, int* slot) {
+    return guarded([&] { *slot = as<CacheManager>(cm, "manager")->admit(id).slot; });
+}
+int llmrs_cm_release(void* cm, int64_t id) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->release(id); });
+}
+int llmrs_cm_pages_needed(void* cm, int live, int64_t id, int n_new, int cached_len, int* out) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->pages_needed(live != 0, id, n_new, cached_len, out); });
+}
+int llmrs_cm_reserve(void* cm, int64_t id, int n_new) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->reserve(id, n_new); });
+}
+int llmrs_cm_cancel(void* cm, int64_t id) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->cancel(id); });
+}
+int llmrs_cm_commit(void* cm, int64_t id, int n_new) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->commit(id, n_new); });
+}
+int llmrs_cm_info(void* cm, int64_t id, int* info3, int64_t* edits) {
+    return guarded([&] {
+        const Record& rec = as<CacheManager>(cm, "manager")->record(id);
+        info3[0] = rec.slot;
+        info3[1] = rec.cached_len;
+        info3[2] = rec.reserved_len;
+        *edits = rec.edits;
+    });
+}
+int llmrs_cm_table(void* cm, int64_t id, int group, int32_t* out, int capacity, int* length) {
+    return guarded([&] {
+        auto* m = as<CacheManager>(cm, "manager");
+        m->pool(group);  // checks the group
+        const auto& table = m->record(id).tables[group];
+        *length = static_cast<int>(table.size());
+        for (int i = 0; i < *length && i < capacity; ++i) out[i] = table[i];
+    });
+}
+int llmrs_cm_pool_counts(void* cm, int group, int* free_pages, int* capacity) {
+    return guarded([&] {
+        const PagePool& p = as<CacheManager>(cm, "manager")->pool(group);
+        *free_pages = p.free_pages();
+        *capacity = p.capacity();
+    });
+}
+int llmrs_cm_check_invariants(void* cm) {
+    return guarded([&] { as<CacheManager>(cm, "manager")->check_invariants(); });
+}
+
+int llmrs_pack_step(void* cm, int n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens,
+                    const int32_t* n_want, const int32_t* want, const int32_t* device_token, int table_round,
+                    int prefill_tile, int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
+                    int32_t* widths, int32_t* shape8, int64_t* total, int* written) {
+    return guarded([&] {
+        StepShape s;
+        bool ok = pack_step(*as<CacheManager>(cm, "manager"), n_entries, ids, n_tokens, tokens, n_want, want,
+                            device_token, table_round, prefill_tile, out, capacity, offsets, sizes, widths, &s);
+        shape8[0] = s.n_tokens;
+        shape8[1] = s.n_requests;
+        shape8[2] = s.n_want;
+        shape8[3] = s.n_prefill_tiles;
+        shape8[4] = s.n_decode;
+        shape8[5] = s.max_decode_kv_len;
+        shape8[6] = s.long_portions;
+        shape8[7] = 0;
+        *total = s.total;
+        *written = ok ? 1 : 0;
+    });
+}
+
+}  // extern "C"

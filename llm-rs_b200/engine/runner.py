@@ -11,15 +11,18 @@ number of new tokens and block tables.
 """
 from __future__ import annotations
 
+import ctypes
 import gc
+import itertools
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..cache import CacheManager, OutOfPages
-from ..cache.manager import RELEASED
+from .. import host
+from ..cache import CacheManager, OutOfPages  # noqa: F401  (OutOfPages is what step() may raise)
+from ..cache.pool import check
 from ..cache.storage import CacheStorage
 from ..config import load_config
 from ..parts import DecoderModel, ModelSpec, Runtime
@@ -103,7 +106,6 @@ class ModelRunner:
         self._meta_flip = 0
         self.steps_run = 0
         self.h2d_bytes = 0  # bytes of index arrays copied to the device so far
-        self._table_rows: Dict[Hashable, list] = {}
         # Steps that only decode (one token per request) are captured in CUDA graphs and
         # replayed: one launch instead of some ten per layer.
         self.use_graphs = False
@@ -133,27 +135,6 @@ class ModelRunner:
     def release(self, request_id: Hashable) -> None:
         """The request is finished: its pages and its slot go back."""
         self.manager.release(request_id)
-        self._table_rows.pop(request_id, None)
-
-    def _table_row(self, rec, g: int) -> np.ndarray:
-        """The request's block table of group ``g`` as an int32 array, kept between steps and
-        extended when a page is appended (rebuilt after any other change to the table)."""
-        cache = self._table_rows.get(rec.request_id)
-        if cache is None or cache[0] is not rec or cache[1] != rec.edits:
-            cache = [rec, rec.edits, [np.empty(64, np.int32) for _ in rec.tables], [0] * len(rec.tables)]
-            if len(self._table_rows) > 4 * self.max_requests:
-                self._table_rows = {k: v for k, v in self._table_rows.items() if k in self.manager.requests}
-            self._table_rows[rec.request_id] = cache
-        table, have = rec.tables[g], cache[3][g]
-        arr = cache[2][g]
-        if len(table) > arr.size:
-            bigger = np.empty(max(2 * arr.size, len(table)), np.int32)
-            bigger[:have] = arr[:have]
-            cache[2][g] = arr = bigger
-        if len(table) > have:
-            arr[have:len(table)] = table[have:]
-        cache[3][g] = len(table)
-        return arr[:len(table)]
 
     def live_requests(self) -> List[Hashable]:
         return list(self.manager.requests)
@@ -202,74 +183,51 @@ class ModelRunner:
             raise
         return admitted
 
-    def _build_context(self, entries: Sequence[StepEntry], table_round: int = 8,
-                       graph: Optional["_DecodeGraph"] = None) -> StepContext:
-        """Pack the step's index arrays, copy them to the device in one transfer and
-        return the context that views them. With ``graph`` the arrays go into that
-        graph's own buffer (same layout every time) and its context is returned."""
-        ctx = StepContext(self)
+    def _pack(self, entries: Sequence[StepEntry], table_round: int) -> "_PackedStep":
+        """Pack the step's index arrays into pinned host memory (the host library does it:
+        tokens, positions, request rows, per-request lengths, wanted rows, prefill tiles,
+        decode list, tokens still on the device, block tables padded to ``table_round``)."""
         R = len(entries)
+        G = len(self.manager.groups)
         T = sum(len(e.tokens) for e in entries)
-        recs = [self.manager.record(e.request_id) for e in entries]
-        token_ids = np.empty(T, np.int32)
-        positions = np.empty(T, np.int32)
-        token_req = np.empty(T, np.int32)
-        q_start = np.empty(R, np.int32)
-        n_new = np.empty(R, np.int32)
-        cached = np.empty(R, np.int32)
-        slots = np.empty(R, np.int32)
-        want_rows: List[int] = []
-        tiles: List[int] = []
-        dec: List[int] = []
-        at = 0
-        max_dec_kv = 0
-        for r, (e, rec) in enumerate(zip(entries, recs)):
-            n = len(e.tokens)
-            token_ids[at:at + n] = e.tokens
-            positions[at:at + n] = np.arange(rec.cached_len, rec.cached_len + n)
-            token_req[at:at + n] = r
-            q_start[r], n_new[r], cached[r], slots[r] = at, n, rec.cached_len, rec.slot
-            want_rows.extend(at + int(w) for w in e.want)
-            if n == 1:
-                dec.append(r)
-                max_dec_kv = max(max_dec_kv, rec.cached_len + 1)
-            else:
-                for off in range(0, n, PREFILL_TILE):
-                    tiles.extend((r, off))
-            at += n
-        tables = []
-        for g in range(len(self.manager.groups)):
-            width = _round_up(max(len(rec.tables[g]) for rec in recs), table_round)
-            tab = np.full((R, width), RELEASED, np.int32)
-            for r, rec in enumerate(recs):
-                row = self._table_row(rec, g)
-                tab[r, :row.size] = row
-            tables.append(tab)
-        pend_dst = np.full(R, -1, np.int32)
-        pend_src = np.zeros(R, np.int32)
-        for r, e in enumerate(entries):
-            if e.device_token >= 0:
-                pend_dst[r], pend_src[r] = q_start[r], e.device_token
-                token_ids[q_start[r]] = 0
-
-        parts = [token_ids, positions, token_req, q_start, n_new, cached, slots,
-                 np.asarray(want_rows, np.int32), np.asarray(tiles, np.int32), np.asarray(dec, np.int32),
-                 pend_dst, pend_src, *[t.reshape(-1) for t in tables]]
-        offsets, total = [], 0
-        for p in parts:
-            offsets.append(total)
-            total += _round_up(max(p.size, 1), 4)
+        numbers = np.fromiter((self.manager.record(e.request_id).number for e in entries), np.int64, R)
+        n_tokens = np.fromiter((len(e.tokens) for e in entries), np.int32, R)
+        tokens = np.fromiter(itertools.chain.from_iterable(e.tokens for e in entries), np.int32, T)
+        n_want = np.fromiter((len(e.want) for e in entries), np.int32, R)
+        want = np.fromiter(itertools.chain.from_iterable(e.want for e in entries), np.int32, int(n_want.sum()))
+        device_token = np.fromiter((e.device_token for e in entries), np.int32, R)
+        offsets = np.empty(host.FIRST_TABLE + G, np.int64)
+        sizes = np.empty(host.FIRST_TABLE + G, np.int64)
+        widths = np.empty(max(G, 1), np.int32)
+        shape = np.empty(8, np.int32)
+        total, written = ctypes.c_int64(), ctypes.c_int()
         flip = self._meta_flip
         self._meta_flip ^= 1
-        if self._meta_host[flip] is None or self._meta_host[flip].numel() < total:
-            self._meta_host[flip] = torch.empty((_round_up(total, 4096),), dtype=torch.int32).pin_memory()
-            self._meta_events[flip] = None
         if self._meta_events[flip] is not None:
             self._meta_events[flip].synchronize()  # the copy that last read this buffer is done
-        host = self._meta_host[flip]
-        host_np = host.numpy()
-        for p, off in zip(parts, offsets):
-            host_np[off:off + p.size] = p
+        lib = host.lib()
+        while True:
+            buf = self._meta_host[flip]
+            cap = 0 if buf is None else buf.numel()
+            check(lib.llmrs_pack_step(
+                self.manager._handle, R, numbers.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data,
+                n_want.ctypes.data, want.ctypes.data, device_token.ctypes.data, table_round, PREFILL_TILE,
+                0 if buf is None else buf.data_ptr(), cap, offsets.ctypes.data, sizes.ctypes.data,
+                widths.ctypes.data, shape.ctypes.data, ctypes.byref(total), ctypes.byref(written)),
+                self.manager._names)
+            if written.value:
+                break
+            self._meta_host[flip] = torch.empty((_round_up(total.value, 4096),), dtype=torch.int32).pin_memory()
+            self._meta_events[flip] = None
+        return _PackedStep(self._meta_host[flip], flip, int(total.value), offsets.tolist(), sizes.tolist(),
+                           widths[:G].tolist(), shape.tolist())
+
+    def _upload(self, packed: "_PackedStep", entries: Sequence[StepEntry],
+                graph: Optional["_DecodeGraph"] = None) -> StepContext:
+        """Copy a packed step to the device in one transfer and return the context that views
+        it. With ``graph`` the arrays go into that graph's own buffer (same layout every
+        time) and its context is returned."""
+        total, offsets, sizes = packed.total, packed.offsets, packed.sizes
         if graph is not None:
             if graph.meta is None:
                 graph.meta = torch.empty((total,), dtype=torch.int32, device=self.device)
@@ -278,41 +236,50 @@ class ModelRunner:
                 raise StepError("a captured step's layout changed")
         else:
             dev = torch.empty((total,), dtype=torch.int32, device=self.device)
-        dev.copy_(host[:total], non_blocking=True)
+        dev.copy_(packed.host[:total], non_blocking=True)
         self.h2d_bytes += total * 4
         ev = torch.cuda.Event()
         ev.record()
-        self._meta_events[flip] = ev
-        host_lists = dict(host_n_new=[int(x) for x in n_new], host_cached_len=[int(x) for x in cached],
-                          host_q_start=[int(x) for x in q_start], host_slot_ids=[int(x) for x in slots],
+        self._meta_events[packed.flip] = ev
+        T, R, n_want, n_tiles, n_dec, max_dec_kv, long_portions = packed.shape[:7]
+        host_np = packed.host.numpy()
+
+        def host_list(i):
+            return host_np[offsets[i]:offsets[i] + sizes[i]].tolist()
+        host_lists = dict(host_n_new=host_list(host.N_NEW), host_cached_len=host_list(host.CACHED_LEN),
+                          host_q_start=host_list(host.Q_START), host_slot_ids=host_list(host.SLOT_IDS),
                           request_ids=[e.request_id for e in entries])
         if graph is not None and graph.ctx is not None:
             graph.ctx.__dict__.update(host_lists)
             return graph.ctx  # its device views already point into graph.meta
 
-        def view(i, size):
-            return dev[offsets[i]:offsets[i] + size]
-        ctx.n_tokens, ctx.n_requests, ctx.n_want = T, R, len(want_rows)
-        ctx.token_ids, ctx.positions, ctx.token_req = view(0, T), view(1, T), view(2, T)
-        ctx.q_start, ctx.n_new, ctx.cached_len, ctx.slot_ids = view(3, R), view(4, R), view(5, R), view(6, R)
-        ctx.want_rows = view(7, len(want_rows))
-        ctx.n_prefill_tiles = len(tiles) // 2
-        # Blocks of 128 queries pay off when the portions fill them at least half on average.
-        blocks = sum(-(-int(n) // 128) for n in n_new if n > 1)
-        ctx.long_portions = blocks > 0 and sum(int(n) for n in n_new if n > 1) >= 64 * blocks
-        ctx.prefill_tiles = view(8, len(tiles)).view(-1, 2) if tiles else view(8, 0)
-        ctx.n_decode = len(dec)
-        ctx.decode_reqs = view(9, len(dec))
+        def view(i):
+            return dev[offsets[i]:offsets[i] + sizes[i]]
+        ctx = StepContext(self)
+        ctx.n_tokens, ctx.n_requests, ctx.n_want = T, R, n_want
+        ctx.token_ids, ctx.positions, ctx.token_req = view(host.TOKEN_IDS), view(host.POSITIONS), view(host.TOKEN_REQ)
+        ctx.q_start, ctx.n_new = view(host.Q_START), view(host.N_NEW)
+        ctx.cached_len, ctx.slot_ids = view(host.CACHED_LEN), view(host.SLOT_IDS)
+        ctx.want_rows = view(host.WANT_ROWS)
+        ctx.n_prefill_tiles = n_tiles
+        ctx.long_portions = bool(long_portions)
+        ctx.prefill_tiles = view(host.PREFILL_TILES).view(-1, 2) if n_tiles else view(host.PREFILL_TILES)
+        ctx.n_decode = n_dec
+        ctx.decode_reqs = view(host.DECODE_REQS)
         ctx.max_decode_kv_len = max_dec_kv
         if graph is not None:
             # Captured launch sizes must hold for every step that replays the graph.
-            ctx.max_decode_kv_len = max(t.shape[1] for t in tables) * self.page_size if tables else max_dec_kv
+            if packed.widths:
+                ctx.max_decode_kv_len = max(packed.widths) * self.page_size
             ctx._scratch_bufs = graph.scratch
             graph.ctx = ctx
-        ctx.pend_dst, ctx.pend_src = view(10, R), view(11, R)
-        ctx.block_tables = [view(12 + g, tables[g].size).view(R, -1) for g in range(len(tables))]
+        ctx.pend_dst, ctx.pend_src = view(host.PEND_DST), view(host.PEND_SRC)
+        ctx.block_tables = [view(host.FIRST_TABLE + g).view(R, -1) for g in range(len(packed.widths))]
         ctx.__dict__.update(host_lists)
         return ctx
+
+    def _build_context(self, entries: Sequence[StepEntry], table_round: int = 8) -> StepContext:
+        return self._upload(self._pack(entries, table_round), entries)
 
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
@@ -354,14 +321,12 @@ class ModelRunner:
             ops.scatter_tokens(ctx.token_ids, ctx.pend_dst, token_source, ctx.pend_src)
 
     def _graph_step(self, entries: Sequence[StepEntry], token_source=None) -> Optional[torch.Tensor]:
-        recs = [self.manager.record(e.request_id) for e in entries]
-        widths = tuple(_round_up(max(len(rec.tables[g]) for rec in recs), GRAPH_TABLE_ROUND)
-                       for g in range(len(self.manager.groups)))
-        key = (len(entries), tuple(len(e.want) for e in entries), widths)
+        packed = self._pack(entries, GRAPH_TABLE_ROUND)
+        key = (len(entries), tuple(len(e.want) for e in entries), tuple(packed.widths))
         graph = self._graphs.get(key)
         if graph is None:
             graph = _DecodeGraph()
-            ctx = self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            ctx = self._upload(packed, entries, graph)
             self._feed_device_tokens(ctx, entries, token_source)
             self.model.forward(ctx)  # warm-up: sizes the workspace; rewrites the same keys and values
             torch.cuda.current_stream().synchronize()
@@ -379,13 +344,25 @@ class ModelRunner:
                     gc.enable()
             self._graphs[key] = graph
         else:
-            ctx = self._build_context(entries, GRAPH_TABLE_ROUND, graph)
+            ctx = self._upload(packed, entries, graph)
             self._feed_device_tokens(ctx, entries, token_source)
         graph.graph.replay()
         return graph.logits
 
 
 GRAPH_TABLE_ROUND = 64  # block-table width of a captured step, in pages
+
+
+@dataclass
+class _PackedStep:
+    """A step's index arrays in pinned host memory, as the host library laid them out."""
+    host: torch.Tensor
+    flip: int
+    total: int
+    offsets: List[int]
+    sizes: List[int]
+    widths: List[int]
+    shape: List[int]
 
 
 class _DecodeGraph:

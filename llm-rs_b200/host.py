@@ -1,0 +1,61 @@
+"""Python face of the host library (C++ under ``csrc/host/``): page pools, the cache
+manager and the packing of a step's index arrays. The bookkeeping runs in the library;
+the classes in ``cache`` and ``engine.runner`` hold its handles.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, byref, c_int, c_int32, c_int64, c_void_p
+
+from .csrc import build as _build
+
+OK, CACHE_ERROR, OUT_OF_PAGES, NO_FREE_SLOT, BAD_ARGUMENT = range(5)
+
+# Order of the arrays in a packed step (StepArray in csrc/host/cache_manager.hpp).
+(TOKEN_IDS, POSITIONS, TOKEN_REQ, Q_START, N_NEW, CACHED_LEN, SLOT_IDS, WANT_ROWS, PREFILL_TILES, DECODE_REQS,
+ PEND_DST, PEND_SRC, FIRST_TABLE) = range(13)
+
+_configured = False
+
+
+def lib() -> ctypes.CDLL:
+    global _configured
+    library = _build.host_library()
+    if not _configured:
+        i32p, i64p, intp = POINTER(c_int32), POINTER(c_int64), POINTER(c_int)
+        sigs = {
+            "llmrs_pool_create": [c_int, POINTER(c_void_p)],
+            "llmrs_pool_destroy": [c_void_p],
+            "llmrs_pool_allocate": [c_void_p, i32p],
+            "llmrs_pool_free": [c_void_p, c_int32, intp],
+            "llmrs_pool_increment_ref": [c_void_p, c_int32],
+            "llmrs_pool_ref_count": [c_void_p, c_int32, intp],
+            "llmrs_pool_counts": [c_void_p, intp, intp],
+            "llmrs_cm_create": [intp, intp, c_int, c_int, c_int, POINTER(c_void_p)],
+            "llmrs_cm_destroy": [c_void_p],
+            "llmrs_cm_admit": [c_void_p, c_int64, intp],
+            "llmrs_cm_release": [c_void_p, c_int64],
+            "llmrs_cm_pages_needed": [c_void_p, c_int, c_int64, c_int, c_int, intp],
+            "llmrs_cm_reserve": [c_void_p, c_int64, c_int],
+            "llmrs_cm_cancel": [c_void_p, c_int64],
+            "llmrs_cm_commit": [c_void_p, c_int64, c_int],
+            "llmrs_cm_info": [c_void_p, c_int64, intp, i64p],
+            "llmrs_cm_table": [c_void_p, c_int64, c_int, i32p, c_int, intp],
+            "llmrs_cm_pool_counts": [c_void_p, c_int, intp, intp],
+            "llmrs_cm_check_invariants": [c_void_p],
+            "llmrs_pack_step": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, i64p, intp],
+        }
+        for name, argtypes in sigs.items():
+            fn = getattr(library, name)
+            fn.argtypes = argtypes
+            fn.restype = None if name.endswith("_destroy") else c_int
+        _configured = True
+    return library
+
+
+def last_error() -> str:
+    return lib().llmrs_host_last_error().decode("utf-8", "replace")
+
+
+__all__ = ["lib", "last_error", "byref", "c_int", "c_int32", "c_int64", "c_void_p"]
