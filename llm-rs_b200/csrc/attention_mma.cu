@@ -46,7 +46,8 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   constexpr int TILE_ELEMS = DM_TILE * ROW;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
-  pdl_wait();
+  // Up to the wait below only data of earlier steps is read: the step's index arrays and
+  // cached keys and values other than the newest position (the only one written in this step).
 
   const int G = n_q_heads / n_kv_heads;
   const int hgroups = (G + 15) / 16;
@@ -70,20 +71,6 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   const int n_my = n_tiles > warp ? (n_tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
 
   bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * DM_STAGES * 2 * TILE_ELEMS;
-
-  // Query rows as A fragments: row gq is head g0+gq, row gq+8 is head g0+gq+8; absent heads are zero.
-  uint32_t qf[DCH][4];
-  {
-    const bf16* qt = q + (size_t)q_start[req] * q_stride + (size_t)(kvh * G + g0) * D;
-#pragma unroll
-    for (int kc = 0; kc < DCH; ++kc) {
-      const int col = kc * 16 + tq * 2;
-      qf[kc][0] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col) : 0u;
-      qf[kc][1] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col) : 0u;
-      qf[kc][2] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col + 8) : 0u;
-      qf[kc][3] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col + 8) : 0u;
-    }
-  }
 
   // When a page holds whole 16-key tiles, a tile is one contiguous run of rows in one
   // page: lane j keeps the page of the warp's j-th tile (of the current 32), so the
@@ -148,11 +135,36 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   const float sl2 = scale * LOG2E;
 
+  // The first tiles are requested before the wait on the preceding kernels (they overlap
+  // those kernels' tails), except a tile that holds the newest key, which this step writes.
+  const int new_tile = (kv_len - 1) / DM_TILE;
 #pragma unroll
   for (int s = 0; s < DM_STAGES - 1; ++s) {
-    if (s < n_my) load_tile(s, s);
+    if (s < n_my && tile_first + warp + s * DM_WARPS < new_tile) load_tile(s, s);
     cp_async_commit();
   }
+  pdl_wait();
+#pragma unroll
+  for (int s = 0; s < DM_STAGES - 1; ++s) {
+    if (s < n_my && tile_first + warp + s * DM_WARPS >= new_tile) load_tile(s, s);
+    cp_async_commit();
+  }
+  // Query rows as A fragments: row gq is head g0+gq, row gq+8 is head g0+gq+8; absent heads are zero.
+  uint32_t qf[DCH][4];
+  {
+    const bf16* qt = q + (size_t)q_start[req] * q_stride + (size_t)(kvh * G + g0) * D;
+#pragma unroll
+    for (int kc = 0; kc < DCH; ++kc) {
+      const int col = kc * 16 + tq * 2;
+      qf[kc][0] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col) : 0u;
+      qf[kc][1] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col) : 0u;
+      qf[kc][2] = gq < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)gq * D + col + 8) : 0u;
+      qf[kc][3] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col + 8) : 0u;
+    }
+  }
+  // The ring was filled with 2 * (DM_STAGES - 1) groups: tile s (s < DM_STAGES - 1) lies in group
+  // s or DM_STAGES - 1 + s, tile i >= DM_STAGES - 1 in group DM_STAGES - 1 + i. Leaving the newest
+  // DM_STAGES - 2 groups pending at iteration i still covers tile i.
   for (int i = 0; i < n_my; ++i) {
     cp_async_wait<DM_STAGES - 2>();
     __syncwarp();
