@@ -382,7 +382,10 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* KV = reinterpret_cast<bf16*>(smem_raw);     // 2 stages x (K [64][ROW], V [64][ROW])
 
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // Blocks start in the order of blockIdx.x: all heads of the last tile first (a later tile of a
+  // prompt sees more keys), so that the long blocks do not end the kernel alone.
+  const int head = blockIdx.x % n_q_heads;
+  const int tile = (int)(gridDim.x / n_q_heads) - 1 - (int)(blockIdx.x / n_q_heads);
   const int kvh = head / (n_q_heads / n_kv_heads);
   const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
   const int rows = min(PM_BQ, n_new[req] - q_off);
@@ -560,7 +563,8 @@ static int launch_prefill_mma(const void* q, long long q_stride, void* out, long
     if (e != cudaSuccess) return llmrs_fail("attn_prefill_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = smem;
   }
-  dim3 grid(n_tiles, n_q_heads);
+  if ((long long)n_tiles * n_q_heads > 2147483647LL) return llmrs_fail("attn_prefill_mma: %d tiles are too many", n_tiles);
+  dim3 grid((unsigned)n_tiles * (unsigned)n_q_heads);
   attn_prefill_mma_kernel<DCH><<<grid, PM_THREADS, smem, stream>>>(
       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, tiles, q_start, n_new, cached_len,
       block_table, table_stride, n_q_heads, n_kv_heads, page_size, window, scale);

@@ -172,8 +172,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   volatile int* page_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // Later tiles of a prompt see more keys: run them first so that the long blocks do not end the kernel alone.
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  // Later tiles of a prompt see more keys: run them first, for every head, so that the long blocks
+  // do not end the kernel alone (blocks start in the order of blockIdx.x, then blockIdx.y).
+  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
   const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
   if (q_off % AT_BQ != 0) return;           // the list names tiles of 64 queries; a block takes two
   if ((sm(base) & 1023u) != 0) {            // never seen; without the alignment the operands would be garbage
@@ -511,7 +512,7 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
     if (e != cudaSuccess) return llmrs_fail("attn_prefill_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(n_tiles, n_q_heads);
+  dim3 grid(n_q_heads, n_tiles);
   attn_prefill_tc_kernel<<<grid, AT_THREADS + 32, smem, stream>>>(map_q, map_kv, (bf16*)out, out_stride, tiles, q_start,
                                                               n_new, cached_len, block_table, table_stride, n_q_heads,
                                                               n_kv_heads, page_size, window, scale);
