@@ -2,22 +2,25 @@
 //
 // A block owns 128 query tokens of one request and one query head; its thread r owns
 // query row r, which is lane r of tensor memory, so the softmax needs no exchange
-// between threads. Per tile of 64 keys:
-//   S = Q K^T   tcgen05.mma, 128x64x128, Q and K in shared memory (TMA, 128-byte swizzle),
-//               S in tensor memory (64 columns of float32);
+// between threads. Shared memory feeds the tensor cores at roughly 64 bytes a cycle, less
+// than two operands of an MMA want, so the left operand of both products lives in tensor
+// memory and shared memory holds only K and V. Per tile of 64 keys:
+//   S = Q K^T   tcgen05.mma, 128x64x128; Q sits in tensor memory (each thread put its row
+//               there once), K in shared memory (TMA, 128-byte swizzle); S goes to tensor
+//               memory (64 columns of float32);
 //   softmax     every thread reads its row of S (tcgen05.ld), masks it if the tile touches
 //               the diagonal or the window's edge, and writes P = 2^(s*c - m) as bfloat16
-//               into shared memory in the layout the MMA expects. The reference maximum m
+//               pairs over the first 32 columns of S (tcgen05.st). The reference maximum m
 //               of a row only moves when the row's maximum grew by more than 8 (a factor
 //               256): then, and only then, the row of O in tensor memory is rescaled
 //               (tcgen05.ld, multiply, tcgen05.st);
-//   O += P V    tcgen05.mma, 128x128x64; V is used as it lies in its pages (keys x head_dim,
-//               MN-major operand).
-// A fifth warp issues the TMA copies (one 16-key box per page and half of the head) and the
-// MMAs, so the softmax threads never wait for issue work. K, V and S are double-buffered:
-// while the threads work on the softmax of tile j the tensor cores already compute S of
-// tile j+1, and the copies of tiles j+1 / j+2 are under way. The roles meet at mbarriers
-// only. Two blocks share an SM. Blocks with the longest rows of keys are scheduled first.
+//   O += P V    tcgen05.mma, 128x128x64; P is read from tensor memory, V is used as it lies
+//               in its pages (keys x head_dim, MN-major operand).
+// A fifth warp issues the TMA copies (one 16-key box per page and half of the head, sixteen
+// boxes of a tile side by side) and the MMAs, so the softmax threads never wait for issue
+// work. K and V go through a ring of three stages. The roles meet at mbarriers only. Two
+// blocks share an SM: while one does its softmax the other's MMAs run. Blocks with the
+// longest rows of keys are scheduled first.
 //
 // Same contract and math as attn_prefill_kernel in attention.cu (scores, softmax and the
 // weighted sum accumulate in float32; llm-core/src/backends/candle.rs:1587-1640). Every
@@ -32,11 +35,13 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int AT_BQ = 128, AT_BK = 64, AT_D = 128, AT_THREADS = 128;
+constexpr int AT_BQ = 128, AT_BK = 64, AT_D = 128, AT_THREADS = 128, AT_STAGES = 3;
 constexpr uint32_t AT_WAIT_LIMIT = 1u << 22;
 constexpr float AT_LOG2E = 1.4426950408889634f;
-constexpr uint32_t Q_BYTES = AT_BQ * AT_D * 2, K_BYTES = AT_BK * AT_D * 2, V_BYTES = K_BYTES, P_BYTES = AT_BQ * AT_BK * 2;
-constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 128;   // S twice (64 columns each), then O
+constexpr uint32_t K_BYTES = AT_BK * AT_D * 2, V_BYTES = K_BYTES, STAGE_BYTES = K_BYTES + V_BYTES;
+// Tensor memory of a block: S (64 columns of float32; P, as bfloat16 pairs, goes over its first 32),
+// O (128 columns), Q (128 bfloat16 = 64 columns).
+constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 64, Q_COL = 192;
 
 __device__ int g_attn_tc_error = 0;
 
@@ -89,12 +94,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __host__ __device__ constexpr uint32_t instr_desc(int n, int b_mn) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
-__device__ __forceinline__ void mma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+// D (+)= A B with A in tensor memory (lane = row, two bfloat16 per column, 8 columns per k16 step)
+// and B described in shared memory.
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b, uint32_t idesc, uint32_t acc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(acc)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void commit(uint32_t bar) {
@@ -131,6 +138,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
 }
+__device__ __forceinline__ void tmem_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -145,30 +162,30 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 }
 
 // Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. Warp 4 feeds
-// them: its lanes 0-7 issue the TMA copies of a tile side by side, its lane 0 every MMA. Nobody meets
+// them: its lanes 0-15 issue the TMA copies of a tile side by side, its lane 0 every MMA. Nobody meets
 // at a block-wide barrier inside the loop; the roles talk through mbarriers:
-//   q, k[2], v[2]  bytes of the TMA copies have landed
-//   s[2]           S of a tile is in tensor memory (tcgen05.commit)
-//   pv             O += P V of a tile is done (tcgen05.commit): P, O and that V buffer are free
-//   p              all 128 softmax threads have written P of a tile (and are done with its S)
+//   q              all 128 threads have put their query rows into tensor memory
+//   full[3]        K and V of a tile have landed in their stage (TMA bytes)
+//   free[3]        O += P V of the tile in that stage is done (tcgen05.commit): the stage may be refilled
+//   s              S of a tile is in tensor memory, and with it everything issued earlier (tcgen05.commit
+//                  tracks all earlier MMAs of the issuing thread), in particular O += P V of the tile before
+//   p              all 128 threads have written P of a tile over its S
+//   done           the last O += P V is done
 __global__ void __launch_bounds__(AT_THREADS + 32)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, long long q_stride,
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
                        int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
-  unsigned char* Qs = base;                 // 2 halves of [128 rows][64 dims]
-  unsigned char* Ks = Qs + Q_BYTES;         // 2 stages x 2 halves of [64 keys][64 dims]
-  unsigned char* Vs = Ks + 2 * K_BYTES;     // 2 stages x 2 halves of [64 keys][64 dims]
-  unsigned char* Ps = Vs + 2 * V_BYTES;     // [128 rows][64 keys]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);   // q, k0, k1, v0, v1, s0, s1, pv, p, vfree0, vfree1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  unsigned char* KV = base;                 // AT_STAGES x (K: 2 halves of [64 keys][64 dims], then V the same)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // full[3], free[3], q, s, p, done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // Pages of the coming tiles, read from the block table three tiles ahead by four softmax
-  // threads (the issuing thread never waits for global memory): tile t's four pages sit in
-  // ring slot t % 4 (-1: no copy). The issuing thread sees them through barrier p.
+  // threads (the issuing warp never waits for global memory): tile t's four pages sit in
+  // ring slot t % 4 (-1: no copy). The issuing warp sees them through barrier p.
   volatile int* page_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -191,13 +208,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int n_tiles = (kv_hi - kv_lo + AT_BK - 1) / AT_BK;
   const int* table = block_table + (size_t)req * table_stride;
 
-  const uint32_t bar_q = sm(bars), bar_k = sm(bars + 1), bar_v = sm(bars + 3), bar_s = sm(bars + 5), bar_pv = sm(bars + 7),
-                 bar_p = sm(bars + 8), bar_vfree = sm(bars + 9);
+  const uint32_t bar_full = sm(bars), bar_free = sm(bars + AT_STAGES), bar_q = sm(bars + 2 * AT_STAGES),
+                 bar_s = bar_q + 8, bar_p = bar_q + 16, bar_done = bar_q + 24;
   if (tid == 0) {
-    for (int i = 0; i < 8; ++i) bar_init(sm(bars + i));
+    for (int i = 0; i < 2 * AT_STAGES; ++i) bar_init(sm(bars + i));
+    bar_init_n(bar_q, AT_THREADS);
+    bar_init(bar_s);
     bar_init_n(bar_p, AT_THREADS);
-    bar_init(bar_vfree);
-    bar_init(bar_vfree + 8);
+    bar_init(bar_done);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -207,8 +225,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   };
   if (tid < 12) fetch_pages(tid >> 2, tid & 3);
   // Rows of K and V that no copy fills (keys past the end) must not hold NaN patterns.
-  for (uint32_t i = tid * 16; i < 2 * K_BYTES + 2 * V_BYTES; i += (AT_THREADS + 32) * 16)
-    *reinterpret_cast<uint4*>(Ks + i) = make_uint4(0u, 0u, 0u, 0u);
+  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 32) * 16)
+    *reinterpret_cast<uint4*>(KV + i) = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm(tmem_slot)), "r"(TMEM_COLS)
@@ -221,119 +239,118 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
 
-  // Copies of tile t, issued by the whole issuing warp at once: per page of 16 keys two boxes
-  // (the halves of head_dim), one box per lane (lanes 0-7), so that eight copies cost the warp
-  // one instruction slot instead of eight in a row.
-  auto load_kv = [&](int which, int t, unsigned char* dst, uint32_t bar) {
-    const int i = (lane >> 1) & 3, h = lane & 1;
-    const int page = page_ring[(t & 3) * 4 + i];
-    const unsigned live = __ballot_sync(0xffffffffu, lane < 8 && page >= 0);
-    if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * 16 * 128);
-    __syncwarp();
-    if (lane < 8 && page >= 0) {
-      const int key = kv_lo + t * AT_BK + 16 * i;
-      const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
-      tma_2d(sm(dst) + h * 8192 + i * 2048, &map_kv, bar, h * 64, row);
-    }
-    __syncwarp();
-  };
-
   if (warp == 4) {
     // ---- the issuing warp: all lanes walk the loop together; lane 0 issues the MMAs -----------
-    auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2
+    // Copies of tile t into its stage, issued by sixteen lanes at once: per page of 16 keys and
+    // per K / V two boxes (the halves of head_dim), one box per lane, so that the sixteen copies
+    // cost the warp one instruction slot instead of sixteen in a row.
+    auto load_tile = [&](int t) {
+      const int st = t % AT_STAGES;
+      const int which = (lane >> 3) & 1, i = (lane >> 1) & 3, h = lane & 1;
+      const int page = page_ring[(t & 3) * 4 + i];
+      const unsigned live = __ballot_sync(0xffffffffu, lane < 16 && page >= 0);
+      const uint32_t bar = bar_full + 8 * st;
+      if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * 2048);
+      __syncwarp();
+      if (lane < 16 && page >= 0) {
+        const int key = kv_lo + t * AT_BK + 16 * i;
+        const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
+        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * 8192 + i * 2048, &map_kv, bar, h * 64, row);
+      }
+      __syncwarp();
+    };
+    auto issue_s = [&](int t) {     // S_t = Q K_t^T; Q is read from tensor memory
       if (lane == 0) {
-        const uint32_t kbuf = sm(Ks) + (t & 1) * K_BYTES;
+        const uint32_t kbuf = sm(KV) + (t % AT_STAGES) * STAGE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_D / 16; ++kk) {
           const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
-          const uint64_t a = smem_desc(sm(Qs) + half * 16384 + (kk % 4) * 32, 16, 1024);
           const uint64_t bd = smem_desc(kbuf + half * 8192 + (kk % 4) * 32, 16, 1024);
-          mma(tmem + S_COL + (t & 1) * AT_BK, a, bd, idesc_s, kk > 0 ? 1u : 0u);
+          mma_ts(tmem + S_COL, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
         }
-        commit(bar_s + 8 * (t & 1));
+        commit(bar_s);
       }
       __syncwarp();
     };
     auto wait_all = [&](uint32_t bar, uint32_t parity) {
       return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
     };
-    if (lane == 0) {
-      bar_expect(bar_q, Q_BYTES);
-      tma_2d(sm(Qs), &map_q, bar_q, head * AT_D, tok0);
-      tma_2d(sm(Qs) + 16384, &map_q, bar_q, head * AT_D + 64, tok0);
-    }
-    __syncwarp();
-    load_kv(0, 0, Ks, bar_k);
-    load_kv(1, 0, Vs, bar_v);
-    if (n_tiles > 1) {
-      load_kv(0, 1, Ks + K_BYTES, bar_k + 8);
-      load_kv(1, 1, Vs + V_BYTES, bar_v + 8);
-    }
-    bool ok = wait_all(bar_q, 0) && wait_all(bar_k, 0);
+    for (int t = 0; t < n_tiles && t < AT_STAGES; ++t) load_tile(t);
+    bool ok = wait_all(bar_q, 0) && wait_all(bar_full, 0);
     if (ok) {
       fence_after();
       issue_s(0);
     }
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      // S of the next tile: its K has landed, and the softmax threads are done with that S
-      // buffer (they said so with P of tile j-1, which was waited for before O += P V of j-1).
-      if (j + 1 < n_tiles) {
-        ok = wait_all(bar_k + 8 * (b ^ 1), ((j + 1) >> 1) & 1);
-        if (!ok) break;
-        fence_after();
-        issue_s(j + 1);
-        // V of the next tile into the buffer that O += P V of tile j-1 has released.
-        if (j >= 1) {
-          ok = wait_all(bar_vfree + 8 * (b ^ 1), ((j - 1) >> 1) & 1);
-          if (!ok) break;
-          load_kv(1, j + 1, Vs + (b ^ 1) * V_BYTES, bar_v + 8 * (b ^ 1));
-        }
-      }
-      // K buffer b is free once S_j is done.
-      if (j + 2 < n_tiles) {
-        ok = wait_all(bar_s + 8 * b, (j >> 1) & 1);
-        if (!ok) break;
-        load_kv(0, j + 2, Ks + b * K_BYTES, bar_k + 8 * b);
-      }
-      // O += P V of tile j: P is written, V has landed.
-      ok = wait_all(bar_p, j & 1) && wait_all(bar_v + 8 * b, (j >> 1) & 1);
+      const int st = j % AT_STAGES;
+      // O += P V of tile j: P is written (its V landed with its K).
+      ok = wait_all(bar_p, j & 1);
       if (!ok) break;
       fence_after();
       if (lane == 0) {
-        const uint32_t vbuf = sm(Vs) + b * V_BYTES;
+        const uint32_t vbuf = sm(KV) + st * STAGE_BYTES + K_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_BK / 16; ++kk) {
-          const uint64_t a = smem_desc(sm(Ps) + kk * 32, 16, 1024);
           const uint64_t bd = smem_desc(vbuf + kk * 2048, 8192, 1024);
-          mma(tmem + O_COL, a, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts(tmem + O_COL, tmem + S_COL + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        commit(bar_pv);
-        commit(bar_vfree + 8 * b);    // the same completion, counted per V buffer (its phases cannot run ahead of the loader)
+        commit(bar_free + 8 * st);
       }
       __syncwarp();
+      // S of the next tile goes over P of this one: the tensor cores run MMAs in the order of issue.
+      if (j + 1 < n_tiles) {
+        ok = wait_all(bar_full + 8 * ((j + 1) % AT_STAGES), ((j + 1) / AT_STAGES) & 1);
+        if (!ok) break;
+        fence_after();
+        issue_s(j + 1);
+      }
+      // The stage of tile j is free once its O += P V is done: refill it.
+      if (j + AT_STAGES < n_tiles) {
+        ok = wait_all(bar_free + 8 * st, (j / AT_STAGES) & 1);
+        if (!ok) break;
+        load_tile(j + AT_STAGES);
+      }
     }
+    if (lane == 0) commit(bar_done);
+    __syncwarp();
   } else {
     // ---- softmax threads ------------------------------------------------------------------
     const int row = tid;                      // this thread's query row = its lane of tensor memory
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    // The query row goes into tensor memory (two bfloat16 per column), where Q K^T reads it as its
+    // A operand: shared memory then only has to feed K.
+    {
+      const uint4* qrow = reinterpret_cast<const uint4*>(q + (size_t)(tok0 + row) * q_stride + (size_t)head * AT_D);
+#pragma unroll
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        uint32_t r[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 v = row < rows ? qrow[hlf * 8 + c] : make_uint4(0u, 0u, 0u, 0u);
+          r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
+        }
+        tmem_st32u(lane_addr + Q_COL + hlf * 32, r);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      fence_before();
+      bar_arrive(bar_q);
+    }
     const int my_pos = pos0 + row;
     const float sl2 = scale * AT_LOG2E;
     float m_ref = -INFINITY, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int kb = kv_lo + j * AT_BK;
-      const int b = j & 1;
-      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * b, (j >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, bar_wait(bar_s, j & 1, abort_flag));
       if (!ok) break;
       fence_after();
       if (tid >= 32 && tid < 36) fetch_pages(j + 3, tid - 32);   // published by this tile's arrival on barrier p
-      // This thread's 64 scores -> probabilities (kept in registers until the P buffer is free).
+      // This thread's 64 scores -> probabilities.
       float s[AT_BK];
       {
         float t0[32], t1[32];
-        tmem_ld32(lane_addr + S_COL + b * AT_BK, t0);
-        tmem_ld32(lane_addr + S_COL + b * AT_BK + 32, t1);
+        tmem_ld32(lane_addr + S_COL, t0);
+        tmem_ld32(lane_addr + S_COL + 32, t1);
 #pragma unroll
         for (int c = 0; c < 32; ++c) { s[c] = t0[c]; s[32 + c] = t1[c]; }
       }
@@ -366,29 +383,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         l_sum *= factor;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      uint4 pk[AT_BK / 8];
+      uint32_t pk[AT_BK / 2];
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int ch = 0; ch < AT_BK / 8; ++ch) {
-        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk[ch]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(fmaf(s[ch * 8 + 2 * e], sl2, -m_use));
-          const float p1 = ex2(fmaf(s[ch * 8 + 2 * e + 1], sl2, -m_use));
-          sum4[e] += p0 + p1;
-          h2[e] = __floats2bfloat162_rn(p0, p1);
-        }
+      for (int c = 0; c < AT_BK / 2; ++c) {
+        const float p0 = ex2(fmaf(s[2 * c], sl2, -m_use));
+        const float p1 = ex2(fmaf(s[2 * c + 1], sl2, -m_use));
+        sum4[c & 3] += p0 + p1;
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+        pk[c] = *reinterpret_cast<const uint32_t*>(&h2);
       }
       l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // O += P V of the previous tile is done: its P and O are free.
-      if (j > 0) {
-        ok = __all_sync(0xffffffffu, bar_wait(bar_pv, (j - 1) & 1, abort_flag));
-        if (!ok) break;
-        fence_after();
-      }
-      // Rescale O where a row's reference moved (rare after the first tiles; the loads and stores
-      // of tensor memory are warp-wide, so the warp decides together), then hand P over: row r is
-      // 128 bytes, its 16-byte chunk c sits at c ^ (r % 8).
+      // S of this tile being there means that O += P V of the tile before is done: O may be
+      // rescaled where a row's reference moved (rare after the first tiles; the loads and stores
+      // of tensor memory are warp-wide, so the warp decides together). Then P goes over S.
       if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll 1
         for (int c = 0; c < AT_D; c += 32) {
@@ -398,16 +406,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int e = 0; e < 32; ++e) o[e] *= factor;
           tmem_st32(lane_addr + O_COL + c, o);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       }
-#pragma unroll
-      for (int ch = 0; ch < AT_BK / 8; ++ch)
-        *reinterpret_cast<uint4*>(Ps + row * 128 + ((ch ^ (row & 7)) * 16)) = pk[ch];
+      tmem_st32u(lane_addr + S_COL, pk);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       fence_before();
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P written by threads, read by the MMA
       bar_arrive(bar_p);
     }
-    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_pv, (n_tiles - 1) & 1, abort_flag));
+    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_done, 0, abort_flag));
     fence_after();
     if (ok) {
       // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
@@ -436,9 +441,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (*abort_flag && tid == AT_THREADS) {
     atomicExch(&g_attn_tc_error, 1);
     // Copies may still be on their way into this block's shared memory.
-    bar_wait(bar_q, 0, abort_flag);
-    for (int i = 0; i < 2; ++i)
-      for (int ph = 0; ph < 2; ++ph) { bar_wait(bar_k + 8 * i, ph, abort_flag); bar_wait(bar_v + 8 * i, ph, abort_flag); }
+    for (int i = 0; i < AT_STAGES; ++i)
+      for (int ph = 0; ph < 2; ++ph) bar_wait(bar_full + 8 * i, ph, abort_flag);
   }
   __syncthreads();
   if (warp == 4) {
@@ -501,11 +505,11 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
                           const int* n_new, const int* cached_len, const int* block_table, int table_stride,
                           int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
                           cudaStream_t stream) {
-  CUtensorMap map_q, map_kv;
+  CUtensorMap map_kv;
   int rc;
-  if ((rc = make_map(&map_q, q, n_tokens, (long long)n_q_heads * AT_D, q_stride, AT_BQ))) return rc;
+  (void)n_tokens;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, 16))) return rc;
-  const size_t smem = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + 11 * 8 + 8 + 16 * 4;
+  const size_t smem = AT_STAGES * STAGE_BYTES + (2 * AT_STAGES + 4) * 8 + 8 + 16 * 4;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -513,8 +517,9 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
     configured = true;
   }
   dim3 grid(n_q_heads, n_tiles);
-  attn_prefill_tc_kernel<<<grid, AT_THREADS + 32, smem, stream>>>(map_q, map_kv, (bf16*)out, out_stride, tiles, q_start,
-                                                              n_new, cached_len, block_table, table_stride, n_q_heads,
-                                                              n_kv_heads, page_size, window, scale);
+  attn_prefill_tc_kernel<<<grid, AT_THREADS + 32, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+                                                              tiles, q_start, n_new, cached_len, block_table,
+                                                              table_stride, n_q_heads, n_kv_heads, page_size, window,
+                                                              scale);
   return llmrs_launch_status("attn_prefill_tc");
 }
