@@ -16,11 +16,12 @@
 //               (tcgen05.ld, multiply, tcgen05.st);
 //   O += P V    tcgen05.mma, 128x128x64; P is read from tensor memory, V is used as it lies
 //               in its pages (keys x head_dim, MN-major operand).
-// A fifth warp issues the TMA copies (one 16-key box per page and half of the head, sixteen
-// boxes of a tile side by side) and the MMAs, so the softmax threads never wait for issue
-// work. K and V go through a ring of three stages. The roles meet at mbarriers only. Two
-// blocks share an SM: while one does its softmax the other's MMAs run. Blocks with the
-// longest rows of keys are scheduled first.
+// A fifth warp issues the MMAs and a sixth the TMA copies (one box per page, or per 64 keys of
+// a larger page, and half of the head; the boxes of a tile are issued by as many lanes side by
+// side, since one copy costs its issuer some 80 cycles), so the softmax threads never wait for
+// issue work and the copies never delay an MMA. K and V go through a ring of three stages. The
+// roles meet at mbarriers only. Two blocks share an SM: while one does its softmax the other's
+// MMAs run. Blocks with the longest rows of keys are scheduled first.
 //
 // Same contract and math as attn_prefill_kernel in attention.cu (scores, softmax and the
 // weighted sum accumulate in float32; llm-core/src/backends/candle.rs:1587-1640). Every
@@ -104,6 +105,12 @@ __device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_
       ::"r"(tmem_d), "r"(tmem_a), "l"(b), "r"(idesc), "r"(acc)
       : "memory");
 }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t leader;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+  return leader != 0;
+}
 __device__ __forceinline__ void commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -161,9 +168,9 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. Warp 4 feeds
-// them: its lanes 0-15 issue the TMA copies of a tile side by side, its lane 0 every MMA. Nobody meets
-// at a block-wide barrier inside the loop; the roles talk through mbarriers:
+// Threads 0..127 (warps 0-3) are the softmax threads: thread r owns query row r. One lane of warp 4
+// issues every MMA, the lanes of warp 5 the TMA copies. Nobody meets at a block-wide barrier inside
+// the loop; the roles talk through mbarriers:
 //   q              all 128 threads have put their query rows into tensor memory
 //   full[3]        K and V of a tile have landed in their stage (TMA bytes)
 //   free[3]        O += P V of the tile in that stage is done (tcgen05.commit): the stage may be refilled
@@ -171,22 +178,18 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 //                  tracks all earlier MMAs of the issuing thread), in particular O += P V of the tile before
 //   p              all 128 threads have written P of a tile over its S
 //   done           the last O += P V is done
-__global__ void __launch_bounds__(AT_THREADS + 32)
+__global__ void __launch_bounds__(AT_THREADS + 64, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, long long q_stride,
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
-                       int n_q_heads, int n_kv_heads, int page_size, int window, float scale) {
+                       int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
   unsigned char* KV = base;                 // AT_STAGES x (K: 2 halves of [64 keys][64 dims], then V the same)
   uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // full[3], free[3], q, s, p, done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // Pages of the coming tiles, read from the block table three tiles ahead by four softmax
-  // threads (the issuing warp never waits for global memory): tile t's four pages sit in
-  // ring slot t % 4 (-1: no copy). The issuing warp sees them through barrier p.
-  volatile int* page_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // Later tiles of a prompt see more keys: run them first, for every head, so that the long blocks
@@ -219,13 +222,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  auto fetch_pages = [&](int t, int i) {     // page of keys kv_lo + 64 t + 16 i .. + 15, or -1
-    const int key = kv_lo + t * AT_BK + 16 * i;
-    page_ring[(t & 3) * 4 + i] = (t < n_tiles && key < kv_hi && key + 15 >= key_floor) ? table[key / page_size] : -1;
-  };
-  if (tid < 12) fetch_pages(tid >> 2, tid & 3);
   // Rows of K and V that no copy fills (keys past the end) must not hold NaN patterns.
-  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 32) * 16)
+  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 64) * 16)
     *reinterpret_cast<uint4*>(KV + i) = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 4) {
@@ -239,43 +237,59 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
 
-  if (warp == 4) {
-    // ---- the issuing warp: all lanes walk the loop together; lane 0 issues the MMAs -----------
-    // Copies of tile t into its stage, issued by sixteen lanes at once: per page of 16 keys and
-    // per K / V two boxes (the halves of head_dim), one box per lane, so that the sixteen copies
-    // cost the warp one instruction slot instead of sixteen in a row.
-    auto load_tile = [&](int t) {
+  auto wait_all = [&](uint32_t bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
+  };
+  if (warp == 5) {
+    // ---- the copying warp: one box per lane; a lane's box of tile t is the same part of every tile
+    const int per_half = AT_BK / box_rows;            // boxes per K or V and half of the head: 4 or 1
+    const int n_boxes = 4 * per_half;
+    const int which = lane / (2 * per_half), h = (lane / per_half) & 1, i = lane % per_half;
+    const uint32_t box_bytes = (uint32_t)box_rows * 128;
+    auto page_of = [&](int t) {     // page of this lane's box of tile t, or -1 (the lane copies nothing)
+      const int key = kv_lo + t * AT_BK + box_rows * i;
+      return (lane < n_boxes && t < n_tiles && key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : -1;
+    };
+    auto load_tile = [&](int t, int page) {
       const int st = t % AT_STAGES;
-      const int which = (lane >> 3) & 1, i = (lane >> 1) & 3, h = lane & 1;
-      const int page = page_ring[(t & 3) * 4 + i];
-      const unsigned live = __ballot_sync(0xffffffffu, lane < 16 && page >= 0);
+      const unsigned live = __ballot_sync(0xffffffffu, page >= 0);
       const uint32_t bar = bar_full + 8 * st;
-      if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * 2048);
+      if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * box_bytes);
       __syncwarp();
-      if (lane < 16 && page >= 0) {
-        const int key = kv_lo + t * AT_BK + 16 * i;
+      if (page >= 0) {
+        const int key = kv_lo + t * AT_BK + box_rows * i;
         const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
-        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * 8192 + i * 2048, &map_kv, bar, h * 64, row);
+        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * 8192 + i * box_bytes, &map_kv, bar, h * 64, row);
       }
       __syncwarp();
     };
+    for (int t = 0; t < n_tiles && t < AT_STAGES; ++t) load_tile(t, page_of(t));
+    int page = page_of(AT_STAGES);                    // looked up one tile ahead of its copy
+    for (int j = 0; j + AT_STAGES < n_tiles; ++j) {
+      const int next = page_of(j + AT_STAGES + 1);
+      // The stage of tile j is free once its O += P V is done.
+      if (!wait_all(bar_free + 8 * (j % AT_STAGES), (j / AT_STAGES) & 1)) break;
+      load_tile(j + AT_STAGES, page);
+      page = next;
+    }
+  } else if (warp == 4) {
+    // ---- the MMA warp: all lanes walk the loop together; lane 0 issues -------------------------
+    // One elected lane issues, but the whole warp computes the operands of every MMA: they are then
+    // the same in all lanes, which lets the compiler keep them in uniform registers, where the MMA
+    // wants them. Issued from a divergent branch (`if (lane == 0)`) an MMA of this size costs its
+    // thread some 120 cycles instead of the 32 to 64 that the tensor cores need for it.
+    const bool leader = elect_one();
     auto issue_s = [&](int t) {     // S_t = Q K_t^T; Q is read from tensor memory
-      if (lane == 0) {
-        const uint32_t kbuf = sm(KV) + (t % AT_STAGES) * STAGE_BYTES;
+      const uint32_t kbuf = sm(KV) + (t % AT_STAGES) * STAGE_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < AT_D / 16; ++kk) {
-          const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
-          const uint64_t bd = smem_desc(kbuf + half * 8192 + (kk % 4) * 32, 16, 1024);
-          mma_ts(tmem + S_COL, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
-        }
-        commit(bar_s);
+      for (int kk = 0; kk < AT_D / 16; ++kk) {
+        const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
+        const uint64_t bd = smem_desc(kbuf + half * 8192 + (kk % 4) * 32, 16, 1024);
+        if (leader) mma_ts(tmem + S_COL, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
       }
+      if (leader) commit(bar_s);
       __syncwarp();
     };
-    auto wait_all = [&](uint32_t bar, uint32_t parity) {
-      return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
-    };
-    for (int t = 0; t < n_tiles && t < AT_STAGES; ++t) load_tile(t);
     bool ok = wait_all(bar_q, 0) && wait_all(bar_full, 0);
     if (ok) {
       fence_after();
@@ -287,14 +301,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       ok = wait_all(bar_p, j & 1);
       if (!ok) break;
       fence_after();
-      if (lane == 0) {
+      {
         const uint32_t vbuf = sm(KV) + st * STAGE_BYTES + K_BYTES;
 #pragma unroll
         for (int kk = 0; kk < AT_BK / 16; ++kk) {
           const uint64_t bd = smem_desc(vbuf + kk * 2048, 8192, 1024);
-          mma_ts(tmem + O_COL, tmem + S_COL + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          if (leader) mma_ts(tmem + O_COL, tmem + S_COL + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        commit(bar_free + 8 * st);
+        if (leader) commit(bar_free + 8 * st);
       }
       __syncwarp();
       // S of the next tile goes over P of this one: the tensor cores run MMAs in the order of issue.
@@ -304,14 +318,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         fence_after();
         issue_s(j + 1);
       }
-      // The stage of tile j is free once its O += P V is done: refill it.
-      if (j + AT_STAGES < n_tiles) {
-        ok = wait_all(bar_free + 8 * st, (j / AT_STAGES) & 1);
-        if (!ok) break;
-        load_tile(j + AT_STAGES);
-      }
     }
-    if (lane == 0) commit(bar_done);
+    if (leader) commit(bar_done);
     __syncwarp();
   } else {
     // ---- softmax threads ------------------------------------------------------------------
@@ -344,7 +352,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       ok = __all_sync(0xffffffffu, bar_wait(bar_s, j & 1, abort_flag));
       if (!ok) break;
       fence_after();
-      if (tid >= 32 && tid < 36) fetch_pages(j + 3, tid - 32);   // published by this tile's arrival on barrier p
       // This thread's 64 scores -> probabilities.
       float s[AT_BK];
       {
@@ -438,7 +445,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   }
   fence_before();
   __syncthreads();
-  if (*abort_flag && tid == AT_THREADS) {
+  if (*abort_flag && tid == AT_THREADS + 32) {
     atomicExch(&g_attn_tc_error, 1);
     // Copies may still be on their way into this block's shared memory.
     for (int i = 0; i < AT_STAGES; ++i)
@@ -508,8 +515,10 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   CUtensorMap map_kv;
   int rc;
   (void)n_tokens;
-  if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, 16))) return rc;
-  const size_t smem = AT_STAGES * STAGE_BYTES + (2 * AT_STAGES + 4) * 8 + 8 + 16 * 4;
+  // One copy per page and half of the head; a page of a multiple of 64 keys is copied 64 keys at a time.
+  const int box_rows = page_size % AT_BK == 0 ? AT_BK : 16;
+  if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
+  const size_t smem = AT_STAGES * STAGE_BYTES + (2 * AT_STAGES + 4) * 8 + 8;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -517,9 +526,9 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
     configured = true;
   }
   dim3 grid(n_q_heads, n_tiles);
-  attn_prefill_tc_kernel<<<grid, AT_THREADS + 32, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+  attn_prefill_tc_kernel<<<grid, AT_THREADS + 64, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                                                               tiles, q_start, n_new, cached_len, block_table,
-                                                              table_stride, n_q_heads, n_kv_heads, page_size, window,
-                                                              scale);
+                                                              table_stride, n_q_heads, n_kv_heads, page_size, box_rows,
+                                                              window, scale);
   return llmrs_launch_status("attn_prefill_tc");
 }
