@@ -36,13 +36,14 @@ typedef __nv_bfloat16 bf16;
 
 namespace {
 
-constexpr int AT_BQ = 128, AT_BK = 64, AT_D = 128, AT_THREADS = 128, AT_STAGES = 3;
+constexpr int AT_BQ = 128, AT_BK = 128, AT_D = 128, AT_THREADS = 128, AT_STAGES = 3;
 constexpr uint32_t AT_WAIT_LIMIT = 1u << 22;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 constexpr uint32_t K_BYTES = AT_BK * AT_D * 2, V_BYTES = K_BYTES, STAGE_BYTES = K_BYTES + V_BYTES;
-// Tensor memory of a block: S (64 columns of float32; P, as bfloat16 pairs, goes over its first 32),
-// O (128 columns), Q (128 bfloat16 = 64 columns).
-constexpr uint32_t TMEM_COLS = 256, S_COL = 0, O_COL = 64, Q_COL = 192;
+constexpr uint32_t HALF_BYTES = AT_BK * 128;   // one half of head_dim of a K or V tile: [128 keys][64 dims]
+// Tensor memory of a block: S twice (128 columns of float32 each; P, as bfloat16 pairs, goes over the
+// first 64 of its S), O (128 columns), Q (128 bfloat16 = 64 columns).
+constexpr uint32_t TMEM_COLS = 512, S_COL = 0, O_COL = 256, Q_COL = 384;
 
 __device__ int g_attn_tc_error = 0;
 
@@ -172,13 +173,14 @@ __device__ __forceinline__ void bar_arrive(uint32_t bar) {
 // issues every MMA, the lanes of warp 5 the TMA copies. Nobody meets at a block-wide barrier inside
 // the loop; the roles talk through mbarriers:
 //   q              all 128 threads have put their query rows into tensor memory
-//   full[3]        K and V of a tile have landed in their stage (TMA bytes)
-//   free[3]        O += P V of the tile in that stage is done (tcgen05.commit): the stage may be refilled
-//   s              S of a tile is in tensor memory, and with it everything issued earlier (tcgen05.commit
-//                  tracks all earlier MMAs of the issuing thread), in particular O += P V of the tile before
-//   p              all 128 threads have written P of a tile over its S
-//   done           the last O += P V is done
-__global__ void __launch_bounds__(AT_THREADS + 64, 2)
+//   kfull[3]       K of a tile has landed in its slot (TMA bytes); vfull[3] the same for V
+//   kfree[3]       the MMAs of S that read the slot are done (tcgen05.commit); vfree[3]: those of O += P V
+//   s[2]           S of a tile is in its buffer of tensor memory
+//   p[2]           all 128 threads have written P of a tile over its S
+//   o[2]           O += P V of a tile is done
+// Barriers that are used every tile come in pairs, one per parity of the tile: the roles run up to
+// two tiles apart, and a wait by parity must never be a whole phase behind its barrier.
+__global__ void __launch_bounds__(AT_THREADS + 96, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q, long long q_stride,
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
@@ -187,8 +189,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
   unsigned char* KV = base;                 // AT_STAGES x (K: 2 halves of [64 keys][64 dims], then V the same)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // full[3], free[3], q, s, p, done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * AT_STAGES + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // kfull[3], kfree[3], vfull[3], vfree[3], s[2], p[2], o[2], q
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -211,19 +213,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   const int n_tiles = (kv_hi - kv_lo + AT_BK - 1) / AT_BK;
   const int* table = block_table + (size_t)req * table_stride;
 
-  const uint32_t bar_full = sm(bars), bar_free = sm(bars + AT_STAGES), bar_q = sm(bars + 2 * AT_STAGES),
-                 bar_s = bar_q + 8, bar_p = bar_q + 16, bar_done = bar_q + 24;
+  const uint32_t bar_kfull = sm(bars), bar_kfree = sm(bars + AT_STAGES), bar_vfull = sm(bars + 2 * AT_STAGES),
+                 bar_vfree = sm(bars + 3 * AT_STAGES), bar_s = sm(bars + 4 * AT_STAGES), bar_p = bar_s + 16,
+                 bar_o = bar_s + 32, bar_q = bar_s + 48;
   if (tid == 0) {
-    for (int i = 0; i < 2 * AT_STAGES; ++i) bar_init(sm(bars + i));
-    bar_init_n(bar_q, AT_THREADS);
-    bar_init(bar_s);
+    for (int i = 0; i < 4 * AT_STAGES + 2; ++i) bar_init(sm(bars + i));
     bar_init_n(bar_p, AT_THREADS);
-    bar_init(bar_done);
+    bar_init_n(bar_p + 8, AT_THREADS);
+    bar_init(bar_o);
+    bar_init(bar_o + 8);
+    bar_init_n(bar_q, AT_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // Rows of K and V that no copy fills (keys past the end) must not hold NaN patterns.
-  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 64) * 16)
+  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 96) * 16)
     *reinterpret_cast<uint4*>(KV + i) = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 4) {
@@ -240,12 +244,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   auto wait_all = [&](uint32_t bar, uint32_t parity) {
     return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
   };
-  if (warp == 5) {
-    // ---- the copying warp: one box per lane; a lane's box of tile t is the same part of every tile
-    const int per_half = AT_BK / box_rows;            // boxes per K or V and half of the head: 4 or 1
-    const int n_boxes = 4 * per_half;
-    const int which = lane / (2 * per_half), h = (lane / per_half) & 1, i = lane % per_half;
+  if (warp >= 5) {
+    // ---- the copying warps: warp 5 brings K, warp 6 V; one box per lane, and a lane's box of tile t
+    // is the same part of every tile. K of a tile is wanted two tiles before its V.
+    const int which = warp - 5;
+    const int per_half = AT_BK / box_rows;            // boxes per half of the head: 8 or 2
+    const int n_boxes = 2 * per_half;
+    const int h = lane / per_half, i = lane % per_half;
     const uint32_t box_bytes = (uint32_t)box_rows * 128;
+    const uint32_t bar_full = which ? bar_vfull : bar_kfull, bar_free = which ? bar_vfree : bar_kfree;
     auto page_of = [&](int t) {     // page of this lane's box of tile t, or -1 (the lane copies nothing)
       const int key = kv_lo + t * AT_BK + box_rows * i;
       return (lane < n_boxes && t < n_tiles && key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : -1;
@@ -259,7 +266,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       if (page >= 0) {
         const int key = kv_lo + t * AT_BK + box_rows * i;
         const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
-        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * 8192 + i * box_bytes, &map_kv, bar, h * 64, row);
+        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * HALF_BYTES + i * box_bytes, &map_kv, bar, h * 64, row);
       }
       __syncwarp();
     };
@@ -267,7 +274,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     int page = page_of(AT_STAGES);                    // looked up one tile ahead of its copy
     for (int j = 0; j + AT_STAGES < n_tiles; ++j) {
       const int next = page_of(j + AT_STAGES + 1);
-      // The stage of tile j is free once its O += P V is done.
+      // The slot of tile j is free once the MMAs that read it are done.
       if (!wait_all(bar_free + 8 * (j % AT_STAGES), (j / AT_STAGES) & 1)) break;
       load_tile(j + AT_STAGES, page);
       page = next;
@@ -279,48 +286,63 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     // wants them. Issued from a divergent branch (`if (lane == 0)`) an MMA of this size costs its
     // thread some 120 cycles instead of the 32 to 64 that the tensor cores need for it.
     const bool leader = elect_one();
-    auto issue_s = [&](int t) {     // S_t = Q K_t^T; Q is read from tensor memory
+    auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2; Q is read from tensor memory
       const uint32_t kbuf = sm(KV) + (t % AT_STAGES) * STAGE_BYTES;
+      const uint32_t s_col = tmem + S_COL + (t & 1) * AT_BK;
 #pragma unroll
       for (int kk = 0; kk < AT_D / 16; ++kk) {
         const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
-        const uint64_t bd = smem_desc(kbuf + half * 8192 + (kk % 4) * 32, 16, 1024);
-        if (leader) mma_ts(tmem + S_COL, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
+        const uint64_t bd = smem_desc(kbuf + half * HALF_BYTES + (kk % 4) * 32, 16, 1024);
+        if (leader) mma_ts(s_col, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
       }
-      if (leader) commit(bar_s);
+      if (leader) {
+        commit(bar_s + 8 * (t & 1));
+        commit(bar_kfree + 8 * (t % AT_STAGES));   // the slot of K may be refilled
+      }
       __syncwarp();
     };
-    bool ok = wait_all(bar_q, 0) && wait_all(bar_full, 0);
+    // S runs one tile ahead of the softmax: S of tiles 0 and 1 now, S of tile j+2 as soon as P of
+    // tile j (which lies over S of tile j) has been used.
+    bool ok = wait_all(bar_q, 0) && wait_all(bar_kfull, 0);
     if (ok) {
       fence_after();
       issue_s(0);
     }
+    if (ok && n_tiles > 1) {
+      ok = wait_all(bar_kfull + 8, 0);
+      if (ok) {
+        fence_after();
+        issue_s(1);
+      }
+    }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int st = j % AT_STAGES;
-      // O += P V of tile j: P is written (its V landed with its K).
-      ok = wait_all(bar_p, j & 1);
+      // K of tile j+2 has landed long before P of tile j is there: look before the wait that matters.
+      if (j + 2 < n_tiles) {
+        ok = wait_all(bar_kfull + 8 * ((j + 2) % AT_STAGES), ((j + 2) / AT_STAGES) & 1);
+        if (!ok) break;
+      }
+      // O += P V of tile j: its V has landed, and P is written.
+      ok = wait_all(bar_vfull + 8 * st, (j / AT_STAGES) & 1) && wait_all(bar_p + 8 * (j & 1), (j >> 1) & 1);
       if (!ok) break;
       fence_after();
       {
         const uint32_t vbuf = sm(KV) + st * STAGE_BYTES + K_BYTES;
+        const uint32_t p_col = tmem + S_COL + (j & 1) * AT_BK;
 #pragma unroll
         for (int kk = 0; kk < AT_BK / 16; ++kk) {
-          const uint64_t bd = smem_desc(vbuf + kk * 2048, 8192, 1024);
-          if (leader) mma_ts(tmem + O_COL, tmem + S_COL + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t bd = smem_desc(vbuf + kk * 2048, HALF_BYTES, 1024);
+          if (leader) mma_ts(tmem + O_COL, p_col + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        if (leader) commit(bar_free + 8 * st);
+        if (leader) {
+          commit(bar_vfree + 8 * st);  // the slot of V may be refilled
+          commit(bar_o + 8 * (j & 1)); // O holds tiles 0..j
+        }
       }
       __syncwarp();
-      // S of the next tile goes over P of this one: the tensor cores run MMAs in the order of issue.
-      if (j + 1 < n_tiles) {
-        ok = wait_all(bar_full + 8 * ((j + 1) % AT_STAGES), ((j + 1) / AT_STAGES) & 1);
-        if (!ok) break;
-        fence_after();
-        issue_s(j + 1);
-      }
+      // S of tile j+2 goes over P of tile j: the tensor cores run MMAs in the order of issue.
+      if (j + 2 < n_tiles) issue_s(j + 2);
     }
-    if (leader) commit(bar_done);
-    __syncwarp();
   } else {
     // ---- softmax threads ------------------------------------------------------------------
     const int row = tid;                      // this thread's query row = its lane of tensor memory
@@ -349,17 +371,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int kb = kv_lo + j * AT_BK;
-      ok = __all_sync(0xffffffffu, bar_wait(bar_s, j & 1, abort_flag));
+      const uint32_t s_addr = lane_addr + S_COL + (j & 1) * AT_BK;
+      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * (j & 1), (j >> 1) & 1, abort_flag));
       if (!ok) break;
       fence_after();
-      // This thread's 64 scores -> probabilities.
+      // This thread's 128 scores -> probabilities.
       float s[AT_BK];
-      {
-        float t0[32], t1[32];
-        tmem_ld32(lane_addr + S_COL, t0);
-        tmem_ld32(lane_addr + S_COL + 32, t1);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) { s[c] = t0[c]; s[32 + c] = t1[c]; }
+      for (int c = 0; c < AT_BK; c += 32) {
+        float t0[32];
+        tmem_ld32(s_addr + c, t0);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) s[c + e] = t0[e];
       }
       const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window);
       if (need_mask) {
@@ -370,7 +393,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
           s[c] = seen ? s[c] : -INFINITY;
         }
       }
-      // Four running maxima (and sums below): a chain of 64 dependent operations would be the
+      // Four running maxima (and sums below): a chain of 128 dependent operations would be the
       // longest thing this thread does.
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -390,21 +413,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         l_sum *= factor;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      uint32_t pk[AT_BK / 2];
+      // P goes over S (all of this thread's S is in registers by now), 64 keys at a time.
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < AT_BK / 2; ++c) {
-        const float p0 = ex2(fmaf(s[2 * c], sl2, -m_use));
-        const float p1 = ex2(fmaf(s[2 * c + 1], sl2, -m_use));
-        sum4[c & 3] += p0 + p1;
-        const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-        pk[c] = *reinterpret_cast<const uint32_t*>(&h2);
+      for (int c0 = 0; c0 < AT_BK / 2; c0 += 32) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const float p0 = ex2(fmaf(s[2 * (c0 + c)], sl2, -m_use));
+          const float p1 = ex2(fmaf(s[2 * (c0 + c) + 1], sl2, -m_use));
+          sum4[c & 3] += p0 + p1;
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+          pk[c] = *reinterpret_cast<const uint32_t*>(&h2);
+        }
+        tmem_st32u(s_addr + c0, pk);
       }
       l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // S of this tile being there means that O += P V of the tile before is done: O may be
-      // rescaled where a row's reference moved (rare after the first tiles; the loads and stores
-      // of tensor memory are warp-wide, so the warp decides together). Then P goes over S.
+      // Where a row's reference moved, O is rescaled (rare after the first tiles; the loads and
+      // stores of tensor memory are warp-wide, so the warp decides together), once O += P V of the
+      // tile before is done (S of tile j implies O += P V of tile j-2 only).
       if (__any_sync(0xffffffffu, moved)) {
+        ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag));
+        if (!ok) break;
+        fence_after();
 #pragma unroll 1
         for (int c = 0; c < AT_D; c += 32) {
           float o[32];
@@ -414,12 +445,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
           tmem_st32(lane_addr + O_COL + c, o);
         }
       }
-      tmem_st32u(lane_addr + S_COL, pk);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       fence_before();
-      bar_arrive(bar_p);
+      bar_arrive(bar_p + 8 * (j & 1));
     }
-    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_done, 0, abort_flag));
+    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag));
     fence_after();
     if (ok) {
       // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
@@ -449,7 +479,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     atomicExch(&g_attn_tc_error, 1);
     // Copies may still be on their way into this block's shared memory.
     for (int i = 0; i < AT_STAGES; ++i)
-      for (int ph = 0; ph < 2; ++ph) bar_wait(bar_full + 8 * i, ph, abort_flag);
+      for (int ph = 0; ph < 2; ++ph) { bar_wait(bar_kfull + 8 * i, ph, abort_flag); bar_wait(bar_vfull + 8 * i, ph, abort_flag); }
   }
   __syncthreads();
   if (warp == 4) {
@@ -516,9 +546,9 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   int rc;
   (void)n_tokens;
   // One copy per page and half of the head; a page of a multiple of 64 keys is copied 64 keys at a time.
-  const int box_rows = page_size % AT_BK == 0 ? AT_BK : 16;
+  const int box_rows = page_size % 64 == 0 ? 64 : 16;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
-  const size_t smem = AT_STAGES * STAGE_BYTES + (2 * AT_STAGES + 4) * 8 + 8;
+  const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 7) * 8 + 8;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -526,7 +556,7 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
     configured = true;
   }
   dim3 grid(n_q_heads, n_tiles);
-  attn_prefill_tc_kernel<<<grid, AT_THREADS + 64, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
+  attn_prefill_tc_kernel<<<grid, AT_THREADS + 96, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                                                               tiles, q_start, n_new, cached_len, block_table,
                                                               table_stride, n_q_heads, n_kv_heads, page_size, box_rows,
                                                               window, scale);
