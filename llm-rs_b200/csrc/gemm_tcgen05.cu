@@ -84,6 +84,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool tc_elect_one() {
+  uint32_t leader;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+  return leader != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -216,21 +222,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // Do not leave while copies may still land in this block's shared memory.
       for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, abort_flag);
     }
-  } else if (warp == 1 && lane == 0) {
-    // MMA issuer: one thread, four k16 steps per stage.
+  } else if (warp == 1) {
+    // MMA issuer: four k16 steps per stage. The whole warp walks the loop and computes the operands, one
+    // elected lane issues: operands that are the same in all lanes stay in uniform registers, where the
+    // MMA wants them (issued from a one-thread branch each MMA costs its thread over a hundred cycles).
     constexpr uint32_t idesc = tc_instr_desc(BN);
+    const bool leader = tc_elect_one();
     for (int i = 0; i < nkb; ++i) {
       const int s = i % STAGES;
-      if (!mbar_wait(full0 + 8 * s, (i / STAGES) & 1, abort_flag)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, abort_flag))) break;
       tc_fence_after();
       const uint32_t a_addr = tc_smem(tiles + (size_t)s * STAGE_BYTES);
       const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + A_BYTES);
 #pragma unroll
       for (int k = 0; k < TC_BK / 16; ++k)
-        tc_mma(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
-      tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs are done
+        if (leader) tc_mma(tmem_base, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      if (leader) tc_commit(empty0 + 8 * s);  // frees the stage when these MMAs are done
+      __syncwarp();
     }
-    tc_commit(accum_bar);
+    if (leader) tc_commit(accum_bar);
   }
   __syncwarp();
   bool ok = true;
