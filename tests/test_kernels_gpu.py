@@ -464,10 +464,13 @@ def test_silu_mul_interleaved_layout(dtype):
 @pytest.mark.parametrize("lens,new,nq,nkv,page,window", [
     ([0], [128], 1, 1, 16, 0), ([0], [64], 2, 1, 16, 0), ([0], [300], 4, 2, 16, 0),
     ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 16, 0), ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 32, 37),
-    ([1000], [1000], 4, 1, 16, 0), ([0, 500], [1100, 700], 8, 8, 16, 200), ([5], [257], 6, 3, 48, 129)])
+    ([1000], [1000], 4, 1, 16, 0), ([0, 500], [1100, 700], 8, 8, 16, 200), ([5], [257], 6, 3, 48, 129),
+    ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 64, 0), ([0, 500], [1100, 700], 8, 8, 64, 200),
+    ([5], [257], 6, 3, 128, 129), ([1000], [1000], 4, 1, 64, 0), ([0], [1], 2, 1, 64, 0)])
 def test_attention_prefill_tcgen05(lens, new, nq, nkv, page, window):
     """Blocks of 128 queries on tcgen05 against the plain attention: partial blocks, several requests,
-    earlier context, windows that start inside a tile, pages larger than a 16-key box."""
+    earlier context, windows that start inside a tile, pages larger than a 16-key box, and pages of a
+    multiple of 64 keys (which are copied 64 keys at a time)."""
     ops = _ops()
     d = 128
     torch.manual_seed(len(lens) * 31 + window)
@@ -487,6 +490,33 @@ def test_attention_prefill_tcgen05(lens, new, nq, nkv, page, window):
     got = out.double().cpu()
     assert torch.isfinite(got).all(), "a row was not written"
     assert float((got - want).abs().max()) < 2.5e-2
+
+
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_prefill_tcgen05_growing_scores(page):
+    """Keys grow along the sequence, so the reference maximum of every row moves again and again:
+    each move rescales O in tensor memory between two tiles."""
+    ops = _ops()
+    nq, nkv, d = 4, 2, 128
+    lens, new = [900], [400]
+    torch.manual_seed(page)
+    table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=page)
+    direction = torch.randn(nkv, d)
+    direction = direction / direction.norm(dim=-1, keepdim=True)
+    for pos in range(lens[0] + new[0]):
+        k = cache[int(table[0, pos // page]), :, 0, pos % page].float() * 0.05 + direction * (pos / 20.0)
+        cache[int(table[0, pos // page]), :, 0, pos % page] = k.to(torch.bfloat16)
+    q = (torch.randn(sum(new), nq, d) * 0.05 + direction.repeat_interleave(2, 0)[None]).reshape(-1, nq * d).to(torch.bfloat16)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, 0, 1.0)
+    dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+    tiles = torch.tensor([(0, off) for off in range(0, new[0], 64)], dtype=torch.int32, device=DEV)
+    out = torch.zeros(new[0], nq * d, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.attn_prefill(dq, out, dc, tiles, tiles.size(0), z, torch.tensor(new, dtype=torch.int32, device=DEV),
+                     torch.tensor(lens, dtype=torch.int32, device=DEV), dt, nq, nkv, d, page, 0, 1.0, prefer_tc=True)
+    torch.cuda.synchronize()
+    ops.check_attention_error()
+    assert float((out.double().cpu() - want).abs().max()) < 2e-2
 
 
 def test_attention_prefill_tcgen05_far_key():
