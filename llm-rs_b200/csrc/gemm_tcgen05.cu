@@ -374,6 +374,183 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---- the persistent kernel for many tokens ----------------------------------------------------
+// Rows of a tile are tokens (A = x), columns features (B = W), tiles of 128 x 256. One block per SM
+// walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (token tiles of one feature tile side by side, so
+// the blocks that run together share weights in L2). Warp 0 copies (TMA), warp 1 issues the MMAs, warps
+// 2-5 run the epilogue. The accumulator is double-buffered in tensor memory (2 x 256 columns): the
+// epilogue of a tile runs under the MMAs of the next one, and the ring of stages never drains between
+// tiles.
+constexpr int PS_BN = 256, PS_STAGES = 4, PS_THREADS = 192;
+constexpr uint32_t PS_A_BYTES = TC_BM * TC_BK * 2, PS_B_BYTES = PS_BN * TC_BK * 2, PS_STAGE_BYTES = PS_A_BYTES + PS_B_BYTES;
+
+__global__ void __launch_bounds__(PS_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          const TcParams p, int n_m, int n_tiles) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)PS_STAGES * PS_STAGE_BYTES);   // full[4], empty[4], acc_full[2], acc_empty[2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PS_STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + PS_STAGES), acc_full0 = tc_smem(bars + 2 * PS_STAGES),
+                 acc_empty0 = acc_full0 + 16;
+  if (tid == 0) {
+    for (int s = 0; s < 2 * PS_STAGES + 2; ++s) mbar_init(full0 + 8 * s, 1);
+    mbar_init(acc_empty0, 128);
+    mbar_init(acc_empty0 + 8, 128);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // x is what an earlier kernel wrote; the epilogue writes what earlier kernels read
+  const int nkb = p.k_blocks;
+
+  if (warp == 0) {
+    // Copies: the whole warp walks the loop, one elected lane issues.
+    const bool leader = tc_elect_one();
+    long long it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int tm = t % n_m, tn = t / n_m;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = (int)(it % PS_STAGES);
+        if (it >= PS_STAGES) {
+          ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, (uint32_t)((it / PS_STAGES) - 1) & 1, abort_flag));
+          if (!ok) break;
+        }
+        if (leader) {
+          mbar_expect_tx(full0 + 8 * s, PS_STAGE_BYTES);
+          const uint32_t a_dst = tc_smem(tiles + (size_t)s * PS_STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, tm * TC_BM);
+          tma_load_2d(a_dst + PS_A_BYTES, &map_b, full0 + 8 * s, kb * TC_BK, tn * PS_BN);
+        }
+        __syncwarp();
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // Do not leave while copies may still land in this block's shared memory.
+      for (long long i = it > PS_STAGES ? it - PS_STAGES : 0; i < it; ++i)
+        mbar_wait(full0 + 8 * (int)(i % PS_STAGES), (uint32_t)(i / PS_STAGES) & 1, abort_flag);
+    }
+  } else if (warp == 1) {
+    // MMAs: operands computed by the whole warp (they stay in uniform registers), issued by one elected lane.
+    constexpr uint32_t idesc = tc_instr_desc(PS_BN);
+    const bool leader = tc_elect_one();
+    long long it = 0;
+    int lt = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+      const int buf = lt & 1;
+      if (lt >= 2) {   // the epilogue has read the tile before last out of this buffer
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8 * buf, (uint32_t)((lt >> 1) - 1) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const uint32_t d_addr = tmem_base + (uint32_t)buf * PS_BN;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = (int)(it % PS_STAGES);
+        ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (uint32_t)(it / PS_STAGES) & 1, abort_flag));
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = tc_smem(tiles + (size_t)s * PS_STAGE_BYTES);
+        const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + PS_A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k)
+          if (leader) tc_mma(d_addr, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+        if (leader) tc_commit(empty0 + 8 * s);
+        __syncwarp();
+      }
+      if (leader && ok) tc_commit(acc_full0 + 8 * buf);
+      __syncwarp();
+    }
+  } else {
+    // Epilogue: thread = one token row of the tile; a warp reaches the 32 lanes of tensor memory
+    // that its index modulo 4 names.
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int lt = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
+      const int tm = t % n_m, tn = t / n_m, buf = lt & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * PS_BN;
+      const int tok = tm * TC_BM + row;
+      const bool t_ok = tok < p.a_rows;
+      if (p.epilogue == TC_SILU_MUL) {
+        // Columns come in groups of 128: 64 gate columns, then the 64 up columns of the same features.
+#pragma unroll 1
+        for (int g = 0; g < PS_BN / 128; ++g) {
+#pragma unroll 1
+          for (int c = 0; c < 64; c += 8) {
+            float gv[8], uv[8];
+            tc_ld8(taddr + g * 128 + c, gv);
+            tc_ld8(taddr + g * 128 + 64 + c, uv);
+            const int f = (tn * PS_BN + g * 128) / 2 + c;
+            if (t_ok && f < p.b_rows / 2) {
+              uint4 pk;
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                h2[e] = __floats2bfloat162_rn(silu_f(gv[2 * e]) * uv[2 * e], silu_f(gv[2 * e + 1]) * uv[2 * e + 1]);
+              *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
+            }
+            __syncwarp();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < PS_BN; c += 8) {
+          float v[8];
+          tc_ld8(taddr + c, v);
+          const int f = tn * PS_BN + c;
+          if (!t_ok || f >= p.b_rows) {
+            // nothing to store for this thread; stay with the warp for the next tcgen05.ld
+          } else if (p.epilogue == TC_RESIDUAL) {
+            float4* hp = reinterpret_cast<float4*>((float*)p.out + (size_t)tok * p.ldo + f);
+            float4 x0 = hp[0], x1 = hp[1];
+            x0.x += v[0]; x0.y += v[1]; x0.z += v[2]; x0.w += v[3];
+            x1.x += v[4]; x1.y += v[5]; x1.z += v[6]; x1.w += v[7];
+            hp[0] = x0; hp[1] = x1;
+          } else if (p.out_dtype == LLMRS_F32) {
+            float4* op = reinterpret_cast<float4*>((float*)p.out + (size_t)tok * p.ldo + f);
+            op[0] = make_float4(v[0], v[1], v[2], v[3]);
+            op[1] = make_float4(v[4], v[5], v[6], v[7]);
+          } else {
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+            *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
+          }
+          __syncwarp();
+        }
+      }
+      tc_fence_before();
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ---- host side --------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -440,6 +617,36 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return llmrs_launch_status("gemm_bf16");
 }
 
+static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_m, int n_tiles,
+                             cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + (2 * PS_STAGES + 4) * 8 + 16;
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("gemm_bf16: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm <= 0) n_sm = 1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_tiles < n_sm ? n_tiles : n_sm);
+  cfg.blockDim = dim3(PS_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  cfg.numAttrs = 0;
+  if (g_llmrs_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 1;
+  }
+  cfg.attrs = attr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel, ma, mb, p, n_m, n_tiles);
+  if (e != cudaSuccess) return llmrs_fail("gemm_bf16 launch: %s", cudaGetErrorString(e));
+  return llmrs_launch_status("gemm_bf16");
+}
+
 // y = x W^T for bfloat16 x [tokens, K] (row stride ldx) and W [features, K] (dense).
 //   epilogue TC_STORE:    out[tokens, features] (out_dtype), row stride ldo
 //   epilogue TC_RESIDUAL: out is the float32 residual stream, out[t, f] += y[t, f]
@@ -481,6 +688,6 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
   if ((rc = make_map(&mb, w, features, K, K, bn))) return rc;
   p.a_rows = tokens; p.b_rows = features;
   dim3 grid((tokens + TC_BM - 1) / TC_BM, (features + bn - 1) / bn, 1);
-  if (bn == 256) return launch_tc<256, 4, 0>(ma, mb, p, grid, 1, stream);
+  if (bn == 256) return launch_persistent(ma, mb, p, grid.x, grid.x * grid.y, stream);
   return launch_tc<128, 6, 0>(ma, mb, p, grid, 1, stream);
 }

@@ -434,8 +434,13 @@ def test_gemm_tcgen05_few_tokens(tokens, features, K, epilogue, out_dtype, split
 @pytest.mark.parametrize("tokens,features,K,epilogue,out_dtype", [
     (65, 128, 64, "store", torch.float32), (128, 256, 512, "store", torch.bfloat16),
     (300, 392, 1000, "store", torch.float32), (200, 512, 4096, "residual", torch.float32),
-    (130, 1024, 512, "silu_mul", torch.bfloat16), (515, 768, 320, "store", torch.bfloat16)])
+    (130, 1024, 512, "silu_mul", torch.bfloat16), (515, 768, 320, "store", torch.bfloat16),
+    (1100, 10496, 192, "store", torch.bfloat16), (2048, 12288, 128, "silu_mul", torch.bfloat16),
+    (1500, 8200, 72, "residual", torch.float32)])
 def test_gemm_tcgen05_many_tokens(tokens, features, K, epilogue, out_dtype):
+    """Tokens on the 128 rows of the MMA; with 256 features or more the persistent kernel, whose blocks
+    walk several tiles each (the last three cases give every block two to four tiles, so that both
+    accumulator buffers and the ring of stages wrap, with a ragged edge in tokens, features and k)."""
     _tc_case(tokens, features, K, epilogue, out_dtype, None)
 
 
