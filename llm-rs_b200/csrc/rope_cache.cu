@@ -82,70 +82,114 @@ __global__ void qk_norm_rope_kvwrite_kernel(
   }
 }
 
-// The same for bfloat16 heads of 128 elements that are rotated whole (or not at all): a lane
-// holds four consecutive elements (one 8-byte load), its partner in the rotation is lane ^ 16,
-// nothing goes through shared memory.
-__global__ void __launch_bounds__(ROPE_THREADS)
+// The same for bfloat16 heads of 128 elements that are rotated whole (or not at all). Sixteen lanes
+// hold a head (eight consecutive elements = one 16-byte load each; the partner in the rotation is
+// lane ^ 8), so a warp works on two heads at a time, and it takes PASSES such pairs of one token one
+// after the other with all their loads in flight together: the position, the page and the row of
+// (cos, sin) are fetched once for all of them. A block walks tokens blockIdx.x, blockIdx.x + gridDim.x,
+// ... Steps of few tokens take one pair per warp (more warps at once, a shorter chain each). Nothing
+// goes through shared memory.
+constexpr int D128_WARPS = 4;
+
+template <int D128_PASSES>
+__global__ void __launch_bounds__(D128_WARPS * 32)
 qk_norm_rope_kvwrite_d128_kernel(__nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ k,
                                  long long k_stride, const __nv_bfloat16* __restrict__ v, long long v_stride,
                                  const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
                                  const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                  const int* __restrict__ token_req, const int* __restrict__ block_table,
                                  int table_stride, __nv_bfloat16* __restrict__ cache, int n_q_heads, int n_kv_heads,
-                                 int page_size, float eps) {
+                                 int page_size, float eps, int n_tokens) {
   constexpr int D = 128;
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int hh = blockIdx.y * ROPE_WARPS + warp;
+  const int sub = lane >> 4, l16 = lane & 15;          // which head of the pair, and the lane's place in it
   const int n_heads_total = n_q_heads + (k ? 2 * n_kv_heads : 0);
-  if (hh >= n_heads_total) return;
+  const int first = ((blockIdx.y * D128_WARPS + warp) * D128_PASSES) * 2 + sub;   // this half-warp's heads: first, first + 2, ...
+  if (first - sub >= n_heads_total) return;
+  for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
   const int pos = positions[t];
-  int kind, head;
-  if (hh < n_q_heads) { kind = 0; head = hh; }
-  else if (hh < n_q_heads + n_kv_heads) { kind = 1; head = hh - n_q_heads; }
-  else { kind = 2; head = hh - n_q_heads - n_kv_heads; }
-  const __nv_bfloat16* src = kind == 0 ? q + (size_t)t * q_stride + (size_t)head * D
-                           : kind == 1 ? k + (size_t)t * k_stride + (size_t)head * D
-                                       : v + (size_t)t * v_stride + (size_t)head * D;
-  __nv_bfloat16* dst;
-  if (kind == 0) {
-    dst = q + (size_t)t * q_stride + (size_t)head * D;
-  } else {
-    const int page = block_table[(size_t)token_req[t] * table_stride + pos / page_size];
-    dst = cache + kv_tile_offset(page, head, kind - 1, n_kv_heads, page_size, D) + (size_t)(pos % page_size) * D;
-  }
-  const uint2 raw = *reinterpret_cast<const uint2*>(src + lane * 4);
-  if (kind == 2) {
-    *reinterpret_cast<uint2*>(dst + lane * 4) = raw;
-    return;
-  }
-  const float2 a01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-  const float2 a23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  float x[4] = {a01.x, a01.y, a23.x, a23.y};
-  const float* w = kind == 0 ? q_norm_w : k_norm_w;
-  if (w) {
-    const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
-    const float inv = 1.0f / sqrtf(ss / (float)D + eps);
-    const float4 wv = *reinterpret_cast<const float4*>(w + lane * 4);
-    x[0] *= inv * wv.x; x[1] *= inv * wv.y; x[2] *= inv * wv.z; x[3] *= inv * wv.w;
-  }
-  if (cos_sin) {
-    // Element i < 64 pairs with i + 64: lanes 0-15 hold the first half, lane ^ 16 the partner.
-    const float* cs = cos_sin + (size_t)pos * D + (size_t)(lane & 15) * 8;   // (cos, sin) of 4 frequencies
-    const float4 cs01 = *reinterpret_cast<const float4*>(cs), cs23 = *reinterpret_cast<const float4*>(cs + 4);
-    const float c[4] = {cs01.x, cs01.z, cs23.x, cs23.z}, sn[4] = {cs01.y, cs01.w, cs23.y, cs23.w};
+  const size_t page_base = k ? (size_t)block_table[(size_t)token_req[t] * table_stride + pos / page_size] : 0;
+
+  const __nv_bfloat16* src[D128_PASSES];
+  __nv_bfloat16* dst[D128_PASSES];
+  int kind[D128_PASSES];
+  uint4 raw[D128_PASSES];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);
-      x[e] = lane < 16 ? x[e] * c[e] - other * sn[e] : x[e] * c[e] + other * sn[e];
+  for (int p = 0; p < D128_PASSES; ++p) {
+    const int hh = first + 2 * p;
+    kind[p] = -1;
+    src[p] = q;
+    dst[p] = q;
+    if (hh < n_heads_total) {
+      int head;
+      if (hh < n_q_heads) { kind[p] = 0; head = hh; }
+      else if (hh < n_q_heads + n_kv_heads) { kind[p] = 1; head = hh - n_q_heads; }
+      else { kind[p] = 2; head = hh - n_q_heads - n_kv_heads; }
+      src[p] = kind[p] == 0 ? q + (size_t)t * q_stride + (size_t)head * D
+             : kind[p] == 1 ? k + (size_t)t * k_stride + (size_t)head * D
+                            : v + (size_t)t * v_stride + (size_t)head * D;
+      dst[p] = kind[p] == 0 ? q + (size_t)t * q_stride + (size_t)head * D
+                            : cache + kv_tile_offset((int)page_base, head, kind[p] - 1, n_kv_heads, page_size, D) +
+                                  (size_t)(pos % page_size) * D;
+      raw[p] = *reinterpret_cast<const uint4*>(src[p] + l16 * 8);
     }
   }
-  uint2 o;
-  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(x[0], x[1]);
-  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(x[2], x[3]);
-  *reinterpret_cast<uint2*>(dst + lane * 4) = o;
+  // (cos, sin) of this lane's eight frequencies: element i < 64 pairs with i + 64, lanes 0-7 of a head
+  // hold the first half, lane ^ 8 the partner.
+  float c[8], sn[8];
+  if (cos_sin) {
+    const float4* cs = reinterpret_cast<const float4*>(cos_sin + (size_t)pos * D + (size_t)(l16 & 7) * 16);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 x = cs[e];
+      c[2 * e] = x.x; sn[2 * e] = x.y; c[2 * e + 1] = x.z; sn[2 * e + 1] = x.w;
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < D128_PASSES; ++p) {
+    // Both halves of the warp take every step together (the shuffles are warp-wide); a half without a
+    // head, or with a head of V, computes on what it has and stores nothing of it.
+    const bool live = kind[p] >= 0;
+    if (kind[p] == 2) *reinterpret_cast<uint4*>(dst[p] + l16 * 8) = raw[p];
+    float x[8];
+    {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[p]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = live ? __bfloat1622float2(h2[e]) : make_float2(0.f, 0.f);
+        x[2 * e] = f.x; x[2 * e + 1] = f.y;
+      }
+    }
+    const float* w = kind[p] == 0 ? q_norm_w : kind[p] == 1 ? k_norm_w : nullptr;
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // within the 16 lanes of a head
+    if (w) {
+      const float inv = 1.0f / sqrtf(ss / (float)D + eps);
+      const float4 w0 = *reinterpret_cast<const float4*>(w + l16 * 8), w1 = *reinterpret_cast<const float4*>(w + l16 * 8 + 4);
+      x[0] *= inv * w0.x; x[1] *= inv * w0.y; x[2] *= inv * w0.z; x[3] *= inv * w0.w;
+      x[4] *= inv * w1.x; x[5] *= inv * w1.y; x[6] *= inv * w1.z; x[7] *= inv * w1.w;
+    }
+    if (cos_sin) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float other = __shfl_xor_sync(0xffffffffu, x[e], 8);
+        x[e] = l16 < 8 ? x[e] * c[e] - other * sn[e] : x[e] * c[e] + other * sn[e];
+      }
+    }
+    if (kind[p] == 0 || kind[p] == 1) {
+      uint4 o;
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(x[2 * e], x[2 * e + 1]);
+      *reinterpret_cast<uint4*>(dst[p] + l16 * 8) = o;
+    }
+  }
+  }
 }
 
 LLMRS_API int llmrs_qk_norm_rope_kvwrite(void* q, long long q_stride, const void* k, long long k_stride,
@@ -164,13 +208,26 @@ LLMRS_API int llmrs_qk_norm_rope_kvwrite(void* q, long long q_stride, const void
   const size_t smem = (size_t)ROPE_WARPS * d * sizeof(float);
   const int heads_total = n_q_heads + (k ? 2 * n_kv_heads : 0);
   dim3 grid(n_tokens, (heads_total + ROPE_WARPS - 1) / ROPE_WARPS);
-  const bool aligned8 = ((uintptr_t)q % 8 == 0) && q_stride % 4 == 0 && (!k || ((uintptr_t)k % 8 == 0 && k_stride % 4 == 0)) &&
-                        (!v || ((uintptr_t)v % 8 == 0 && v_stride % 4 == 0));
-  if (dtype == LLMRS_BF16 && d == 128 && (rotary_dim == 128 || rotary_dim == 0 || !cos_sin) && aligned8) {
-    llmrs_launch(qk_norm_rope_kvwrite_d128_kernel, grid, dim3(ROPE_THREADS), 0, stream, true, (__nv_bfloat16*)q,
-                 q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm_w, k_norm_w,
-                 (rotary_dim == 128 ? cos_sin : (const float*)nullptr), positions, token_req, block_table, table_stride,
-                 (__nv_bfloat16*)cache, n_q_heads, n_kv_heads, page_size, eps);
+  const bool aligned16 = ((uintptr_t)q % 16 == 0) && q_stride % 8 == 0 && (!k || ((uintptr_t)k % 16 == 0 && k_stride % 8 == 0)) &&
+                         (!v || ((uintptr_t)v % 16 == 0 && v_stride % 8 == 0)) && (!cache || (uintptr_t)cache % 16 == 0);
+  if (dtype == LLMRS_BF16 && d == 128 && (rotary_dim == 128 || rotary_dim == 0 || !cos_sin) && aligned16) {
+    const float* cs = rotary_dim == 128 ? cos_sin : (const float*)nullptr;
+    if (n_tokens <= 64) {
+      const int per_block = D128_WARPS * 2;   // heads per block
+      const dim3 grid128(n_tokens, (heads_total + per_block - 1) / per_block);
+      llmrs_launch(qk_norm_rope_kvwrite_d128_kernel<1>, grid128, dim3(D128_WARPS * 32), 0, stream, true, (__nv_bfloat16*)q,
+                   q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm_w, k_norm_w,
+                   cs, positions, token_req, block_table, table_stride, (__nv_bfloat16*)cache, n_q_heads, n_kv_heads,
+                   page_size, eps, n_tokens);
+    } else {
+      const int per_block = D128_WARPS * 3 * 2;
+      const int gy = (heads_total + per_block - 1) / per_block;
+      const int gx = n_tokens < 148 * 16 / gy ? n_tokens : 148 * 16 / gy;
+      llmrs_launch(qk_norm_rope_kvwrite_d128_kernel<3>, dim3(gx > 0 ? gx : 1, gy), dim3(D128_WARPS * 32), 0, stream, true,
+                   (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride,
+                   q_norm_w, k_norm_w, cs, positions, token_req, block_table, table_stride, (__nv_bfloat16*)cache,
+                   n_q_heads, n_kv_heads, page_size, eps, n_tokens);
+    }
     return llmrs_launch_status("qk_norm_rope_kvwrite");
   }
   if (dtype == LLMRS_F32)
