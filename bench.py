@@ -38,6 +38,16 @@ QWEN3_8B = dict(
     max_position_embeddings=40960, hidden_act="silu", eos_token_id=151645)
 FULL_LAYERS = 36
 PREFILL_TOKENS = 2048
+# Two further workloads, run through the engine's public API from host token ids to host tokens
+# (``--workload``): a mixed load on the layer sizes of Qwen3-14B and a memory stress on those of Qwen3-32B.
+QWEN3_14B = dict(QWEN3_8B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, intermediate_size=25600)
+WORKLOADS = {
+    "mixed14b": dict(model="Qwen3-14B shape", cfg=QWEN3_14B, seed=3, requests=32, prompt_lo=128, prompt_hi=3072,
+                     new_tokens=256, temperature=0.8, prefill_chunk=512),
+    "stress32b": dict(model="Qwen3-32B shape", cfg=QWEN3_32B, seed=4, requests=16, prompt_lo=8192, prompt_hi=8192,
+                      new_tokens=512, temperature=0.0, prefill_chunk=512),
+}
 
 
 def peaks():
@@ -119,6 +129,94 @@ def prefill_flops(cfg, n_layers, tokens):
     return linear + attention
 
 
+def run_workload(args):
+    """A whole serving run through ``Engine``: requests in, tokens out, scheduler, chunked prefill
+    beside decoding, sampling, preemption if the pool is made small. Prints one JSON line."""
+    import numpy as np
+    import torch
+    import llm_rs_b200  # noqa: F401
+    from llm_rs_b200 import ops
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import Engine, EngineConfig, ModelRunner
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel
+    from llm_rs_b200.sampling import SamplingParams
+    from llm_rs_b200.weights import random_tensors
+
+    w = WORKLOADS[args.workload]
+    torch.cuda.set_device(0)
+    layers = args.layers if args.layers != FULL_LAYERS else w["cfg"]["num_hidden_layers"]
+    raw = dict(w["cfg"], num_hidden_layers=layers)
+    cfg = Qwen3Config.from_dict(raw)
+    spec = build_spec(cfg)
+    page = 16
+    rng = np.random.default_rng(w["seed"])
+    lens = rng.integers(w["prompt_lo"], w["prompt_hi"] + 1, w["requests"]).tolist()
+    need_tokens = sum(-(-(n + w["new_tokens"]) // page) * page for n in lens)
+    pool_tokens = args.pool_tokens or need_tokens + 64 * page
+    t0 = time.time()
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=w["seed"], sigma=0.02, dtype=torch.bfloat16,
+                             device="cuda:0")
+    runner = ModelRunner(spec, tensors, torch.bfloat16, "cuda:0", max_tokens=pool_tokens, page_size=page,
+                         max_requests=w["requests"] + 1)
+    del tensors
+    torch.cuda.empty_cache()
+    runner.use_graphs = not args.no_graphs
+    print(f"[bench] {w['model']}: model on device in {time.time() - t0:.1f} s, "
+          f"{torch.cuda.memory_allocated() / 2**30:.1f} GiB allocated, pool of {pool_tokens} tokens "
+          f"({need_tokens} needed to hold every request whole)", file=sys.stderr, flush=True)
+    engine = Engine(EngineConfig(model_path="", block_pool_size=pool_tokens // page, page_size=page,
+                                 max_requests=w["requests"] + 1, max_tokens_per_step=2048,
+                                 prefill_chunk=w["prefill_chunk"], cuda_graphs=not args.no_graphs), runner=runner)
+    sp = SamplingParams(temperature=w["temperature"], max_new_tokens=w["new_tokens"], ignore_eos=True, seed=7)
+
+    def run_once():
+        for n in lens:
+            engine.add_request(rng.integers(0, cfg.vocab_size, n).tolist(), sp)
+        stats0 = dict(engine.stats)
+        pre0 = engine.scheduler.stats["preemptions"]
+        launches0 = ops.launch_count
+        torch.cuda.synchronize()
+        t_start = time.perf_counter()
+        got, first = 0, None
+        while engine.has_work():
+            for _, tok, _ in engine.step():
+                if tok is not None:
+                    got += 1
+                    if first is None:
+                        first = time.perf_counter() - t_start
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t_start
+        st = {k: engine.stats[k] - stats0[k] for k in stats0 if k != "max_step_tokens"}
+        return dt, got, first, st, engine.scheduler.stats["preemptions"] - pre0, ops.launch_count - launches0
+
+    run_once()                      # warm-up: graph captures, workspace, first-call set-up
+    sampler = ClockSampler()
+    sampler.start()
+    dt, got, first, st, preempt, launches = run_once()
+    clocks = sampler.stop()
+    engine.check_kernels()
+    runner.manager.check_invariants()
+    result = {
+        "metric": f"{w['model']} bf16 serving run: {w['requests']} requests, prompts {w['prompt_lo']}-{w['prompt_hi']} "
+                  f"tokens, {w['new_tokens']} new tokens each",
+        "value": round(got / dt, 2), "unit": "generated tokens/s", "n_gpus": 1, "impl": "ours", "dtype": "bf16",
+        "data": f"synthetic: random weights (seed {w['seed']}), uniform-random token ids",
+        "seconds": round(dt, 3), "generated_tokens": got, "prompt_tokens": int(sum(lens)),
+        "all_tokens_per_s": round((got + sum(lens)) / dt, 1), "first_token_s": round(first or 0.0, 4),
+        "steps": st, "preemptions": preempt, "gpu_launches_eager": launches,
+        "config": {"model": w["model"], "layers": layers, "layers_full": w["cfg"]["num_hidden_layers"],
+                   "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "requests": w["requests"], "pool_tokens": pool_tokens, "page_size": page,
+                   "prefill_chunk": w["prefill_chunk"], "max_tokens_per_step": 2048,
+                   "temperature": w["temperature"], "cuda_graphs": not args.no_graphs},
+        "clocks": clocks,
+    }
+    print(json.dumps(result))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -133,6 +231,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself "
                     "(for a profiler's launch list)")
+    ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS],
+                    help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
+                    "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B")
+    ap.add_argument("--pool-tokens", type=int, default=0, help="size of the cache pool of a --workload run in "
+                    "tokens (default: what holds every request whole); smaller makes the scheduler preempt")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -143,6 +246,8 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "decode":
+        return run_workload(args)
     W = max(3, args.warmup)
     K = max(1, args.steps)
 

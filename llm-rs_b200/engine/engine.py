@@ -60,6 +60,10 @@ class Engine:
         self._tok_bufs = [None, None]
         self._tok_flip = 0
         self._steps_since_check = 0
+        # What the steps were made of: steps of decoded tokens only, of prompt portions only, of both;
+        # tokens that entered the model as prompt portions and as single decoded tokens.
+        self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0,
+                      "prompt_tokens": 0, "decode_tokens": 0, "max_step_tokens": 0}
 
     # -- requests --------------------------------------------------------------------
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -114,6 +118,14 @@ class Engine:
                 self._inflight = None
                 raise
             self.scheduler.on_launched(batch)
+            n_dec = sum(1 for s in batch if len(s.tokens) == 1 and s.sample)
+            n_pre = sum(len(s.tokens) for s in batch) - n_dec
+            st = self.stats
+            st["steps"] += 1
+            st["decode_steps" if not n_pre else "prefill_steps" if not n_dec else "mixed_steps"] += 1
+            st["prompt_tokens"] += n_pre
+            st["decode_tokens"] += n_dec
+            st["max_step_tokens"] = max(st["max_step_tokens"], n_pre + n_dec)
             launched = {"batch": batch, "tokens": tokens, "host": host, "event": event,
                         "row_of": {s.request.request_id: i for i, s in enumerate(sampled)}}
         outs: List[Output] = []
