@@ -1,6 +1,7 @@
 """Replay on the GPU against the plain implementation: whole, tail one by one, portions
 of changing size, and mixed batches with so few pages that they are used again; in
-float32 and in bfloat16; for three tiny configurations."""
+float32 and in bfloat16; for three tiny configurations and one with heads of 128 elements (at
+two page sizes), the size at which the bfloat16 engine takes its tcgen05 kernels."""
 import json
 import os
 import subprocess
@@ -23,7 +24,8 @@ TOL_F32 = 1e-4
 # bound that a wrong key, page or position (errors of the order of the logits) cannot meet.
 TOL_BF16_REL = 0.02
 
-LENGTHS = {"A": [5, 17, 33, 64, 100, 161], "B": [1, 9, 40, 77, 128, 200], "C": [3, 30, 48, 65, 97, 150]}
+LENGTHS = {"A": [5, 17, 33, 64, 100, 161], "B": [1, 9, 40, 77, 128, 200], "C": [3, 30, 48, 65, 97, 150],
+           "D": [40, 130, 300, 520, 257], "E": [40, 130, 300, 520, 257]}
 MODES = ["whole", "tail", "portions", "mixed"]
 
 

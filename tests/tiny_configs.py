@@ -25,8 +25,19 @@ TINY_C = dict(
     use_sliding_window=True, sliding_window=24, max_window_layers=2, no_rope_layers=[False, False, False, True],
     eos_token_id=1)
 
-# name -> (config.json, seed, sigma of matrices, page size)
-TINY = {"A": (TINY_A, 0, 0.02, 16), "B": (TINY_B, 1, 0.03, 8), "C": (TINY_C, 5, 0.05, 16)}
+# Heads of 128 elements, a feed-forward width that is a multiple of 128 and a width that is a multiple
+# of 8: the sizes at which the bfloat16 engine takes its tcgen05 kernels (attention over long portions,
+# products with fused epilogues) and the vectorised rotation kernel.
+TINY_D = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+    intermediate_size=384, vocab_size=520, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    tie_word_embeddings=False, attention_bias=False, max_position_embeddings=2048, hidden_act="silu",
+    eos_token_id=519)
+
+# name -> (config.json, seed, sigma of matrices, page size); E is D with pages of 64 keys
+TINY = {"A": (TINY_A, 0, 0.02, 16), "B": (TINY_B, 1, 0.03, 8), "C": (TINY_C, 5, 0.05, 16),
+        "D": (TINY_D, 6, 0.04, 16), "E": (TINY_D, 6, 0.04, 64)}
 
 
 def write_tiny_model(name: str, folder: str, sigma_scale: float = 1.0, norm_dtype=None) -> str:
