@@ -112,6 +112,7 @@ class CacheManager:
         self.requests: Dict[Hashable, RequestRecord] = {}
         self._names: Dict[int, Hashable] = {}
         self._next_number = 0
+        self._other_numbers: Dict[Hashable, int] = {}
         self._need_buf = (c_int * max(G, 1))()
 
     def __del__(self):
@@ -123,14 +124,28 @@ class CacheManager:
     def admit(self, request_id: Hashable) -> RequestRecord:
         if request_id in self.requests:
             raise CacheError(f"request {request_id!r} is already live")
-        number = self._next_number
+        number = self.number_of(request_id)
         slot = c_int()
         check(self._lib.llmrs_cm_admit(self._handle, number, byref(slot)), self._names)
-        self._next_number += 1
         rec = RequestRecord(self, request_id, number, slot.value)
         self.requests[request_id] = rec
         self._names[number] = request_id
         return rec
+
+    def number_of(self, request_id: Hashable) -> int:
+        """The request's number inside the host library: a non-negative integer id is its own number
+        (the scheduler, which lives in the same library, then knows the request by the caller's id);
+        any other id gets a negative number of its own."""
+        if isinstance(request_id, int) and not isinstance(request_id, bool) and 0 <= request_id < 2 ** 62:
+            return request_id
+        number = self._other_numbers.get(request_id)
+        if number is None:
+            self._next_number += 1
+            number = self._other_numbers[request_id] = -self._next_number
+            if len(self._other_numbers) > 4 * self.n_slots + 64:    # forget ids that are no longer live
+                self._other_numbers = {k: v for k, v in self._other_numbers.items()
+                                       if k in self.requests or k == request_id}
+        return number
 
     def has_free_slot(self) -> bool:
         return len(self.requests) < self.n_slots

@@ -31,7 +31,7 @@ ABI_VERSION = 2
 HOST_DIR = os.path.join(CSRC_DIR, "host")
 HOST_LIB_NAME = "libllmrs_b200_host.so"
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
-HOST_ABI_VERSION = 1
+HOST_ABI_VERSION = 2
 
 _lib: Optional[ctypes.CDLL] = None
 _host_lib: Optional[ctypes.CDLL] = None

@@ -4,6 +4,7 @@
 #include <string>
 
 #include "cache_manager.hpp"
+#include "scheduler.hpp"
 
 using namespace llmrs_host;
 
@@ -33,7 +34,7 @@ T* as(void* handle, const char* what) {
 
 extern "C" {
 
-int llmrs_host_abi_version(void) { return 1; }
+int llmrs_host_abi_version(void) { return 2; }
 const char* llmrs_host_last_error(void) { return g_error.c_str(); }
 
 int llmrs_pool_create(int capacity, void** pool) {
@@ -130,6 +131,100 @@ int llmrs_pack_step(void* cm, int n_entries, const int64_t* ids, const int32_t* 
         *total = s.total;
         *written = ok ? 1 : 0;
     });
+}
+
+
+int llmrs_sched_create(void* cm, int max_positions, const int32_t* eos, int n_eos, int max_tokens_per_step,
+                       int prefill_chunk, int max_requests_per_step, void** sched) {
+    return guarded([&] {
+        *sched = new Scheduler(as<CacheManager>(cm, "manager"), max_positions, eos, n_eos, max_tokens_per_step,
+                               prefill_chunk, max_requests_per_step);
+    });
+}
+void llmrs_sched_destroy(void* sched) { delete static_cast<Scheduler*>(sched); }
+int llmrs_sched_add(void* sched, int64_t id, int prompt_len, int max_new_tokens, int ignore_eos) {
+    return guarded([&] { as<Scheduler>(sched, "scheduler")->add(id, prompt_len, max_new_tokens, ignore_eos != 0); });
+}
+int llmrs_sched_has_work(void* sched, int* out) {
+    return guarded([&] { *out = as<Scheduler>(sched, "scheduler")->has_work() ? 1 : 0; });
+}
+int llmrs_sched_schedule(void* sched, int64_t* ids, int32_t* fields4, int capacity, int* n, int64_t* batch) {
+    return guarded([&] {
+        std::vector<SchedEntry> entries;
+        *batch = as<Scheduler>(sched, "scheduler")->schedule(&entries);
+        *n = static_cast<int>(entries.size());
+        if (*n > capacity) throw Failure{kBadArgument, "the buffer for the step's entries is too small"};
+        for (int i = 0; i < *n; ++i) {
+            ids[i] = entries[i].id;
+            fields4[4 * i] = entries[i].start;
+            fields4[4 * i + 1] = entries[i].n_tokens;
+            fields4[4 * i + 2] = entries[i].sample ? 1 : 0;
+            fields4[4 * i + 3] = entries[i].pending ? 1 : 0;
+        }
+    });
+}
+int llmrs_sched_on_launched(void* sched, int64_t batch) {
+    return guarded([&] { as<Scheduler>(sched, "scheduler")->on_launched(batch); });
+}
+namespace {
+void copy_outputs(const std::vector<SchedOutput>& outs, int64_t* out_ids, int32_t* out_fields3, int capacity, int* n_out) {
+    *n_out = static_cast<int>(outs.size());
+    if (*n_out > capacity) throw Failure{kBadArgument, "the buffer for the outputs is too small"};
+    for (int i = 0; i < *n_out; ++i) {
+        out_ids[i] = outs[i].id;
+        out_fields3[3 * i] = outs[i].token;
+        out_fields3[3 * i + 1] = outs[i].finished ? 1 : 0;
+        out_fields3[3 * i + 2] = outs[i].reason;
+    }
+}
+}  // namespace
+int llmrs_sched_on_result(void* sched, int64_t batch, const int32_t* tokens, int n_tokens, int64_t* out_ids,
+                          int32_t* out_fields3, int capacity, int* n_out) {
+    return guarded([&] {
+        std::vector<SchedOutput> outs;
+        as<Scheduler>(sched, "scheduler")->on_result(batch, tokens, n_tokens, &outs);
+        copy_outputs(outs, out_ids, out_fields3, capacity, n_out);
+    });
+}
+int llmrs_sched_abort_all(void* sched, int reason, int64_t* out_ids, int32_t* out_fields3, int capacity, int* n_out) {
+    return guarded([&] {
+        std::vector<SchedOutput> outs;
+        as<Scheduler>(sched, "scheduler")->abort_all(reason, &outs);
+        copy_outputs(outs, out_ids, out_fields3, capacity, n_out);
+    });
+}
+int llmrs_sched_take(void* sched, int which, int64_t* ids, int capacity, int* n) {
+    return guarded([&] {
+        auto* s = as<Scheduler>(sched, "scheduler");
+        std::vector<int64_t> v;
+        if (which == 0) s->take_releases(&v);
+        else if (which == 1) s->take_changed(&v);
+        else if (which == 2) v.assign(s->waiting().begin(), s->waiting().end());
+        else if (which == 3) v = s->running();
+        else throw Failure{kBadArgument, "llmrs_sched_take: which must be 0..3"};
+        *n = static_cast<int>(v.size());
+        // Lists that are taken (0, 1) must not be lost to a small buffer: the caller sizes it by the
+        // number of requests it has ever added.
+        if (*n > capacity) throw Failure{kBadArgument, "the buffer for the request ids is too small"};
+        for (int i = 0; i < *n; ++i) ids[i] = v[i];
+    });
+}
+int llmrs_sched_get(void* sched, int64_t id, int32_t* state6) {
+    return guarded([&] {
+        const SchedRequest& r = as<Scheduler>(sched, "scheduler")->request(id);
+        state6[0] = r.status;
+        state6[1] = r.finish_reason;
+        state6[2] = r.n_output;
+        state6[3] = r.n_computed;
+        state6[4] = r.n_inflight;
+        state6[5] = r.preemptions;
+    });
+}
+int llmrs_sched_forget(void* sched, int64_t id) {
+    return guarded([&] { as<Scheduler>(sched, "scheduler")->forget(id); });
+}
+int llmrs_sched_stats(void* sched, int64_t* stats3) {
+    return guarded([&] { as<Scheduler>(sched, "scheduler")->stats(stats3, stats3 + 1, stats3 + 2); });
 }
 
 }  // extern "C"

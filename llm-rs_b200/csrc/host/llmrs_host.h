@@ -48,6 +48,29 @@ int llmrs_pack_step(void* cm, int n_entries, const int64_t* ids, const int32_t* 
                     int prefill_tile, int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
                     int32_t* widths, int32_t* shape8, int64_t* total, int* written);
 
+/* The scheduler (decisions only; see scheduler.hpp). It reads the cache manager `cm`, which must
+ * outlive it, and never changes it: after every call that returns `n_release > 0` ids through
+ * llmrs_sched_take, the caller releases those requests in the manager before it calls again.
+ * Finish reasons: 0 none, 1 stop (EOS), 2 length, 3 too long for the pool, 4 a step failed. */
+int llmrs_sched_create(void* cm, int max_positions, const int32_t* eos, int n_eos, int max_tokens_per_step,
+                       int prefill_chunk, int max_requests_per_step, void** sched);
+void llmrs_sched_destroy(void* sched);
+int llmrs_sched_add(void* sched, int64_t id, int prompt_len, int max_new_tokens, int ignore_eos);
+int llmrs_sched_has_work(void* sched, int* out);
+/* entries: per entry id, and 4 ints: start (-1: the token in flight), n_tokens, sample, pending. *batch: handle, 0 if empty. */
+int llmrs_sched_schedule(void* sched, int64_t* ids, int32_t* fields4, int capacity, int* n, int64_t* batch);
+int llmrs_sched_on_launched(void* sched, int64_t batch);
+/* tokens: one per sampling entry of the batch, in order. outs: per output id, and 3 ints: token (-1 none), finished, reason. */
+int llmrs_sched_on_result(void* sched, int64_t batch, const int32_t* tokens, int n_tokens, int64_t* out_ids,
+                          int32_t* out_fields3, int capacity, int* n_out);
+int llmrs_sched_abort_all(void* sched, int reason, int64_t* out_ids, int32_t* out_fields3, int capacity, int* n_out);
+/* which = 0: requests to release now; 1: requests whose state changed; 2: waiting queue; 3: running list. */
+int llmrs_sched_take(void* sched, int which, int64_t* ids, int capacity, int* n);
+/* state6: status (0 waiting, 1 running, 2 finished), finish reason, n_output, n_computed, n_inflight, preemptions */
+int llmrs_sched_get(void* sched, int64_t id, int32_t* state6);
+int llmrs_sched_forget(void* sched, int64_t id);
+int llmrs_sched_stats(void* sched, int64_t* stats3);
+
 #ifdef __cplusplus
 }
 #endif

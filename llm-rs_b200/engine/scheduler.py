@@ -22,14 +22,20 @@ What this scheduler does differently, and why:
     "in flight" is scheduled with that token taken from the device; one that will end by
     its length is not scheduled further; one that turns out to have ended at EOS has its
     last, superfluous token dropped.
+
+The decisions are made in C++ (``csrc/host/scheduler.cpp``), which knows requests by their
+lengths; this module keeps the requests' tokens and parameters, hands the library the numbers
+it needs and mirrors its state into the ``Request`` objects after every call.
 """
 from __future__ import annotations
 
-from collections import deque
+from ctypes import byref, c_int, c_int32, c_int64, c_void_p
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence
 
+from .. import host
 from ..cache.manager import CacheManager
+from ..cache.pool import check
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
@@ -86,6 +92,15 @@ class Output:
     reason: Optional[str] = None
 
 
+_STATUS = {0: WAITING, 1: RUNNING, 2: FINISHED}
+_REASON = {0: None, 1: "stop", 2: "length", 3: "error_too_long", 4: "error_step_failed"}
+
+
+class Batch(list):
+    """The ``Scheduled`` entries of one step, with the library's handle of the step."""
+    handle = 0
+
+
 class Scheduler:
     def __init__(self, manager: CacheManager, max_positions: int, eos_token_ids: Sequence[int] = (),
                  max_tokens_per_step: int = 2048, prefill_chunk: int = 512, max_requests_per_step: int = 64):
@@ -95,185 +110,147 @@ class Scheduler:
         self.max_tokens_per_step = max_tokens_per_step
         self.prefill_chunk = prefill_chunk
         self.max_requests_per_step = max_requests_per_step
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []          # in order of admission
-        self.stats = {"steps": 0, "preemptions": 0, "tokens": 0}
-        self._finished_early: List[Output] = []
+        self._lib = host.lib()
+        self._handle = c_void_p()
+        eos = (c_int32 * max(len(self.eos), 1))(*sorted(self.eos))
+        check(self._lib.llmrs_sched_create(manager._handle, max_positions, eos, len(self.eos), max_tokens_per_step,
+                                           prefill_chunk, max_requests_per_step, byref(self._handle)))
+        self._requests: Dict[int, Request] = {}
+        self._ids = (c_int64 * 64)()
+        self._fields = (c_int32 * (4 * 64))()
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            self._lib.llmrs_sched_destroy(self._handle)
+            self._handle = None
+
+    # -- plumbing --------------------------------------------------------------------
+    def _buffers(self, n: int):
+        if len(self._ids) < n:
+            self._ids = (c_int64 * (2 * n))()
+            self._fields = (c_int32 * (8 * n))()
+        return self._ids, self._fields
+
+    def _take(self, which: int) -> List[int]:
+        ids, _ = self._buffers(len(self._requests) + 8)
+        n = c_int()
+        check(self._lib.llmrs_sched_take(self._handle, which, ids, len(ids), byref(n)))
+        return list(ids[:n.value])
+
+    def _sync(self) -> None:
+        """Give back the pages of the requests that the library released, and copy the state of
+        the requests it touched into their ``Request`` objects."""
+        for rid in self._take(0):
+            if rid in self.manager.requests:
+                self.manager.release(rid)
+        state = (c_int32 * 6)()
+        for rid in set(self._take(1)):
+            req = self._requests.get(rid)
+            if req is None:
+                continue
+            check(self._lib.llmrs_sched_get(self._handle, rid, state))
+            req.status, req.finish_reason = _STATUS[state[0]], _REASON[state[1]] if state[0] == 2 else None
+            req.n_computed, req.n_inflight, req.preemptions = state[3], state[4], state[5]
+            if state[0] == 2 and state[4] == 0:
+                if getattr(req, "_abort_reason", None):
+                    req.finish_reason = req._abort_reason
+                self._lib.llmrs_sched_forget(self._handle, rid)
+                del self._requests[rid]
+
+    def _outputs(self, n: int) -> List[Output]:
+        outs = []
+        for i in range(n):
+            rid, token, finished, reason = self._ids[i], self._fields[3 * i], self._fields[3 * i + 1], self._fields[3 * i + 2]
+            if token >= 0:
+                self._requests[rid].output.append(token)
+            outs.append(Output(rid, token if token >= 0 else None, bool(finished), _REASON[reason]))
+        return outs
 
     # -- intake ----------------------------------------------------------------------
     def add_request(self, request: Request) -> None:
-        if not request.prompt:
-            raise ValueError("a request needs at least one prompt token")
-        if len(request.prompt) >= self.max_positions:
-            raise ValueError(f"prompt of {len(request.prompt)} tokens leaves no room under the limit of "
-                             f"{self.max_positions} positions")
+        rid = request.request_id
+        if not isinstance(rid, int) or isinstance(rid, bool) or not 0 <= rid < 2 ** 62:
+            raise ValueError(f"the scheduler takes non-negative integer request ids, got {rid!r}")
         request.status = WAITING
-        self.waiting.append(request)
+        check(self._lib.llmrs_sched_add(self._handle, rid, len(request.prompt) + len(request.output),
+                                        request.params.max_new_tokens - len(request.output),
+                                        int(request.params.ignore_eos)))
+        self._requests[rid] = request
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running or self._finished_early)
+        out = c_int()
+        check(self._lib.llmrs_sched_has_work(self._handle, byref(out)))
+        return bool(out.value)
 
-    # -- pages -----------------------------------------------------------------------
-    def _fits(self, req: Request, n_new: int, free: List[int]) -> bool:
-        live = req.request_id in self.manager.requests
-        need = self.manager.pages_needed(req.request_id if live else None, n_new, 0 if not live else None)
-        if all(n <= f for n, f in zip(need, free)):
-            for g, n in enumerate(need):
-                free[g] -= n
-            return True
-        return False
+    # -- views -----------------------------------------------------------------------
+    @property
+    def waiting(self) -> List[Request]:
+        return [self._requests[i] for i in self._take(2)]
 
-    def _preempt_last(self, free: List[int], keep: Optional[Request] = None) -> Optional[Request]:
-        """Send the request admitted last back to the waiting queue; its pages become free."""
-        if not self.running:
-            return None
-        victim = self.running.pop()
-        if victim.request_id in self.manager.requests:
-            before = [p.free_pages() for p in self.manager.pools]
-            self.manager.release(victim.request_id)
-            for g, pool in enumerate(self.manager.pools):
-                free[g] += pool.free_pages() - before[g]
-        victim.n_computed = 0
-        victim.status = WAITING
-        victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
-        return victim
+    @property
+    def running(self) -> List[Request]:
+        return [self._requests[i] for i in self._take(3)]
 
-    def _finish(self, req: Request, reason: str) -> None:
-        req.status, req.finish_reason = FINISHED, reason
-        if req in self.running:
-            self.running.remove(req)
-        elif req in self.waiting:
-            self.waiting.remove(req)   # it was preempted while its last token was in flight
-        if req.request_id in self.manager.requests:
-            self.manager.release(req.request_id)
+    @property
+    def stats(self) -> Dict[str, int]:
+        v = (c_int64 * 3)()
+        check(self._lib.llmrs_sched_stats(self._handle, v))
+        return {"steps": v[0], "preemptions": v[1], "tokens": v[2]}
 
     # -- one step --------------------------------------------------------------------
-    def schedule(self) -> List[Scheduled]:
+    def schedule(self) -> Batch:
         """Decide the next step's batch. May preempt (see the module's header) and may
-        finish requests that can never fit; those show up in the next ``update``."""
-        while True:
-            batch = self._try_schedule()
-            if batch or not self.running:
-                return batch
-            # Nothing to run. Either every running request only waits for tokens that are in
-            # flight, or requests are running and none could get its pages.
-            stuck = [r for r in self.running if r.remaining >= 1 and not self._ends_by_length(r)]
-            if not stuck:
-                return batch
-            if len(self.running) == 1:
-                req = self.running[0]
-                self._finish(req, "error_too_long")
-                self._finished_early.append(Output(req.request_id, None, True, "error_too_long"))
-            else:
-                self._preempt_last([0] * len(self.manager.pools))
-
-    def _try_schedule(self) -> List[Scheduled]:
-        free = [p.free_pages() for p in self.manager.pools]
-        budget = self.max_tokens_per_step
-        batch: List[Scheduled] = []
-
-        # 1. decoding requests, in order of admission; make room by preempting from the back
-        i = 0
-        while i < len(self.running) and budget >= 1 and len(batch) < self.max_requests_per_step:
-            req = self.running[i]
-            if req.remaining != 1 or self._ends_by_length(req):
-                i += 1
-                continue
-            fits = self._fits(req, 1, free)
-            while not fits and self.running[-1] is not req:
-                self._preempt_last(free)
-                fits = self._fits(req, 1, free)
-            if not fits:
-                break  # req is the last one running; schedule() decides what becomes of it
-            if req.n_inflight:
-                batch.append(Scheduled(req, [0], True, pending=True))
-            else:
-                batch.append(Scheduled(req, req.token_slice(req.n_known - 1, req.n_known), True))
-            budget -= 1
-            i += 1
-
-        # 2. running requests that still have prompt left, in order of admission
-        for req in self.running:
-            if req.remaining > 1 and budget >= 1 and len(batch) < self.max_requests_per_step:
-                n = min(req.n_known - req.n_computed, self.prefill_chunk, budget)   # known tokens only
-                if n >= 1 and self._fits(req, n, free):
-                    toks = req.token_slice(req.n_computed, req.n_computed + n)
-                    batch.append(Scheduled(req, toks, req.n_computed + n == req.n_known and not req.n_inflight))
-                    budget -= n
-
-        # 3. admit from the front of the waiting queue while a slot, budget and pages last
-        slots = self.manager.n_slots - len(self.manager.requests)
-        while self.waiting and budget >= 1 and slots > 0 and len(batch) < self.max_requests_per_step:
-            req = self.waiting[0]
-            n = min(req.n_known - req.n_computed, self.prefill_chunk, budget)
-            if not self._fits(req, n, free):
-                if not self.running and not batch:
-                    # Nothing else holds pages: this request can never start.
-                    self.waiting.popleft()
-                    self._finish(req, "error_too_long")
-                    self._finished_early.append(Output(req.request_id, None, True, "error_too_long"))
-                    continue
-                break  # the queue waits behind its head (llm-scheduler/src/scheduler.rs:86-89)
-            self.waiting.popleft()
-            req.status = RUNNING
-            self.running.append(req)
-            slots -= 1
-            toks = req.token_slice(req.n_computed, req.n_computed + n)
-            batch.append(Scheduled(req, toks, req.n_computed + n == req.n_known and not req.n_inflight))
-            budget -= n
+        finish requests that can never fit; those show up in the next ``on_result``."""
+        ids, fields = self._buffers(self.max_requests_per_step)
+        n, handle = c_int(), c_int64()
+        check(self._lib.llmrs_sched_schedule(self._handle, ids, fields, len(ids), byref(n), byref(handle)))
+        batch = Batch()
+        batch.handle = handle.value
+        for i in range(n.value):
+            req = self._requests[ids[i]]
+            start, count, sample, pending = fields[4 * i], fields[4 * i + 1], fields[4 * i + 2], fields[4 * i + 3]
+            tokens = [0] if pending else req.token_slice(start, start + count)
+            batch.append(Scheduled(req, tokens, bool(sample), bool(pending)))
+        self._sync()
         return batch
 
-    def _ends_by_length(self, req: Request) -> bool:
-        """True when the tokens already sampled (read or not) complete the request."""
-        n_out = len(req.output) + req.n_inflight
-        return n_out >= req.params.max_new_tokens or len(req.prompt) + n_out >= self.max_positions
-
-    def on_launched(self, batch: Sequence[Scheduled]) -> None:
+    def on_launched(self, batch: Batch) -> None:
         """The step is queued on the GPU: its tokens count as computed, its samples as in flight."""
-        self.stats["steps"] += 1
-        for s in batch:
-            s.request.n_computed += len(s.tokens)
-            self.stats["tokens"] += len(s.tokens)
-            if s.sample:
-                s.request.n_inflight += 1
+        if not batch:
+            return
+        check(self._lib.llmrs_sched_on_launched(self._handle, batch.handle))
+        self._sync()
 
-    def on_result(self, batch: Sequence[Scheduled], sampled: Dict[int, int]) -> List[Output]:
+    def on_result(self, batch, sampled: Dict[int, int]) -> List[Output]:
         """The step's tokens are on the host: ``sampled`` maps request id -> chosen token for
-        the entries with ``sample``. Returns what happened, finished requests freed."""
-        outputs, self._finished_early = list(self._finished_early), []
-        for s in batch:
-            req = s.request
-            if not s.sample:
-                continue
-            req.n_inflight -= 1
-            if req.status == FINISHED:
-                continue          # it had ended at EOS one step earlier: this token is one too many
-            token = int(sampled[req.request_id])
-            req.output.append(token)
-            reason = None
-            if token in self.eos and not req.params.ignore_eos:
-                reason = "stop"          # the EOS token is emitted (scheduler.rs:150-156)
-            elif len(req.output) >= req.params.max_new_tokens:
-                reason = "length"
-            elif len(req.prompt) + len(req.output) >= self.max_positions:
-                reason = "length"
-            if reason:
-                self._finish(req, reason)
-            outputs.append(Output(req.request_id, token, reason is not None, reason))
-        return outputs
+        the entries with ``sample``. Returns what happened, finished requests freed. An empty
+        ``batch`` collects the requests that ended without a step."""
+        handle = getattr(batch, "handle", 0) if batch else 0
+        toks = [int(sampled[s.request.request_id]) for s in batch if s.sample] if handle else []
+        arr = (c_int32 * max(len(toks), 1))(*toks)
+        ids, fields = self._buffers(len(self._requests) + 8)
+        n = c_int()
+        check(self._lib.llmrs_sched_on_result(self._handle, handle, arr, len(toks), ids, fields, len(ids), byref(n)))
+        outs = self._outputs(n.value)
+        self._sync()
+        return outs
 
-    def update(self, batch: Sequence[Scheduled], sampled: Dict[int, int]) -> List[Output]:
+    def update(self, batch, sampled: Dict[int, int]) -> List[Output]:
         """``on_launched`` and ``on_result`` in one call, for a caller that reads every step's tokens at once."""
-        self.on_launched(batch)
+        if batch:
+            self.on_launched(batch)
         return self.on_result(batch, sampled)
 
     def abort_all(self, reason: str = "error_step_failed") -> List[Output]:
         """A step failed: every running request ends and frees its pages
         (llm-scheduler/src/engine.rs:92-99, scheduler.rs:193-200)."""
-        outs = []
-        for req in list(self.running):
-            self._finish(req, reason)
-            outs.append(Output(req.request_id, None, True, reason))
+        ids, fields = self._buffers(len(self._requests) + 8)
+        n = c_int()
+        for req in self._requests.values():
+            req._abort_reason = reason
+        check(self._lib.llmrs_sched_abort_all(self._handle, 4, ids, fields, len(ids), byref(n)))
+        outs = [Output(ids[i], None, True, reason) for i in range(n.value)]
+        self._sync()
+        for req in self._requests.values():
+            req._abort_reason = None
         return outs

@@ -1,5 +1,5 @@
 """Python face of the host library (C++ under ``csrc/host/``): page pools, the cache
-manager and the packing of a step's index arrays. The bookkeeping runs in the library;
+manager, the scheduler and the packing of a step's index arrays. The bookkeeping runs in the library;
 the classes in ``cache`` and ``engine.runner`` hold its handles.
 """
 from __future__ import annotations
@@ -43,6 +43,18 @@ def lib() -> ctypes.CDLL:
             "llmrs_cm_table": [c_void_p, c_int64, c_int, i32p, c_int, intp],
             "llmrs_cm_pool_counts": [c_void_p, c_int, intp, intp],
             "llmrs_cm_check_invariants": [c_void_p],
+            "llmrs_sched_create": [c_void_p, c_int, i32p, c_int, c_int, c_int, c_int, POINTER(c_void_p)],
+            "llmrs_sched_destroy": [c_void_p],
+            "llmrs_sched_add": [c_void_p, c_int64, c_int, c_int, c_int],
+            "llmrs_sched_has_work": [c_void_p, intp],
+            "llmrs_sched_schedule": [c_void_p, i64p, i32p, c_int, intp, i64p],
+            "llmrs_sched_on_launched": [c_void_p, c_int64],
+            "llmrs_sched_on_result": [c_void_p, c_int64, i32p, c_int, i64p, i32p, c_int, intp],
+            "llmrs_sched_abort_all": [c_void_p, c_int, i64p, i32p, c_int, intp],
+            "llmrs_sched_take": [c_void_p, c_int, i64p, c_int, intp],
+            "llmrs_sched_get": [c_void_p, c_int64, i32p],
+            "llmrs_sched_forget": [c_void_p, c_int64],
+            "llmrs_sched_stats": [c_void_p, i64p],
             "llmrs_pack_step": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                 c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, i64p, intp],
         }
