@@ -7,7 +7,7 @@
 // most probable tokens whose mass reaches top_p -> draw.
 //
 // Where the reference sorts and draws from an unseeded generator, this kernel finds
-// the two cut-off values by bisection on the float bit pattern, keeps ties at a cut-off,
+// the two cut-off values digit by digit on the float bit pattern, keeps ties at a cut-off,
 // and draws in vocabulary order with a Philox4x32-10 number keyed by (seed; request id,
 // index of the generated token), so a request's tokens do not depend on what else is
 // in the batch. The distribution drawn from is the reference's.
@@ -35,6 +35,21 @@ LLMRS_API float llmrs_philox_uniform(unsigned long long seed, unsigned long long
   philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), (uint32_t)request_id, (uint32_t)(request_id >> 32), index, 0u,
                 r);
   return (float)(r[0] >> 8) * (1.0f / 16777216.0f);
+}
+
+// Calls f(index, value) for every element of a row, the block's threads striding over it; four
+// elements per load when the row allows it (every row then starts on a 16-byte boundary).
+template <typename F>
+__device__ __forceinline__ void for_each_elem(const float* __restrict__ x, int vocab, F&& f) {
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+      const float4 v = x4[i];
+      f(4 * i, v.x); f(4 * i + 1, v.y); f(4 * i + 2, v.z); f(4 * i + 3, v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(i, x[i]);
+  }
 }
 
 struct ArgMax {
@@ -74,6 +89,83 @@ __device__ ArgMax block_argmax(ArgMax a, ArgMax* red) {
   return red[32];
 }
 
+// ---- selection of a cut-off value by digits ------------------------------------------------
+// The values e are floats in [0, 1], whose bit patterns are ordered like the values. A cut-off is
+// found digit by digit (11, 11 and 8 bits, highest first): one pass over the row builds a histogram
+// of the current digit among the values that share the digits found so far, and the digit is the
+// highest bin at which the running total from the top reaches what is asked: a number of values
+// (top_k) or a mass (top_p). Three passes instead of the thirty of a bisection, and every pass
+// reads the row in coalesced order. Masses are added as 64-bit fixed point (2^-40 units), so the
+// histogram does not depend on the order in which the threads arrive.
+constexpr int SEL_BINS = 2048;
+constexpr float SEL_FIX = 1099511627776.0f;   // 2^40
+
+struct SelectScratch {
+  unsigned long long bins[SEL_BINS];   // counts or fixed-point masses
+  unsigned long long warp_tot[32];
+  unsigned long long found_above;
+  int found_bin;
+};
+
+__device__ __forceinline__ unsigned long long to_fixed(float e) { return (unsigned long long)(e * SEL_FIX); }
+
+// Highest bin b with sum(bins[b..]) >= need; returns b (or -1) and leaves sum(bins[b+1..]) in sc->found_above.
+// All threads of the block call it; bins are read top-down, two per thread.
+__device__ int find_bin(SelectScratch* sc, unsigned long long need) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int b0 = SEL_BINS - 1 - 2 * tid, b1 = b0 - 1;            // this thread's two bins, the higher first
+  const unsigned long long v0 = sc->bins[b0], v1 = sc->bins[b1];
+  unsigned long long incl = v0 + v1;                              // inclusive scan over threads, top-down
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (tid == 0) sc->found_bin = -1;
+  if (lane == 31) sc->warp_tot[warp] = incl;
+  __syncthreads();
+  unsigned long long before = 0;                                  // everything above this thread's bins
+  for (int w = 0; w < warp; ++w) before += sc->warp_tot[w];
+  before += incl - (v0 + v1);
+  // Exactly one thread sees the running total cross `need` (need >= 1).
+  if (before < need && before + v0 >= need) { sc->found_bin = b0; sc->found_above = before; }
+  else if (before + v0 < need && before + v0 + v1 >= need) { sc->found_bin = b1; sc->found_above = before + v0; }
+  __syncthreads();
+  return sc->found_bin;
+}
+
+// The largest t >= floor_bits (as a bit pattern) such that the values e >= t number at least
+// `need` (by_mass = false) or weigh at least `need` in fixed point (by_mass = true). Values below
+// `floor_bits` do not take part. Returns floor_bits when nothing qualifies.
+__device__ uint32_t select_cut(const float* __restrict__ x, int vocab, uint32_t floor_bits, unsigned long long need,
+                               bool by_mass, SelectScratch* sc) {
+  const int tid = threadIdx.x;
+  uint32_t prefix = 0;            // digits found so far, in place
+  uint32_t prefix_mask = 0;
+  const int shifts[3] = {19, 8, 0}, widths[3] = {11, 11, 8};
+  if (need == 0) need = 1;
+#pragma unroll 1
+  for (int level = 0; level < 3; ++level) {
+    for (int i = tid; i < SEL_BINS; i += SM_THREADS) sc->bins[i] = 0;
+    __syncthreads();
+    const int shift = shifts[level];
+    const uint32_t digit_mask = (1u << widths[level]) - 1u;
+    for_each_elem(x, vocab, [&](int, float e) {
+      const uint32_t bits = __float_as_uint(e);
+      if (bits >= floor_bits && (bits & prefix_mask) == prefix)
+        atomicAdd(&sc->bins[(bits >> shift) & digit_mask], by_mass ? to_fixed(e) : 1ull);
+    });
+    __syncthreads();
+    const int bin = find_bin(sc, need);
+    if (bin < 0) return floor_bits;
+    need -= sc->found_above;
+    prefix |= (uint32_t)bin << shift;
+    prefix_mask |= digit_mask << shift;
+    __syncthreads();
+  }
+  return prefix > floor_bits ? prefix : floor_bits;
+}
+
 // logits [n_rows, vocab] are changed in place (penalty, then exp(x - max)).
 __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
@@ -81,11 +173,11 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
               const int* __restrict__ hist_tokens, const int* __restrict__ hist_offsets,
               const unsigned long long* __restrict__ seeds, const unsigned long long* __restrict__ request_ids,
               const int* __restrict__ gen_index, int* __restrict__ out_tokens) {
-  __shared__ float red[33];
   __shared__ ArgMax ared[33];
+  __shared__ SelectScratch sel;
   __shared__ float scan[SM_THREADS];
   __shared__ int chosen;
-  const int row = blockIdx.x, tid = threadIdx.x;
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float* x = logits + (size_t)row * vocab;
 
   const float pen = penalty ? penalty[row] : 1.0f;
@@ -102,7 +194,7 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
 
   const float T = temperature ? temperature[row] : 0.f;
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int i = tid; i < vocab; i += SM_THREADS) best = better(best, ArgMax{x[i], i});
+  for_each_elem(x, vocab, [&](int i, float v) { best = better(best, ArgMax{v, i}); });
   best = block_argmax(best, ared);
   if (best.i >= vocab) best.i = 0;  // a row of NaN has no maximum
   if (T <= 1e-5f) {
@@ -110,105 +202,122 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
     return;
   }
 
-  // e_i = exp(x_i / T - max / T); contiguous chunk per thread so that sums run in vocabulary order.
-  const int chunk = (vocab + SM_THREADS - 1) / SM_THREADS;
-  const int lo = min(tid * chunk, vocab), hi = min(lo + chunk, vocab);
+  // e_i = exp(x_i / T - max / T), in [0, 1].
   const float mx = best.v / T;
-  float mass = 0.f;
-  for (int i = lo; i < hi; ++i) {
-    const float e = expf(x[i] / T - mx);
-    x[i] = e;
-    mass += e;
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    float4* x4 = reinterpret_cast<float4*>(x);
+    for (int i = tid; i < vocab / 4; i += SM_THREADS) {
+      float4 v = x4[i];
+      float* e = reinterpret_cast<float*>(&v);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float y = expf(e[c] / T - mx);
+        e[c] = y >= 0.f ? y : 0.f;   // a NaN logit keeps no mass
+      }
+      x4[i] = v;
+    }
+  } else {
+    for (int i = tid; i < vocab; i += SM_THREADS) {
+      const float e = expf(x[i] / T - mx);
+      x[i] = e >= 0.f ? e : 0.f;
+    }
   }
   __syncthreads();
 
-  float cut = 0.f;  // keep e_i >= cut
+  uint32_t cut_bits = 0u;  // keep e_i >= cut
   const int k = top_k ? top_k[row] : 0;
-  if (k > 0 && k < vocab) {
-    // Largest t with count(e >= t) >= k, by bisection on the bit pattern (e >= 0: bits are ordered).
-    uint32_t lo_b = 0u, hi_b = 0x3f800000u;  // e lies in [0, 1]
-    while (lo_b < hi_b) {
-      const uint32_t mid = lo_b + (hi_b - lo_b + 1) / 2;
-      const float t = __uint_as_float(mid);
-      float cnt = 0.f;
-      for (int i = lo; i < hi; ++i) cnt += x[i] >= t ? 1.f : 0.f;
-      cnt = block_sum(cnt, red);
-      if (cnt >= (float)k) lo_b = mid; else hi_b = mid - 1;
-    }
-    cut = __uint_as_float(lo_b);
-    mass = 0.f;
-    for (int i = lo; i < hi; ++i) mass += x[i] >= cut ? x[i] : 0.f;
-  }
-  float total = block_sum(mass, red);
+  if (k > 0 && k < vocab) cut_bits = select_cut(x, vocab, 0u, (unsigned long long)k, false, &sel);   // the k-th largest value
   const float p = top_p ? top_p[row] : 1.0f;
   if (p < 1.0f) {
-    // Largest t >= cut with mass(e >= t) >= p * total.
-    const float need = p * total;
-    uint32_t lo_b = __float_as_uint(cut), hi_b = 0x3f800000u;
-    while (lo_b < hi_b) {
-      const uint32_t mid = lo_b + (hi_b - lo_b + 1) / 2;
-      const float t = __uint_as_float(mid);
-      float ms = 0.f;
-      for (int i = lo; i < hi; ++i) ms += x[i] >= t ? x[i] : 0.f;
-      ms = block_sum(ms, red);
-      if (ms >= need) lo_b = mid; else hi_b = mid - 1;
-    }
-    cut = __uint_as_float(lo_b);
-    mass = 0.f;
-    for (int i = lo; i < hi; ++i) mass += x[i] >= cut ? x[i] : 0.f;
-    total = block_sum(mass, red);
+    // Mass of what top_k kept, then the largest t >= cut with mass(e >= t) >= p * that mass.
+    unsigned long long part = 0;
+    for_each_elem(x, vocab, [&](int, float e) {
+      if (__float_as_uint(e) >= cut_bits) part += to_fixed(e);
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    __syncthreads();
+    if (lane == 0) sel.warp_tot[warp] = part;
+    __syncthreads();
+    unsigned long long total_fx = 0;
+    for (int w = 0; w < SM_THREADS / 32; ++w) total_fx += sel.warp_tot[w];
+    __syncthreads();
+    const unsigned long long need = (unsigned long long)((double)total_fx * (double)p);
+    cut_bits = select_cut(x, vocab, cut_bits, need, true, &sel);
   }
+  const float cut = __uint_as_float(cut_bits);
 
-  // Draw: first index, in vocabulary order, whose running sum of kept e exceeds u * total.
+  // Draw: first index, in vocabulary order, whose running sum of kept e exceeds u * total. The
+  // vocabulary is cut into 1024 runs of consecutive indices; a warp sums 32 of the runs (coalesced
+  // loads, a fixed order of additions), one thread walks the 1024 sums in order, and the thread
+  // that owns the run in which the target falls walks that run.
+  const int chunk = (vocab + SM_THREADS - 1) / SM_THREADS;
+  for (int c = warp * 32; c < warp * 32 + 32; ++c) {
+    const int lo_c = min(c * chunk, vocab), hi_c = min(lo_c + chunk, vocab);
+    float part = 0.f;
+    for (int i = lo_c + lane; i < hi_c; i += 32) {
+      const float e = x[i];
+      part += e >= cut ? e : 0.f;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if (lane == 0) scan[c] = part;
+  }
+  if (tid == 0) chosen = -1;
+  __syncthreads();
   uint32_t r[4];
   const unsigned long long seed = seeds ? seeds[row] : 0ull, rid = request_ids ? request_ids[row] : 0ull;
   philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), (uint32_t)rid, (uint32_t)(rid >> 32),
                 gen_index ? (uint32_t)gen_index[row] : 0u, 0u, r);
   const float u = (float)(r[0] >> 8) * (1.0f / 16777216.0f);
-  const float target = u * total;
-  scan[tid] = mass;
-  if (tid == 0) chosen = -1;
-  __syncthreads();
+  __shared__ float s_target, s_before;
   if (tid == 0) {
-    // Serial scan over the 1024 chunk sums keeps the order of the additions fixed.
-    float run = 0.f;
+    // Serial walks keep the order of the additions fixed.
+    float total = 0.f;
+    for (int t = 0; t < SM_THREADS; ++t) total += scan[t];
+    const float target = u * total;
+    float run = 0.f, before = 0.f;
     int owner = -1;
-    float before = 0.f;
     for (int t = 0; t < SM_THREADS; ++t) {
       const float next = run + scan[t];
-      if (owner < 0 && next > target) { owner = t; before = run; }
+      if (next > target) { owner = t; before = run; break; }
       run = next;
     }
     if (owner < 0) {
-      // Rounding left the target at or above the sum: the last chunk with kept mass owns it.
+      // Rounding left the target at or above the sum: the last run with kept mass owns it.
       for (int t = SM_THREADS - 1; t >= 0; --t)
         if (scan[t] > 0.f) { owner = t; break; }
       before = -1.f;
     }
-    scan[0] = before;
-    chosen = owner;  // chunk index for now
+    s_target = target;
+    s_before = before;
+    chosen = owner;
   }
   __syncthreads();
   const int owner = chosen;
-  const float before = scan[0];
-  __syncthreads();
-  if (tid == owner) {
-    int pick = -1, last_kept = -1;
-    float run = before;
-    for (int i = lo; i < hi; ++i) {
-      if (x[i] >= cut && x[i] > 0.f) {
-        last_kept = i;
-        if (before >= 0.f) {
-          run += x[i];
-          if (run > target) { pick = i; break; }
+  if (tid == 0) {
+    if (owner < 0) {
+      out_tokens[row] = best.i;
+    } else {
+      const float target = s_target, before = s_before;
+      const int lo = min(owner * chunk, vocab), hi = min(lo + chunk, vocab);
+      int pick = -1, last_kept = -1;
+      float run = before;
+      for (int i = lo; i < hi; ++i) {
+        const float e = x[i];
+        if (e >= cut && e > 0.f) {
+          last_kept = i;
+          if (before >= 0.f) {
+            run += e;
+            if (run > target) { pick = i; break; }
+          }
         }
       }
+      // The walk reached the run's end without a pick: rounding; take the run's last kept token.
+      if (pick < 0) pick = last_kept >= 0 ? last_kept : best.i;
+      out_tokens[row] = pick;
     }
-    // The loop ran to the chunk's end without a pick: rounding; take the chunk's last kept token.
-    if (pick < 0) pick = last_kept >= 0 ? last_kept : best.i;
-    out_tokens[row] = pick;
   }
-  if (owner < 0 && tid == 0) out_tokens[row] = best.i;
 }
 
 LLMRS_API int llmrs_sample(float* logits, int n_rows, int vocab, const float* temperature, const int* top_k,
@@ -229,7 +338,7 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
   __shared__ ArgMax ared[33];
   const float* x = logits + (size_t)blockIdx.x * vocab;
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += SM_THREADS) best = better(best, ArgMax{x[i], i});
+  for_each_elem(x, vocab, [&](int i, float v) { best = better(best, ArgMax{v, i}); });
   best = block_argmax(best, ared);
   if (threadIdx.x == 0) out_tokens[blockIdx.x] = best.i < vocab ? best.i : 0;  // a row of NaN has no maximum
 }
