@@ -270,28 +270,47 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
   philox4x32_10((uint32_t)seed, (uint32_t)(seed >> 32), (uint32_t)rid, (uint32_t)(rid >> 32),
                 gen_index ? (uint32_t)gen_index[row] : 0u, 0u, r);
   const float u = (float)(r[0] >> 8) * (1.0f / 16777216.0f);
-  __shared__ float s_target, s_before;
-  if (tid == 0) {
-    // Serial walks keep the order of the additions fixed.
-    float total = 0.f;
-    for (int t = 0; t < SM_THREADS; ++t) total += scan[t];
+  __shared__ float s_target, s_before, wsum[32];
+  __shared__ int wfirst[32], wlast[32];
+  {
+    // Running sums of the 1024 runs by a block-wide scan (a fixed order of additions), then the first
+    // run whose running sum exceeds the target.
+    const float v = scan[tid];
+    float incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    float before_warp = 0.f, total = 0.f;
+    for (int w = 0; w < SM_THREADS / 32; ++w) {
+      if (w == warp) before_warp = total;
+      total += wsum[w];
+    }
+    incl += before_warp;
     const float target = u * total;
-    float run = 0.f, before = 0.f;
-    int owner = -1;
-    for (int t = 0; t < SM_THREADS; ++t) {
-      const float next = run + scan[t];
-      if (next > target) { owner = t; before = run; break; }
-      run = next;
+    const unsigned hit = __ballot_sync(0xffffffffu, incl > target);
+    const unsigned kept = __ballot_sync(0xffffffffu, v > 0.f);
+    if (lane == 0) {
+      wfirst[warp] = hit ? warp * 32 + __ffs(hit) - 1 : 0x7fffffff;
+      wlast[warp] = kept ? warp * 32 + 31 - __clz(kept) : -1;
     }
-    if (owner < 0) {
+    __syncthreads();
+    int first = 0x7fffffff, last = -1;
+    for (int w = 0; w < SM_THREADS / 32; ++w) {
+      first = min(first, wfirst[w]);
+      last = max(last, wlast[w]);
+    }
+    if (first != 0x7fffffff) {
+      if (tid == first) { s_before = incl - v; s_target = target; chosen = first; }
+    } else if (tid == 0) {
       // Rounding left the target at or above the sum: the last run with kept mass owns it.
-      for (int t = SM_THREADS - 1; t >= 0; --t)
-        if (scan[t] > 0.f) { owner = t; break; }
-      before = -1.f;
+      s_before = -1.f;
+      s_target = target;
+      chosen = last;
     }
-    s_target = target;
-    s_before = before;
-    chosen = owner;
   }
   __syncthreads();
   const int owner = chosen;
