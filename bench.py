@@ -400,7 +400,8 @@ def main():
             # Prompts are prefilled four at a time, so some requests start decoding several steps
             # before the others, and results are read one step late: give every request enough
             # tokens to decode through the whole timed region, inside the context length.
-            spare = 2 * (-(-(ctx) // 512)) + 8
+            # (the prompts of the whole batch take batch * context / 2048 steps to prefill)
+            spare = -(-(args.batch * ctx) // 2048) + 2 * (-(-(ctx) // 512)) + 8
             sp = SamplingParams(temperature=0.0, max_new_tokens=W + K + spare, ignore_eos=True)
             plen = ctx - (W + K + spare) - 2
             rids = [engine.add_request(rng.integers(0, V, plen).tolist(), sp) for _ in range(args.batch)]
