@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import gc
 import itertools
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -112,7 +113,10 @@ class ModelRunner:
         # A mixer that plans work on the host per step sets ``graph_safe = False``.
         self._graph_safe = all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks
                                if hasattr(b, "mixer"))
-        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
+        # Captured steps by (batch size, wanted rows, table widths), least recently used first; a
+        # captured step keeps its own logits and workspace, so their number is bounded.
+        self._graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
+        self.max_graphs = 48
 
     # -- construction ----------------------------------------------------------------
     @classmethod
@@ -324,6 +328,8 @@ class ModelRunner:
         packed = self._pack(entries, GRAPH_TABLE_ROUND)
         key = (len(entries), tuple(len(e.want) for e in entries), tuple(packed.widths))
         graph = self._graphs.get(key)
+        if graph is not None:
+            self._graphs.move_to_end(key)
         if graph is None:
             graph = _DecodeGraph()
             ctx = self._upload(packed, entries, graph)
@@ -343,6 +349,10 @@ class ModelRunner:
                 if gc_was_on:
                     gc.enable()
             self._graphs[key] = graph
+            if len(self._graphs) > self.max_graphs:
+                torch.cuda.current_stream().synchronize()   # no replay may be running when its graph goes
+                while len(self._graphs) > self.max_graphs:
+                    self._graphs.popitem(last=False)        # the step replayed longest ago
         else:
             ctx = self._upload(packed, entries, graph)
             self._feed_device_tokens(ctx, entries, token_source)

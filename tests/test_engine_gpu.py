@@ -151,6 +151,39 @@ def test_long_decoding(models, dtype):
     assert worst <= tol, worst
 
 
+def test_captured_steps_are_bounded_and_evicted(models):
+    """Decode steps of changing batch size with room for two captured steps only: steps whose graph
+    was evicted are captured again and give the same logits."""
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    path, cfg, w = models["A"]
+    rng = np.random.default_rng(11)
+    seqs = [rng.integers(0, cfg["vocab_size"], 30).tolist() for _ in range(4)]
+    refs = [P.forward(cfg, w, s).numpy() for s in seqs]
+    runner = ModelRunner.from_model_dir(path, dtype=torch.float32, max_tokens=512, page_size=16, max_requests=4)
+    runner.use_graphs = True
+    runner.max_graphs = 2
+    for r, s in enumerate(seqs):
+        runner.step([StepEntry(r, s[:10], [])])
+    worst = 0.0
+    for i in range(10, 30):
+        live = [r for r in range(4) if (i + r) % 4 != 0] or [0]      # batch sizes 3 and 4 in turn, varying members
+        batches = [live[:n] for n in (len(live), 2, 1)] if i % 3 == 0 else [live]
+        done = set()
+        for batch in batches:
+            batch = [r for r in batch if r not in done]
+            if not batch:
+                continue
+            rows = runner.step([StepEntry(r, [seqs[r][i]], [0]) for r in batch]).cpu().numpy()
+            for k, r in enumerate(batch):
+                worst = max(worst, float(np.abs(rows[k] - refs[r][i]).max()))
+                done.add(r)
+        for r in range(4):
+            if r not in done:
+                runner.step([StepEntry(r, [seqs[r][i]], [])])
+    assert len(runner._graphs) <= 2
+    assert worst <= 1e-4, worst
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("name", list(TINY))
 def test_first_tokens(models, name, dtype):
