@@ -190,7 +190,9 @@ def run_workload(args):
         st = {k: engine.stats[k] - stats0[k] for k in stats0 if k != "max_step_tokens"}
         return dt, got, first, st, engine.scheduler.stats["preemptions"] - pre0, ops.launch_count - launches0
 
-    run_once()                      # warm-up: graph captures, workspace, first-call set-up
+    cold = run_once()               # warm-up: graph captures, workspace, first-call set-up
+    print(f"[bench] first run (with graph captures and first-call set-up): {cold[0]:.2f} s, "
+          f"{len(runner._graphs)} captured steps", file=sys.stderr, flush=True)
     sampler = ClockSampler()
     sampler.start()
     dt, got, first, st, preempt, launches = run_once()
