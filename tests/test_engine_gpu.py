@@ -398,3 +398,188 @@ def test_toy_mixer_with_state_plugs_in(models):
         assert n == sum(len(t) for t in reqs.values()) and worst < 1e-4, (worst, where)
     finally:
         unregister("mixer", "toy_running_mean")
+
+
+# -- a toy feed-forward with routing, defined here ---------------------------------------------------
+def test_toy_routed_feed_forward_plugs_in(models):
+    """A feed-forward that sends every token to the one of three small experts its router prefers
+    (router logits and probabilities in float32) is registered from this file and takes the place of
+    one layer's feed-forward; cache, scheduler and the other parts do not change."""
+    import dataclasses
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel, FeedForward, PartSpec, WeightSpec, register, unregister
+    from llm_rs_b200.weights import open_model_files
+    E, I = 3, 40
+
+    @register("feed_forward", "toy_top1_experts", replace=True)
+    class Top1Experts(FeedForward):
+        """out = p_e * down_e(relu(up_e x)) for e = argmax(router x), p = softmax(router x)."""
+
+        def __init__(self, hidden_size, n_experts, expert_size, prefix=""):
+            self.H, self.E, self.I, self.prefix = hidden_size, n_experts, expert_size, prefix
+
+        def weight_specs(self):
+            p = self.prefix
+            return [WeightSpec(p + "router.weight", (self.E, self.H)), WeightSpec(p + "up.weight", (self.E, self.I, self.H)),
+                    WeightSpec(p + "down.weight", (self.E, self.H, self.I))]
+
+        def bind(self, tensors, runtime):
+            p = self.prefix
+            self.router, self.up, self.down = (tensors[p + n].float() for n in ("router.weight", "up.weight", "down.weight"))
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.t(), dim=-1)
+            pick = prob.argmax(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.E):
+                rows = (pick == e).nonzero(as_tuple=True)[0]
+                if rows.numel():
+                    y = torch.relu(xf[rows] @ self.up[e].t()) @ self.down[e].t()
+                    out[rows] = y * prob[rows, e:e + 1]
+            return out.to(x.dtype)
+
+    try:
+        path, cfg, w = models["A"]
+        spec = build_spec(Qwen3Config.from_dict(cfg))
+        toy = dataclasses.replace(spec.layers[0], feed_forward=PartSpec(
+            "toy_top1_experts", {"hidden_size": 64, "n_experts": E, "expert_size": I}), feed_forward_scope="moe.")
+        spec = dataclasses.replace(spec, layers=(toy, spec.layers[1]))
+        names = [s.name for s in DecoderModel(spec).weight_specs()]
+        assert "model.layers.0.moe.router.weight" in names and "model.layers.0.mlp.gate_proj.weight" not in names
+        f = open_model_files(path)[0]
+        tensors = {n: f.tensor(n).float().to(DEV) for n in names if n in f.names()}
+        g = torch.Generator().manual_seed(3)
+        router, up, down = torch.randn(E, 64, generator=g), torch.randn(E, I, 64, generator=g) * 0.1, torch.randn(E, 64, I, generator=g) * 0.1
+        for n, t in (("router", router), ("up", up), ("down", down)):
+            tensors[f"model.layers.0.moe.{n}.weight"] = t.to(DEV)
+        runner = ModelRunner(spec, tensors, torch.float32, DEV, max_tokens=256, page_size=16, max_requests=3)
+
+        def plain(toks):
+            pos = list(range(len(toks)))
+            eps = cfg["rms_norm_eps"]
+            h = P.embedding(w["model.embed_tokens.weight"], toks)
+            h = h + P.attention_block(P.rms_norm(h, w["model.layers.0.input_layernorm.weight"], eps), w,
+                                      "model.layers.0.self_attn.", cfg, pos, 0)
+            x = P.rms_norm(h, w["model.layers.0.post_attention_layernorm.weight"], eps)
+            prob = torch.softmax(x @ router.double().t(), dim=-1)
+            pick = prob.argmax(dim=-1)
+            y = torch.stack([torch.relu(x[t] @ up[int(e)].double().t()) @ down[int(e)].double().t() * prob[t, int(e)]
+                             for t, e in enumerate(pick)])
+            h = h + y
+            h = P.decoder_layer(h, w, 1, cfg, pos, 0)
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+        rng = np.random.default_rng(8)
+        reqs = {f"r{i}": rng.integers(0, 256, n).tolist() for i, n in enumerate((41, 17, 60))}
+        ref = {r: plain(t).numpy() for r, t in reqs.items()}
+        got = RU.run_steps(runner, RU.mixed(reqs, seed=2, max_live=3))
+        worst, where, n = RU.max_diff(got, ref)
+        assert n == sum(len(t) for t in reqs.values()) and worst < 2e-4, (worst, where)
+    finally:
+        unregister("feed_forward", "toy_top1_experts")
+
+
+# -- toy position encodings, defined here ------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["toy_linear_rotation", "toy_learned_offsets"])
+def test_toy_position_encodings_plug_in(models, kind):
+    """Two position encodings registered from this file: a rotation with angles of its own (a table
+    for the fused kernel) and learned vectors added to queries and keys (weights of its own, applied
+    before the fused kernel). Only the mixer's ``position`` parameter changes."""
+    import dataclasses
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel, PartSpec, PositionEncoding, WeightSpec, register, unregister
+    from llm_rs_b200.weights import open_model_files
+    d, max_pos = 16, 200
+
+    @register("position", "toy_linear_rotation", replace=True)
+    class LinearRotation(PositionEncoding):
+        """Angle of pair i at position p: p * (i + 1) * step."""
+
+        def __init__(self, head_dim, step, prefix=""):
+            self.head_dim, self.step, self.rotary_dim = head_dim, step, head_dim
+
+        def bind(self, tensors, runtime):
+            ang = torch.arange(runtime.max_positions, dtype=torch.float64)[:, None] * \
+                (torch.arange(1, self.head_dim // 2 + 1, dtype=torch.float64) * self.step)[None, :]
+            self._table = torch.stack([ang.cos(), ang.sin()], dim=-1).float().contiguous().to(runtime.device)
+
+        def rotation_table(self):
+            return self._table
+
+    @register("position", "toy_learned_offsets", replace=True)
+    class LearnedOffsets(PositionEncoding):
+        """q and k of every head get table[position] added (before the per-head norms)."""
+
+        def __init__(self, head_dim, max_positions, prefix=""):
+            self.head_dim, self.max_positions, self.prefix = head_dim, max_positions, prefix
+
+        def weight_specs(self):
+            return [WeightSpec(self.prefix + "position_table", (self.max_positions, self.head_dim))]
+
+        def bind(self, tensors, runtime):
+            self.table = tensors[self.prefix + "position_table"].to(runtime.act_dtype)
+
+        def apply_unfused(self, q, k, positions):
+            add = self.table[positions.long()]
+            for t in (q, k):
+                if t is not None:
+                    t.view(t.size(0), -1, self.head_dim).add_(add[:, None, :])
+
+    try:
+        path, cfg, w = models["A"]
+        spec = build_spec(Qwen3Config.from_dict(cfg))
+        position = (PartSpec("toy_linear_rotation", {"head_dim": d, "step": 0.037}) if kind == "toy_linear_rotation"
+                    else PartSpec("toy_learned_offsets", {"head_dim": d, "max_positions": max_pos}))
+        layers = tuple(dataclasses.replace(l, mixer=PartSpec(l.mixer.kind, {**l.mixer.params, "position": position}))
+                       for l in spec.layers)
+        spec = dataclasses.replace(spec, layers=layers)
+        names = [s.name for s in DecoderModel(spec).weight_specs()]
+        f = open_model_files(path)[0]
+        tensors = {n: f.tensor(n).float().to(DEV) for n in names if n in f.names()}
+        tables = {}
+        if kind == "toy_learned_offsets":
+            extra = [n for n in names if n.endswith("position_table")]
+            assert len(extra) == 2
+            for i, n in enumerate(extra):
+                tables[n] = torch.randn(max_pos, d, generator=torch.Generator().manual_seed(20 + i)) * 0.5
+                tensors[n] = tables[n].to(DEV)
+        runner = ModelRunner(spec, tensors, torch.float32, DEV, max_tokens=256, page_size=16, max_requests=3)
+
+        def attention_block(x, i, pos):
+            p = f"model.layers.{i}.self_attn."
+            nq, nkv, eps, T = 4, 2, cfg["rms_norm_eps"], x.shape[0]
+            q = P.linear(x, w[p + "q_proj.weight"]).reshape(T, nq, d)
+            k = P.linear(x, w[p + "k_proj.weight"]).reshape(T, nkv, d)
+            v = P.linear(x, w[p + "v_proj.weight"]).reshape(T, nkv, d)
+            if kind == "toy_learned_offsets":
+                add = tables[p + "position_table"].double()[pos][:, None, :]
+                q, k = q + add, k + add
+            q, k = P.rms_norm(q, w[p + "q_norm.weight"], eps), P.rms_norm(k, w[p + "k_norm.weight"], eps)
+            if kind == "toy_linear_rotation":
+                ang = torch.as_tensor(pos, dtype=torch.float64)[:, None] * (torch.arange(1, d // 2 + 1, dtype=torch.float64) * 0.037)[None, :]
+                q, k = P.rotate_half(q, ang), P.rotate_half(k, ang)
+            return P.linear(P.attention(q, k, v), w[p + "o_proj.weight"])
+
+        def plain(toks):
+            pos, eps = list(range(len(toks))), cfg["rms_norm_eps"]
+            h = P.embedding(w["model.embed_tokens.weight"], toks)
+            for i in range(2):
+                pre = f"model.layers.{i}."
+                h = h + attention_block(P.rms_norm(h, w[pre + "input_layernorm.weight"], eps), i, pos)
+                h = h + P.swiglu(P.rms_norm(h, w[pre + "post_attention_layernorm.weight"], eps), w, pre + "mlp.")
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["model.embed_tokens.weight"])
+
+        rng = np.random.default_rng(9)
+        reqs = {f"r{i}": rng.integers(0, 256, n).tolist() for i, n in enumerate((37, 64, 12))}
+        ref = {r: plain(t).numpy() for r, t in reqs.items()}
+        got = RU.run_steps(runner, RU.mixed(reqs, seed=5, max_live=3))
+        worst, where, n = RU.max_diff(got, ref)
+        assert n == sum(len(t) for t in reqs.values()) and worst < 2e-4, (worst, where)
+    finally:
+        unregister("position", "toy_linear_rotation")
+        unregister("position", "toy_learned_offsets")
