@@ -234,3 +234,53 @@ def test_pipelined_preemption_keeps_every_token():
     assert s.stats["preemptions"] >= 1
     assert sorted(o.request_id for o in outs if o.token is not None) == [1] * 6 + [2] * 6
     assert not m.requests and m.free_pages() == 4
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workloads_finish_every_request_and_lose_no_page(seed):
+    """Requests of random lengths arrive at random times into a pool that is too small for all of
+    them; results come back one step late. Every request ends with exactly the tokens it asked for
+    (or at EOS), nothing is scheduled twice in a step, no step exceeds its budget, and all pages
+    are back at the end."""
+    import random
+    rng = random.Random(seed)
+    page, n_pages, slots, budget, chunk = 4, rng.choice([12, 20, 40]), rng.choice([3, 5]), rng.choice([8, 16]), rng.choice([4, 8])
+    m, s = make(n_pages=n_pages, page=page, slots=slots, budget=budget, chunk=chunk, eos=(99,), max_positions=n_pages * page)
+    todo = [(rng.randint(1, 3 * page * 2), rng.randint(1, 9)) for _ in range(rng.randint(6, 14))]
+    want, got, flight, next_id, steps = {}, {}, None, 1, 0
+    while todo or s.has_work() or flight is not None:
+        while todo and rng.random() < 0.5:
+            n, max_new = todo.pop()
+            n = min(n, n_pages * page - max_new - 1)
+            s.add_request(req(next_id, n, max_new=max_new))
+            want[next_id], got[next_id] = max_new, []
+            next_id += 1
+        batch = s.schedule()
+        ids = [b.request.request_id for b in batch]
+        assert len(ids) == len(set(ids)) and sum(len(b.tokens) for b in batch) <= budget and len(batch) <= slots
+        for b in batch:
+            if b.request.request_id not in m.requests:
+                m.admit(b.request.request_id)
+            m.reserve(b.request.request_id, len(b.tokens))       # must fit: the scheduler counted the pages
+            m.commit(b.request.request_id, len(b.tokens))
+        s.on_launched(batch)
+        m.check_invariants()
+        launched = (batch, {b.request.request_id: (99 if rng.random() < 0.03 else 7) for b in batch if b.sample}) if batch else None
+        outs = s.on_result(*flight) if flight is not None else []
+        flight = launched
+        if launched is None and flight is None:
+            outs += s.on_result([], {})
+        for o in outs:
+            if o.token is not None:
+                got[o.request_id].append(o.token)
+            if o.finished:
+                assert o.reason in ("stop", "length", "error_too_long")
+                if o.reason == "length":
+                    assert len(got[o.request_id]) == want[o.request_id]
+                elif o.reason == "stop":
+                    assert got[o.request_id][-1] == 99 and len(got[o.request_id]) <= want[o.request_id]
+                want.pop(o.request_id)
+        steps += 1
+        assert steps < 3000, "the scheduler does not come to an end"
+    assert not want, f"requests {sorted(want)} never finished"
+    assert not m.requests and m.free_pages() == n_pages
