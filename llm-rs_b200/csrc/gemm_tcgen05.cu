@@ -32,7 +32,24 @@ constexpr int TC_BK = 64;         // k per stage: 64 bf16 = one 128-byte swizzle
 constexpr int TC_THREADS = 128;
 constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;  // polls of a barrier before giving up (some seconds)
 
-enum TcEpilogue : int { TC_STORE = 0, TC_RESIDUAL = 1, TC_SILU_MUL = 2 };
+enum TcEpilogue : int { TC_STORE = 0, TC_RESIDUAL = 1, TC_SILU_MUL = 2, TC_QKV_ROPE = 3 };
+
+// What the epilogue TC_QKV_ROPE needs beside the product: the rows of W are the heads of q, then of k,
+// then of v (128 features each); q gets its per-head norm and rotation and goes to q_out, k the same and
+// goes to its page of the cache, v goes to its page as it is.
+struct QkvRope {
+  __nv_bfloat16* q_out;        // [tokens, ldq]
+  long long ldq;
+  __nv_bfloat16* cache;        // one layer's [n_pages, n_kv_heads, 2, page_size, 128]
+  const float* q_norm_w;       // [128] or null
+  const float* k_norm_w;
+  const float* cos_sin;        // [positions, 64, 2] or null
+  const int* positions;        // per token
+  const int* token_req;        // per token: row of the block table
+  const int* block_table;
+  int table_stride, n_q_heads, n_kv_heads, page_size;
+  float eps;
+};
 
 struct TcParams {
   void* out;            // TC_STORE / TC_SILU_MUL: [tokens, ldo] of out_dtype; TC_RESIDUAL: float32 h
@@ -42,6 +59,7 @@ struct TcParams {
   int a_rows, b_rows;   // valid extents (tokens / features according to the mode)
   int k_blocks;         // ceil(K / 64)
   int* error_flag;
+  QkvRope qr;           // TC_QKV_ROPE only
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -334,6 +352,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int per = 64 / splits;                 // feature pairs (i, i + 64) owned by this block
     const uint32_t red_addr = tc_smem(red);
     const int n_tok = min(BN, p.b_rows - tile_b * BN);
+    if (p.epilogue == TC_QKV_ROPE) {
+      // The tile is one head. A block of the cluster takes every splits-th token, a warp one token at a
+      // time: lane l holds features l, l + 32, l + 64, l + 96, i.e. the rotation's pairs (l, l + 64) and
+      // (l + 32, l + 96), and the head's sum of squares is one warp reduction.
+      const QkvRope& g = p.qr;
+      const int head = tile_a;
+      const int kind = head < g.n_q_heads ? 0 : head < g.n_q_heads + g.n_kv_heads ? 1 : 2;
+      const int hidx = kind == 0 ? head : kind == 1 ? head - g.n_q_heads : head - g.n_q_heads - g.n_kv_heads;
+      for (int j = (int)rank + splits * warp; j < n_tok; j += splits * (TC_THREADS / 32)) {
+        float x[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int f = lane + 32 * q;
+          float acc = 0.f;
+          if (splits > 1) {
+            for (int r = 0; r < splits; ++r) acc += ld_cluster_f32(red_addr + (uint32_t)(f * RS + j) * 4, (uint32_t)r);
+          } else {
+            acc = red[f * RS + j];
+          }
+          x[q] = acc;
+        }
+        const int t = tile_b * BN + j;
+        const int pos = g.positions[t];
+        if (kind != 2) {
+          const float* w = kind == 0 ? g.q_norm_w : g.k_norm_w;
+          if (w) {
+            float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv = 1.0f / sqrtf(ss / 128.0f + g.eps);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) x[q] *= inv * w[lane + 32 * q];
+          }
+          if (g.cos_sin) {
+            const float2 cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
+            const float2 cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
+            const float a0 = x[0] * cs0.x - x[2] * cs0.y, b0 = x[2] * cs0.x + x[0] * cs0.y;
+            const float a1 = x[1] * cs1.x - x[3] * cs1.y, b1 = x[3] * cs1.x + x[1] * cs1.y;
+            x[0] = a0; x[2] = b0; x[1] = a1; x[3] = b1;
+          }
+        }
+        bf16* dst;
+        if (kind == 0) {
+          dst = g.q_out + (size_t)t * g.ldq + (size_t)hidx * 128;
+        } else {
+          const int page = g.block_table[(size_t)g.token_req[t] * g.table_stride + pos / g.page_size];
+          dst = g.cache + kv_tile_offset(page, hidx, kind - 1, g.n_kv_heads, g.page_size, 128) +
+                (size_t)(pos % g.page_size) * 128;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = __float2bfloat16_rn(x[q]);
+      }
+    } else
     for (int idx = tid; idx < per * n_tok; idx += TC_THREADS) {
       const int pr = idx % per, j = idx / per;
       const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
@@ -617,6 +688,31 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return llmrs_launch_status("gemm_bf16");
 }
 
+static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
+                          int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
+                          const QkvRope* qr, cudaStream_t stream);
+
+// q | k | v = x Wqkv^T with the per-head norms, the rotation and the cache write in the product's
+// epilogue (few tokens, heads of 128 features): q goes to q_out (bfloat16 [tokens, ldq]), k and v to the
+// pages that block_table names for the tokens' positions. Same arithmetic as the product followed by
+// llmrs_qk_norm_rope_kvwrite, without rounding q, k and v to bfloat16 in between.
+LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, int tokens, int K, int splits,
+                                  void* q_out, long long ldq, void* cache, const float* q_norm_w,
+                                  const float* k_norm_w, const float* cos_sin, const int* positions,
+                                  const int* token_req, const int* block_table, int table_stride, int n_q_heads,
+                                  int n_kv_heads, int page_size, float eps, int* error_flag, cudaStream_t stream) {
+  LLMRS_REQUIRE(tokens > 0 && tokens <= 64, "gemm_qkv_rope: takes 1 to 64 tokens, got %d", tokens);
+  LLMRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_stride > 0, "gemm_qkv_rope: bad sizes");
+  LLMRS_REQUIRE(q_out && cache && positions && token_req && block_table, "gemm_qkv_rope: missing argument");
+  QkvRope qr;
+  qr.q_out = (__nv_bfloat16*)q_out; qr.ldq = ldq; qr.cache = (__nv_bfloat16*)cache; qr.q_norm_w = q_norm_w;
+  qr.k_norm_w = k_norm_w; qr.cos_sin = cos_sin; qr.positions = positions; qr.token_req = token_req;
+  qr.block_table = block_table; qr.table_stride = table_stride; qr.n_q_heads = n_q_heads; qr.n_kv_heads = n_kv_heads;
+  qr.page_size = page_size; qr.eps = eps;
+  return gemm_bf16_impl(x, ldx, w, q_out, ldq, tokens, (n_q_heads + 2 * n_kv_heads) * 128, K, TC_QKV_ROPE, LLMRS_BF16,
+                        splits, error_flag, &qr, stream);
+}
+
 static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_m, int n_tiles,
                              cudaStream_t stream) {
   const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + (2 * PS_STAGES + 4) * 8 + 16;
@@ -655,6 +751,13 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const
 LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
                               int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
                               cudaStream_t stream) {
+  LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
+  return gemm_bf16_impl(x, ldx, w, out, ldo, tokens, features, K, epilogue, out_dtype, splits, error_flag, nullptr, stream);
+}
+
+static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
+                          int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
+                          const QkvRope* qr, cudaStream_t stream) {
   LLMRS_REQUIRE(tokens > 0 && features > 0 && K > 0, "gemm_bf16: bad sizes");
   LLMRS_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_bf16: K = %d and the row stride %lld must be multiples of 8", K, ldx);
   LLMRS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
@@ -662,8 +765,8 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
                 "multiples of 8", features, ldo);
   LLMRS_REQUIRE(epilogue != TC_SILU_MUL || features % 128 == 0,
                 "gemm_bf16: SiLU*up needs features in groups of 128, got %d", features);
-  LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
   TcParams p;
+  if (qr) p.qr = *qr; else p.qr = QkvRope{};
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
   p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
   CUtensorMap ma, mb;

@@ -381,6 +381,41 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor,
+                  q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
+                  positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, n_q_heads: int,
+                  n_kv_heads: int, page_size: int, eps: float, splits: Optional[int] = None) -> torch.Tensor:
+    """q | k | v = ``x @ w.T`` for at most 64 tokens and heads of 128 features, with the per-head norms,
+    the rotation and the cache write in the product's epilogue: q lands in ``q_out`` (bfloat16
+    [tokens, n_q_heads * 128]), k and v in the pages of ``cache`` that ``block_table`` names. The same
+    arithmetic as ``gemm_bf16`` followed by ``qk_norm_rope_kvwrite``, one kernel and one rounding less."""
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    _need(q_out, "q_out", torch.bfloat16)
+    _need(cache, "cache", torch.bfloat16)
+    tokens, K = x.shape
+    features = (n_q_heads + 2 * n_kv_heads) * 128
+    if w.shape != (features, K):
+        raise KernelError(f"w is {tuple(w.shape)}, expected {(features, K)}")
+    if q_out.shape != (tokens, n_q_heads * 128):
+        raise KernelError(f"q_out is {tuple(q_out.shape)}, expected {(tokens, n_q_heads * 128)}")
+    for name, t in (("q_norm_w", q_norm_w), ("k_norm_w", k_norm_w), ("cos_sin", cos_sin)):
+        if t is not None:
+            _need(t, name, torch.float32)
+    if cos_sin is not None and cos_sin.size(1) != 64:
+        raise KernelError(f"cos_sin table is for rotary_dim {cos_sin.size(1) * 2}, this kernel rotates 128")
+    for name, t in (("positions", positions), ("token_req", token_req), ("block_table", block_table)):
+        _need(t, name, torch.int32)
+    if splits is None:
+        splits = tc_splits(tokens, features, K, torch.cuda.get_device_properties(x.device).multi_processor_count)
+    _check(_lib().llmrs_gemm_qkv_rope(
+        _ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), tokens, K, splits, _ptr(q_out),
+        ctypes.c_longlong(q_out.stride(0)), _ptr(cache), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin),
+        _ptr(positions), _ptr(token_req), _ptr(block_table), block_table.size(1), n_q_heads, n_kv_heads, page_size,
+        ctypes.c_float(eps), _ptr(tc_error_flag(x.device)), _stream()), "gemm_qkv_rope")
+    return q_out
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """[2I, K]: 64 rows of gate, the 64 matching rows of up, and so on (I a multiple of 64)."""
     I, K = gate.shape

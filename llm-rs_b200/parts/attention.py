@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Mixer, Runtime
+from .base import Mixer, PositionEncoding, Runtime
 from .linear import Linear
 from .registry import build, register
 from .spec import CacheNeed, PartSpec, WeightSpec
@@ -17,6 +17,9 @@ from .spec import CacheNeed, PartSpec, WeightSpec
 _SM_COUNT = {}
 # The tcgen05 prefill kernel for long portions (head_dim 128); LLMRS_ATTN_TC=0 keeps the mma.sync kernel.
 _ATTN_TC = os.environ.get("LLMRS_ATTN_TC", "1") != "0"
+# Norms, rotation and cache write as the epilogue of the q|k|v product for few tokens; LLMRS_FUSE_QKV_ROPE=0
+# keeps the separate kernel.
+_FUSE_QKV_ROPE = os.environ.get("LLMRS_FUSE_QKV_ROPE", "1") != "0"
 
 
 def _sm_count(device) -> int:
@@ -97,6 +100,16 @@ class GQAttention(Mixer):
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.n_kv_heads, self.head_dim, self.window)
 
+    def _fuses_rope(self, x, cache, cos_sin) -> bool:
+        """True when the q|k|v product can take norms, rotation and cache write as its epilogue."""
+        if not (_FUSE_QKV_ROPE and cache.owns and self.head_dim == 128 and x.dtype == torch.bfloat16):
+            return False
+        if self.qkv_proj.bias is not None or not self.qkv_proj.uses_tc(x.size(0)) or x.size(0) > 64:
+            return False
+        if cos_sin is None:      # no rotation at all is fine; an encoding applied outside the kernel is not
+            return type(self.position).apply_unfused is PositionEncoding.apply_unfused
+        return self.position.rotary_dim == 128 and cos_sin.dtype == torch.float32
+
     def _choose_split(self, n_decode: int, max_kv_len: int, q: torch.Tensor) -> int:
         """Keys per split of decode attention: long enough that a block streams many tiles,
         short enough that the step's blocks fill the GPU about once. The choice changes
@@ -112,19 +125,26 @@ class GQAttention(Mixer):
     def forward(self, x, ctx, cache, residual=None):
         nq, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
         table = cache.block_table
-        if cache.owns:
-            qkv = self.qkv_proj.forward(x)
-            q = qkv[:, : self.q_width]
-            k = qkv[:, self.q_width: self.q_width + self.kv_width]
-            v = qkv[:, self.q_width + self.kv_width:]
-        else:
-            q, k, v = self.q_proj.forward(x), None, None
         cos_sin = self.position.rotation_table()
-        if cos_sin is None:
-            self.position.apply_unfused(q, k, ctx.positions)
-        ops.qk_norm_rope_kvwrite(q, k, v, self.q_norm_w, self.k_norm_w, cos_sin, ctx.positions, ctx.token_req,
-                                 table, cache.kv if cache.owns else None, nq, nkv, d, self.position.rotary_dim,
-                                 cache.page_size, self.qk_norm_eps)
+        if self._fuses_rope(x, cache, cos_sin):
+            # Few tokens, heads of 128: the norms, the rotation and the cache write are the epilogue of the
+            # q|k|v product (one kernel less in every layer of a decode step).
+            q = torch.empty((ctx.n_tokens, self.q_width), dtype=x.dtype, device=x.device)
+            ops.gemm_qkv_rope(x, self.qkv_proj.weight, q, cache.kv, self.q_norm_w, self.k_norm_w, cos_sin,
+                              ctx.positions, ctx.token_req, table, nq, nkv, cache.page_size, self.qk_norm_eps)
+        else:
+            if cache.owns:
+                qkv = self.qkv_proj.forward(x)
+                q = qkv[:, : self.q_width]
+                k = qkv[:, self.q_width: self.q_width + self.kv_width]
+                v = qkv[:, self.q_width + self.kv_width:]
+            else:
+                q, k, v = self.q_proj.forward(x), None, None
+            if cos_sin is None:
+                self.position.apply_unfused(q, k, ctx.positions)
+            ops.qk_norm_rope_kvwrite(q, k, v, self.q_norm_w, self.k_norm_w, cos_sin, ctx.positions, ctx.token_req,
+                                     table, cache.kv if cache.owns else None, nq, nkv, d, self.position.rotary_dim,
+                                     cache.page_size, self.qk_norm_eps)
         out = torch.empty((ctx.n_tokens, self.q_width), dtype=q.dtype, device=q.device)
         if ctx.n_prefill_tiles:
             ops.attn_prefill(q, out, cache.kv, ctx.prefill_tiles, ctx.n_prefill_tiles, ctx.q_start, ctx.n_new,

@@ -546,3 +546,56 @@ def test_attention_prefill_tcgen05_far_key():
                          torch.tensor(lens, dtype=torch.int32, device=DEV), dt, nq, nkv, d, page, 0, 1.0, prefer_tc=True)
         torch.cuda.synchronize()
         assert float((out.double().cpu() - want).abs().max()) < 2e-2, far
+
+
+@pytest.mark.parametrize("tokens,nq,nkv,K,page,rope,norm", [
+    (8, 4, 2, 256, 16, True, True), (1, 2, 1, 128, 16, True, True), (13, 8, 2, 512, 32, True, False),
+    (33, 4, 4, 192, 16, False, True), (64, 6, 3, 320, 64, True, True)])
+def test_gemm_qkv_rope_epilogue(tokens, nq, nkv, K, page, rope, norm):
+    """The q|k|v product with norms, rotation and cache write in its epilogue against the product
+    followed by the separate kernel's arithmetic in float64."""
+    ops = _ops()
+    d = 128
+    torch.manual_seed(tokens + nq)
+    x = (torch.randn(tokens, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, K) * 0.05).to(torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(d)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d)) if norm else None
+    n_req = 3
+    req_of = torch.tensor([i % n_req for i in range(tokens)], dtype=torch.int32)
+    pos = torch.tensor([5 + 7 * (i // n_req) + (i % n_req) * 40 for i in range(tokens)], dtype=torch.int32)
+    max_pos = int(pos.max()) + 1
+    pages_per = -(-max_pos // page)
+    table = torch.randperm(n_req * pages_per).to(torch.int32).view(n_req, pages_per)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * (1e4 ** (-torch.arange(64, dtype=torch.float64) / 64))[None, :]
+    cos_sin = torch.stack([ang.cos(), ang.sin()], -1).float() if rope else None
+    eps = 1e-5
+    # reference in float64
+    y = x.double() @ w.double().t()
+    q = y[:, : nq * d].reshape(tokens, nq, d)
+    k = y[:, nq * d: (nq + nkv) * d].reshape(tokens, nkv, d)
+    v = y[:, (nq + nkv) * d:].reshape(tokens, nkv, d)
+    if norm:
+        q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * qw.double()
+        k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * kw.double()
+    if rope:
+        a = ang[pos.long()][:, None, :]
+        rot = lambda z: torch.cat([z[..., :64] * a.cos() - z[..., 64:] * a.sin(), z[..., 64:] * a.cos() + z[..., :64] * a.sin()], -1)
+        q, k = rot(q), rot(k)
+    cache = torch.zeros(n_req * pages_per, nkv, 2, page, d, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.full((tokens, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    dev = lambda t: None if t is None else t.to(DEV)
+    ops.gemm_qkv_rope(x.to(DEV), w.to(DEV), q_out, cache, dev(qw), dev(kw), dev(cos_sin), pos.to(DEV), req_of.to(DEV),
+                      table.to(DEV), nq, nkv, page, eps)
+    torch.cuda.synchronize()
+    ops.check_tc_error(DEV)
+    tol = 2e-2 * float(max(q.abs().max(), k.abs().max(), v.abs().max()))
+    assert float((q_out.double().cpu().reshape(tokens, nq, d) - q).abs().max()) < tol
+    host = cache.double().cpu()
+    touched = torch.zeros(cache.shape[0], page, dtype=torch.bool)
+    for t in range(tokens):
+        pg, slot = int(table[int(req_of[t]), int(pos[t]) // page]), int(pos[t]) % page
+        touched[pg, slot] = True
+        assert float((host[pg, :, 0, slot] - k[t]).abs().max()) < tol
+        assert float((host[pg, :, 1, slot] - v[t]).abs().max()) < tol
+    assert float(host[~touched[:, None, None, :, None].expand_as(host)].abs().max()) == 0.0   # nothing else was written
