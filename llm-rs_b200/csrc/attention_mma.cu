@@ -30,6 +30,17 @@ __device__ __forceinline__ float ex2(float x) {
 // ---------------------------------------------------------------------------------
 // Decode
 // ---------------------------------------------------------------------------------
+__device__ __forceinline__ void dm_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float dm_ld_cluster(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_STAGES = 3, DM_TILE = 16;
 
 template <int DCH>
@@ -39,7 +50,8 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
                              const int* __restrict__ cached_len, const int* __restrict__ block_table,
                              int table_stride, float* __restrict__ part, int max_splits, int split_keys,
                              int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
-                             bf16* __restrict__ out, long long out_stride, int* __restrict__ counters) {
+                             bf16* __restrict__ out, long long out_stride, int* __restrict__ counters,
+                             int cluster_merge) {
   constexpr int D = 16 * DCH;
   constexpr int ROW = D + 8;               // 16 bytes of padding: ldmatrix rows fall into distinct banks
   constexpr int CH = D / 8;                // 16-byte chunks per row
@@ -61,12 +73,15 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   const int kv_lo = window > 0 ? max(0, kv_len - window) : 0;
   const int k_begin = max(split * split_keys, kv_lo);
   const int k_end = min((split + 1) * split_keys, kv_len);
-  if (k_begin >= k_end) return;
+  // A split without keys has nothing to do, but as a member of a cluster that merges the splits it
+  // still has to meet the others at the cluster's barriers (with an empty record).
+  const bool empty = k_begin >= k_end;
+  if (empty && !cluster_merge) return;
   const int* table = block_table + (size_t)req * table_stride;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gq = lane >> 2, tq = lane & 3;
 
-  const int tile_first = k_begin / DM_TILE, tile_last = (k_end - 1) / DM_TILE;
+  const int tile_first = k_begin / DM_TILE, tile_last = empty ? tile_first - 1 : (k_end - 1) / DM_TILE;
   const int n_tiles = tile_last - tile_first + 1;
   const int n_my = n_tiles > warp ? (n_tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
 
@@ -277,10 +292,41 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       acc += Om[((size_t)w * 16 + g) * D + e] * f;
     }
     const int head = kvh * G + g0 + g;
+    if (cluster_merge) {
+      float* cp = Lm + DM_WARPS * 16 + (size_t)g * (D + 2);     // this block's record of head g, for the cluster
+      cp[2 + e] = acc;
+      if (e == 0) { cp[0] = M; cp[1] = L; }
+      continue;
+    }
     float* pp = part + ((size_t)((size_t)di * n_q_heads + head) * max_splits + split) * (D + 2);
     pp[2 + e] = acc;
     // The combine step works with natural logarithms: hand it the maximum in that domain.
     if (e == 0) { pp[0] = M / LOG2E; pp[1] = L; }
+  }
+  if (cluster_merge) {
+    // The splits of a (request, key head) are the blocks of one cluster: each leaves its record in its
+    // shared memory, and after the cluster's barrier the blocks share the merge among themselves,
+    // reading the others' records through distributed shared memory. No pass through global memory, no
+    // second kernel.
+    const int S = (int)gridDim.z;
+    const uint32_t cp_addr = (uint32_t)__cvta_generic_to_shared(Lm + DM_WARPS * 16);
+    dm_cluster_sync();
+    for (int i = split * DM_THREADS + (int)threadIdx.x; i < ng * D; i += S * DM_THREADS) {
+      const int g = i / D, e = i - g * D;
+      const uint32_t rec = cp_addr + (uint32_t)(g * (D + 2)) * 4;
+      float M = -INFINITY;
+      for (int r = 0; r < S; ++r) M = fmaxf(M, dm_ld_cluster(rec, (uint32_t)r));
+      float L = 0.f, a = 0.f;
+      for (int r = 0; r < S; ++r) {
+        const float mr = dm_ld_cluster(rec, (uint32_t)r);
+        const float f = mr == -INFINITY ? 0.f : ex2(mr - M);
+        L += dm_ld_cluster(rec + 4, (uint32_t)r) * f;
+        a += dm_ld_cluster(rec + (uint32_t)(2 + e) * 4, (uint32_t)r) * f;
+      }
+      out[(size_t)q_start[req] * out_stride + (size_t)(kvh * G + g0 + g) * D + e] = __float2bfloat16_rn(a / L);
+    }
+    dm_cluster_sync();   // nobody leaves while another block still reads its record
+    return;
   }
   if (counters == nullptr) return;   // a separate kernel merges the splits
 
@@ -322,10 +368,10 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
                              const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                              float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
                              int page_size, int window, float scale, void* out, long long out_stride, int* counters,
-                             cudaStream_t stream) {
+                             int cluster_merge, cudaStream_t stream) {
   constexpr int D = 16 * DCH;
   const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
-  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16) * sizeof(float);
+  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16 + 16 * (D + 2)) * sizeof(float);
   const size_t smem = pipe > merge ? pipe : merge;
   static size_t configured = 0;
   if (smem > configured) {
@@ -336,26 +382,52 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   }
   const int G = n_q_heads / n_kv_heads;
   dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
-  llmrs_launch(attn_decode_split_mma_kernel<DCH>, grid, dim3(DM_THREADS), smem, stream, true,
-      (const bf16*)q, q_stride, (const bf16*)cache, dec_reqs, q_start, cached_len, block_table, table_stride, scratch,
-      max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out, out_stride, counters);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(DM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  unsigned n_attr = 0;
+  if (g_llmrs_pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  if (cluster_merge) {   // the splits of a (request, key head) form a cluster
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = max_splits;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_split_mma_kernel<DCH>, (const bf16*)q, q_stride, (const bf16*)cache,
+                                     dec_reqs, q_start, cached_len, block_table, table_stride, scratch, max_splits,
+                                     split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out,
+                                     out_stride, counters, cluster_merge);
+  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma launch: %s", cudaGetErrorString(e));
   return llmrs_launch_status("attn_decode_split_mma");
 }
 
 // The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).
 // Writes the same per-split records as the generic split kernel. With `counters` (zeroed ints, one per
 // request and head group; the kernel leaves them zero) the last block of each group also merges the
-// splits into `out`; with counters == nullptr the caller runs the combine kernel.
+// splits into `out`; with `cluster_merge` (max_splits <= 8) the splits of a group run as one cluster and
+// merge through distributed shared memory; else the caller runs the combine kernel.
 int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
                                 int page_size, int window, float scale, void* out, long long out_stride,
-                                int* counters, cudaStream_t stream) {
+                                int* counters, int cluster_merge, cudaStream_t stream) {
+  if (cluster_merge && (max_splits < 1 || max_splits > 8))
+    return llmrs_fail("attn_decode_mma: a cluster merges at most 8 splits, got %d", max_splits);
 #define LLMRS_DM_CASE(N)                                                                                          \
   case N:                                                                                                          \
     return launch_decode_mma<N>(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table, table_stride, \
                                 scratch, max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, out, \
-                                out_stride, counters, stream)
+                                out_stride, counters, cluster_merge, stream)
   switch (d / 16) {
     LLMRS_DM_CASE(1); LLMRS_DM_CASE(2); LLMRS_DM_CASE(3); LLMRS_DM_CASE(4);
     LLMRS_DM_CASE(5); LLMRS_DM_CASE(6); LLMRS_DM_CASE(7); LLMRS_DM_CASE(8);

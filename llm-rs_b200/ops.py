@@ -232,7 +232,9 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
                 window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
     """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
     the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace of
-    ``attn_decode_scratch_floats`` elements. With ``counters`` (int32, at least n_dec * n_q_heads,
+    ``attn_decode_scratch_floats`` elements. (bfloat16 with head_dim <= 128 and at most 8 splits: the splits
+    of a request and key head run as one thread-block cluster and merge through distributed shared memory,
+    one kernel; else a second kernel merges them.) With ``counters`` (int32, at least n_dec * n_q_heads,
     all zero; the call leaves them zero) the tensor-core kernel merges the splits itself instead
     of a second kernel doing it."""
     _need(q, "q", contiguous=False)
@@ -253,7 +255,9 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
         _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
         _ptr(cache), _ptr(dec_reqs), n_dec, _ptr(q_start), _ptr(cached_len), _ptr(block_table), block_table.size(1),
         _ptr(scratch), _ptr(counters), max_splits, split_keys, n_q_heads, n_kv_heads, head_dim, page_size, window,
-        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode", launches=1 if counters is not None else 2)
+        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode",
+        launches=1 if counters is not None or (q.dtype == torch.bfloat16 and head_dim <= 128 and max_splits <= 8
+                                               and not _generic_only) else 2)
 
 
 def scatter_tokens(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor, src_idx: torch.Tensor) -> None:
@@ -305,8 +309,13 @@ def philox_uniform(seed: int, request_id: int, index: int) -> float:
                     ctypes.c_uint(index)))
 
 
+_generic_only = False
+
+
 def attention_generic_only(on: bool) -> None:
     """Make bfloat16 attention take the generic kernels too (tests compare both implementations)."""
+    global _generic_only
+    _generic_only = bool(on)
     fn = _lib().llmrs_attention_generic_only
     fn.restype = None
     fn(1 if on else 0)
