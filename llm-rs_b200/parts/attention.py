@@ -117,6 +117,12 @@ class GQAttention(Mixer):
         sms = _sm_count(q.device)
         groups = self.n_kv_heads * (-(-(self.n_heads // self.n_kv_heads) // 16))
         splits = max(1, (2 * sms) // max(1, n_decode * groups))
+        if splits > 8 and q.dtype == torch.bfloat16 and self.head_dim <= 128:
+            # Up to eight splits merge inside the kernel (as a cluster), which beats more, shorter splits
+            # followed by a second kernel as long as a split stays short.
+            keys8 = -(-(-(-max(max_kv_len, 1) // 8)) // 64) * 64
+            if keys8 <= 1024:
+                return max(keys8, 128)
         keys = -(-max(max_kv_len, 1) // splits)
         keys = -(-keys // 64) * 64
         return min(max(keys, 128), 1024 if q.dtype == torch.float32 or self.head_dim > 128 else 2048)
