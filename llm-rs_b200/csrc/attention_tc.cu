@@ -226,10 +226,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // Rows of K and V that no copy fills (keys past the end) must not hold NaN patterns.
-  for (uint32_t i = tid * 16; i < AT_STAGES * STAGE_BYTES; i += (AT_THREADS + 96) * 16)
-    *reinterpret_cast<uint4*>(KV + i) = make_uint4(0u, 0u, 0u, 0u);
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(sm(tmem_slot)), "r"(TMEM_COLS)
                  : "memory");
@@ -253,9 +249,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     const int h = lane / per_half, i = lane % per_half;
     const uint32_t box_bytes = (uint32_t)box_rows * 128;
     const uint32_t bar_full = which ? bar_vfull : bar_kfull, bar_free = which ? bar_vfree : bar_kfree;
-    auto page_of = [&](int t) {     // page of this lane's box of tile t, or -1 (the lane copies nothing)
+    // Page of this lane's box of tile t, or -1 (the lane copies nothing). A box whose keys no query of
+    // the block may see (past the end, or before the window) is filled from the page of the newest key
+    // instead: whatever a slot holds must be finite (it meets a probability of zero), and shared memory
+    // that no copy ever wrote need not be.
+    const int spare_page = table[(kv_hi - 1) / page_size];
+    auto page_of = [&](int t) {
       const int key = kv_lo + t * AT_BK + box_rows * i;
-      return (lane < n_boxes && t < n_tiles && key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : -1;
+      if (lane >= n_boxes || t >= n_tiles) return -1;
+      return (key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : spare_page;
     };
     auto load_tile = [&](int t, int page) {
       const int st = t % AT_STAGES;
