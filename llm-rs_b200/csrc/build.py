@@ -27,7 +27,7 @@ LIB_NAME = "libllmrs_b200.so"
 # Fast math stays off: norms, softmax and rotation are checked against float32 references.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
-ABI_VERSION = 2
+ABI_VERSION = 3
 HOST_DIR = os.path.join(CSRC_DIR, "host")
 HOST_LIB_NAME = "libllmrs_b200_host.so"
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]

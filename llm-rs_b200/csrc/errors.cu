@@ -30,4 +30,4 @@ int g_llmrs_pdl = 1;
 LLMRS_API void llmrs_set_pdl(int on) { g_llmrs_pdl = on; }
 
 // Version of the entry points' signatures; the Python side checks it after loading.
-LLMRS_API int llmrs_abi_version() { return 2; }
+LLMRS_API int llmrs_abi_version() { return 3; }

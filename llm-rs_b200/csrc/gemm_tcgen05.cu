@@ -60,6 +60,19 @@ struct TcParams {
   int k_blocks;         // ceil(K / 64)
   int* error_flag;
   QkvRope qr;           // TC_QKV_ROPE only
+  // A norm that is spread over two products (few tokens). The product BEFORE the norm (TC_RESIDUAL) also
+  // writes emit_xw = (h + product) * emit_w in bfloat16, the norm's input times its weight, and each of
+  // its clusters leaves the sum of squares of the 128 features of h it wrote in emit_part[tile][token]. The
+  // product AFTER the norm takes emit_xw as its x and multiplies its rows by 1/sqrt(sum / scale_dim +
+  // scale_eps), sum being the scale_parts entries of scale_part for the row's token, added in order.
+  const float* emit_w;
+  bf16* emit_xw;
+  long long emit_ld;
+  float* emit_part;
+  const float* scale_part;
+  int part_stride;      // tokens per row of emit_part / scale_part
+  int scale_parts, scale_dim;
+  float scale_eps;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -163,6 +176,12 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
   return v;
 }
 
+__device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // ---- the kernel ----------------------------------------------------------------------------
@@ -189,6 +208,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int kb0 = (int)(((long long)split * p.k_blocks) / splits);
   const int kb1 = (int)(((long long)(split + 1) * p.k_blocks) / splits);
   const int nkb = kb1 - kb0;
+
+  // Row scales of a product that follows a norm spread over two products (see TcParams).
+  __shared__ float inv_s[64], inv_part[64];
+  __shared__ float ss_ranks[8 * 64];   // in the cluster's first block: every block's sums of squares per token
+  const bool scaled = MODE == 1 && p.scale_part != nullptr;
 
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
   if (tid == 0) {
@@ -259,6 +283,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
     }
     if (leader) tc_commit(accum_bar);
+  } else if (MODE == 1 && warp >= 2 && p.scale_part) {
+    // Warps 2 and 3, while the product runs: the row scales 1/sqrt(sum of the pieces / dim + eps) of this
+    // tile's tokens. A piece's row holds all tokens side by side, so the 64 threads read whole rows:
+    // n_pow tokens wide, 64 / n_pow rows at a time; the groups' sums are then added in order.
+    pdl_wait();
+    const int u = tid - 64;
+    const int n_tok_s = min(BN, p.b_rows - tile_b * BN);
+    int n_pow = 1;
+    while (n_pow < n_tok_s) n_pow <<= 1;
+    const int j = u % n_pow, g = u / n_pow, n_groups = 64 / n_pow;
+    float ss = 0.f;
+    if (j < n_tok_s) {
+      const float* src = p.scale_part + tile_b * BN + j;
+#pragma unroll 8
+      for (int q = g; q < p.scale_parts; q += n_groups) ss += __ldcg(src + (size_t)q * p.part_stride);
+    }
+    inv_part[u] = ss;
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (u < n_tok_s) {
+      float sum = 0.f;
+      for (int k = 0; k < n_groups; ++k) sum += inv_part[k * n_pow + u];
+      inv_s[u] = 1.0f / sqrtf(sum / (float)p.scale_dim + p.scale_eps);
+    }
   }
   __syncwarp();
   bool ok = true;
@@ -371,7 +418,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           } else {
             acc = red[f * RS + j];
           }
-          x[q] = acc;
+          x[q] = scaled ? acc * inv_s[j] : acc;
         }
         const int t = tile_b * BN + j;
         const int pos = g.positions[t];
@@ -405,40 +452,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = __float2bfloat16_rn(x[q]);
       }
     } else
-    for (int idx = tid; idx < per * n_tok; idx += TC_THREADS) {
-      const int pr = idx % per, j = idx / per;
+    for (int base = 0; base < per * n_tok; base += TC_THREADS) {   // every thread walks the loop (warp shuffles below)
+      const int idx = base + tid;
+      const bool live = idx < per * n_tok;
+      const int pr = idx % per, j = live ? idx / per : 0;
       const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
       float lo = 0.f, hi = 0.f;
-      if (splits > 1) {
-        for (int r = 0; r < splits; ++r) {
-          lo += ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r);
-          hi += ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r);
+      if (live) {
+        if (splits > 1) {
+          for (int r = 0; r < splits; ++r) {
+            lo += ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r);
+            hi += ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r);
+          }
+        } else {
+          lo = red[i_lo * RS + j];
+          hi = red[i_hi * RS + j];
         }
-      } else {
-        lo = red[i_lo * RS + j];
-        hi = red[i_hi * RS + j];
+        if (scaled) {
+          lo *= inv_s[j];
+          hi *= inv_s[j];
+        }
       }
       const int t = tile_b * BN + j;
       const int f_lo = tile_a * TC_BM + i_lo, f_hi = f_lo + 64;
       if (p.epilogue == TC_SILU_MUL) {
         const int f = tile_a * (TC_BM / 2) + i_lo;
-        if (f < p.a_rows / 2) ((bf16*)p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_f(lo) * hi);
+        if (live && f < p.a_rows / 2) ((bf16*)p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_f(lo) * hi);
       } else if (p.epilogue == TC_RESIDUAL) {
         float* h = (float*)p.out + (size_t)t * p.ldo;
-        if (f_lo < p.a_rows) h[f_lo] += lo;
-        if (f_hi < p.a_rows) h[f_hi] += hi;
+        float n_lo = 0.f, n_hi = 0.f;
+        if (live && f_lo < p.a_rows) { n_lo = h[f_lo] + lo; h[f_lo] = n_lo; }
+        if (live && f_hi < p.a_rows) { n_hi = h[f_hi] + hi; h[f_hi] = n_hi; }
+        if (p.emit_w) {
+          // The norm that follows: its input times its weight, and this block's share of the sum of
+          // squares per token (the `per` threads of a token sit side by side in a warp).
+          if (live && f_lo < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * p.emit_w[f_lo]);
+          if (live && f_hi < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * p.emit_w[f_hi]);
+          float ss = n_lo * n_lo + n_hi * n_hi;
+          for (int o = per >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (live && pr == 0) st_cluster_f32(tc_smem(ss_ranks + (int)rank * 64 + j), 0u, ss);
+        }
       } else if (p.out_dtype == LLMRS_F32) {
         float* o = (float*)p.out + (size_t)t * p.ldo;
-        if (f_lo < p.a_rows) o[f_lo] = lo;
-        if (f_hi < p.a_rows) o[f_hi] = hi;
+        if (live && f_lo < p.a_rows) o[f_lo] = lo;
+        if (live && f_hi < p.a_rows) o[f_hi] = hi;
       } else {
         bf16* o = (bf16*)p.out + (size_t)t * p.ldo;
-        if (f_lo < p.a_rows) o[f_lo] = __float2bfloat16_rn(lo);
-        if (f_hi < p.a_rows) o[f_hi] = __float2bfloat16_rn(hi);
+        if (live && f_lo < p.a_rows) o[f_lo] = __float2bfloat16_rn(lo);
+        if (live && f_hi < p.a_rows) o[f_hi] = __float2bfloat16_rn(hi);
       }
     }
     // No block may leave while another still reads its shared memory.
     if (splits > 1) cluster_sync_all(); else __syncthreads();
+    if (p.emit_w && p.epilogue == TC_RESIDUAL && rank == 0 && tid < n_tok) {
+      // The cluster's sums of squares, added in the order of its blocks: one piece per tile of features.
+      float ss = 0.f;
+      for (int r = 0; r < splits; ++r) ss += ss_ranks[r * 64 + tid];
+      p.emit_part[(size_t)tile_a * p.part_stride + tile_b * BN + tid] = ss;
+    }
   }
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -688,9 +759,20 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return llmrs_launch_status("gemm_bf16");
 }
 
+// The two halves of a norm that is spread over two products (see TcParams).
+struct NormLink {
+  const float* emit_w = nullptr;
+  void* emit_xw = nullptr;
+  long long emit_ld = 0;
+  float* emit_part = nullptr;
+  const float* scale_part = nullptr;
+  int part_stride = 0, scale_parts = 0, scale_dim = 0;
+  float scale_eps = 0.f;
+};
+
 static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
                           int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
-                          const QkvRope* qr, cudaStream_t stream);
+                          const QkvRope* qr, const NormLink* nl, cudaStream_t stream);
 
 // q | k | v = x Wqkv^T with the per-head norms, the rotation and the cache write in the product's
 // epilogue (few tokens, heads of 128 features): q goes to q_out (bfloat16 [tokens, ldq]), k and v to the
@@ -700,7 +782,9 @@ LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, i
                                   void* q_out, long long ldq, void* cache, const float* q_norm_w,
                                   const float* k_norm_w, const float* cos_sin, const int* positions,
                                   const int* token_req, const int* block_table, int table_stride, int n_q_heads,
-                                  int n_kv_heads, int page_size, float eps, int* error_flag, cudaStream_t stream) {
+                                  int n_kv_heads, int page_size, float eps, const float* scale_part, int part_stride,
+                                  int scale_parts, int scale_dim, float scale_eps, int* error_flag,
+                                  cudaStream_t stream) {
   LLMRS_REQUIRE(tokens > 0 && tokens <= 64, "gemm_qkv_rope: takes 1 to 64 tokens, got %d", tokens);
   LLMRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_stride > 0, "gemm_qkv_rope: bad sizes");
   LLMRS_REQUIRE(q_out && cache && positions && token_req && block_table, "gemm_qkv_rope: missing argument");
@@ -709,8 +793,11 @@ LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, i
   qr.k_norm_w = k_norm_w; qr.cos_sin = cos_sin; qr.positions = positions; qr.token_req = token_req;
   qr.block_table = block_table; qr.table_stride = table_stride; qr.n_q_heads = n_q_heads; qr.n_kv_heads = n_kv_heads;
   qr.page_size = page_size; qr.eps = eps;
+  NormLink nl;
+  nl.scale_part = scale_part; nl.part_stride = part_stride; nl.scale_parts = scale_parts; nl.scale_dim = scale_dim;
+  nl.scale_eps = scale_eps;
   return gemm_bf16_impl(x, ldx, w, q_out, ldq, tokens, (n_q_heads + 2 * n_kv_heads) * 128, K, TC_QKV_ROPE, LLMRS_BF16,
-                        splits, error_flag, &qr, stream);
+                        splits, error_flag, &qr, &nl, stream);
 }
 
 static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_m, int n_tiles,
@@ -752,12 +839,36 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
                               int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
                               cudaStream_t stream) {
   LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
-  return gemm_bf16_impl(x, ldx, w, out, ldo, tokens, features, K, epilogue, out_dtype, splits, error_flag, nullptr, stream);
+  return gemm_bf16_impl(x, ldx, w, out, ldo, tokens, features, K, epilogue, out_dtype, splits, error_flag, nullptr,
+                        nullptr, stream);
+}
+
+// llmrs_gemm_bf16 for at most 64 tokens as one half of a norm that is spread over two products:
+// with emit_w (TC_RESIDUAL, splits >= 2) it also writes emit_xw[tokens, emit_ld] = (h + y) * emit_w in
+// bfloat16 and emit_part[ceil(features / 128), part_stride], its clusters' sums of squares per
+// token; with scale_part it multiplies the rows of y by 1 / sqrt(sum of the scale_parts entries of the
+// row's token / scale_dim + scale_eps) before its epilogue.
+LLMRS_API int llmrs_gemm_bf16_norm(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
+                                   int features, int K, int epilogue, int out_dtype, int splits, const float* emit_w,
+                                   void* emit_xw, long long emit_ld, float* emit_part, const float* scale_part,
+                                   int part_stride, int scale_parts, int scale_dim, float scale_eps,
+                                   int* error_flag, cudaStream_t stream) {
+  LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
+  LLMRS_REQUIRE(tokens <= 64, "gemm_bf16_norm: takes at most 64 tokens, got %d", tokens);
+  LLMRS_REQUIRE(!emit_w || (epilogue == TC_RESIDUAL && splits >= 2 && emit_xw && emit_part && part_stride >= tokens),
+                "gemm_bf16_norm: the next norm's input is written by a residual epilogue with 2 or more splits");
+  LLMRS_REQUIRE(!scale_part || (scale_parts > 0 && scale_dim > 0 && part_stride >= tokens),
+                "gemm_bf16_norm: bad description of the row scales");
+  NormLink nl;
+  nl.emit_w = emit_w; nl.emit_xw = emit_xw; nl.emit_ld = emit_ld; nl.emit_part = emit_part; nl.scale_part = scale_part;
+  nl.part_stride = part_stride; nl.scale_parts = scale_parts; nl.scale_dim = scale_dim; nl.scale_eps = scale_eps;
+  return gemm_bf16_impl(x, ldx, w, out, ldo, tokens, features, K, epilogue, out_dtype, splits, error_flag, nullptr, &nl,
+                        stream);
 }
 
 static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
                           int features, int K, int epilogue, int out_dtype, int splits, int* error_flag,
-                          const QkvRope* qr, cudaStream_t stream) {
+                          const QkvRope* qr, const NormLink* nl, cudaStream_t stream) {
   LLMRS_REQUIRE(tokens > 0 && features > 0 && K > 0, "gemm_bf16: bad sizes");
   LLMRS_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_bf16: K = %d and the row stride %lld must be multiples of 8", K, ldx);
   LLMRS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
@@ -767,6 +878,11 @@ static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out
                 "gemm_bf16: SiLU*up needs features in groups of 128, got %d", features);
   TcParams p;
   if (qr) p.qr = *qr; else p.qr = QkvRope{};
+  const NormLink none;
+  const NormLink& L = nl ? *nl : none;
+  p.emit_w = L.emit_w; p.emit_xw = (bf16*)L.emit_xw; p.emit_ld = L.emit_ld; p.emit_part = L.emit_part;
+  p.scale_part = L.scale_part; p.part_stride = L.part_stride; p.scale_parts = L.scale_parts; p.scale_dim = L.scale_dim;
+  p.scale_eps = L.scale_eps;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
   p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
   CUtensorMap ma, mb;

@@ -356,13 +356,24 @@ def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     return 1
 
 
+def norm_parts(features: int) -> int:
+    """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per 128 features."""
+    return -(-features // 128)
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, epilogue: str = "store",
-              out_dtype: torch.dtype = torch.bfloat16, splits: Optional[int] = None) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, splits: Optional[int] = None, emit=None, scale=None) -> torch.Tensor:
     """``x @ w.T`` for bfloat16 ``x`` [tokens, K] and ``w`` [features, K] on tcgen05 (see csrc/gemm_tcgen05.cu).
 
     epilogue "store": returns [tokens, features] in ``out_dtype``. "residual": ``out`` is the
     float32 residual stream and gets the product added. "silu_mul": ``w`` alternates 64
     gate rows and 64 up rows; returns silu(gate) * up, [tokens, features / 2] bfloat16.
+
+    A norm spread over two products (at most 64 tokens): ``emit`` = (norm weight float32 [features],
+    xw bfloat16 [tokens, features], parts float32 [norm_parts(features), stride]) makes a
+    "residual" epilogue also write xw = (out + product) * weight and the sums of squares of each 128 features;
+    ``scale`` = (parts, n_parts, dim, eps) multiplies the product's rows by
+    1 / sqrt(sum(parts[:n_parts, token]) / dim + eps).
     """
     _need(x, "x", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16)
@@ -384,20 +395,45 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         _need(out, "out", odt)
     if splits is None:
         splits = tc_splits(tokens, features, K, torch.cuda.get_device_properties(x.device).multi_processor_count)
-    _check(_lib().llmrs_gemm_bf16(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
-                                  ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
-                                  splits, _ptr(tc_error_flag(x.device)), _stream()), "gemm_bf16")
+    if emit is None and scale is None:
+        _check(_lib().llmrs_gemm_bf16(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
+                                      ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
+                                      splits, _ptr(tc_error_flag(x.device)), _stream()), "gemm_bf16")
+        return out
+    e_w = e_xw = e_part = s_part = None
+    stride = n_parts = dim = 0
+    eps = 0.0
+    if emit is not None:
+        e_w, e_xw, e_part = emit
+        _need(e_w, "emit weight", torch.float32)
+        _need(e_xw, "emit xw", torch.bfloat16)
+        _need(e_part, "emit parts", torch.float32)
+        if e_w.numel() != features or e_xw.shape != (tokens, features) or e_part.size(0) < norm_parts(features):
+            raise KernelError("emit: weight, xw or parts do not fit the product")
+        stride = e_part.size(1)
+    if scale is not None:
+        s_part, n_parts, dim, eps = scale
+        _need(s_part, "scale parts", torch.float32)
+        if emit is not None and s_part.size(1) != stride:
+            raise KernelError("emit and scale parts must have rows of the same length")
+        stride = s_part.size(1)
+    _check(_lib().llmrs_gemm_bf16_norm(
+        _ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out), ctypes.c_longlong(out.stride(0)), tokens,
+        features, K, epi, dtype_code(odt), splits, _ptr(e_w), _ptr(e_xw),
+        ctypes.c_longlong(e_xw.stride(0) if e_xw is not None else 0), _ptr(e_part), _ptr(s_part), stride, n_parts, dim,
+        ctypes.c_float(eps), _ptr(tc_error_flag(x.device)), _stream()), "gemm_bf16")
     return out
 
 
 def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache: torch.Tensor,
                   q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], cos_sin: Optional[torch.Tensor],
                   positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, n_q_heads: int,
-                  n_kv_heads: int, page_size: int, eps: float, splits: Optional[int] = None) -> torch.Tensor:
+                  n_kv_heads: int, page_size: int, eps: float, splits: Optional[int] = None, scale=None) -> torch.Tensor:
     """q | k | v = ``x @ w.T`` for at most 64 tokens and heads of 128 features, with the per-head norms,
     the rotation and the cache write in the product's epilogue: q lands in ``q_out`` (bfloat16
     [tokens, n_q_heads * 128]), k and v in the pages of ``cache`` that ``block_table`` names. The same
-    arithmetic as ``gemm_bf16`` followed by ``qk_norm_rope_kvwrite``, one kernel and one rounding less."""
+    arithmetic as ``gemm_bf16`` followed by ``qk_norm_rope_kvwrite``, one kernel and one rounding less.
+    ``scale``: as in ``gemm_bf16`` (the rows of the product are scaled before the head norms)."""
     _need(x, "x", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16)
     _need(q_out, "q_out", torch.bfloat16)
@@ -421,7 +457,9 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache: 
         _ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), tokens, K, splits, _ptr(q_out),
         ctypes.c_longlong(q_out.stride(0)), _ptr(cache), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin),
         _ptr(positions), _ptr(token_req), _ptr(block_table), block_table.size(1), n_q_heads, n_kv_heads, page_size,
-        ctypes.c_float(eps), _ptr(tc_error_flag(x.device)), _stream()), "gemm_qkv_rope")
+        ctypes.c_float(eps), _ptr(scale[0] if scale else None), scale[0].size(1) if scale else 0,
+        scale[1] if scale else 0, scale[2] if scale else 0, ctypes.c_float(scale[3] if scale else 0.0),
+        _ptr(tc_error_flag(x.device)), _stream()), "gemm_qkv_rope")
     return q_out
 
 

@@ -8,7 +8,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Mixer, PositionEncoding, Runtime
+from .base import Mixer, PositionEncoding, PreNormed, Runtime
 from .linear import Linear
 from .registry import build, register
 from .spec import CacheNeed, PartSpec, WeightSpec
@@ -127,17 +127,29 @@ class GQAttention(Mixer):
         keys = -(-keys // 64) * 64
         return min(max(keys, 128), 1024 if q.dtype == torch.float32 or self.head_dim > 128 else 2048)
 
+    def takes_prenormed(self, n_tokens: int) -> bool:
+        return self.qkv_proj.takes_prenormed(n_tokens) and self.q_proj.takes_prenormed(n_tokens)
+
+    def emits_prenormed(self, n_tokens: int) -> bool:
+        return self.o_proj.emits_prenormed(n_tokens)
+
     # -- step ------------------------------------------------------------------------
-    def forward(self, x, ctx, cache, residual=None):
+    def forward(self, x, ctx, cache, residual=None, next_norm=None):
         nq, nkv, d = self.n_heads, self.n_kv_heads, self.head_dim
         table = cache.block_table
         cos_sin = self.position.rotation_table()
-        if self._fuses_rope(x, cache, cos_sin):
+        scale = None
+        if isinstance(x, PreNormed):     # only when takes_prenormed: the products below scale their rows
+            scale, xin = x.scale, x.xw
+        else:
+            xin = x
+        if self._fuses_rope(xin, cache, cos_sin):
             # Few tokens, heads of 128: the norms, the rotation and the cache write are the epilogue of the
             # q|k|v product (one kernel less in every layer of a decode step).
-            q = torch.empty((ctx.n_tokens, self.q_width), dtype=x.dtype, device=x.device)
-            ops.gemm_qkv_rope(x, self.qkv_proj.weight, q, cache.kv, self.q_norm_w, self.k_norm_w, cos_sin,
-                              ctx.positions, ctx.token_req, table, nq, nkv, cache.page_size, self.qk_norm_eps)
+            q = torch.empty((ctx.n_tokens, self.q_width), dtype=xin.dtype, device=xin.device)
+            ops.gemm_qkv_rope(xin, self.qkv_proj.weight, q, cache.kv, self.q_norm_w, self.k_norm_w, cos_sin,
+                              ctx.positions, ctx.token_req, table, nq, nkv, cache.page_size, self.qk_norm_eps,
+                              scale=scale)
         else:
             if cache.owns:
                 qkv = self.qkv_proj.forward(x)
@@ -166,6 +178,8 @@ class GQAttention(Mixer):
             ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
                             self.scale)
+        if next_norm is not None:
+            return self.o_proj.forward_into_residual_for_norm(out, residual, *next_norm)
         if residual is not None:
             return self.o_proj.forward_into_residual(out, residual)
         return self.o_proj.forward(out)

@@ -35,6 +35,22 @@ class Part:
         """Take the tensors named in ``weight_specs`` (already on ``runtime.device``)."""
 
 
+class PreNormed:
+    """The input of a norm whose two halves are spread over the products around it (steps of few
+    tokens): ``xw`` = h * weight in the activation type and ``parts`` [n_parts, stride], per token the
+    sums of squares of h in pieces. The normed activations are ``xw / sqrt(sum(parts) / dim + eps)``;
+    a part whose ``takes_prenormed(n_tokens)`` is true gets this object as its ``x`` and applies the
+    factor to the rows of its first product. A part whose ``emits_prenormed(n_tokens)`` is true takes
+    ``next_norm=(weight, eps)`` with ``residual=h`` and returns such an object for the norm after it."""
+
+    def __init__(self, xw: torch.Tensor, parts: torch.Tensor, n_parts: int, dim: int, eps: float):
+        self.xw, self.parts, self.n_parts, self.dim, self.eps = xw, parts, n_parts, dim, eps
+
+    @property
+    def scale(self):
+        return (self.parts, self.n_parts, self.dim, self.eps)
+
+
 class Norm(Part):
     """``forward(h, delta)``: ``h += delta`` (float32 residual stream, in place; ``delta``
     may be None) and return the normed rows in the activation type. With ``rows`` only
@@ -42,6 +58,11 @@ class Norm(Part):
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None):
         raise NotImplementedError
+
+    def link(self):
+        """(weight float32 [dim], eps) when this norm is ``x / sqrt(mean(x^2) + eps) * weight`` and may be
+        spread over the products around it (see ``PreNormed``); None otherwise."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -75,6 +96,14 @@ class Mixer(Part):
     """
     fuses_residual = False
 
+    def takes_prenormed(self, n_tokens: int) -> bool:
+        """True when ``forward`` accepts a ``PreNormed`` as ``x`` in a step of ``n_tokens`` tokens."""
+        return False
+
+    def emits_prenormed(self, n_tokens: int) -> bool:
+        """True when ``forward(..., residual=h, next_norm=(weight, eps))`` returns a ``PreNormed``."""
+        return False
+
     def cache_need(self) -> Optional[CacheNeed]:
         return None
 
@@ -90,6 +119,12 @@ class FeedForward(Part):
     ``fuses_residual = True`` it also takes ``residual=h`` as a mixer does."""
     fuses_residual = False
 
+    def takes_prenormed(self, n_tokens: int) -> bool:
+        return False
+
+    def emits_prenormed(self, n_tokens: int) -> bool:
+        return False
+
     def forward(self, x, ctx):
         raise NotImplementedError
 
@@ -100,7 +135,13 @@ class Block(Part):
     ``forward(h, pending, ctx, cache) -> (h, pending)``: ``h`` is the float32 residual
     stream; ``pending`` is a branch output that has not been added to ``h`` yet (None at
     the first layer), so that the sum can be fused with the next norm.
+
+    A block with ``links_norms = True`` also has ``accepts_prenormed(n_tokens)`` (its first norm and
+    mixer can take a ``PreNormed`` as ``pending``: ``h`` then holds the sum already) and takes
+    ``next_norm=(weight, eps)``, the first norm of the block that runs after it, for which its last
+    part may return a ``PreNormed``.
     """
+    links_norms = False
 
     def forward(self, h, pending, ctx, cache):
         raise NotImplementedError

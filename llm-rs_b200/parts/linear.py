@@ -17,11 +17,21 @@ from typing import Optional
 import torch
 
 from .. import ops
+from .base import PreNormed
 
 # Steps with at most this many tokens take the tcgen05 kernel; 0 switches it off.
 TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "32"))
 # Also for larger steps (prefill) when set; by default those stay with the library product.
 TC_PREFILL = os.environ.get("LLMRS_TC_PREFILL", "0") == "1"
+
+
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    if device not in _SM_COUNT:
+        _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[device]
 
 
 class Linear:
@@ -40,8 +50,10 @@ class Linear:
     def uses_tc(self, n_tokens: int) -> bool:
         return self.tc_ok and n_tokens > 0 and (n_tokens <= TC_MAX_TOKENS or (TC_PREFILL and TC_MAX_TOKENS > 0))
 
-    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
+        if isinstance(x, PreNormed):     # only when takes_prenormed
+            return ops.gemm_bf16(x.xw, self.weight, out_dtype=out_dtype, scale=x.scale)
         if self.weight.dtype == torch.float32:
             xf = x if x.dtype == torch.float32 else x.to(torch.float32)
             y = ops.gemm_f32(xf, self.weight, self.bias)
@@ -55,6 +67,30 @@ class Linear:
                 y += self.bias.to(torch.float32)
             return y
         return torch.nn.functional.linear(xb, self.weight, self.bias)
+
+    def _splits(self, n_tokens: int) -> int:
+        n, k = self.weight.shape
+        return ops.tc_splits(n_tokens, n, k, _sm_count(self.weight.device))
+
+    def takes_prenormed(self, n_tokens: int) -> bool:
+        """True when ``forward`` accepts a ``PreNormed`` (the tcgen05 kernel for few tokens scales its rows)."""
+        return self.uses_tc(n_tokens) and n_tokens <= 64
+
+    def emits_prenormed(self, n_tokens: int) -> bool:
+        """True when ``forward_into_residual`` can also write the input of the norm that follows."""
+        return self.uses_tc(n_tokens) and n_tokens <= 64 and self._splits(n_tokens) >= 2
+
+    def forward_into_residual_for_norm(self, x: torch.Tensor, h: torch.Tensor, norm_weight: torch.Tensor,
+                                       eps: float) -> PreNormed:
+        """``h += x @ weight.T`` and, in the same epilogue, the input of the norm that follows
+        (see ``PreNormed``). Only when ``emits_prenormed``."""
+        n = self.weight.size(0)
+        splits = self._splits(x.size(0))
+        n_parts = ops.norm_parts(n)
+        xw = torch.empty((x.size(0), n), dtype=torch.bfloat16, device=x.device)
+        parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
+        ops.gemm_bf16(x, self.weight, out=h, epilogue="residual", splits=splits, emit=(norm_weight, xw, parts))
+        return PreNormed(xw, parts, n_parts, n, eps)
 
     def forward_into_residual(self, x: torch.Tensor, h: torch.Tensor) -> Optional[torch.Tensor]:
         """``h += x @ weight.T`` inside the product's epilogue when the tcgen05 kernel runs

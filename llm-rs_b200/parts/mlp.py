@@ -6,7 +6,7 @@ import os
 import torch
 
 from .. import ops
-from .base import FeedForward, Runtime
+from .base import FeedForward, PreNormed, Runtime
 from .linear import Linear
 from .registry import register
 from .spec import WeightSpec
@@ -48,7 +48,18 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(w, None, runtime.act_dtype)
         self.down = Linear(tensors[p + "down_proj.weight"], None, runtime.act_dtype)
 
-    def forward(self, x, ctx, residual=None):
+    def takes_prenormed(self, n_tokens: int) -> bool:
+        return bool(self.block) and self.gate_up.tc_ok and FUSE_GATE_UP and 0 < n_tokens <= 64
+
+    def emits_prenormed(self, n_tokens: int) -> bool:
+        return self.down.emits_prenormed(n_tokens)
+
+    def forward(self, x, ctx, residual=None, next_norm=None):
+        if isinstance(x, PreNormed):     # only when takes_prenormed
+            act = ops.gemm_bf16(x.xw, self.gate_up.weight, epilogue="silu_mul", scale=x.scale)
+            if next_norm is not None:
+                return self.down.forward_into_residual_for_norm(act, residual, *next_norm)
+            return self.down.forward_into_residual(act, residual) if residual is not None else self.down.forward(act)
         # With interleaved weights the product and SiLU(gate) * up are one kernel at every number of
         # tokens: for many tokens the persistent tcgen05 kernel with this epilogue is level with the
         # library product followed by the SiLU kernel, or ahead of it (2,048 tokens: 295 against 315 us).
@@ -56,6 +67,8 @@ class SwiGLU(FeedForward):
             act = ops.gemm_bf16(x, self.gate_up.weight, epilogue="silu_mul")
         else:
             act = ops.silu_mul(self.gate_up.forward(x), block=self.block)
+        if next_norm is not None:
+            return self.down.forward_into_residual_for_norm(act, residual, *next_norm)
         if residual is not None:
             return self.down.forward_into_residual(act, residual)
         return self.down.forward(act)

@@ -54,8 +54,16 @@ class DecoderModel:
         wanted rows ([wanted, vocab]), or None when nothing is wanted."""
         h = self.embedding.forward(ctx.token_ids)
         pending = None
-        for s, step in enumerate(self.spec.run_order):
-            h, pending = self.blocks[step.layer].forward(h, pending, ctx, ctx.layer_cache(s))
+        order = self.spec.run_order
+        for s, step in enumerate(order):
+            block = self.blocks[step.layer]
+            after = self.blocks[order[s + 1].layer] if s + 1 < len(order) else None
+            if (getattr(block, "links_norms", False) and getattr(after, "links_norms", False)
+                    and after.accepts_prenormed(ctx.n_tokens)):
+                # The norm between the two blocks is spread over this block's last product and the next one's first.
+                h, pending = block.forward(h, pending, ctx, ctx.layer_cache(s), next_norm=after.mixer_norm.link())
+            else:
+                h, pending = block.forward(h, pending, ctx, ctx.layer_cache(s))
         if ctx.n_want == 0:
             return None
         x = self.final_norm.forward(h, pending, rows=ctx.want_rows)

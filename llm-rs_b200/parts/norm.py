@@ -31,3 +31,6 @@ class RMSNorm(Norm):
 
     def forward(self, h, delta, rows=None):
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.act_dtype, rows=rows)
+
+    def link(self):
+        return (self.weight, self.eps) if self.act_dtype == torch.bfloat16 else None

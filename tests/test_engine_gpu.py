@@ -204,6 +204,33 @@ def test_first_tokens(models, name, dtype):
         runner.release(f"s{n}")
 
 
+def test_norms_spread_over_products_in_small_steps(models, monkeypatch):
+    """In a bfloat16 step of few tokens the norm kernel runs for the first layer and the last norm only:
+    every other norm is made by the product before it and applied by the product after it. The logits agree
+    with the ones that the norm kernels give, and with the plain implementation."""
+    from llm_rs_b200 import ops
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.parts import block as block_module
+    path, cfg, w = models["D"]
+    toks = np.random.default_rng(4).integers(0, cfg["vocab_size"], 12).tolist()
+    ref = P.forward(cfg, w, toks).numpy()
+    calls, real = [], ops.add_rmsnorm
+    monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (calls.append(1), real(*a, **k))[1])
+    got = {}
+    for linked in (True, False):
+        monkeypatch.setattr(block_module, "LINK_NORMS", linked)
+        runner = ModelRunner.from_model_dir(path, dtype=torch.bfloat16, max_tokens=256, page_size=16, max_requests=4)
+        rows = []
+        for i in range(0, 12, 3):
+            del calls[:]
+            rows.append(runner.step([StepEntry("a", toks[i:i + 3], [0, 1, 2])]).float().cpu().numpy())
+            assert len(calls) == (2 if linked else 2 * cfg["num_hidden_layers"] + 1), (linked, len(calls))
+        got[linked] = np.concatenate(rows)
+    scale = np.abs(ref).max()
+    assert np.abs(got[True] - ref).max() < 0.02 * scale
+    assert np.abs(got[True] - got[False]).max() < 0.02 * scale
+
+
 # -- weights stored in 32-bit --------------------------------------------------------------------
 def test_tensors_stored_in_32_bit_stay_32_bit(folder):
     """A folder whose matrices are float32: the bfloat16 engine keeps them (its products then

@@ -599,3 +599,70 @@ def test_gemm_qkv_rope_epilogue(tokens, nq, nkv, K, page, rope, norm):
         assert float((host[pg, :, 0, slot] - k[t]).abs().max()) < tol
         assert float((host[pg, :, 1, slot] - v[t]).abs().max()) < tol
     assert float(host[~touched[:, None, None, :, None].expand_as(host)].abs().max()) == 0.0   # nothing else was written
+
+
+@pytest.mark.parametrize("tokens,features,K,splits,consumer", [
+    (8, 256, 512, 2, "store"), (1, 384, 256, 4, "silu_mul"), (19, 200, 1024, 8, "store"), (32, 512, 512, 2, "qkv_rope"),
+    (64, 136, 256, 2, "silu_mul")])
+def test_gemm_norm_spread_over_two_products(tokens, features, K, splits, consumer):
+    """A residual epilogue that also writes the next norm's input (h * weight and sums of squares in
+    pieces), and the products that take it and scale their rows, against
+    rmsnorm(h + x W^T) W2^T in float64."""
+    ops = _ops()
+    torch.manual_seed(tokens * 7 + features)
+    x = (torch.randn(tokens, K) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(features, K) * 0.05).to(torch.bfloat16)
+    h0 = torch.randn(tokens, features) * torch.linspace(0.2, 3.0, tokens)[:, None]   # rows of different size
+    nw = 1 + 0.2 * torch.randn(features)
+    eps = 3e-5
+    h = h0.to(DEV).clone()
+    xw = torch.full((tokens, features), float("nan"), dtype=torch.bfloat16, device=DEV)
+    n_parts = ops.norm_parts(features)
+    parts = torch.full((n_parts, 64), float("nan"), dtype=torch.float32, device=DEV)
+    ops.gemm_bf16(x.to(DEV), w.to(DEV), out=h, epilogue="residual", splits=splits, emit=(nw.to(DEV), xw, parts))
+    torch.cuda.synchronize()
+    ops.check_tc_error(DEV)
+    want_h = h0.double() + x.double() @ w.double().t()
+    assert float((h.double().cpu() - want_h).abs().max()) < 1e-3
+    ss = parts[:, :tokens].double().cpu().sum(0)
+    assert float(((ss - (want_h ** 2).sum(-1)) / (want_h ** 2).sum(-1)).abs().max()) < 1e-4
+    assert float((xw.double().cpu() - want_h * nw.double()).abs().max()) < 2e-2 * float((want_h * nw.double()).abs().max())
+    normed = want_h / torch.sqrt((want_h ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+    scale = (parts, n_parts, features, eps)
+    if consumer == "store":
+        w2 = (torch.randn(264, features) * 0.05).to(torch.bfloat16)
+        got = ops.gemm_bf16(xw, w2.to(DEV), out_dtype=torch.float32, scale=scale)
+        want = normed @ w2.double().t()
+    elif consumer == "silu_mul":
+        g, u = (torch.randn(128, features) * 0.05).to(torch.bfloat16), (torch.randn(128, features) * 0.05).to(torch.bfloat16)
+        got = ops.gemm_bf16(xw, ops.interleave_gate_up(g, u).to(DEV), epilogue="silu_mul", scale=scale)
+        a, b = normed @ g.double().t(), normed @ u.double().t()
+        want = a * torch.sigmoid(a) * b
+    else:
+        nq, nkv, d, page = 2, 1, 128, 16
+        w2 = (torch.randn((nq + 2 * nkv) * d, features) * 0.05).to(torch.bfloat16)
+        pos = torch.arange(tokens, dtype=torch.int32)
+        table = torch.arange(-(-tokens // page), dtype=torch.int32).view(1, -1)
+        cache = torch.zeros(table.numel(), nkv, 2, page, d, dtype=torch.bfloat16, device=DEV)
+        got = torch.empty(tokens, nq * d, dtype=torch.bfloat16, device=DEV)
+        ops.gemm_qkv_rope(xw, w2.to(DEV), got, cache, None, None, None, pos.to(DEV), torch.zeros(tokens, dtype=torch.int32, device=DEV),
+                          table.to(DEV), nq, nkv, page, 1e-6, scale=scale)
+        y = normed @ w2.double().t()
+        want = y[:, : nq * d]
+        k_got = torch.stack([cache[t // page, :, 0, t % page] for t in range(tokens)]).double().cpu().reshape(tokens, -1)
+        assert float((k_got - y[:, nq * d: (nq + nkv) * d]).abs().max()) < 2e-2 * float(y.abs().max())
+    torch.cuda.synchronize()
+    ops.check_tc_error(DEV)
+    assert float((got.double().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max())
+
+
+def test_gemm_norm_emission_refusals():
+    ops = _ops()
+    x = torch.zeros(8, 256, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(256, 256, dtype=torch.bfloat16, device=DEV)
+    h = torch.zeros(8, 256, device=DEV)
+    nw, xw, parts = torch.ones(256, device=DEV), torch.empty(8, 256, dtype=torch.bfloat16, device=DEV), torch.empty(8, 64, device=DEV)
+    with pytest.raises(ops.KernelError):      # one split: the sums of squares would need 64 threads a token
+        ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=1, emit=(nw, xw, parts))
+    with pytest.raises(ops.KernelError):      # too few rows for the pieces
+        ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=4, emit=(nw, xw, parts[:1]))

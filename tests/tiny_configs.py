@@ -31,7 +31,7 @@ TINY_C = dict(
 TINY_D = dict(
     architectures=["Qwen3ForCausalLM"], model_type="qwen3",
     num_hidden_layers=2, hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
-    intermediate_size=384, vocab_size=520, rope_theta=1000000.0, rms_norm_eps=1e-6,
+    intermediate_size=640, vocab_size=520, rope_theta=1000000.0, rms_norm_eps=1e-6,
     tie_word_embeddings=False, attention_bias=False, max_position_embeddings=2048, hidden_act="silu",
     eos_token_id=519)
 
