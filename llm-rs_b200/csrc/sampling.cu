@@ -42,8 +42,19 @@ LLMRS_API float llmrs_philox_uniform(unsigned long long seed, unsigned long long
 template <typename F>
 __device__ __forceinline__ void for_each_elem(const float* __restrict__ x, int vocab, F&& f) {
   if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    // Four loads in flight per thread: one block reads the whole row, and with a single load per
+    // thread it waits for the memory's latency on every step.
     const float4* x4 = reinterpret_cast<const float4*>(x);
-    for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) {
+    const int n4 = vocab / 4, bd = blockDim.x;
+    int i = threadIdx.x;
+    for (; i + 3 * bd < n4; i += 4 * bd) {
+      const float4 v0 = x4[i], v1 = x4[i + bd], v2 = x4[i + 2 * bd], v3 = x4[i + 3 * bd];
+      f(4 * i, v0.x); f(4 * i + 1, v0.y); f(4 * i + 2, v0.z); f(4 * i + 3, v0.w);
+      f(4 * (i + bd), v1.x); f(4 * (i + bd) + 1, v1.y); f(4 * (i + bd) + 2, v1.z); f(4 * (i + bd) + 3, v1.w);
+      f(4 * (i + 2 * bd), v2.x); f(4 * (i + 2 * bd) + 1, v2.y); f(4 * (i + 2 * bd) + 2, v2.z); f(4 * (i + 2 * bd) + 3, v2.w);
+      f(4 * (i + 3 * bd), v3.x); f(4 * (i + 3 * bd) + 1, v3.y); f(4 * (i + 3 * bd) + 2, v3.z); f(4 * (i + 3 * bd) + 3, v3.w);
+    }
+    for (; i < n4; i += bd) {
       const float4 v = x4[i];
       f(4 * i, v.x); f(4 * i + 1, v.y); f(4 * i + 2, v.z); f(4 * i + 3, v.w);
     }
@@ -101,7 +112,9 @@ constexpr int SEL_BINS = 2048;
 constexpr float SEL_FIX = 1099511627776.0f;   // 2^40
 
 struct SelectScratch {
-  unsigned long long bins[SEL_BINS];   // counts or fixed-point masses
+  // Counts or fixed-point masses, as two 32-bit halves: shared memory adds 32-bit words natively, while a
+  // 64-bit add is a compare-and-swap loop that crawls when many threads meet in one bin.
+  uint32_t lo[SEL_BINS], hi[SEL_BINS];
   unsigned long long warp_tot[32];
   unsigned long long found_above;
   int found_bin;
@@ -109,12 +122,26 @@ struct SelectScratch {
 
 __device__ __forceinline__ unsigned long long to_fixed(float e) { return (unsigned long long)(e * SEL_FIX); }
 
+// bins[b] += add, exactly: the low word's carry goes into the high word.
+__device__ __forceinline__ void bin_add(SelectScratch* sc, uint32_t b, unsigned long long add) {
+  const uint32_t lo = (uint32_t)add;
+  uint32_t hi = (uint32_t)(add >> 32);
+  if (lo) {
+    const uint32_t old = atomicAdd(&sc->lo[b], lo);
+    if (old > 0xffffffffu - lo) ++hi;
+  }
+  if (hi) atomicAdd(&sc->hi[b], hi);
+}
+__device__ __forceinline__ unsigned long long bin_value(const SelectScratch* sc, int b) {
+  return ((unsigned long long)sc->hi[b] << 32) | sc->lo[b];
+}
+
 // Highest bin b with sum(bins[b..]) >= need; returns b (or -1) and leaves sum(bins[b+1..]) in sc->found_above.
 // All threads of the block call it; bins are read top-down, two per thread.
 __device__ int find_bin(SelectScratch* sc, unsigned long long need) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int b0 = SEL_BINS - 1 - 2 * tid, b1 = b0 - 1;            // this thread's two bins, the higher first
-  const unsigned long long v0 = sc->bins[b0], v1 = sc->bins[b1];
+  const unsigned long long v0 = bin_value(sc, b0), v1 = bin_value(sc, b1);
   unsigned long long incl = v0 + v1;                              // inclusive scan over threads, top-down
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
@@ -146,14 +173,14 @@ __device__ uint32_t select_cut(const float* __restrict__ x, int vocab, uint32_t 
   if (need == 0) need = 1;
 #pragma unroll 1
   for (int level = 0; level < 3; ++level) {
-    for (int i = tid; i < SEL_BINS; i += SM_THREADS) sc->bins[i] = 0;
+    for (int i = tid; i < SEL_BINS; i += SM_THREADS) sc->lo[i] = sc->hi[i] = 0u;
     __syncthreads();
     const int shift = shifts[level];
     const uint32_t digit_mask = (1u << widths[level]) - 1u;
     for_each_elem(x, vocab, [&](int, float e) {
       const uint32_t bits = __float_as_uint(e);
       if (bits >= floor_bits && (bits & prefix_mask) == prefix)
-        atomicAdd(&sc->bins[(bits >> shift) & digit_mask], by_mass ? to_fixed(e) : 1ull);
+        bin_add(sc, (bits >> shift) & digit_mask, by_mass ? to_fixed(e) : 1ull);
     });
     __syncthreads();
     const int bin = find_bin(sc, need);
@@ -206,15 +233,23 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
   const float mx = best.v / T;
   if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     float4* x4 = reinterpret_cast<float4*>(x);
-    for (int i = tid; i < vocab / 4; i += SM_THREADS) {
-      float4 v = x4[i];
-      float* e = reinterpret_cast<float*>(&v);
+    const int n4 = vocab / 4;
+    for (int i0 = tid; i0 < n4; i0 += 4 * SM_THREADS) {
+      float4 v[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float y = expf(e[c] / T - mx);
-        e[c] = y >= 0.f ? y : 0.f;   // a NaN logit keeps no mass
+      for (int q = 0; q < 4; ++q)
+        if (i0 + q * SM_THREADS < n4) v[q] = x4[i0 + q * SM_THREADS];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (i0 + q * SM_THREADS >= n4) break;
+        float* e = reinterpret_cast<float*>(&v[q]);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float y = expf(e[c] / T - mx);
+          e[c] = y >= 0.f ? y : 0.f;   // a NaN logit keeps no mass
+        }
+        x4[i0 + q * SM_THREADS] = v[q];
       }
-      x4[i] = v;
     }
   } else {
     for (int i = tid; i < vocab; i += SM_THREADS) {
@@ -252,16 +287,22 @@ sample_kernel(float* __restrict__ logits, int vocab, const float* __restrict__ t
   // loads, a fixed order of additions), one thread walks the 1024 sums in order, and the thread
   // that owns the run in which the target falls walks that run.
   const int chunk = (vocab + SM_THREADS - 1) / SM_THREADS;
-  for (int c = warp * 32; c < warp * 32 + 32; ++c) {
-    const int lo_c = min(c * chunk, vocab), hi_c = min(lo_c + chunk, vocab);
-    float part = 0.f;
-    for (int i = lo_c + lane; i < hi_c; i += 32) {
-      const float e = x[i];
-      part += e >= cut ? e : 0.f;
+  for (int c = warp * 32; c < warp * 32 + 32; c += 4) {   // four runs at a time: their loads are in flight together
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int off = lane; off < chunk; off += 32) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int lo_c = min((c + q) * chunk, vocab), hi_c = min(lo_c + chunk, vocab);
+        const float e = lo_c + off < hi_c ? x[lo_c + off] : 0.f;
+        part[q] += e >= cut ? e : 0.f;
+      }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    if (lane == 0) scan[c] = part;
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) part[q] += __shfl_xor_sync(0xffffffffu, part[q], o);
+      if (lane == 0) scan[c + q] = part[q];
+    }
   }
   if (tid == 0) chosen = -1;
   __syncthreads();
