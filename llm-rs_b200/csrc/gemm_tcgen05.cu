@@ -215,6 +215,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const bool scaled = MODE == 1 && p.scale_part != nullptr;
 
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
+  const int early = MODE == 1 ? min(nkb, STAGES) : 0;   // stages whose weight tile is requested before the wait
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -236,12 +237,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Mode 1: the items of the epilogue are dealt out so that warps 2 and 3, which have nothing to do while
+  // the product runs, own the first ones, and they fetch what those items need from global memory (the
+  // residual's old values, positions, rotation, page) under the product instead of after it.
+  const int etid = MODE == 1 ? ((tid + 64) & (TC_THREADS - 1)) : tid;
+  const int ewarp = etid >> 5;
+  const uint32_t rank = (MODE == 1 && splits > 1) ? cluster_rank() : 0u;
+  const int per = 64 / splits;                 // feature pairs (i, i + 64) owned by this block
+  const int n_tok = MODE == 1 ? min(BN, p.b_rows - tile_b * BN) : 0;
+  bool pf = false;
+  float pf_h_lo = 0.f, pf_h_hi = 0.f, pf_w_lo = 0.f, pf_w_hi = 0.f;
+  int pf_pos = 0, pf_page = 0;
+  float2 pf_cs0 = make_float2(1.f, 0.f), pf_cs1 = make_float2(1.f, 0.f);
+
   if (warp == 0 && lane == 0) {
     // Producer: one thread feeds the ring of stages by TMA. In mode 1 the A operand is the
     // weight, which no earlier kernel writes: its first tiles are requested before the
-    // wait on the preceding kernel, whose tail they overlap.
+    // wait on the preceding kernel, whose tail they overlap. (Requesting them still earlier, before
+    // tensor memory is allocated, made the decode step slower: 3.83 -> 3.96 ms.)
     int issued = 0;
-    const int early = MODE == 1 ? min(nkb, STAGES) : 0;
     for (int i = 0; i < early; ++i) {
       mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
       tma_load_2d(tc_smem(tiles + (size_t)i * STAGE_BYTES), &map_a, full0 + 8 * i, (kb0 + i) * TC_BK, tile_a * TC_BM);
@@ -283,28 +297,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       __syncwarp();
     }
     if (leader) tc_commit(accum_bar);
-  } else if (MODE == 1 && warp >= 2 && p.scale_part) {
-    // Warps 2 and 3, while the product runs: the row scales 1/sqrt(sum of the pieces / dim + eps) of this
-    // tile's tokens. A piece's row holds all tokens side by side, so the 64 threads read whole rows:
-    // n_pow tokens wide, 64 / n_pow rows at a time; the groups' sums are then added in order.
+  } else if (MODE == 1 && warp >= 2) {
     pdl_wait();
-    const int u = tid - 64;
-    const int n_tok_s = min(BN, p.b_rows - tile_b * BN);
-    int n_pow = 1;
-    while (n_pow < n_tok_s) n_pow <<= 1;
-    const int j = u % n_pow, g = u / n_pow, n_groups = 64 / n_pow;
-    float ss = 0.f;
-    if (j < n_tok_s) {
-      const float* src = p.scale_part + tile_b * BN + j;
-#pragma unroll 8
-      for (int q = g; q < p.scale_parts; q += n_groups) ss += __ldcg(src + (size_t)q * p.part_stride);
+    if (p.epilogue == TC_RESIDUAL) {
+      if (etid < per * n_tok) {
+        const int pr = etid % per, j = etid / per;
+        const int f_lo = tile_a * TC_BM + (int)rank * per + pr, f_hi = f_lo + 64;
+        const float* h = (const float*)p.out + (size_t)(tile_b * BN + j) * p.ldo;
+        if (f_lo < p.a_rows) { pf_h_lo = h[f_lo]; if (p.emit_w) pf_w_lo = p.emit_w[f_lo]; }
+        if (f_hi < p.a_rows) { pf_h_hi = h[f_hi]; if (p.emit_w) pf_w_hi = p.emit_w[f_hi]; }
+        pf = true;
+      }
+    } else if (p.epilogue == TC_QKV_ROPE) {
+      const QkvRope& g = p.qr;
+      const int j = (int)rank + splits * ewarp;
+      if (j < n_tok) {
+        const int t = tile_b * BN + j;
+        pf_pos = g.positions[t];
+        if (g.cos_sin && tile_a < g.n_q_heads + g.n_kv_heads) {
+          pf_cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pf_pos * 64 + lane) * 2);
+          pf_cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pf_pos * 64 + lane + 32) * 2);
+        }
+        if (tile_a >= g.n_q_heads) pf_page = g.block_table[(size_t)g.token_req[t] * g.table_stride + pf_pos / g.page_size];
+        pf = true;
+      }
     }
-    inv_part[u] = ss;
-    asm volatile("bar.sync 1, 64;" ::: "memory");
-    if (u < n_tok_s) {
-      float sum = 0.f;
-      for (int k = 0; k < n_groups; ++k) sum += inv_part[k * n_pow + u];
-      inv_s[u] = 1.0f / sqrtf(sum / (float)p.scale_dim + p.scale_eps);
+    if (p.scale_part) {
+      // While the product runs: the row scales 1/sqrt(sum of the pieces / dim + eps) of this
+      // tile's tokens. A piece's row holds all tokens side by side, so the 64 threads read whole rows:
+      // n_pow tokens wide, 64 / n_pow rows at a time; the groups' sums are then added in order.
+      const int u = tid - 64;
+      const int n_tok_s = min(BN, p.b_rows - tile_b * BN);
+      int n_pow = 1;
+      while (n_pow < n_tok_s) n_pow <<= 1;
+      const int j = u % n_pow, g = u / n_pow, n_groups = 64 / n_pow;
+      float ss = 0.f;
+      if (j < n_tok_s) {
+        const float* src = p.scale_part + tile_b * BN + j;
+#pragma unroll 8
+        for (int q = g; q < p.scale_parts; q += n_groups) ss += __ldcg(src + (size_t)q * p.part_stride);
+      }
+      inv_part[u] = ss;
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (u < n_tok_s) {
+        float sum = 0.f;
+        for (int k = 0; k < n_groups; ++k) sum += inv_part[k * n_pow + u];
+        inv_s[u] = 1.0f / sqrtf(sum / (float)p.scale_dim + p.scale_eps);
+      }
     }
   }
   __syncwarp();
@@ -395,10 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     if (splits > 1) cluster_sync_all(); else __syncthreads();
 
-    const uint32_t rank = splits > 1 ? cluster_rank() : 0u;
-    const int per = 64 / splits;                 // feature pairs (i, i + 64) owned by this block
     const uint32_t red_addr = tc_smem(red);
-    const int n_tok = min(BN, p.b_rows - tile_b * BN);
     if (p.epilogue == TC_QKV_ROPE) {
       // The tile is one head. A block of the cluster takes every splits-th token, a warp one token at a
       // time: lane l holds features l, l + 32, l + 64, l + 96, i.e. the rotation's pairs (l, l + 64) and
@@ -407,7 +443,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int head = tile_a;
       const int kind = head < g.n_q_heads ? 0 : head < g.n_q_heads + g.n_kv_heads ? 1 : 2;
       const int hidx = kind == 0 ? head : kind == 1 ? head - g.n_q_heads : head - g.n_q_heads - g.n_kv_heads;
-      for (int j = (int)rank + splits * warp; j < n_tok; j += splits * (TC_THREADS / 32)) {
+      bool first = true;
+      for (int j = (int)rank + splits * ewarp; j < n_tok; j += splits * (TC_THREADS / 32), first = false) {
+        const bool fetched = pf && first;
         float x[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -421,7 +459,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           x[q] = scaled ? acc * inv_s[j] : acc;
         }
         const int t = tile_b * BN + j;
-        const int pos = g.positions[t];
+        const int pos = fetched ? pf_pos : g.positions[t];
         if (kind != 2) {
           const float* w = kind == 0 ? g.q_norm_w : g.k_norm_w;
           if (w) {
@@ -433,8 +471,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int q = 0; q < 4; ++q) x[q] *= inv * w[lane + 32 * q];
           }
           if (g.cos_sin) {
-            const float2 cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
-            const float2 cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
+            const float2 cs0 = fetched ? pf_cs0 : *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
+            const float2 cs1 = fetched ? pf_cs1 : *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
             const float a0 = x[0] * cs0.x - x[2] * cs0.y, b0 = x[2] * cs0.x + x[0] * cs0.y;
             const float a1 = x[1] * cs1.x - x[3] * cs1.y, b1 = x[3] * cs1.x + x[1] * cs1.y;
             x[0] = a0; x[2] = b0; x[1] = a1; x[3] = b1;
@@ -444,7 +482,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (kind == 0) {
           dst = g.q_out + (size_t)t * g.ldq + (size_t)hidx * 128;
         } else {
-          const int page = g.block_table[(size_t)g.token_req[t] * g.table_stride + pos / g.page_size];
+          const int page = fetched ? pf_page : g.block_table[(size_t)g.token_req[t] * g.table_stride + pos / g.page_size];
           dst = g.cache + kv_tile_offset(page, hidx, kind - 1, g.n_kv_heads, g.page_size, 128) +
                 (size_t)(pos % g.page_size) * 128;
         }
@@ -453,8 +491,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
     } else
     for (int base = 0; base < per * n_tok; base += TC_THREADS) {   // every thread walks the loop (warp shuffles below)
-      const int idx = base + tid;
+      const int idx = base + etid;
       const bool live = idx < per * n_tok;
+      const bool fetched = pf && base == 0;
       const int pr = idx % per, j = live ? idx / per : 0;
       const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
       float lo = 0.f, hi = 0.f;
@@ -481,13 +520,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       } else if (p.epilogue == TC_RESIDUAL) {
         float* h = (float*)p.out + (size_t)t * p.ldo;
         float n_lo = 0.f, n_hi = 0.f;
-        if (live && f_lo < p.a_rows) { n_lo = h[f_lo] + lo; h[f_lo] = n_lo; }
-        if (live && f_hi < p.a_rows) { n_hi = h[f_hi] + hi; h[f_hi] = n_hi; }
+        if (live && f_lo < p.a_rows) { n_lo = (fetched ? pf_h_lo : h[f_lo]) + lo; h[f_lo] = n_lo; }
+        if (live && f_hi < p.a_rows) { n_hi = (fetched ? pf_h_hi : h[f_hi]) + hi; h[f_hi] = n_hi; }
         if (p.emit_w) {
           // The norm that follows: its input times its weight, and this block's share of the sum of
           // squares per token (the `per` threads of a token sit side by side in a warp).
-          if (live && f_lo < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * p.emit_w[f_lo]);
-          if (live && f_hi < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * p.emit_w[f_hi]);
+          if (live && f_lo < p.a_rows)
+            p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * (fetched ? pf_w_lo : p.emit_w[f_lo]));
+          if (live && f_hi < p.a_rows)
+            p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * (fetched ? pf_w_hi : p.emit_w[f_hi]));
           float ss = n_lo * n_lo + n_hi * n_hi;
           for (int o = per >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
           if (live && pr == 0) st_cluster_f32(tc_smem(ss_ranks + (int)rank * 64 + j), 0u, ss);

@@ -172,9 +172,9 @@ class GQAttention(Mixer):
             split_keys = self.split_keys or self._choose_split(ctx.n_decode, ctx.max_decode_kv_len, q)
             max_splits = max(1, -(-ctx.max_decode_kv_len // split_keys))
             scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(ctx.n_decode, nq, d, max_splits))
-            # The splits are merged by a second, small kernel. (Merging them in the split kernel's
-            # last block, ops.attn_decode(counters=...), measured no faster inside the step and
-            # slower at batch 1.)
+            # Up to eight splits form a thread-block cluster and merge inside the kernel; more are merged by
+            # a second, small kernel. (Merging them in the split kernel's last block,
+            # ops.attn_decode(counters=...), measured no faster inside the step and slower at batch 1.)
             ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
                             self.scale)
