@@ -184,6 +184,19 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t ran
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
+// The q|k|v epilogue's look-ups for a warp's tokens, one token per lane: the warp's i-th token is
+// rank + splits * (ewarp + 4 * i); lane i fetches its position and (for key and value heads) its page.
+__device__ __forceinline__ void qkv_fetch_tokens(const QkvRope& g, int rank, int splits, int ewarp, int lane, int n_tok,
+                                                 int t0, int head, int& pos, int& page) {
+  const int j = rank + splits * (ewarp + (TC_THREADS / 32) * lane);
+  pos = 0;
+  page = 0;
+  if (j < n_tok) {
+    pos = g.positions[t0 + j];
+    if (head >= g.n_q_heads) page = g.block_table[(size_t)g.token_req[t0 + j] * g.table_stride + pos / g.page_size];
+  }
+}
+
 // ---- the kernel ----------------------------------------------------------------------------
 // MODE 0: rows of the tile are tokens (A = x), columns features (B = W); one block per tile.
 // MODE 1: rows are features (A = W), columns tokens (B = x); gridDim.z = cluster size = k splits.
@@ -309,18 +322,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         pf = true;
       }
     } else if (p.epilogue == TC_QKV_ROPE) {
-      const QkvRope& g = p.qr;
-      const int j = (int)rank + splits * ewarp;
-      if (j < n_tok) {
-        const int t = tile_b * BN + j;
-        pf_pos = g.positions[t];
-        if (g.cos_sin && tile_a < g.n_q_heads + g.n_kv_heads) {
-          pf_cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pf_pos * 64 + lane) * 2);
-          pf_cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pf_pos * 64 + lane + 32) * 2);
-        }
-        if (tile_a >= g.n_q_heads) pf_page = g.block_table[(size_t)g.token_req[t] * g.table_stride + pf_pos / g.page_size];
-        pf = true;
+      qkv_fetch_tokens(p.qr, (int)rank, splits, ewarp, lane, n_tok, tile_b * BN, tile_a, pf_pos, pf_page);
+      if (p.qr.cos_sin && tile_a < p.qr.n_q_heads + p.qr.n_kv_heads) {   // the rotation of the warp's first token
+        const int pos0 = __shfl_sync(0xffffffffu, pf_pos, 0);
+        pf_cs0 = *reinterpret_cast<const float2*>(p.qr.cos_sin + ((size_t)pos0 * 64 + lane) * 2);
+        pf_cs1 = *reinterpret_cast<const float2*>(p.qr.cos_sin + ((size_t)pos0 * 64 + lane + 32) * 2);
       }
+      pf = true;
     }
     if (p.scale_part) {
       // While the product runs: the row scales 1/sqrt(sum of the pieces / dim + eps) of this
@@ -443,9 +451,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int head = tile_a;
       const int kind = head < g.n_q_heads ? 0 : head < g.n_q_heads + g.n_kv_heads ? 1 : 2;
       const int hidx = kind == 0 ? head : kind == 1 ? head - g.n_q_heads : head - g.n_q_heads - g.n_kv_heads;
-      bool first = true;
-      for (int j = (int)rank + splits * ewarp; j < n_tok; j += splits * (TC_THREADS / 32), first = false) {
-        const bool fetched = pf && first;
+      const bool cs_fetched = pf;
+      if (!pf) qkv_fetch_tokens(g, (int)rank, splits, ewarp, lane, n_tok, tile_b * BN, head, pf_pos, pf_page);
+      int it = 0;
+      for (int j = (int)rank + splits * ewarp; j < n_tok; j += splits * (TC_THREADS / 32), ++it) {
+        // Global loads first (they only need the position), then the sums over the cluster.
+        const int pos = __shfl_sync(0xffffffffu, pf_pos, it & 31);
+        const int page = __shfl_sync(0xffffffffu, pf_page, it & 31);
+        float2 cs0 = pf_cs0, cs1 = pf_cs1;
+        if (kind != 2 && g.cos_sin && !(cs_fetched && it == 0)) {
+          cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
+          cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
+        }
         float x[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -459,7 +476,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           x[q] = scaled ? acc * inv_s[j] : acc;
         }
         const int t = tile_b * BN + j;
-        const int pos = fetched ? pf_pos : g.positions[t];
         if (kind != 2) {
           const float* w = kind == 0 ? g.q_norm_w : g.k_norm_w;
           if (w) {
@@ -471,8 +487,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int q = 0; q < 4; ++q) x[q] *= inv * w[lane + 32 * q];
           }
           if (g.cos_sin) {
-            const float2 cs0 = fetched ? pf_cs0 : *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
-            const float2 cs1 = fetched ? pf_cs1 : *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
             const float a0 = x[0] * cs0.x - x[2] * cs0.y, b0 = x[2] * cs0.x + x[0] * cs0.y;
             const float a1 = x[1] * cs1.x - x[3] * cs1.y, b1 = x[3] * cs1.x + x[1] * cs1.y;
             x[0] = a0; x[2] = b0; x[1] = a1; x[3] = b1;
@@ -482,7 +496,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (kind == 0) {
           dst = g.q_out + (size_t)t * g.ldq + (size_t)hidx * 128;
         } else {
-          const int page = fetched ? pf_page : g.block_table[(size_t)g.token_req[t] * g.table_stride + pos / g.page_size];
           dst = g.cache + kv_tile_offset(page, hidx, kind - 1, g.n_kv_heads, g.page_size, 128) +
                 (size_t)(pos % g.page_size) * 128;
         }
@@ -496,6 +509,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool fetched = pf && base == 0;
       const int pr = idx % per, j = live ? idx / per : 0;
       const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
+      const int t = tile_b * BN + j;
+      const int f_lo = tile_a * TC_BM + i_lo, f_hi = f_lo + 64;
+      // The residual's old values (and the next norm's weight) are asked for before the sums over the
+      // cluster, so that the two latencies overlap.
+      float h_lo = 0.f, h_hi = 0.f, w_lo = 0.f, w_hi = 0.f;
+      if (p.epilogue == TC_RESIDUAL && live) {
+        const float* h = (const float*)p.out + (size_t)t * p.ldo;
+        if (f_lo < p.a_rows) {
+          h_lo = fetched ? pf_h_lo : h[f_lo];
+          if (p.emit_w) w_lo = fetched ? pf_w_lo : p.emit_w[f_lo];
+        }
+        if (f_hi < p.a_rows) {
+          h_hi = fetched ? pf_h_hi : h[f_hi];
+          if (p.emit_w) w_hi = fetched ? pf_w_hi : p.emit_w[f_hi];
+        }
+      }
       float lo = 0.f, hi = 0.f;
       if (live) {
         if (splits > 1) {
@@ -512,23 +541,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           hi *= inv_s[j];
         }
       }
-      const int t = tile_b * BN + j;
-      const int f_lo = tile_a * TC_BM + i_lo, f_hi = f_lo + 64;
       if (p.epilogue == TC_SILU_MUL) {
         const int f = tile_a * (TC_BM / 2) + i_lo;
         if (live && f < p.a_rows / 2) ((bf16*)p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_f(lo) * hi);
       } else if (p.epilogue == TC_RESIDUAL) {
         float* h = (float*)p.out + (size_t)t * p.ldo;
         float n_lo = 0.f, n_hi = 0.f;
-        if (live && f_lo < p.a_rows) { n_lo = (fetched ? pf_h_lo : h[f_lo]) + lo; h[f_lo] = n_lo; }
-        if (live && f_hi < p.a_rows) { n_hi = (fetched ? pf_h_hi : h[f_hi]) + hi; h[f_hi] = n_hi; }
+        if (live && f_lo < p.a_rows) { n_lo = h_lo + lo; h[f_lo] = n_lo; }
+        if (live && f_hi < p.a_rows) { n_hi = h_hi + hi; h[f_hi] = n_hi; }
         if (p.emit_w) {
           // The norm that follows: its input times its weight, and this block's share of the sum of
           // squares per token (the `per` threads of a token sit side by side in a warp).
-          if (live && f_lo < p.a_rows)
-            p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * (fetched ? pf_w_lo : p.emit_w[f_lo]));
-          if (live && f_hi < p.a_rows)
-            p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * (fetched ? pf_w_hi : p.emit_w[f_hi]));
+          if (live && f_lo < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * w_lo);
+          if (live && f_hi < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * w_hi);
           float ss = n_lo * n_lo + n_hi * n_hi;
           for (int o = per >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
           if (live && pr == 0) st_cluster_f32(tc_smem(ss_ranks + (int)rank * 64 + j), 0u, ss);
