@@ -411,6 +411,50 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   return llmrs_launch_status("attn_decode_split_mma");
 }
 
+template <int DCH>
+static int decode_mma_capacity(int cluster, int* blocks) {
+  constexpr int D = 16 * DCH;
+  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
+  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16 + 16 * (D + 2)) * sizeof(float);
+  const size_t smem = pipe > merge ? pipe : merge;
+  cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem);
+  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(64, 8, cluster);
+  cfg.blockDim = dim3(DM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = cluster;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  e = cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH>, &cfg);
+  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: occupancy of clusters of %d: %s", cluster, cudaGetErrorString(e));
+  *blocks = n * cluster;
+  return 0;
+}
+
+// How many blocks of the tensor-core decode kernel the device holds at a time when they come in clusters
+// of `cluster` (1 to 8): what the caller needs to cut the keys so that a step's blocks fill whole waves.
+LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int* blocks) {
+  if (cluster < 1 || cluster > 8 || d % 16 || d < 16 || d > 128)
+    return llmrs_fail("attn_decode_capacity: head_dim %d, clusters of %d", d, cluster);
+  switch (d / 16) {
+    case 1: return decode_mma_capacity<1>(cluster, blocks);
+    case 2: return decode_mma_capacity<2>(cluster, blocks);
+    case 3: return decode_mma_capacity<3>(cluster, blocks);
+    case 4: return decode_mma_capacity<4>(cluster, blocks);
+    case 5: return decode_mma_capacity<5>(cluster, blocks);
+    case 6: return decode_mma_capacity<6>(cluster, blocks);
+    case 7: return decode_mma_capacity<7>(cluster, blocks);
+    default: return decode_mma_capacity<8>(cluster, blocks);
+  }
+}
+
 // The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).
 // Writes the same per-split records as the generic split kernel. With `counters` (zeroed ints, one per
 // request and head group; the kernel leaves them zero) the last block of each group also merges the

@@ -220,6 +220,20 @@ def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_sp
     return int(_lib_ll("llmrs_attn_decode_scratch_floats")(n_dec, n_q_heads, head_dim, max_splits))
 
 
+_decode_capacity = {}
+
+
+def attn_decode_capacity(head_dim: int, cluster: int, device=None) -> int:
+    """Blocks of the tensor-core decode attention kernel that the device holds at a time when they come in
+    thread-block clusters of ``cluster`` (1 to 8)."""
+    key = (head_dim, cluster, device)
+    if key not in _decode_capacity:
+        blocks = ctypes.c_int()
+        _check(_lib().llmrs_attn_decode_capacity(head_dim, cluster, ctypes.byref(blocks)), "attn_decode_capacity", launches=0)
+        _decode_capacity[key] = blocks.value
+    return _decode_capacity[key]
+
+
 def _lib_ll(name: str):
     fn = getattr(_lib(), name)
     fn.restype = ctypes.c_longlong

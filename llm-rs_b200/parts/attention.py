@@ -22,6 +22,11 @@ _ATTN_TC = os.environ.get("LLMRS_ATTN_TC", "1") != "0"
 _FUSE_QKV_ROPE = os.environ.get("LLMRS_FUSE_QKV_ROPE", "1") != "0"
 
 
+# A decode attention block's fixed cost (start, merge of its warps and of the cluster) in keys' worth of
+# streaming; see GQAttention._choose_split.
+FIXED_KEYS = 192
+
+
 def _sm_count(device) -> int:
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
@@ -111,21 +116,34 @@ class GQAttention(Mixer):
         return self.position.rotary_dim == 128 and cos_sin.dtype == torch.float32
 
     def _choose_split(self, n_decode: int, max_kv_len: int, q: torch.Tensor) -> int:
-        """Keys per split of decode attention: long enough that a block streams many tiles,
-        short enough that the step's blocks fill the GPU about once. The choice changes
-        results by rounding only (every split is merged in float32)."""
+        """Keys per split of decode attention. The choice changes results by rounding only (every split is
+        merged in float32)."""
         sms = _sm_count(q.device)
         groups = self.n_kv_heads * (-(-(self.n_heads // self.n_kv_heads) // 16))
-        splits = max(1, (2 * sms) // max(1, n_decode * groups))
-        if splits > 8 and q.dtype == torch.bfloat16 and self.head_dim <= 128:
-            # Up to eight splits merge inside the kernel (as a cluster), which beats more, shorter splits
-            # followed by a second kernel as long as a split stays short.
-            keys8 = -(-(-(-max(max_kv_len, 1) // 8)) // 64) * 64
-            if keys8 <= 1024:
-                return max(keys8, 128)
-        keys = -(-max(max_kv_len, 1) // splits)
-        keys = -(-keys // 64) * 64
-        return min(max(keys, 128), 1024 if q.dtype == torch.float32 or self.head_dim > 128 else 2048)
+        units = max(1, n_decode * groups)
+        length = max(max_kv_len, 1)
+        if q.dtype != torch.bfloat16 or self.head_dim > 128:
+            # The generic kernel: enough blocks to fill the GPU about twice.
+            keys = -(-length // max(1, (2 * sms) // units))
+            return min(max(-(-keys // 64) * 64, 128), 1024)
+        # The tensor-core kernel. Up to 8 splits merge inside the kernel as a thread-block cluster, and the
+        # cluster's size decides how many blocks the device holds at a time (284 in clusters of 4, 264 in
+        # clusters of 8, ...). A step whose blocks need a second wave that stays nearly empty loses more than
+        # longer splits cost, so: the cut with the least waves x (keys per split + a block's fixed cost).
+        best_keys, best_cost = 0, None
+        for splits in range(1, 9):
+            keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
+            real = -(-length // keys)
+            # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
+            held = int(0.95 * ops.attn_decode_capacity(self.head_dim, real, q.device))
+            cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
+            if best_cost is None or cost < best_cost:
+                best_keys, best_cost, best_real = keys, cost, real
+        if best_real == 8 and best_keys > 1024 and 16 * units <= ops.attn_decode_capacity(self.head_dim, 1, q.device):
+            # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
+            splits = min(64, ops.attn_decode_capacity(self.head_dim, 1, q.device) // units)
+            return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)
+        return best_keys
 
     def takes_prenormed(self, n_tokens: int) -> bool:
         return self.qkv_proj.takes_prenormed(n_tokens) and self.q_proj.takes_prenormed(n_tokens)
