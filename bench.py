@@ -230,6 +230,8 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the timed prompt (the contract's figure is the default, 2,048)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself "
                     "(for a profiler's launch list)")
@@ -272,7 +274,7 @@ def main():
     page = 16
     ctx = args.context
     max_batch = args.batch if args.no_points else max(args.batch, 64)
-    pool_tokens = max_batch * (ctx + 64) + PREFILL_TOKENS + 64
+    pool_tokens = max_batch * (ctx + 64) + args.prefill_tokens + 64
     t0 = time.time()
     tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=2, sigma=0.02, dtype=torch.bfloat16,
                              device="cuda:0")
@@ -374,20 +376,21 @@ def main():
 
     if not args.no_prefill:
         try:
-            prompt = rng.integers(0, V, PREFILL_TOKENS).tolist()
+            n_prompt = args.prefill_tokens
+            prompt = rng.integers(0, V, n_prompt).tolist()
             times = []
             for it in range(4):
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
-                runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+                runner.step([StepEntry("p", prompt, [n_prompt - 1])])
                 end.record()
                 torch.cuda.synchronize()
                 runner.release("p")
                 if it >= 1:
                     times.append(start.elapsed_time(end))
             pms = statistics.median(times)
-            fl = prefill_flops(raw, args.layers, PREFILL_TOKENS)
-            result["prefill"] = {"value": round(PREFILL_TOKENS / (pms / 1e3), 1), "tokens": PREFILL_TOKENS,
+            fl = prefill_flops(raw, args.layers, n_prompt)
+            result["prefill"] = {"value": round(n_prompt / (pms / 1e3), 1), "tokens": n_prompt,
                                  "ms": round(pms, 3),
                                  "frac": round(fl / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
         except Exception as e:
