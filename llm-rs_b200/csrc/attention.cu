@@ -462,7 +462,7 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
                                    block_table, table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads,
                                    d, page_size, window, scale, stream);
   if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only && scale > 0.f) {
-    if (counters == nullptr && max_splits <= 8)   // the splits merge inside the kernel, as a cluster
+    if (counters == nullptr && max_splits <= 16)  // the splits merge inside the kernel, as a cluster
       return llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
                                          table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
                                          page_size, window, scale, out, out_stride, nullptr, 1, stream);

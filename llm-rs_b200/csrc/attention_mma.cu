@@ -378,6 +378,9 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
     cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    // Clusters of up to 16 blocks (more than the portable 8) for few requests.
+    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
     configured = smem;
   }
   const int G = n_q_heads / n_kv_heads;
@@ -420,6 +423,8 @@ static int decode_mma_capacity(int cluster, int* blocks) {
   cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+  e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(64, 8, cluster);
   cfg.blockDim = dim3(DM_THREADS);
@@ -439,9 +444,9 @@ static int decode_mma_capacity(int cluster, int* blocks) {
 }
 
 // How many blocks of the tensor-core decode kernel the device holds at a time when they come in clusters
-// of `cluster` (1 to 8): what the caller needs to cut the keys so that a step's blocks fill whole waves.
+// of `cluster` (1 to 16): what the caller needs to cut the keys so that a step's blocks fill whole waves.
 LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int* blocks) {
-  if (cluster < 1 || cluster > 8 || d % 16 || d < 16 || d > 128)
+  if (cluster < 1 || cluster > 16 || d % 16 || d < 16 || d > 128)
     return llmrs_fail("attn_decode_capacity: head_dim %d, clusters of %d", d, cluster);
   switch (d / 16) {
     case 1: return decode_mma_capacity<1>(cluster, blocks);
@@ -458,15 +463,15 @@ LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int* blocks) {
 // The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).
 // Writes the same per-split records as the generic split kernel. With `counters` (zeroed ints, one per
 // request and head group; the kernel leaves them zero) the last block of each group also merges the
-// splits into `out`; with `cluster_merge` (max_splits <= 8) the splits of a group run as one cluster and
+// splits into `out`; with `cluster_merge` (max_splits <= 16) the splits of a group run as one cluster and
 // merge through distributed shared memory; else the caller runs the combine kernel.
 int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
                                 int page_size, int window, float scale, void* out, long long out_stride,
                                 int* counters, int cluster_merge, cudaStream_t stream) {
-  if (cluster_merge && (max_splits < 1 || max_splits > 8))
-    return llmrs_fail("attn_decode_mma: a cluster merges at most 8 splits, got %d", max_splits);
+  if (cluster_merge && (max_splits < 1 || max_splits > 16))
+    return llmrs_fail("attn_decode_mma: a cluster merges at most 16 splits, got %d", max_splits);
 #define LLMRS_DM_CASE(N)                                                                                          \
   case N:                                                                                                          \
     return launch_decode_mma<N>(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table, table_stride, \

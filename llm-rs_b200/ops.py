@@ -225,7 +225,7 @@ _decode_capacity = {}
 
 def attn_decode_capacity(head_dim: int, cluster: int, device=None) -> int:
     """Blocks of the tensor-core decode attention kernel that the device holds at a time when they come in
-    thread-block clusters of ``cluster`` (1 to 8)."""
+    thread-block clusters of ``cluster`` (1 to 16)."""
     key = (head_dim, cluster, device)
     if key not in _decode_capacity:
         blocks = ctypes.c_int()
@@ -246,7 +246,7 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
                 window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
     """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
     the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace of
-    ``attn_decode_scratch_floats`` elements. (bfloat16 with head_dim <= 128 and at most 8 splits: the splits
+    ``attn_decode_scratch_floats`` elements. (bfloat16 with head_dim <= 128 and at most 16 splits: the splits
     of a request and key head run as one thread-block cluster and merge through distributed shared memory,
     one kernel; else a second kernel merges them.) With ``counters`` (int32, at least n_dec * n_q_heads,
     all zero; the call leaves them zero) the tensor-core kernel merges the splits itself instead
@@ -270,7 +270,7 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
         _ptr(cache), _ptr(dec_reqs), n_dec, _ptr(q_start), _ptr(cached_len), _ptr(block_table), block_table.size(1),
         _ptr(scratch), _ptr(counters), max_splits, split_keys, n_q_heads, n_kv_heads, head_dim, page_size, window,
         ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attn_decode",
-        launches=1 if counters is not None or (q.dtype == torch.bfloat16 and head_dim <= 128 and max_splits <= 8
+        launches=1 if counters is not None or (q.dtype == torch.bfloat16 and head_dim <= 128 and max_splits <= 16
                                                and not _generic_only) else 2)
 
 

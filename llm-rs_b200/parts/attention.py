@@ -25,6 +25,8 @@ _FUSE_QKV_ROPE = os.environ.get("LLMRS_FUSE_QKV_ROPE", "1") != "0"
 # A decode attention block's fixed cost (start, merge of its warps and of the cluster) in keys' worth of
 # streaming; see GQAttention._choose_split.
 FIXED_KEYS = 192
+CAPACITY_USED = 0.975   # of the blocks the device holds: 256 of 264 ran in one wave, 280 of 280 did not
+MAX_CLUSTER = 16     # splits that the kernel merges itself
 
 
 def _sm_count(device) -> int:
@@ -126,20 +128,20 @@ class GQAttention(Mixer):
             # The generic kernel: enough blocks to fill the GPU about twice.
             keys = -(-length // max(1, (2 * sms) // units))
             return min(max(-(-keys // 64) * 64, 128), 1024)
-        # The tensor-core kernel. Up to 8 splits merge inside the kernel as a thread-block cluster, and the
+        # The tensor-core kernel. Up to 16 splits merge inside the kernel as a thread-block cluster, and the
         # cluster's size decides how many blocks the device holds at a time (284 in clusters of 4, 264 in
         # clusters of 8, ...). A step whose blocks need a second wave that stays nearly empty loses more than
         # longer splits cost, so: the cut with the least waves x (keys per split + a block's fixed cost).
         best_keys, best_cost = 0, None
-        for splits in range(1, 9):
+        for splits in range(1, MAX_CLUSTER + 1):
             keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
             real = -(-length // keys)
             # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
-            held = int(0.95 * ops.attn_decode_capacity(self.head_dim, real, q.device))
+            held = int(CAPACITY_USED * ops.attn_decode_capacity(self.head_dim, real, q.device))
             cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
             if best_cost is None or cost < best_cost:
                 best_keys, best_cost, best_real = keys, cost, real
-        if best_real == 8 and best_keys > 1024 and 16 * units <= ops.attn_decode_capacity(self.head_dim, 1, q.device):
+        if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= ops.attn_decode_capacity(self.head_dim, 1, q.device):
             # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
             splits = min(64, ops.attn_decode_capacity(self.head_dim, 1, q.device) // units)
             return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)

@@ -291,33 +291,33 @@ def test_part_rotary_table():
 
 
 def test_decode_attention_split_choice():
-    """The cut of the keys for decode attention: multiples of 64 keys, and among the cuts of up to 8 splits
+    """The cut of the keys for decode attention: multiples of 64 keys, and among the cuts of up to 16 splits
     (which the kernel's cluster merges) the one with the least waves x (keys + fixed cost), waves counted
-    against what the device really holds in clusters of that size; more than 8 splits only for few requests
+    against what the device really holds in clusters of that size; more splits only for few requests
     with long contexts."""
     from llm_rs_b200 import ops
     from llm_rs_b200.parts import PartSpec, build
-    from llm_rs_b200.parts.attention import FIXED_KEYS
+    from llm_rs_b200.parts.attention import CAPACITY_USED, FIXED_KEYS, MAX_CLUSTER
     att = build("mixer", PartSpec("gqa_attention", {
         "hidden_size": 1024, "n_heads": 32, "n_kv_heads": 8, "head_dim": 128,
         "position": PartSpec("none", {"head_dim": 128})}))
     q = torch.empty(1, 1, dtype=torch.bfloat16, device=DEV)
-    held = {s: int(0.95 * ops.attn_decode_capacity(128, s, DEV)) for s in range(1, 9)}
-    assert all(148 <= held[s] <= 2 * 148 for s in held)
+    held = {s: int(CAPACITY_USED * ops.attn_decode_capacity(128, s, DEV)) for s in range(1, MAX_CLUSTER + 1)}
+    assert all(128 <= held[s] <= 2 * 148 for s in held)
     for length in (100, 4096, 5000, 32768):
         for n in range(1, 41):
             keys = att._choose_split(n, length, q)
             splits = -(-length // keys)
             assert keys % 64 == 0 and keys >= 128
             costs = {}
-            for s in range(1, 9):
+            for s in range(1, MAX_CLUSTER + 1):
                 k = max(-(-(-(-length // s)) // 64) * 64, 128)
                 real = -(-length // k)
                 costs.setdefault(real, -(-(real * n * 8) // held[real]) * (k + FIXED_KEYS))
-            if splits <= 8:
+            if splits <= MAX_CLUSTER:
                 assert costs[splits] == min(costs.values()), (length, n, keys, costs)
             else:
-                assert n * 8 * 16 <= ops.attn_decode_capacity(128, 1, DEV) and length > 8 * 1024, (length, n, keys)
+                assert n * 8 * 2 * MAX_CLUSTER <= ops.attn_decode_capacity(128, 1, DEV) and length > MAX_CLUSTER * 1024, (length, n, keys)
 
 
 # -- run order: a layer named twice, a layer that reads another's cache ----------------------------
