@@ -41,7 +41,30 @@ __device__ __forceinline__ float dm_ld_cluster(uint32_t local_addr, uint32_t ran
   return v;
 }
 
+__device__ __forceinline__ void dm_st_cluster(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+__device__ __forceinline__ void dm_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void dm_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_STAGES = 3, DM_TILE = 16;
+
+// Shared memory of the decode kernel: the warps' rings of tiles (re-used for their merge), and behind them,
+// when the splits merge as a cluster, what the other blocks send: per sender the maximum and the sum of each
+// of the ng heads, and this block's share of the ng * d outputs (dealt out in runs of 32 over the blocks).
+__host__ __device__ constexpr size_t dm_ring_bytes(int d) {
+  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (d + 8) * 2;
+  const size_t merge = (size_t)(DM_WARPS * 16 * d + 2 * DM_WARPS * 16 + 16 * (d + 2)) * 4;
+  return ((pipe > merge ? pipe : merge) + 15) / 16 * 16;
+}
+__host__ __device__ inline int dm_share(int ng, int d, int splits) {   // outputs a block merges, a multiple of 32
+  return (ng * d + 32 * splits - 1) / (32 * splits) * 32;
+}
+__host__ __device__ inline size_t dm_inbox_bytes(int ng, int d, int splits) {
+  return (size_t)splits * (2 * ng + dm_share(ng, d, splits)) * 4;
+}
 
 template <int DCH>
 __global__ void __launch_bounds__(DM_THREADS)
@@ -58,6 +81,9 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   constexpr int TILE_ELEMS = DM_TILE * ROW;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_launch_dependents();
+  // A block may write into another's shared memory only once that block runs: every block of the cluster
+  // says so here, and waits for the others just before its first such write.
+  if (cluster_merge) dm_cluster_arrive();
   // Up to the wait below only data of earlier steps is read: the step's index arrays and
   // cached keys and values other than the newest position (the only one written in this step).
 
@@ -278,6 +304,11 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     Lm[warp * 16 + gq] = l_row[0]; Lm[warp * 16 + gq + 8] = l_row[1];
   }
   __syncthreads();
+  const int S = (int)gridDim.z;
+  const int share = dm_share(ng, D, S);
+  float* inbox_ml = reinterpret_cast<float*>(smem_raw + dm_ring_bytes(D));   // [S][ng][2]
+  float* inbox_o = inbox_ml + (size_t)S * ng * 2;                            // [S][share]
+  if (cluster_merge) dm_cluster_wait();   // every block of the cluster runs
   for (int i = threadIdx.x; i < ng * D; i += DM_THREADS) {
     const int g = i / D, e = i - g * D;
     float M = -INFINITY;
@@ -293,9 +324,18 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     }
     const int head = kvh * G + g0 + g;
     if (cluster_merge) {
-      float* cp = Lm + DM_WARPS * 16 + (size_t)g * (D + 2);     // this block's record of head g, for the cluster
-      cp[2 + e] = acc;
-      if (e == 0) { cp[0] = M; cp[1] = L; }
+      // The splits of a (request, key head) are the blocks of one cluster. Output i goes to the block that
+      // merges it (runs of 32 outputs go round the blocks), each head's maximum and sum to all of them.
+      const int run = i >> 5;
+      dm_st_cluster((uint32_t)__cvta_generic_to_shared(inbox_o + (size_t)split * share + (run / S) * 32 + (i & 31)),
+                    (uint32_t)(run % S), acc);
+      if (e == 0) {
+        const uint32_t ml = (uint32_t)__cvta_generic_to_shared(inbox_ml + ((size_t)split * ng + g) * 2);
+        for (int r = 0; r < S; ++r) {
+          dm_st_cluster(ml, (uint32_t)r, M);
+          dm_st_cluster(ml + 4, (uint32_t)r, L);
+        }
+      }
       continue;
     }
     float* pp = part + ((size_t)((size_t)di * n_q_heads + head) * max_splits + split) * (D + 2);
@@ -304,28 +344,26 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     if (e == 0) { pp[0] = M / LOG2E; pp[1] = L; }
   }
   if (cluster_merge) {
-    // The splits of a (request, key head) are the blocks of one cluster: each leaves its record in its
-    // shared memory, and after the cluster's barrier the blocks share the merge among themselves,
-    // reading the others' records through distributed shared memory. No pass through global memory, no
-    // second kernel.
-    const int S = (int)gridDim.z;
-    const uint32_t cp_addr = (uint32_t)__cvta_generic_to_shared(Lm + DM_WARPS * 16);
-    dm_cluster_sync();
-    for (int i = split * DM_THREADS + (int)threadIdx.x; i < ng * D; i += S * DM_THREADS) {
+    // After the cluster's barrier every block holds what the others sent it and merges its share: no pass
+    // through global memory, no second kernel, and nobody reads another block's memory, so a block may
+    // leave as soon as it is done.
+    dm_cluster_arrive();
+    dm_cluster_wait();
+    for (int s = (int)threadIdx.x; s < share; s += DM_THREADS) {
+      const int i = ((s >> 5) * S + split) * 32 + (s & 31);
+      if (i >= ng * D) continue;
       const int g = i / D, e = i - g * D;
-      const uint32_t rec = cp_addr + (uint32_t)(g * (D + 2)) * 4;
       float M = -INFINITY;
-      for (int r = 0; r < S; ++r) M = fmaxf(M, dm_ld_cluster(rec, (uint32_t)r));
+      for (int r = 0; r < S; ++r) M = fmaxf(M, inbox_ml[((size_t)r * ng + g) * 2]);
       float L = 0.f, a = 0.f;
       for (int r = 0; r < S; ++r) {
-        const float mr = dm_ld_cluster(rec, (uint32_t)r);
+        const float mr = inbox_ml[((size_t)r * ng + g) * 2];
         const float f = mr == -INFINITY ? 0.f : ex2(mr - M);
-        L += dm_ld_cluster(rec + 4, (uint32_t)r) * f;
-        a += dm_ld_cluster(rec + (uint32_t)(2 + e) * 4, (uint32_t)r) * f;
+        L += inbox_ml[((size_t)r * ng + g) * 2 + 1] * f;
+        a += inbox_o[(size_t)r * share + s] * f;
       }
       out[(size_t)q_start[req] * out_stride + (size_t)(kvh * G + g0 + g) * D + e] = __float2bfloat16_rn(a / L);
     }
-    dm_cluster_sync();   // nobody leaves while another block still reads its record
     return;
   }
   if (counters == nullptr) return;   // a separate kernel merges the splits
@@ -370,9 +408,8 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
                              int page_size, int window, float scale, void* out, long long out_stride, int* counters,
                              int cluster_merge, cudaStream_t stream) {
   constexpr int D = 16 * DCH;
-  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
-  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16 + 16 * (D + 2)) * sizeof(float);
-  const size_t smem = pipe > merge ? pipe : merge;
+  const int ng_max = n_q_heads / n_kv_heads < 16 ? n_q_heads / n_kv_heads : 16;
+  const size_t smem = dm_ring_bytes(D) + (cluster_merge ? dm_inbox_bytes(ng_max, D, max_splits) : 0);
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
@@ -415,11 +452,9 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
 }
 
 template <int DCH>
-static int decode_mma_capacity(int cluster, int* blocks) {
+static int decode_mma_capacity(int cluster, int ng, int* blocks) {
   constexpr int D = 16 * DCH;
-  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (D + 8) * sizeof(bf16);
-  const size_t merge = (size_t)(DM_WARPS * 16 * D + 2 * DM_WARPS * 16 + 16 * (D + 2)) * sizeof(float);
-  const size_t smem = pipe > merge ? pipe : merge;
+  const size_t smem = dm_ring_bytes(D) + (cluster > 1 ? dm_inbox_bytes(ng, D, cluster) : 0);
   cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem);
   if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
@@ -444,19 +479,20 @@ static int decode_mma_capacity(int cluster, int* blocks) {
 }
 
 // How many blocks of the tensor-core decode kernel the device holds at a time when they come in clusters
-// of `cluster` (1 to 16): what the caller needs to cut the keys so that a step's blocks fill whole waves.
-LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int* blocks) {
-  if (cluster < 1 || cluster > 16 || d % 16 || d < 16 || d > 128)
-    return llmrs_fail("attn_decode_capacity: head_dim %d, clusters of %d", d, cluster);
+// of `cluster` (1 to 16) and serve `ng` query heads (1 to 16) per key head: what the caller needs to cut the
+// keys so that a step's blocks fill whole waves.
+LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int ng, int* blocks) {
+  if (cluster < 1 || cluster > 16 || ng < 1 || ng > 16 || d % 16 || d < 16 || d > 128)
+    return llmrs_fail("attn_decode_capacity: head_dim %d, clusters of %d, %d heads", d, cluster, ng);
   switch (d / 16) {
-    case 1: return decode_mma_capacity<1>(cluster, blocks);
-    case 2: return decode_mma_capacity<2>(cluster, blocks);
-    case 3: return decode_mma_capacity<3>(cluster, blocks);
-    case 4: return decode_mma_capacity<4>(cluster, blocks);
-    case 5: return decode_mma_capacity<5>(cluster, blocks);
-    case 6: return decode_mma_capacity<6>(cluster, blocks);
-    case 7: return decode_mma_capacity<7>(cluster, blocks);
-    default: return decode_mma_capacity<8>(cluster, blocks);
+    case 1: return decode_mma_capacity<1>(cluster, ng, blocks);
+    case 2: return decode_mma_capacity<2>(cluster, ng, blocks);
+    case 3: return decode_mma_capacity<3>(cluster, ng, blocks);
+    case 4: return decode_mma_capacity<4>(cluster, ng, blocks);
+    case 5: return decode_mma_capacity<5>(cluster, ng, blocks);
+    case 6: return decode_mma_capacity<6>(cluster, ng, blocks);
+    case 7: return decode_mma_capacity<7>(cluster, ng, blocks);
+    default: return decode_mma_capacity<8>(cluster, ng, blocks);
   }
 }
 

@@ -223,13 +223,14 @@ def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_sp
 _decode_capacity = {}
 
 
-def attn_decode_capacity(head_dim: int, cluster: int, device=None) -> int:
+def attn_decode_capacity(head_dim: int, cluster: int, heads: int = 4, device=None) -> int:
     """Blocks of the tensor-core decode attention kernel that the device holds at a time when they come in
-    thread-block clusters of ``cluster`` (1 to 16)."""
-    key = (head_dim, cluster, device)
+    thread-block clusters of ``cluster`` (1 to 16) and serve ``heads`` query heads per key head (at most 16)."""
+    key = (head_dim, cluster, heads, device)
     if key not in _decode_capacity:
         blocks = ctypes.c_int()
-        _check(_lib().llmrs_attn_decode_capacity(head_dim, cluster, ctypes.byref(blocks)), "attn_decode_capacity", launches=0)
+        _check(_lib().llmrs_attn_decode_capacity(head_dim, cluster, heads, ctypes.byref(blocks)), "attn_decode_capacity",
+               launches=0)
         _decode_capacity[key] = blocks.value
     return _decode_capacity[key]
 

@@ -123,6 +123,7 @@ class GQAttention(Mixer):
         sms = _sm_count(q.device)
         groups = self.n_kv_heads * (-(-(self.n_heads // self.n_kv_heads) // 16))
         units = max(1, n_decode * groups)
+        heads = min(16, self.n_heads // self.n_kv_heads)
         length = max(max_kv_len, 1)
         if q.dtype != torch.bfloat16 or self.head_dim > 128:
             # The generic kernel: enough blocks to fill the GPU about twice.
@@ -137,13 +138,13 @@ class GQAttention(Mixer):
             keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
             real = -(-length // keys)
             # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
-            held = int(CAPACITY_USED * ops.attn_decode_capacity(self.head_dim, real, q.device))
+            held = int(CAPACITY_USED * ops.attn_decode_capacity(self.head_dim, real, heads, q.device))
             cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
             if best_cost is None or cost < best_cost:
                 best_keys, best_cost, best_real = keys, cost, real
-        if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= ops.attn_decode_capacity(self.head_dim, 1, q.device):
+        if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= ops.attn_decode_capacity(self.head_dim, 1, heads, q.device):
             # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
-            splits = min(64, ops.attn_decode_capacity(self.head_dim, 1, q.device) // units)
+            splits = min(64, ops.attn_decode_capacity(self.head_dim, 1, heads, q.device) // units)
             return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)
         return best_keys
 

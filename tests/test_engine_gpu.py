@@ -302,7 +302,7 @@ def test_decode_attention_split_choice():
         "hidden_size": 1024, "n_heads": 32, "n_kv_heads": 8, "head_dim": 128,
         "position": PartSpec("none", {"head_dim": 128})}))
     q = torch.empty(1, 1, dtype=torch.bfloat16, device=DEV)
-    held = {s: int(CAPACITY_USED * ops.attn_decode_capacity(128, s, DEV)) for s in range(1, MAX_CLUSTER + 1)}
+    held = {s: int(CAPACITY_USED * ops.attn_decode_capacity(128, s, 4, DEV)) for s in range(1, MAX_CLUSTER + 1)}
     assert all(128 <= held[s] <= 2 * 148 for s in held)
     for length in (100, 4096, 5000, 32768):
         for n in range(1, 41):
@@ -317,7 +317,7 @@ def test_decode_attention_split_choice():
             if splits <= MAX_CLUSTER:
                 assert costs[splits] == min(costs.values()), (length, n, keys, costs)
             else:
-                assert n * 8 * 2 * MAX_CLUSTER <= ops.attn_decode_capacity(128, 1, DEV) and length > MAX_CLUSTER * 1024, (length, n, keys)
+                assert n * 8 * 2 * MAX_CLUSTER <= ops.attn_decode_capacity(128, 1, 4, DEV) and length > MAX_CLUSTER * 1024, (length, n, keys)
 
 
 # -- run order: a layer named twice, a layer that reads another's cache ----------------------------

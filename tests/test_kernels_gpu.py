@@ -244,6 +244,25 @@ def test_attention_prefill_and_decode(nq, nkv, d, page, window, dtype, impl):
                           f"first at {bad.nonzero()[0].tolist()}"
 
 
+@pytest.mark.parametrize("nq,nkv,d,split_keys,lens", [
+    (16, 1, 128, 64, [1000, 517, 30, 0]),      # 16 heads per key head, 16 splits: the largest merge in shared memory
+    (32, 8, 128, 128, [2000, 1, 640]),        # 16 splits of 128 keys
+    (12, 4, 64, 64, [575, 300]),              # 9 splits, three heads per key head
+    (40, 2, 32, 64, [830, 831, 832])])        # 13 splits, two groups of heads per key head (16 and 4)
+def test_decode_attention_merged_by_large_clusters(nq, nkv, d, split_keys, lens):
+    """Single new tokens whose keys are cut into 9 to 16 splits that merge inside the kernel (clusters beyond
+    the portable 8 blocks), some of them empty for the shorter requests."""
+    new = [1] * len(lens)
+    torch.manual_seed(nq + d)
+    table, cache = _paged_setup(lens, new, nkv, d, 16, torch.bfloat16, seed=3)
+    q = (torch.randn(len(lens), nq * d) * 1.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    assert 8 < -(-(max(lens) + 1) // split_keys) <= 16
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, 16, 0, scale)
+    got = _run_attention(q, cache, table, lens, new, nq, nkv, d, 16, 0, scale, split_keys=split_keys, fused_merge=False)
+    assert torch.allclose(got, want, atol=2.5e-2, rtol=2e-2), float((got - want).abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 257, 1000, 1999])
 def test_one_far_key_among_thousands(dtype, far):
