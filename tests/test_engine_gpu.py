@@ -231,6 +231,35 @@ def test_norms_spread_over_products_in_small_steps(models, monkeypatch):
     assert np.abs(got[True] - got[False]).max() < 0.02 * scale
 
 
+@pytest.mark.parametrize("hidden,heads,kv_heads,inter", [(2048, 16, 8, 6144), (2560, 32, 8, 9728), (5120, 40, 8, 17408)])
+def test_layer_sizes_of_the_family_bf16_against_float32(hidden, heads, kv_heads, inter):
+    """Two layers at the layer sizes of larger models of the family (heads of 128, widths that are no power
+    of two): the bfloat16 engine, which takes its tcgen05 kernels with all their fused epilogues there, against
+    the float32 engine on the same weights; prompts of three lengths in one step, then decode steps."""
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel
+    from llm_rs_b200.weights import random_tensors
+    raw = dict(TINY_B, num_hidden_layers=2, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv_heads,
+               head_dim=128, intermediate_size=inter, vocab_size=8000, max_position_embeddings=2048, eos_token_id=1)
+    spec = build_spec(Qwen3Config.from_dict(raw))
+    t16 = random_tensors(DecoderModel(spec).weight_specs(), seed=5, sigma=0.02, dtype=torch.bfloat16, device=DEV)
+    rng = np.random.default_rng(hidden)
+    prompts = [rng.integers(0, 8000, n).tolist() for n in (100, 37, 300)]
+    later = rng.integers(0, 8000, (10, 3)).tolist()
+    outs = []
+    for dtype, tensors in ((torch.bfloat16, t16), (torch.float32, {k: v.float() for k, v in t16.items()})):
+        runner = ModelRunner(spec, tensors, dtype, DEV, max_tokens=1024, page_size=16, max_requests=4)
+        rows = [runner.step([StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)]).float().cpu()]
+        for s in range(10):
+            rows.append(runner.step([StepEntry(i, [later[s][i]], [0]) for i in range(3)]).float().cpu())
+        outs.append(torch.cat(rows))
+        del runner
+    diff, scale = float((outs[0] - outs[1]).abs().max()), float(outs[1].abs().max())
+    assert diff < 0.03 * scale, (diff, scale)
+
+
 # -- weights stored in 32-bit --------------------------------------------------------------------
 def test_tensors_stored_in_32_bit_stay_32_bit(folder):
     """A folder whose matrices are float32: the bfloat16 engine keeps them (its products then
