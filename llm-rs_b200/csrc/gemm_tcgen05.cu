@@ -182,6 +182,18 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t ran
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
+// Sum over the cluster's blocks, in rank order, of the float at `local_addr` in each block's shared memory.
+// All loads are issued before the first is used: one round trip through the cluster instead of one per block.
+__device__ __forceinline__ float cluster_sum_f32(uint32_t local_addr, int splits) {
+  float v[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_cluster_f32(local_addr, (uint32_t)r) : 0.f;
+  float acc = 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r) acc += v[r];
+  return acc;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 
 // The q|k|v epilogue's look-ups for a warp's tokens, one token per lane: the warp's i-th token is
@@ -469,7 +481,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           const int f = lane + 32 * q;
           float acc = 0.f;
           if (splits > 1) {
-            for (int r = 0; r < splits; ++r) acc += ld_cluster_f32(red_addr + (uint32_t)(f * RS + j) * 4, (uint32_t)r);
+            acc = cluster_sum_f32(red_addr + (uint32_t)(f * RS + j) * 4, splits);
           } else {
             acc = red[f * RS + j];
           }
@@ -528,10 +540,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       float lo = 0.f, hi = 0.f;
       if (live) {
         if (splits > 1) {
-          for (int r = 0; r < splits; ++r) {
-            lo += ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r);
-            hi += ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r);
+          float vlo[8], vhi[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {   // all loads first: one round trip through the cluster, not one per block
+            vlo[r] = r < splits ? ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r) : 0.f;
+            vhi[r] = r < splits ? ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r) : 0.f;
           }
+#pragma unroll
+          for (int r = 0; r < 8; ++r) { lo += vlo[r]; hi += vhi[r]; }
         } else {
           lo = red[i_lo * RS + j];
           hi = red[i_hi * RS + j];
