@@ -29,6 +29,31 @@ CAPACITY_USED = 0.975   # of the blocks the device holds: 256 of 264 ran in one 
 MAX_CLUSTER = 16     # splits that the kernel merges itself
 
 
+def cut_keys(length: int, units: int, capacity) -> int:
+    """Keys per split for the tensor-core decode attention kernel: ``length`` keys at most per request,
+    ``units`` (request, key head group) pairs, ``capacity(cluster)`` the blocks the device holds at a time in
+    thread-block clusters of that size.
+
+    Up to ``MAX_CLUSTER`` splits merge inside the kernel as a cluster, and the cluster's size decides how many
+    blocks are held (on a B200 284 in clusters of 4, 264 in clusters of 8, ...). A step whose blocks need a
+    second wave that stays nearly empty loses more than longer splits cost, so: the cut with the least
+    waves x (keys per split + a block's fixed cost); the fewest splits among equals."""
+    best_keys, best_cost, best_real = 0, None, 0
+    for splits in range(1, MAX_CLUSTER + 1):
+        keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
+        real = -(-length // keys)
+        # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
+        held = max(1, int(CAPACITY_USED * capacity(real)))
+        cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
+        if best_cost is None or cost < best_cost:
+            best_keys, best_cost, best_real = keys, cost, real
+    if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= capacity(1):
+        # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
+        splits = min(64, capacity(1) // units)
+        return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)
+    return best_keys
+
+
 def _sm_count(device) -> int:
     if device not in _SM_COUNT:
         _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
@@ -129,24 +154,7 @@ class GQAttention(Mixer):
             # The generic kernel: enough blocks to fill the GPU about twice.
             keys = -(-length // max(1, (2 * sms) // units))
             return min(max(-(-keys // 64) * 64, 128), 1024)
-        # The tensor-core kernel. Up to 16 splits merge inside the kernel as a thread-block cluster, and the
-        # cluster's size decides how many blocks the device holds at a time (284 in clusters of 4, 264 in
-        # clusters of 8, ...). A step whose blocks need a second wave that stays nearly empty loses more than
-        # longer splits cost, so: the cut with the least waves x (keys per split + a block's fixed cost).
-        best_keys, best_cost = 0, None
-        for splits in range(1, MAX_CLUSTER + 1):
-            keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
-            real = -(-length // keys)
-            # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
-            held = int(CAPACITY_USED * ops.attn_decode_capacity(self.head_dim, real, heads, q.device))
-            cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
-            if best_cost is None or cost < best_cost:
-                best_keys, best_cost, best_real = keys, cost, real
-        if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= ops.attn_decode_capacity(self.head_dim, 1, heads, q.device):
-            # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
-            splits = min(64, ops.attn_decode_capacity(self.head_dim, 1, heads, q.device) // units)
-            return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)
-        return best_keys
+        return cut_keys(length, units, lambda cluster: ops.attn_decode_capacity(self.head_dim, cluster, heads, q.device))
 
     def takes_prenormed(self, n_tokens: int) -> bool:
         return self.qkv_proj.takes_prenormed(n_tokens) and self.q_proj.takes_prenormed(n_tokens)
