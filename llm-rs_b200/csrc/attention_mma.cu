@@ -8,8 +8,11 @@
 //            share the key head are the rows of one 16-row tile, so one pass over the
 //            keys serves them all. Each of the 4 warps streams its own 16-key tiles
 //            through a 3-stage cp.async pipeline; the warps' partial results are merged
-//            in shared memory and written as one (max, sum, weighted values) record per
-//            head, which the combine kernel of attention.cu merges across splits.
+//            in shared memory into one (max, sum, weighted values) record per head. Up
+//            to 16 splits of a (request, key head) run as one thread-block cluster and
+//            merge there: every block sends its records into the shared memory of the
+//            block that merges that part of the output. More splits write their records
+//            to global memory, and the combine kernel of attention.cu merges them.
 //   prefill: a block owns (64 query tokens of one request, query head); 4 warps of 16
 //            rows; keys and values come in tiles of 64 through a double buffer.
 #include "common.cuh"

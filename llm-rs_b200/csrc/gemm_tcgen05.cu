@@ -12,8 +12,14 @@
 //                         thread-block cluster, which add up their partial tiles through
 //                         distributed shared memory in a fixed order, so that a skinny
 //                         product still puts some hundred blocks on the GPU.
-// Epilogues: store (bfloat16 or float32), add into the float32 residual stream, or
-// SiLU(gate)*up for a weight whose rows alternate 64 gate rows and 64 up rows.
+// Epilogues: store (bfloat16 or float32), add into the float32 residual stream,
+// SiLU(gate)*up for a weight whose rows alternate 64 gate rows and 64 up rows, or (mode 1,
+// heads of 128) q | k | v with the per-head norms, the rotation and the write into the
+// paged cache. In mode 1 a residual epilogue can also leave the input of the RMSNorm that
+// follows (the new residual times the norm's weight, and its sums of squares), and every
+// epilogue can scale its rows by the factor such a norm still owes (see TcParams): a
+// decode step then runs no norm kernel between its products. A many-token variant walks
+// its tiles with one block per SM (gemm_tc_persistent_kernel).
 //
 // Every block loads its own tiles (no multicast). Every wait on an mbarrier is bounded:
 // when a wait runs out the kernel records a code in *error_flag, waits (bounded) for its
