@@ -3,7 +3,7 @@
 The package folder carries the project's name, which holds a hyphen and so cannot be
 written in an ``import`` statement. ``import llm_rs_b200`` finds this file; it loads
 the folder's ``__init__.py`` as the real package (with its sub-packages) and puts
-that in ``sys.modules`` under the importable name.
+that in ``sys.modules`` under the importable name. Run as ``python -m llm_rs_b200 ...`` it is the command line.
 """
 import importlib.util
 import os
@@ -16,3 +16,7 @@ _spec = importlib.util.spec_from_file_location(
 _module = importlib.util.module_from_spec(_spec)
 sys.modules["llm_rs_b200"] = _module
 _spec.loader.exec_module(_module)
+
+if __name__ == "__main__":      # ``python -m llm_rs_b200 <command> ...`` runs this file: hand over to the command line
+    from llm_rs_b200.cli import main
+    sys.exit(main())
