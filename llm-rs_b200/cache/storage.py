@@ -85,6 +85,18 @@ class CacheStorage:
             for t in tensors.values():
                 t[slot].zero_()
 
+    def snapshot_state(self, slots: Sequence[int]):
+        """Copies of the fixed-size state that the given slots hold (for ``restore_state``)."""
+        if not any(self.state):
+            return []
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        return [(t, idx, t.index_select(0, idx)) for tensors in self.state for t in tensors.values()]
+
+    @staticmethod
+    def restore_state(saved) -> None:
+        for t, idx, copy in saved:
+            t.index_copy_(0, idx, copy)
+
     def layer_cache(self, s: int, block_tables: Sequence[Optional[torch.Tensor]]) -> LayerCache:
         g, i = self.entry_group[s], self.entry_index[s]
         src = self.run_order[s].cache_of

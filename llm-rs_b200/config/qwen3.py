@@ -110,11 +110,24 @@ class Qwen3Config:
         act = raw.get("hidden_act", "silu")
         if act != "silu":
             raise ConfigError(f"hidden_act {act!r} is not supported for Qwen3 (silu only)")
-        scaling = raw.get("rope_scaling")
-        if scaling not in (None, {}):
-            kind = scaling.get("rope_type", scaling.get("type")) if isinstance(scaling, dict) else scaling
-            if kind != "default":
-                raise ConfigError(f"rope_scaling {scaling!r} is not supported")
+        # The rotation's base and kind: top-level ``rope_theta`` / ``rope_scaling`` (the keys the
+        # reference knows, config.rs:25), or the ``rope_parameters`` object in which newer files of the
+        # architecture store both ({"rope_theta": ..., "rope_type": "default"}) with no top-level key.
+        theta_raw = {k: raw[k] for k in ("rope_theta",) if raw.get(k) is not None}
+        for key in ("rope_scaling", "rope_parameters"):
+            obj = raw.get(key)
+            if obj in (None, {}):
+                continue
+            if not isinstance(obj, dict):
+                raise ConfigError(f"{key} must be an object, got {obj!r}")
+            kind = obj.get("rope_type", obj.get("type", "default"))
+            if kind not in ("default", None):
+                raise ConfigError(f"{key} {obj!r} is not supported (only the default rotation is)")
+            if obj.get("rope_theta") is not None:
+                inner = obj["rope_theta"]
+                if "rope_theta" in theta_raw and float(theta_raw["rope_theta"]) != float(inner):
+                    raise ConfigError(f"rope_theta {theta_raw['rope_theta']!r} and {key}.rope_theta {inner!r} disagree")
+                theta_raw["rope_theta"] = inner
 
         use_window = _bool(raw, "use_sliding_window", False)
         window = raw.get("sliding_window")
@@ -154,9 +167,13 @@ class Qwen3Config:
                 raise ConfigError(f"no_rope_layers must list {layers} entries")
             no_rope = [bool(v) for v in no_rope]
 
+        # Absent: the reference's default 2 (candle.rs:711-722). null: the model names no end token,
+        # so nothing ends a request but its length.
         eos = raw.get("eos_token_id", 2)
+        if eos is None:
+            eos = []
         if isinstance(eos, bool) or not isinstance(eos, (int, list)):
-            raise ConfigError(f"eos_token_id must be an integer or a list, got {eos!r}")
+            raise ConfigError(f"eos_token_id must be an integer, a list or null, got {eos!r}")
         eos_ids = tuple(eos) if isinstance(eos, list) else (eos,)
         if not all(isinstance(e, int) and not isinstance(e, bool) for e in eos_ids):
             raise ConfigError(f"eos_token_id must hold integers, got {eos!r}")
@@ -165,7 +182,7 @@ class Qwen3Config:
         if dtype not in ("float32", "float16", "bfloat16"):
             raise ConfigError(f"torch_dtype {dtype!r} is not supported")
 
-        theta = _float(raw, "rope_theta", 10000.0)
+        theta = _float(theta_raw, "rope_theta", 10000.0)
         eps = _float(raw, "rms_norm_eps", 1e-5)
         if theta <= 0:
             raise ConfigError(f"rope_theta must be positive, got {theta}")
@@ -185,7 +202,8 @@ class Qwen3Config:
             max_window_layers=max_window_layers)
 
     def to_dict(self) -> Dict[str, Any]:
-        """The config.json form (round-trips through ``from_dict``)."""
+        """The config.json form (round-trips through ``from_dict``). Keys without a value are left out
+        rather than written as null, which stricter readers of the same file refuse."""
         d: Dict[str, Any] = {
             "architectures": [self.architecture], "model_type": self.model_type,
             "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
@@ -194,16 +212,21 @@ class Qwen3Config:
             "num_key_value_heads": self.num_key_value_heads, "head_dim": self.head_dim,
             "intermediate_size": self.intermediate_size,
             "max_position_embeddings": self.max_position_embeddings,
-            "rope_theta": self.rope_theta, "rope_scaling": None,
+            "rope_theta": self.rope_theta,
             "rms_norm_eps": self.rms_norm_eps,
             "tie_word_embeddings": self.tie_word_embeddings, "hidden_act": self.hidden_act,
             "attention_bias": self.attention_bias,
             "use_sliding_window": self.use_sliding_window,
-            "sliding_window": self.sliding_window,
-            "max_window_layers": self.max_window_layers,
-            "eos_token_id": self.eos_token_ids[0] if len(self.eos_token_ids) == 1 else list(self.eos_token_ids),
             "torch_dtype": self.torch_dtype,
         }
+        if self.sliding_window is not None:
+            d["sliding_window"] = self.sliding_window
+        if self.max_window_layers is not None:
+            d["max_window_layers"] = self.max_window_layers
+        if len(self.eos_token_ids) == 1:
+            d["eos_token_id"] = self.eos_token_ids[0]
+        else:
+            d["eos_token_id"] = list(self.eos_token_ids)   # [] = no end token (absent would mean 2)
         if any(self.layer_windows):
             d["layer_types"] = ["sliding_attention" if w else "full_attention" for w in self.layer_windows]
         if any(self.no_rope_layers):

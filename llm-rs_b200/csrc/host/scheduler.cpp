@@ -278,6 +278,13 @@ void Scheduler::abort_all(int reason, std::vector<SchedOutput>* outs) {
         finish(r, reason);
         outs->push_back({id, -1, true, reason});
     }
+    // No step that was scheduled or queued before the failure will be reported any more: close their
+    // batches and count nothing as in flight, so that the finished requests can be forgotten.
+    batches_.clear();
+    for (auto& kv : requests_) {
+        if (kv.second.n_inflight) changed_.push_back(kv.first);
+        kv.second.n_inflight = 0;
+    }
 }
 
 }  // namespace llmrs_host

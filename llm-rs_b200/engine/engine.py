@@ -112,10 +112,18 @@ class Engine:
                     event = torch.cuda.Event()
                     event.record()
             except Exception:
-                outs = self.scheduler.abort_all()
+                # The step before this one may still be in flight: its tokens were sampled and are
+                # reported, and the scheduler closes its batch, before everything is aborted.
+                outs = []
+                if self._inflight is not None:
+                    flight, self._inflight = self._inflight, None
+                    try:
+                        outs += self._collect(flight)
+                    except Exception:
+                        pass            # its tokens cannot be read either; abort_all closes its batch
+                outs += self.scheduler.abort_all()
                 for o in outs:
                     self._events.setdefault(o.request_id, []).append(o)
-                self._inflight = None
                 raise
             self.scheduler.on_launched(batch)
             n_dec = sum(1 for s in batch if len(s.tokens) == 1 and s.sample)

@@ -110,9 +110,10 @@ class ModelRunner:
         # Steps that only decode (one token per request) are captured in CUDA graphs and
         # replayed: one launch instead of some ten per layer.
         self.use_graphs = False
-        # A mixer that plans work on the host per step sets ``graph_safe = False``.
-        self._graph_safe = all(getattr(b.mixer, "graph_safe", True) for b in self.model.blocks
-                               if hasattr(b, "mixer"))
+        # A part that plans work on the host per step sets ``graph_safe = False`` (a block's mixer, its
+        # feed-forward, its norms, or the block itself).
+        self._graph_safe = all(getattr(part, "graph_safe", True)
+                               for b in self.model.blocks for part in [b, *getattr(b, "parts", list)()])
         # Captured steps by (batch size, wanted rows, table widths), least recently used first; a
         # captured step keeps its own logits and workspace, so their number is bounded.
         self._graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
@@ -334,7 +335,11 @@ class ModelRunner:
             graph = _DecodeGraph()
             ctx = self._upload(packed, entries, graph)
             self._feed_device_tokens(ctx, entries, token_source)
-            self.model.forward(ctx)  # warm-up: sizes the workspace; rewrites the same keys and values
+            # Warm-up: sizes the workspace. The replay below runs the same tokens again: keys and values
+            # are rewritten with the same numbers, fixed-size state is put back to what it was.
+            saved = self.storage.snapshot_state(ctx.host_slot_ids)
+            self.model.forward(ctx)
+            self.storage.restore_state(saved)
             torch.cuda.current_stream().synchronize()
             graph.graph = torch.cuda.CUDAGraph()
             # A collection that ran during the capture could destroy an older runner's graphs,

@@ -33,7 +33,8 @@ class LinearHead(Part):
     """``logits = x @ W^T`` in float32, no bias, no soft cap
     (llm-core/src/graph/builder.rs:408-437). ``tied_to`` names the embedding table that
     serves as W when the model ties them (llm-core/src/backends/weights.rs:144-157): one
-    buffer, used by both."""
+    buffer, used by both. A tied model's folder may still store the head's matrix (a copy of the
+    table); it is accepted and not read."""
 
     def __init__(self, vocab_size: int, hidden_size: int, name: str = "lm_head.weight", tied_to: str = "",
                  prefix: str = ""):
@@ -42,7 +43,7 @@ class LinearHead(Part):
 
     def weight_specs(self):
         if self.tied_to:
-            return []
+            return [WeightSpec(self.name, (self.vocab_size, self.hidden_size), optional=True, load=False)]
         return [WeightSpec(self.name, (self.vocab_size, self.hidden_size))]
 
     def bind(self, tensors, runtime: Runtime):

@@ -49,6 +49,10 @@ class Linear:
         self.tc_ok = (weight.dtype == torch.bfloat16 and bias is None and weight.is_contiguous()
                       and k % 8 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0)
 
+    def tc_enabled(self) -> bool:
+        """The tcgen05 kernel can take this weight and has not been switched off (LLMRS_TC_MAX_TOKENS=0)."""
+        return self.tc_ok and TC_MAX_TOKENS > 0
+
     def uses_tc(self, n_tokens: int) -> bool:
         return self.tc_ok and n_tokens > 0 and (n_tokens <= TC_MAX_TOKENS or (TC_PREFILL and TC_MAX_TOKENS > 0))
 

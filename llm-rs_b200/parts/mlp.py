@@ -49,7 +49,7 @@ class SwiGLU(FeedForward):
         self.down = Linear(tensors[p + "down_proj.weight"], None, runtime.act_dtype)
 
     def takes_prenormed(self, n_tokens: int) -> bool:
-        return bool(self.block) and self.gate_up.tc_ok and FUSE_GATE_UP and 0 < n_tokens <= 32
+        return bool(self.block) and self.gate_up.tc_enabled() and FUSE_GATE_UP and 0 < n_tokens <= 32
 
     def emits_prenormed(self, n_tokens: int) -> bool:
         return self.down.emits_prenormed(n_tokens)
@@ -65,7 +65,7 @@ class SwiGLU(FeedForward):
         # library product followed by the SiLU kernel, or ahead of it (2,048 tokens: 295 against 315 us).
         # (From 33 to 64 tokens the few-token kernel's widest tile is behind the library product followed by the
         # SiLU kernel: 10.53 against 10.38 ms a step at 64 tokens.)
-        if (self.block and x.dtype == torch.bfloat16 and self.gate_up.tc_ok and FUSE_GATE_UP
+        if (self.block and x.dtype == torch.bfloat16 and self.gate_up.tc_enabled() and FUSE_GATE_UP
                 and not 32 < x.size(0) <= 64):
             act = ops.gemm_bf16(x, self.gate_up.weight, epilogue="silu_mul")
         else:

@@ -82,12 +82,15 @@ class WeightSpec:
       "norm"       1 + N(0, norm_jitter); held as float32 (exact from bfloat16)
       "bias"       ~N(0, sigma)
       "int_table"  integers, held as int32
-    ``optional`` tensors may be absent from the folder.
+    ``optional`` tensors may be absent from the folder. ``load=False`` marks a tensor that the folder
+    may hold but the part does not use (a stored copy of a tied matrix): its shape is checked, it is
+    not read, and the random-weights mode does not write it.
     """
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
+    load: bool = True
 
 
 @dataclass(frozen=True)

@@ -71,7 +71,7 @@ def load_weights(model_dir: str, specs: Sequence[WeightSpec], act_dtype: torch.d
         raise WeightError(model_dir, missing, unexpected, wrong_shape, wrong_dtype, duplicates)
     out = {}
     for s in specs:
-        if s.name not in where:
+        if s.name not in where or not s.load:
             continue
         f = where[s.name]
         t = f.tensor(s.name)

@@ -46,7 +46,7 @@ def random_tensors(specs: Sequence[WeightSpec], seed: int, sigma: float = 0.02, 
                    dtype: torch.dtype = torch.bfloat16, device="cpu", norm_dtype: Optional[torch.dtype] = None
                    ) -> Dict[str, torch.Tensor]:
     out = {}
-    for index, spec in enumerate(sorted(specs, key=lambda s: s.name)):
+    for index, spec in enumerate(sorted((s for s in specs if s.load), key=lambda s: s.name)):
         dt = (norm_dtype or dtype) if spec.role == "norm" else dtype
         out[spec.name] = _make(spec, seed, index, sigma, norm_jitter, dt, device)
     return out

@@ -47,6 +47,37 @@ def test_refusals(patch, msg):
         Qwen3Config.from_dict({**TINY_A, **patch})
 
 
+def test_rope_parameters_object():
+    """Newer files of the architecture keep the rotation's base inside ``rope_parameters`` and have no
+    top-level ``rope_theta``; reading only the top-level key would rotate with the default 10000."""
+    raw = {k: v for k, v in TINY_B.items() if k != "rope_theta"}
+    raw["rope_parameters"] = {"rope_theta": 1000000.0, "rope_type": "default"}
+    assert Qwen3Config.from_dict(raw).rope_theta == 1e6
+    assert Qwen3Config.from_dict({**raw, "rope_theta": 1000000.0}).rope_theta == 1e6
+    with pytest.raises(ConfigError, match="disagree"):
+        Qwen3Config.from_dict({**raw, "rope_theta": 10000.0})
+    with pytest.raises(ConfigError, match="rope_parameters"):
+        Qwen3Config.from_dict({**raw, "rope_parameters": {"rope_theta": 1e6, "rope_type": "yarn", "factor": 4.0}})
+    with pytest.raises(ConfigError, match="rope_parameters"):
+        Qwen3Config.from_dict({**raw, "rope_parameters": "linear"})
+    # rope_scaling with a base of its own is read the same way
+    assert Qwen3Config.from_dict({**TINY_A, "rope_scaling": {"type": "default"}}).rope_theta == 10000.0
+
+
+def test_end_token_absent_null_or_list():
+    base = {k: v for k, v in TINY_A.items() if k != "eos_token_id"}
+    assert Qwen3Config.from_dict(base).eos_token_ids == (2,)          # llm-core/src/backends/candle.rs:711-722
+    none = Qwen3Config.from_dict({**base, "eos_token_id": None})
+    assert none.eos_token_ids == ()
+    assert Qwen3Config.from_dict(json.loads(json.dumps(none.to_dict()))) == none
+
+
+def test_config_json_has_no_null_values():
+    for raw in (TINY_A, TINY_B, TINY_C):
+        d = Qwen3Config.from_dict(raw).to_dict()
+        assert all(v is not None for v in d.values()), d
+
+
 def test_window_layers_and_unrotated_layers():
     c = Qwen3Config.from_dict(TINY_C)
     assert c.layer_windows == (0, 0, 24, 24)

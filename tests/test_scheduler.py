@@ -174,6 +174,34 @@ def test_abort_frees_everything():
     assert not m.requests and m.free_pages() == 16
 
 
+def test_abort_with_a_step_in_flight_leaves_nothing_behind():
+    """A step is queued (its samples in flight), the next one is scheduled, and then the step function
+    fails: after ``abort_all`` the scheduler knows no request and no batch, in the library or here."""
+    m, s = make()
+    s.add_request(req(1, 5, max_new=8))
+    s.add_request(req(2, 5, max_new=8))
+    first = s.schedule()
+    for b in first:
+        m.admit(b.request.request_id)
+        m.reserve(b.request.request_id, len(b.tokens))
+        m.commit(b.request.request_id, len(b.tokens))
+    s.on_launched(first)
+    assert all(b.request.n_inflight == 1 for b in first)
+    second = s.schedule()                       # scheduled with the tokens still on the device ...
+    assert second and all(b.pending for b in second)
+    outs = s.abort_all()                        # ... and never launched: the step function raised
+    assert sorted(o.request_id for o in outs) == [1, 2]
+    assert not s._requests and not s.has_work()
+    assert not m.requests and m.free_pages() == 16
+    m.check_invariants()
+    # The scheduler is usable afterwards.
+    s.add_request(req(3, 4, max_new=2))
+    done = []
+    while s.has_work():
+        done += run_step(m, s)[1]
+    assert [o.token for o in done] == [7, 7] and not s._requests
+
+
 def run_async(m, s, token_of, max_steps=200):
     """The engine's pipelined loop with a fake step function: a step's tokens are handed to
     the scheduler only after the NEXT step has been scheduled and 'launched'."""

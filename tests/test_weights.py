@@ -60,19 +60,37 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del tensors["model.norm.weight"]
     tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(64, 63, dtype=torch.bfloat16)
     tensors["model.layers.7.extra.weight"] = torch.zeros(2)
-    tensors["lm_head.weight"] = torch.zeros(256, 64)   # the model ties its head to the embedding
+    tensors["lm_head.weight"] = torch.zeros(256, 60)   # a stored copy of the tied head: accepted, shape checked
     tensors["model.layers.0.input_layernorm.weight"] = torch.ones(64, dtype=torch.int32)
     save_file(tensors, str(tmp_path / "model.safetensors"))
     with pytest.raises(WeightError) as e:
         load_weights(str(tmp_path), specs, torch.bfloat16, "cpu")
     err = e.value
     assert err.missing == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
-    assert err.unexpected == ["lm_head.weight", "model.layers.7.extra.weight"]
-    assert err.wrong_shape == [("model.layers.0.self_attn.q_proj.weight", (64, 64), (64, 63))]
+    assert err.unexpected == ["model.layers.7.extra.weight"]
+    assert sorted(err.wrong_shape) == [("lm_head.weight", (256, 64), (256, 60)),
+                                       ("model.layers.0.self_attn.q_proj.weight", (64, 64), (64, 63))]
     assert err.wrong_dtype == [("model.layers.0.input_layernorm.weight", "int32")]
     text = str(err)
-    for needle in ("missing (2)", "unexpected (2)", "is [64, 63], expected [64, 64]", "model.norm.weight"):
+    for needle in ("missing (2)", "unexpected (1)", "is [64, 63], expected [64, 64]", "model.norm.weight"):
         assert needle in text
+
+
+def test_tied_model_that_also_stores_its_head(tmp_path):
+    """Tied checkpoints may store ``lm_head.weight`` beside the embedding table (the reference uses a
+    stored head when there is one and falls back to the table otherwise,
+    llm-core/src/backends/weights.rs:143-157). Such a folder loads; the copy is not read."""
+    specs = _specs(TINY_A)
+    tensors = random_tensors(specs, seed=0)
+    assert "lm_head.weight" not in tensors
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    save_file(tensors, str(tmp_path / "model.safetensors"))
+    got = load_weights(str(tmp_path), specs, torch.bfloat16, "cpu")
+    assert "lm_head.weight" not in got and "model.embed_tokens.weight" in got
+    model = DecoderModel(build_spec(Qwen3Config.from_dict(TINY_A)))
+    from llm_rs_b200.parts import Runtime
+    model.bind(got, Runtime(torch.device("cpu"), torch.bfloat16, 64))
+    assert model.lm_head.proj.weight.data_ptr() == model.embedding.table.data_ptr()
 
 
 def test_duplicate_across_shards(tmp_path):
@@ -106,7 +124,7 @@ def test_random_model_folder_is_deterministic_and_complete(tmp_path):
     a = write_tiny_model("A", str(tmp_path / "x"))
     b = write_tiny_model("A", str(tmp_path / "y"))
     fa, fb = open_model_files(a)[0], open_model_files(b)[0]
-    assert sorted(fa.names()) == sorted(s.name for s in _specs(TINY_A))
+    assert sorted(fa.names()) == sorted(s.name for s in _specs(TINY_A) if s.load)
     assert "lm_head.weight" not in fa.names()       # tied
     for n in fa.names():
         assert torch.equal(fa.tensor(n), fb.tensor(n))
