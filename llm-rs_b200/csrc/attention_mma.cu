@@ -15,6 +15,8 @@
 //            to global memory, and the combine kernel of attention.cu merges them.
 //   prefill: a block owns (64 query tokens of one request, query head); 4 warps of 16
 //            rows; keys and values come in tiles of 64 through a double buffer.
+#include <mutex>
+
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -404,6 +406,25 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   }
 }
 
+// Lets the kernel use `smem` bytes of dynamic shared memory and clusters of up to 16 blocks (more than the
+// portable 8, for few requests). The limit only ever grows: the launcher and the capacity query below share
+// it, and a query for a small cluster must not take away what a launch with a large one was given.
+template <int DCH>
+static int decode_mma_allow(size_t smem) {
+  static size_t allowed = 0;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
+    allowed = smem;
+  }
+  return 0;
+}
+
 template <int DCH>
 static int launch_decode_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                              const int* q_start, const int* cached_len, const int* block_table, int table_stride,
@@ -413,16 +434,7 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   constexpr int D = 16 * DCH;
   const int ng_max = n_q_heads / n_kv_heads < 16 ? n_q_heads / n_kv_heads : 16;
   const size_t smem = dm_ring_bytes(D) + (cluster_merge ? dm_inbox_bytes(ng_max, D, max_splits) : 0);
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    // Clusters of up to 16 blocks (more than the portable 8) for few requests.
-    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
-    configured = smem;
-  }
+  if (int rc = decode_mma_allow<DCH>(smem)) return rc;
   const int G = n_q_heads / n_kv_heads;
   dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
   cudaLaunchConfig_t cfg = {};
@@ -458,11 +470,8 @@ template <int DCH>
 static int decode_mma_capacity(int cluster, int ng, int* blocks) {
   constexpr int D = 16 * DCH;
   const size_t smem = dm_ring_bytes(D) + (cluster > 1 ? dm_inbox_bytes(ng, D, cluster) : 0);
-  cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem);
-  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
-  e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-  if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
+  if (int rc = decode_mma_allow<DCH>(smem)) return rc;
+  cudaError_t e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(64, 8, cluster);
   cfg.blockDim = dim3(DM_THREADS);

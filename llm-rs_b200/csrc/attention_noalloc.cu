@@ -16,7 +16,8 @@ extern "C" int llmrs_attn_decode(const void* q, long long q_stride, void* out, l
                                  int d, int page_size, int window, float scale, int dtype, cudaStream_t stream);
 extern "C" long long llmrs_attn_decode_scratch_floats(int n_dec, int n_q_heads, int d, int max_splits);
 
-// 8 MiB per GPU, held from library load to process exit. In host code this name is only
+// 8 MiB per GPU, held from the moment this file's device code is loaded on it (with lazy module
+// loading: the first cudaGetSymbolAddress below) to process exit. In host code this name is only
 // a handle for cudaGetSymbolAddress, never an address to hand to a kernel.
 static __device__ __align__(256) float g_static_scratch[LLMRS_NOALLOC_SCRATCH_BYTES / sizeof(float)];
 

@@ -14,14 +14,19 @@
  * array in the library's device image.
  *
  * What it costs: LLMRS_NOALLOC_SCRATCH_BYTES (8 MiB) of device memory on every GPU
- * that loads the library, from load until the process exits, used or not.
+ * on which the library's device code is loaded, until the process exits, used or not.
+ * With CUDA's lazy module loading (the default) that moment is the first call of this
+ * entry point on the device, not the loading of the shared library: the driver brings
+ * the array into being inside that call. A caller that must not see any allocation
+ * after start-up therefore makes one call per device at start-up; a call with
+ * n_dec = 0 does the look-up, launches nothing and needs no valid pointers.
  *
  * Limits and rules:
  *  - n_dec * n_q_heads * max_splits * (head_dim + 2) floats must fit in the array;
  *    a larger request is refused with a message (llmrs_last_error) and nothing runs.
  *  - The first call on each device looks up the array's device address (once per device,
- *    for the device that is current at the call). Make that first call outside any
- *    stream capture.
+ *    for the device that is current at the call; see "What it costs"). Make that first
+ *    call at start-up and outside any stream capture.
  *  - All calls share the one array, and it keeps what the last call left in it. The
  *    kernels write every slot they later read, so nothing needs clearing between calls.
  *    Two calls whose kernels may overlap on the GPU (different streams, no dependency

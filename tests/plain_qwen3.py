@@ -56,7 +56,7 @@ def layer_windows(config: dict) -> List[int]:
 def embedding(table: torch.Tensor, ids: Sequence[int]) -> torch.Tensor:
     """h0[t] = E[id_t], no scale: llm-core/src/graph/builder.rs:8-14,
     llm-core/src/backends/candle.rs:1238-1261."""
-    return table[torch.as_tensor(list(ids), dtype=torch.long)]
+    return table[torch.as_tensor(list(ids), dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -72,13 +72,13 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return y if bias is None else y + bias
 
 
-def rope_angles(positions: Sequence[int], head_dim: int, theta: float, dtype) -> torch.Tensor:
+def rope_angles(positions: Sequence[int], head_dim: int, theta: float, dtype, device=None) -> torch.Tensor:
     """ang[t, i] = pos_t * theta^(-2i/d), i < d/2:
     llm-core/src/backends/attention.rs:178-214."""
     i = torch.arange(head_dim // 2, dtype=torch.float64)
     inv_freq = float(theta) ** (-2.0 * i / head_dim)
     pos = torch.as_tensor(list(positions), dtype=torch.float64)
-    return (pos[:, None] * inv_freq[None, :]).to(dtype)
+    return (pos[:, None] * inv_freq[None, :]).to(dtype).to(device)
 
 
 def rotate_half(x: torch.Tensor, ang: torch.Tensor) -> torch.Tensor:
@@ -104,8 +104,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0
     vv = v.repeat_interleave(G, dim=1)
     s = torch.einsum("qhd,khd->hqk", q, kk)
     s = s / math.sqrt(d) if scale is None else s * scale
-    qi = torch.arange(T)[:, None]
-    ki = torch.arange(T)[None, :]
+    qi = torch.arange(T, device=q.device)[:, None]
+    ki = torch.arange(T, device=q.device)[None, :]
     hidden = ki > qi
     if window and window > 0:
         hidden = hidden | (ki <= qi - window)
@@ -129,7 +129,7 @@ def attention_block(x: torch.Tensor, w: Dict[str, torch.Tensor], prefix: str, co
     q = rms_norm(q, w[prefix + "q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "k_norm.weight"], eps)
     if use_rope:
-        ang = rope_angles(positions, d, config.get("rope_theta", 10000.0), x.dtype)
+        ang = rope_angles(positions, d, config.get("rope_theta", 10000.0), x.dtype, x.device)
         q, k = rotate_half(q, ang), rotate_half(k, ang)
     o = attention(q, k, v, window)
     return linear(o, w[prefix + "o_proj.weight"], w.get(prefix + "o_proj.bias"))

@@ -38,10 +38,11 @@ def portions(reqs: Dict[str, List[int]], sizes=(7, 2, 13, 5, 2, 31, 3, 17, 2, 64
     return steps
 
 
-def mixed(reqs: Dict[str, List[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12):
+def mixed(reqs: Dict[str, List[int]], seed: int = 0, max_live: int = 4, decode_tail: int = 12,
+          sizes=(2, 3, 5, 8, 16, 17, 29, 40)):
     """Up to ``max_live`` live requests: portions of some beside single tokens of others.
-    Each request is fed in random portions, its last ``decode_tail`` tokens one by one;
-    a request may sit out a step. A finished request is ended and the next one admitted."""
+    Each request is fed in random portions (of the given ``sizes``), its last ``decode_tail`` tokens
+    one by one; a request may sit out a step. A finished request is ended and the next one admitted."""
     rng = random.Random(seed)
     waiting = list(reqs.items())
     live: Dict[str, int] = {}
@@ -59,7 +60,7 @@ def mixed(reqs: Dict[str, List[int]], seed: int = 0, max_live: int = 4, decode_t
             if left <= decode_tail:
                 n = 1
             else:
-                n = min(left - decode_tail, rng.choice([2, 3, 5, 8, 16, 17, 29, 40]))
+                n = min(left - decode_tail, rng.choice(list(sizes)))
             entries.append({"id": r, "tokens": toks[at:at + n], "want": list(range(n))})
             live[r] = at + n
             if live[r] == len(toks):
@@ -68,6 +69,23 @@ def mixed(reqs: Dict[str, List[int]], seed: int = 0, max_live: int = 4, decode_t
         if entries:
             steps.append({"entries": entries, "end": end})
     return steps
+
+
+def want_only(steps, wanted: Dict[str, set]):
+    """The same trace asking for logits at the absolute positions in ``wanted[request]`` only."""
+    at: Dict[str, int] = {}
+    out = []
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            base = at.get(e["id"], 0)
+            entries.append({"id": e["id"], "tokens": e["tokens"],
+                            "want": [i for i in range(len(e["tokens"])) if base + i in wanted[e["id"]]]})
+            at[e["id"]] = base + len(e["tokens"])
+        for r in st["end"]:
+            at.pop(r, None)
+        out.append({"entries": entries, "end": st["end"]})
+    return out
 
 
 def live_token_peak(steps) -> int:

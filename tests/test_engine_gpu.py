@@ -105,7 +105,25 @@ def test_temperature_sampling_is_seeded_and_batch_independent(models):
     a = run([0, 1, 2], 64)
     b = run([2, 1, 0], 17)          # other order, other cuts: same tokens
     assert a == b
-    # The first sampled token follows the plain sampler on the plain logits.
+    # Every sampled token is the plain sampler's choice on the engine's own float32 logits at that place
+    # (taken by feeding prompt + output back through the step function), with the request's history.
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    runner = ModelRunner.from_model_dir(path, dtype=torch.float32, max_tokens=256, page_size=8, max_requests=2)
+    for i, (prompt, out, p) in enumerate(zip(prompts, a, sp)):
+        seq = prompt + out
+        rows = runner.step([StepEntry("t", seq[:-1], list(range(len(prompt) - 1, len(seq) - 1)))]).cpu().numpy()
+        runner.release("t")
+        for j, tok in enumerate(out):
+            want = P.sample(rows[j], p.temperature, p.top_k, p.top_p, p.repetition_penalty, seq[:len(prompt) + j],
+                            seed=p.seed, request_id=i + 1, index=j)
+            if want != tok:
+                # The draw may fall within float32 rounding of a boundary between two tokens.
+                probs = P.kept_probabilities(rows[j], p.temperature, p.top_k, p.top_p, p.repetition_penalty,
+                                             seq[:len(prompt) + j]) if p.temperature > 1e-5 else None
+                assert probs is not None, (i, j, tok, want)
+                cum, u = np.cumsum(probs), P.uniform(p.seed, i + 1, j)
+                assert (cum[tok - 1] if tok else 0.0) - 1e-5 <= u * cum[-1] <= cum[tok] + 1e-5, (i, j, tok, want)
+    # And the first one also follows the plain sampler on the plain logits.
     logits = P.forward(cfg, w, prompts[0])[-1].numpy()
     probs = P.kept_probabilities(logits, 0.7)
     u = P.uniform(7, 1, 0)
@@ -232,10 +250,11 @@ def test_norms_spread_over_products_in_small_steps(models, monkeypatch):
 
 
 @pytest.mark.parametrize("hidden,heads,kv_heads,inter", [(2048, 16, 8, 6144), (2560, 32, 8, 9728), (5120, 40, 8, 17408)])
-def test_layer_sizes_of_the_family_bf16_against_float32(hidden, heads, kv_heads, inter):
+def test_layer_sizes_of_the_family_against_plain(hidden, heads, kv_heads, inter):
     """Two layers at the layer sizes of larger models of the family (heads of 128, widths that are no power
-    of two): the bfloat16 engine, which takes its tcgen05 kernels with all their fused epilogues there, against
-    the float32 engine on the same weights; prompts of three lengths in one step, then decode steps."""
+    of two): the bfloat16 engine, which takes its tcgen05 kernels with all their fused epilogues there, and
+    the float32 engine on the same weights, each against the plain implementation (float64, on the device);
+    prompts of three lengths in one step, then decode steps."""
     from llm_rs_b200.config import Qwen3Config
     from llm_rs_b200.engine import ModelRunner, StepEntry
     from llm_rs_b200.models.qwen3 import build_spec
@@ -256,8 +275,12 @@ def test_layer_sizes_of_the_family_bf16_against_float32(hidden, heads, kv_heads,
             rows.append(runner.step([StepEntry(i, [later[s][i]], [0]) for i in range(3)]).float().cpu())
         outs.append(torch.cat(rows))
         del runner
-    diff, scale = float((outs[0] - outs[1]).abs().max()), float(outs[1].abs().max())
-    assert diff < 0.03 * scale, (diff, scale)
+    w64 = {k: v.double() for k, v in t16.items()}
+    fulls = [P.forward(raw, w64, p + [later[k][i] for k in range(10)]) for i, p in enumerate(prompts)]
+    want = torch.stack([fulls[i][len(prompts[i]) - 1 + s] for s in range(11) for i in range(3)]).float().cpu()
+    scale = float(want.abs().max())
+    assert float((outs[1] - want).abs().max()) <= 1e-4, float((outs[1] - want).abs().max())
+    assert float((outs[0] - want).abs().max()) < 0.02 * scale, (float((outs[0] - want).abs().max()), scale)
 
 
 # -- weights stored in 32-bit --------------------------------------------------------------------

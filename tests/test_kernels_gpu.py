@@ -263,6 +263,24 @@ def test_decode_attention_merged_by_large_clusters(nq, nkv, d, split_keys, lens)
     assert torch.allclose(got, want, atol=2.5e-2, rtol=2e-2), float((got - want).abs().max())
 
 
+def test_capacity_query_between_two_large_cluster_launches():
+    """The capacity query (how many blocks the device holds in clusters of a size) sets the same kernel's
+    shared-memory limit as the launcher: asked about small clusters between two launches with clusters of 16
+    it must not lower the limit that the second launch needs."""
+    ops = _ops()
+    nq, nkv, d, lens = 16, 1, 128, [1000, 517]
+    new = [1, 1]
+    table, cache = _paged_setup(lens, new, nkv, d, 16, torch.bfloat16, seed=9)
+    q = torch.randn(2, nq * d).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, 16, 0, scale)
+    for _ in range(2):
+        got = _run_attention(q, cache, table, lens, new, nq, nkv, d, 16, 0, scale, split_keys=64, fused_merge=False)
+        assert torch.allclose(got, want, atol=2.5e-2, rtol=2e-2)
+        ops._decode_capacity.clear()        # ask the library, not the cache of its answers
+        assert ops.attn_decode_capacity(128, 1, 1, DEV) >= ops.attn_decode_capacity(128, 2, 2, DEV) > 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("far", [0, 15, 16, 255, 256, 257, 1000, 1999])
 def test_one_far_key_among_thousands(dtype, far):

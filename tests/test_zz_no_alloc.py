@@ -5,9 +5,11 @@ serving loop that has sworn off cudaMalloc after start-up because an allocation 
 every stream, or a plug-in that is handed fixed buffers by its host. For them the library
 has ``llmrs_attn_decode_static_scratch``, which keeps the partial results of its key
 splits in a fixed 8 MiB array of its own instead of a caller's buffer. This test checks
-that it gives what the regular entry point gives, on two calls in a row that share the
-array (the second with other sizes, so that what the first left behind is in the way),
-and that it refuses a request that does not fit.
+that it gives what the regular entry point gives, and what a plain attention over the
+gathered keys gives, on calls in a row that share the array (each with other sizes, so
+that what the last one left behind is in the way), and that it refuses a request that does
+not fit. In bfloat16 up to 16 splits merge inside the kernel and never touch the array,
+so some cases cut the keys into more splits than that.
 
 Collected last (the file's name, and the sort in conftest.py), so that a run that stops
 at the first failure has already run every other test.
@@ -40,12 +42,34 @@ def _case(seed, n_req, n_heads, n_kv, d, page, lens, dtype):
                 cached_len=torch.tensor(lens, dtype=torch.int32, device=dev))
 
 
-def _run_both(case, n_heads, n_kv, d, page, split_keys, window):
-    from llm_rs_b200 import ops
+def _library():
     from llm_rs_b200.csrc import build
     lib = build.library()
+    lib.llmrs_attn_decode_static_scratch.restype = ctypes.c_int
+    lib.llmrs_last_error.restype = ctypes.c_char_p
+    return lib
+
+
+def _plain(case, n_heads, n_kv, d, page, window, scale):
+    """softmax(q k^T * scale) v per request over its gathered keys, float64: [requests, heads * d]."""
+    q, cache, table, lens = case["q"].double().cpu(), case["cache"].double().cpu(), case["table"].cpu(), case["cached_len"].tolist()
+    outs = []
+    for r, n in enumerate(lens):
+        total = n + 1                   # the new token's key is in the cache already
+        pages = [int(table[r, i // page]) for i in range(0, total, page)]
+        kv = torch.cat([cache[p] for p in pages], dim=2)[:, :, :total]        # [n_kv, 2, total, d]
+        k, v = kv[:, 0].repeat_interleave(n_heads // n_kv, 0), kv[:, 1].repeat_interleave(n_heads // n_kv, 0)
+        s = torch.einsum("hd,hkd->hk", q[r].reshape(n_heads, d), k) * scale
+        if window > 0:
+            s[:, :max(0, total - window)] = float("-inf")
+        outs.append(torch.einsum("hk,hkd->hd", torch.softmax(s, -1), v).reshape(-1))
+    return torch.stack(outs)
+
+
+def _run_both(case, n_heads, n_kv, d, page, split_keys, window):
+    from llm_rs_b200 import ops
+    lib = _library()
     fn = lib.llmrs_attn_decode_static_scratch   # the exported C symbol
-    fn.restype = ctypes.c_int
     q, cache, table = case["q"], case["cache"], case["table"]
     n = q.size(0)
     max_splits = -(-(int(case["cached_len"].max()) + 1) // split_keys)
@@ -61,32 +85,44 @@ def _run_both(case, n_heads, n_kv, d, page, split_keys, window):
             max_splits, split_keys, n_heads, n_kv, d, page, window, ctypes.c_float(scale),
             ops.dtype_code(q.dtype), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
-    return rc, out, ref, lib
+    return rc, out, ref, _plain(case, n_heads, n_kv, d, page, window, scale), lib
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)])
 def test_static_scratch_matches_regular_entry_point(dtype, tol):
-    # First call: long contexts, many splits. Second call: other sizes on the same array.
+    # Calls in a row on the same array: few splits, then 18 and 22 splits (more than the bfloat16 kernel
+    # merges by itself, so the partial results go through the array), then other sizes again.
     for seed, (n_req, n_heads, n_kv, d, page, lens, split, window) in enumerate([
             (3, 8, 2, 64, 16, [700, 33, 255], 128, 0),
-            (5, 6, 3, 48, 8, [10, 90, 300, 17, 64], 64, 40)]):
+            (2, 8, 2, 128, 16, [1100, 40], 64, 0),
+            (3, 4, 4, 32, 16, [700, 699, 5], 32, 0),
+            (5, 6, 3, 48, 8, [10, 90, 300, 17, 64], 64, 40),
+            (2, 16, 8, 128, 16, [1500, 1501], 64, 300)]):
         case = _case(seed, n_req, n_heads, n_kv, d, page, lens, dtype)
-        rc, out, ref, lib = _run_both(case, n_heads, n_kv, d, page, split, window)
+        rc, out, ref, plain, lib = _run_both(case, n_heads, n_kv, d, page, split, window)
         assert rc == 0, lib.llmrs_last_error().decode()
         assert torch.isfinite(out.float()).all()
         diff = (out.float() - ref.float()).abs().max().item()
         assert diff <= tol, f"call {seed}: differs from llmrs_attn_decode by {diff}"
+        diff = (out.double().cpu() - plain).abs().max().item()
+        assert diff <= tol, f"call {seed}: differs from the plain attention by {diff}"
+
+
+def test_start_up_call_with_no_requests():
+    """The call a caller makes once per device at start-up: nothing to attend to, no pointers, returns 0."""
+    lib = _library()
+    null = ctypes.c_void_p(0)
+    rc = lib.llmrs_attn_decode_static_scratch(null, ctypes.c_longlong(0), null, ctypes.c_longlong(0), null, null, 0,
+                                              null, null, null, 0, 1, 64, 8, 2, 64, 16, 0, ctypes.c_float(1.0), 1, null)
+    assert rc == 0, lib.llmrs_last_error().decode()
 
 
 def test_static_scratch_refuses_what_does_not_fit():
-    from llm_rs_b200.csrc import build
-    lib = build.library()
+    lib = _library()
     fn = lib.llmrs_attn_decode_static_scratch
-    fn.restype = ctypes.c_int
     null = ctypes.c_void_p(0)
     # 64 requests x 64 heads x 64 splits x 130 floats = 136 MB: far beyond 8 MiB. Refused before any pointer is read.
     rc = fn(null, ctypes.c_longlong(0), null, ctypes.c_longlong(0), null, null, 64, null, null, null, 0,
             64, 256, 64, 8, 128, 16, 0, ctypes.c_float(1.0), 1, null)
     assert rc != 0
-    lib.llmrs_last_error.restype = ctypes.c_char_p
     assert b"do not fit" in lib.llmrs_last_error()
