@@ -415,7 +415,7 @@ def main():
             for _ in range(W):
                 engine.step()
             torch.cuda.synchronize()
-            h2d0 = runner.h2d_bytes
+            h2d0, d2h0 = runner.h2d_bytes, engine.d2h_bytes
             graphs0, pre0 = len(runner._graphs), engine.scheduler.stats["preemptions"]
             t_start = time.perf_counter()
             got = 0
@@ -428,7 +428,7 @@ def main():
                   file=sys.stderr, flush=True)
             result["e2e"] = {"value": round(got / dt, 2), "unit": "tokens/s",
                              "h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // K,
-                             "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": round(dt / K * 1e3, 4)}
+                             "d2h_bytes_per_step": (engine.d2h_bytes - d2h0) // K, "ms_per_step": round(dt / K * 1e3, 4)}
             while engine.has_work():
                 engine.step()
         except Exception as e:

@@ -30,7 +30,8 @@ bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const vo
 int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                           const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
                           const int* n_new, const int* cached_len, const int* block_table, int table_stride,
-                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale, cudaStream_t stream);
+                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale, int* error_flag,
+                          cudaStream_t stream);
 
 // 1: bfloat16 also takes the generic kernels (tests compare the two implementations).
 static int g_generic_only = 0;
@@ -160,13 +161,15 @@ attn_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__
 
 // `n_tokens` rows of q and out; `n_pages` pages in `cache`. `prefer_tc` = 1 asks for the tcgen05
 // kernel (128-query blocks; worth it when the portions are long) where it applies: bfloat16,
-// head_dim 128, pages of a multiple of 16 keys.
+// head_dim 128, pages of a multiple of 16 keys. That kernel's waits are bounded; a block that gives up
+// writes 2 into *error_flag (an int of the caller's on the device; null: a word inside the library that
+// llmrs_attention_tc_error reads).
 LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, long long out_stride,
                                  const void* cache, const int* tiles, int n_tiles, const int* q_start,
                                  const int* n_new, const int* cached_len, const int* block_table,
                                  int table_stride, int n_q_heads, int n_kv_heads, int d, int page_size,
                                  int window, float scale, int dtype, int n_tokens, int n_pages, int prefer_tc,
-                                 cudaStream_t stream) {
+                                 int* error_flag, cudaStream_t stream) {
   LLMRS_REQUIRE(n_tiles >= 0 && n_q_heads > 0 && n_kv_heads > 0 && page_size > 0, "attn_prefill: bad sizes");
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "attn_prefill: %d query heads are no multiple of %d key heads",
                 n_q_heads, n_kv_heads);
@@ -182,7 +185,7 @@ LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, l
     return llmrs_attn_prefill_tc(q, q_stride, n_tokens, out, out_stride, cache,
                                  (long long)n_pages * n_kv_heads * 2 * page_size, tiles, n_tiles, q_start, n_new,
                                  cached_len, block_table, table_stride, n_q_heads, n_kv_heads, page_size, window, scale,
-                                 stream);
+                                 error_flag, stream);
   if (dtype == LLMRS_BF16 && d <= 128 && !g_generic_only && scale > 0.f)
     return llmrs_attn_prefill_mma(q, q_stride, out, out_stride, cache, tiles, n_tiles, q_start, n_new, cached_len,
                                   block_table, table_stride, n_q_heads, n_kv_heads, d, page_size, window, scale,

@@ -25,8 +25,10 @@
 //
 // Same contract and math as attn_prefill_kernel in attention.cu (scores, softmax and the
 // weighted sum accumulate in float32; llm-core/src/backends/candle.rs:1587-1640). Every
-// wait is bounded; a block that gives up sets the error flag, waits for its copies and
-// frees its tensor memory.
+// wait is bounded (llmrs_attention_tc_set_wait_limit polls, 2^22 by default); when one runs out
+// the block raises a flag in its shared memory at which all its roles leave their loops, waits
+// (bounded) for its copies and MMAs in flight, records the error, stores nothing and frees its
+// tensor memory.
 #include <cuda.h>
 #include <mutex>
 
@@ -52,17 +54,20 @@ __device__ __forceinline__ void bar_init(uint32_t bar) { asm volatile("mbarrier.
 __device__ __forceinline__ void bar_expect(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < AT_WAIT_LIMIT; ++it) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (ok) return true;
+__device__ __forceinline__ bool bar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, uint32_t limit, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (bar_try(bar, parity)) return true;
     if (it > 128) {
       __nanosleep(32);
       if (*abort_flag) return false;
@@ -70,6 +75,13 @@ __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile
   }
   *abort_flag = 1;
   return false;
+}
+// Bounded wait of a block that has given up already, for what it still has in flight: the flag does not cut it short.
+__device__ __forceinline__ void bar_drain(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (bar_try(bar, parity)) return;
+    if (it > 128) __nanosleep(32);
+  }
 }
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
@@ -185,12 +197,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
-                       int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale) {
+                       int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale,
+                       int* __restrict__ error_flag, uint32_t wait_limit, int test_skip_tile) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
   unsigned char* KV = base;                 // AT_STAGES x (K: 2 halves of [64 keys][64 dims], then V the same)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // kfull[3], kfree[3], vfull[3], vfree[3], s[2], p[2], o[2], q
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 7);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // kfull[3], kfree[3], vfull[3], vfree[3], s[2], p[2], o[2], q, drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -200,7 +213,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
   if (q_off % AT_BQ != 0) return;           // the list names tiles of 64 queries; a block takes two
   if ((sm(base) & 1023u) != 0) {            // never seen; without the alignment the operands would be garbage
-    if (threadIdx.x == 0) atomicExch(&g_attn_tc_error, 2);
+    if (threadIdx.x == 0) atomicExch(error_flag ? error_flag : &g_attn_tc_error, 3);
     return;
   }
   const int kvh = head / (n_q_heads / n_kv_heads);
@@ -215,7 +228,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 
   const uint32_t bar_kfull = sm(bars), bar_kfree = sm(bars + AT_STAGES), bar_vfull = sm(bars + 2 * AT_STAGES),
                  bar_vfree = sm(bars + 3 * AT_STAGES), bar_s = sm(bars + 4 * AT_STAGES), bar_p = bar_s + 16,
-                 bar_o = bar_s + 32, bar_q = bar_s + 48;
+                 bar_o = bar_s + 32, bar_q = bar_s + 48, bar_drain_mma = bar_s + 56;
   if (tid == 0) {
     for (int i = 0; i < 4 * AT_STAGES + 2; ++i) bar_init(sm(bars + i));
     bar_init_n(bar_p, AT_THREADS);
@@ -223,6 +236,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     bar_init(bar_o);
     bar_init(bar_o + 8);
     bar_init_n(bar_q, AT_THREADS);
+    bar_init(bar_drain_mma);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -237,8 +251,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
 
+  int copies = 0;   // copying warps: tiles whose copies the warp has requested
   auto wait_all = [&](uint32_t bar, uint32_t parity) {
-    return __all_sync(0xffffffffu, bar_wait(bar, parity, abort_flag));
+    return __all_sync(0xffffffffu, bar_wait(bar, parity, wait_limit, abort_flag));
   };
   if (warp >= 5) {
     // ---- the copying warps: warp 5 brings K, warp 6 V; one box per lane, and a lane's box of tile t
@@ -260,6 +275,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       return (key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : spare_page;
     };
     auto load_tile = [&](int t, int page) {
+      copies = t + 1;
+      if (which == 0 && t == test_skip_tile) return;  // tests only: K of this tile never arrives
       const int st = t % AT_STAGES;
       const unsigned live = __ballot_sync(0xffffffffu, page >= 0);
       const uint32_t bar = bar_full + 8 * st;
@@ -374,7 +391,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     for (int j = 0; j < n_tiles; ++j) {
       const int kb = kv_lo + j * AT_BK;
       const uint32_t s_addr = lane_addr + S_COL + (j & 1) * AT_BK;
-      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * (j & 1), (j >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * (j & 1), (j >> 1) & 1, wait_limit, abort_flag));
       if (!ok) break;
       fence_after();
       // This thread's 128 scores -> probabilities.
@@ -435,7 +452,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       // stores of tensor memory are warp-wide, so the warp decides together), once O += P V of the
       // tile before is done (S of tile j implies O += P V of tile j-2 only).
       if (__any_sync(0xffffffffu, moved)) {
-        ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag));
+        ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, wait_limit, abort_flag));
         if (!ok) break;
         fence_after();
 #pragma unroll 1
@@ -451,7 +468,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
       fence_before();
       bar_arrive(bar_p + 8 * (j & 1));
     }
-    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag));
+    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, wait_limit, abort_flag));
     fence_after();
     if (ok) {
       // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
@@ -477,13 +494,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   }
   fence_before();
   __syncthreads();
-  if (*abort_flag && tid == AT_THREADS + 32) {
-    atomicExch(&g_attn_tc_error, 1);
-    // Copies may still be on their way into this block's shared memory.
-    for (int i = 0; i < AT_STAGES; ++i)
-      for (int ph = 0; ph < 2; ++ph) { bar_wait(bar_kfull + 8 * i, ph, abort_flag); bar_wait(bar_vfull + 8 * i, ph, abort_flag); }
+  if (*abort_flag) {
+    // The block gave up. Before tensor memory is freed and the block leaves: the MMAs that were issued must be
+    // done, and no copy may still be on its way into this block's shared memory.
+    if (warp == 4) {
+      if (elect_one()) commit(bar_drain_mma);
+      __syncwarp();
+      bar_drain(bar_drain_mma, 0, wait_limit);
+    } else if (warp >= 5) {
+      const int which = warp - 5;
+      const uint32_t bar_full = which ? bar_vfull : bar_kfull;
+      for (int t = max(0, copies - AT_STAGES); t < copies; ++t)
+        if (!(which == 0 && t == test_skip_tile)) bar_drain(bar_full + 8 * (t % AT_STAGES), (t / AT_STAGES) & 1, wait_limit);
+    } else if (tid == 0) {
+      atomicExch(error_flag ? error_flag : &g_attn_tc_error, 2);
+    }
   }
-  __syncthreads();
   if (warp == 4) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }
@@ -520,9 +546,20 @@ int make_map(CUtensorMap* map, const void* basep, long long rows, long long cols
   return 0;
 }
 
+uint32_t g_wait_limit = AT_WAIT_LIMIT;
+int g_test_skip_tile = -1;
+
 }  // namespace
 
-// 1 if a block of the tcgen05 prefill kernel gave up on a wait since the last call (clears the flag).
+// Polls of a barrier before a wait of the tcgen05 prefill kernel gives up (0: the default, 2^22).
+LLMRS_API void llmrs_attention_tc_set_wait_limit(unsigned polls) { g_wait_limit = polls ? polls : AT_WAIT_LIMIT; }
+
+// For the test of the bounded waits only: the next launches never copy K of their tile with this index, so that a
+// wait of every block runs out (-1, the default: every copy is made).
+LLMRS_API void llmrs_attention_tc_test_skip_copy(int tile) { g_test_skip_tile = tile; }
+
+// Non-zero if a block of the tcgen05 prefill kernel that was launched without an error word of the caller's
+// gave up on a wait since the last call (clears the flag).
 LLMRS_API int llmrs_attention_tc_error() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_attn_tc_error, sizeof(int)) != cudaSuccess) return -1;
@@ -542,7 +579,7 @@ bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const vo
 int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void* out, long long out_stride,
                           const void* cache, long long cache_rows, const int* tiles, int n_tiles, const int* q_start,
                           const int* n_new, const int* cached_len, const int* block_table, int table_stride,
-                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
+                          int n_q_heads, int n_kv_heads, int page_size, int window, float scale, int* error_flag,
                           cudaStream_t stream) {
   CUtensorMap map_kv;
   int rc;
@@ -550,7 +587,7 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   // One copy per page and half of the head; a page of a multiple of 64 keys is copied 64 keys at a time.
   const int box_rows = page_size % 64 == 0 ? 64 : 16;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
-  const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 7) * 8 + 8;
+  const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 8) * 8 + 8;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -561,6 +598,6 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   attn_prefill_tc_kernel<<<grid, AT_THREADS + 96, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                                                               tiles, q_start, n_new, cached_len, block_table,
                                                               table_stride, n_q_heads, n_kv_heads, page_size, box_rows,
-                                                              window, scale);
+                                                              window, scale, error_flag, g_wait_limit, g_test_skip_tile);
   return llmrs_launch_status("attn_prefill_tc");
 }

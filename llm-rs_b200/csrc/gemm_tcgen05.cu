@@ -21,9 +21,11 @@
 // decode step then runs no norm kernel between its products. A many-token variant walks
 // its tiles with one block per SM (gemm_tc_persistent_kernel).
 //
-// Every block loads its own tiles (no multicast). Every wait on an mbarrier is bounded:
-// when a wait runs out the kernel records a code in *error_flag, waits (bounded) for its
-// copies in flight, frees its tensor memory and returns.
+// Every block loads its own tiles (no multicast). Every wait on an mbarrier is bounded
+// (llmrs_tc_set_wait_limit polls, 2^22 by default): when a wait runs out the block raises a flag
+// in its shared memory, at which every other wait of the block returns too; the block then
+// waits (bounded) for its copies and MMAs in flight, records a code in *error_flag, lets its
+// epilogue write nothing (zeros into a cluster's sums), frees its tensor memory and returns.
 //
 // The reference's products are library calls (llm-core/src/backends/candle.rs:1276-1340).
 #include <cuda.h>
@@ -36,7 +38,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int TC_BM = 128;        // rows of A per tile = M of the MMA
 constexpr int TC_BK = 64;         // k per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int TC_THREADS = 128;
-constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;  // polls of a barrier before giving up (some seconds)
+constexpr uint32_t TC_WAIT_LIMIT = 1u << 22;  // default polls of a barrier before giving up (a second or so)
 
 enum TcEpilogue : int { TC_STORE = 0, TC_RESIDUAL = 1, TC_SILU_MUL = 2, TC_QKV_ROPE = 3 };
 
@@ -65,6 +67,8 @@ struct TcParams {
   int a_rows, b_rows;   // valid extents (tokens / features according to the mode)
   int k_blocks;         // ceil(K / 64)
   int* error_flag;
+  uint32_t wait_limit;  // polls of a barrier before a wait gives up
+  int test_skip_kb;     // tests only: the producer leaves out the copy of its k block with this index (-1: none)
   QkvRope qr;           // TC_QKV_ROPE only
   // A norm that is spread over two products (few tokens). The product BEFORE the norm (TC_RESIDUAL) also
   // writes emit_xw = (h + product) * emit_w in bfloat16, the norm's input times its weight, and each of
@@ -102,8 +106,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. False: gave up (or another thread of the block already had).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < TC_WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 128) {
       __nanosleep(64);
@@ -112,6 +116,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+// Bounded wait of a block that has given up already, for what it still has in flight (copies into its shared
+// memory, MMAs into its tensor memory): the flag does not cut it short.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (it > 128) __nanosleep(64);
+  }
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
@@ -281,33 +293,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   int pf_pos = 0, pf_page = 0;
   float2 pf_cs0 = make_float2(1.f, 0.f), pf_cs1 = make_float2(1.f, 0.f);
 
+  int issued = 0;                      // thread 0: k blocks whose copies it has requested
+  const int skip = p.test_skip_kb;     // -1 outside the test of the bounded waits
   if (warp == 0 && lane == 0) {
     // Producer: one thread feeds the ring of stages by TMA. In mode 1 the A operand is the
     // weight, which no earlier kernel writes: its first tiles are requested before the
     // wait on the preceding kernel, whose tail they overlap. (Requesting them still earlier, before
     // tensor memory is allocated, made the decode step slower: 3.83 -> 3.96 ms.)
-    int issued = 0;
     for (int i = 0; i < early; ++i) {
+      if (i == skip) continue;
       mbar_expect_tx(full0 + 8 * i, STAGE_BYTES);
       tma_load_2d(tc_smem(tiles + (size_t)i * STAGE_BYTES), &map_a, full0 + 8 * i, (kb0 + i) * TC_BK, tile_a * TC_BM);
     }
     pdl_wait();
-    for (int i = 0; i < early; ++i)
+    for (int i = 0; i < early; ++i) {
+      if (i == skip) continue;
       tma_load_2d(tc_smem(tiles + (size_t)i * STAGE_BYTES) + A_BYTES, &map_b, full0 + 8 * i, (kb0 + i) * TC_BK,
                   tile_b * BN);
+    }
     issued = early;
     for (int i = early; i < nkb; ++i) {
       const int s = i % STAGES;
-      if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, abort_flag)) break;
+      if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, p.wait_limit, abort_flag)) break;
+      issued = i + 1;
+      if (i == skip) continue;
       mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
       const uint32_t a_dst = tc_smem(tiles + (size_t)s * STAGE_BYTES);
       tma_load_2d(a_dst, &map_a, full0 + 8 * s, (kb0 + i) * TC_BK, tile_a * TC_BM);
       tma_load_2d(a_dst + A_BYTES, &map_b, full0 + 8 * s, (kb0 + i) * TC_BK, tile_b * BN);
-      issued = i + 1;
-    }
-    if (*abort_flag) {
-      // Do not leave while copies may still land in this block's shared memory.
-      for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, abort_flag);
     }
   } else if (warp == 1) {
     // MMA issuer: four k16 steps per stage. The whole warp walks the loop and computes the operands, one
@@ -317,7 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const bool leader = tc_elect_one();
     for (int i = 0; i < nkb; ++i) {
       const int s = i % STAGES;
-      if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, abort_flag))) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (i / STAGES) & 1, p.wait_limit, abort_flag))) break;
       tc_fence_after();
       const uint32_t a_addr = tc_smem(tiles + (size_t)s * STAGE_BYTES);
       const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + A_BYTES);
@@ -373,11 +386,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   }
   __syncwarp();
-  bool ok = true;
-  if (nkb > 0) ok = mbar_wait(accum_bar, 0, abort_flag);
+  if (nkb > 0) mbar_wait(accum_bar, 0, p.wait_limit, abort_flag);
   tc_fence_after();
-  __syncwarp();
-  if (!ok && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+  // Every MMA has finished (accumulator barrier), so the stages are free for the epilogue's use; and from
+  // here on all threads agree on whether the block gave up: tcgen05.ld below is warp-wide, and a cluster's
+  // barriers want every block.
+  __syncthreads();
+  const bool ok = *abort_flag == 0;
+  if (!ok) {
+    // MMAs that were issued before the block gave up write tensor memory and read the stages: they are
+    // waited for (their commit on the accumulator barrier was issued all the same) before either is touched.
+    if (warp == 1 && nkb > 0) mbar_drain(accum_bar, 0, p.wait_limit);
+    if (tid == 0) {
+      // Nor may copies still land in this block's shared memory, which the epilogue reuses.
+      for (int i = max(0, issued - STAGES); i < issued; ++i)
+        if (i != skip) mbar_drain(full0 + 8 * (i % STAGES), (i / STAGES) & 1, p.wait_limit);
+      if (p.error_flag) atomicExch(p.error_flag, 1);
+    }
+    tc_fence_after();
+    __syncthreads();
+  }
 
   pdl_wait();  // the epilogue writes (and for the residual reads) what earlier kernels touch
   const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16);
@@ -442,8 +470,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // Rows are features, columns tokens. Partial tile -> shared memory -> sum over the
     // cluster's blocks in rank order -> epilogue for the rows this block owns.
-    __syncthreads();  // the stages are free: every MMA has finished (accumulator barrier)
-    float* red = reinterpret_cast<float*>(tiles);  // [128][BN + 1]
+    float* red = reinterpret_cast<float*>(tiles);  // [128][BN + 1]; the stages are free (see the join above)
     constexpr int RS = BN + 1;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 8) {
@@ -619,18 +646,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                           const TcParams p, int n_m, int n_tiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)PS_STAGES * PS_STAGE_BYTES);   // full[4], empty[4], acc_full[2], acc_empty[2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PS_STAGES + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)PS_STAGES * PS_STAGE_BYTES);   // full[4], empty[4], acc_full[2], acc_empty[2], drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PS_STAGES + 5);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + PS_STAGES), acc_full0 = tc_smem(bars + 2 * PS_STAGES),
-                 acc_empty0 = acc_full0 + 16;
+                 acc_empty0 = acc_full0 + 16, drain_bar = acc_full0 + 32;
   if (tid == 0) {
     for (int s = 0; s < 2 * PS_STAGES + 2; ++s) mbar_init(full0 + 8 * s, 1);
     mbar_init(acc_empty0, 128);
     mbar_init(acc_empty0 + 8, 128);
+    mbar_init(drain_bar, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -646,6 +674,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait();   // x is what an earlier kernel wrote; the epilogue writes what earlier kernels read
   const int nkb = p.k_blocks;
+  long long copies = 0;   // warp 0: stages whose copies it has requested
 
   if (warp == 0) {
     // Copies: the whole warp walks the loop, one elected lane issues.
@@ -657,10 +686,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it % PS_STAGES);
         if (it >= PS_STAGES) {
-          ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, (uint32_t)((it / PS_STAGES) - 1) & 1, abort_flag));
+          ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, (uint32_t)((it / PS_STAGES) - 1) & 1, p.wait_limit, abort_flag));
           if (!ok) break;
         }
-        if (leader) {
+        if (leader && it != p.test_skip_kb) {
           mbar_expect_tx(full0 + 8 * s, PS_STAGE_BYTES);
           const uint32_t a_dst = tc_smem(tiles + (size_t)s * PS_STAGE_BYTES);
           tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * TC_BK, tm * TC_BM);
@@ -669,11 +698,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         __syncwarp();
       }
     }
-    if (*abort_flag && lane == 0) {
-      // Do not leave while copies may still land in this block's shared memory.
-      for (long long i = it > PS_STAGES ? it - PS_STAGES : 0; i < it; ++i)
-        mbar_wait(full0 + 8 * (int)(i % PS_STAGES), (uint32_t)(i / PS_STAGES) & 1, abort_flag);
-    }
+    copies = it;
   } else if (warp == 1) {
     // MMAs: operands computed by the whole warp (they stay in uniform registers), issued by one elected lane.
     constexpr uint32_t idesc = tc_instr_desc(PS_BN);
@@ -684,14 +709,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
       const int buf = lt & 1;
       if (lt >= 2) {   // the epilogue has read the tile before last out of this buffer
-        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8 * buf, (uint32_t)((lt >> 1) - 1) & 1, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8 * buf, (uint32_t)((lt >> 1) - 1) & 1, p.wait_limit, abort_flag));
         if (!ok) break;
         tc_fence_after();
       }
       const uint32_t d_addr = tmem_base + (uint32_t)buf * PS_BN;
       for (int kb = 0; kb < nkb; ++kb, ++it) {
         const int s = (int)(it % PS_STAGES);
-        ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (uint32_t)(it / PS_STAGES) & 1, abort_flag));
+        ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (uint32_t)(it / PS_STAGES) & 1, p.wait_limit, abort_flag));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = tc_smem(tiles + (size_t)s * PS_STAGE_BYTES);
@@ -714,7 +739,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
       const int tm = t % n_m, tn = t / n_m, buf = lt & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * buf, (uint32_t)(lt >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * buf, (uint32_t)(lt >> 1) & 1, p.wait_limit, abort_flag));
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * PS_BN;
@@ -775,13 +800,36 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   }
   tc_fence_before();
   __syncthreads();
-  if (*abort_flag && tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+  if (*abort_flag) {
+    // The block gave up. Before tensor memory is freed and the block leaves: the MMAs that were issued must be
+    // done, and no copy may still be on its way into this block's shared memory.
+    if (warp == 1) {
+      if (tc_elect_one()) tc_commit(drain_bar);
+      __syncwarp();
+      mbar_drain(drain_bar, 0, p.wait_limit);
+    } else if (tid == 0) {
+      for (long long i = copies > PS_STAGES ? copies - PS_STAGES : 0; i < copies; ++i)
+        if (i != p.test_skip_kb) mbar_drain(full0 + 8 * (int)(i % PS_STAGES), (uint32_t)(i / PS_STAGES) & 1, p.wait_limit);
+      if (p.error_flag) atomicExch(p.error_flag, 1);
+    }
+    __syncthreads();
+  }
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
 // ---- host side --------------------------------------------------------------------------------
+static uint32_t g_tc_wait_limit = TC_WAIT_LIMIT;
+static int g_tc_test_skip_kb = -1;
+
+// Polls of a barrier before a wait of the tcgen05 product kernels gives up (0: the default, 2^22).
+LLMRS_API void llmrs_tc_set_wait_limit(unsigned polls) { g_tc_wait_limit = polls ? polls : TC_WAIT_LIMIT; }
+
+// For the test of the bounded waits only: the producers of the next launches leave out the copy of their
+// k block with this index, so that a wait of every block runs out (-1, the default: every copy is made).
+LLMRS_API void llmrs_tc_test_skip_copy(int k_block) { g_tc_test_skip_kb = k_block; }
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -890,7 +938,7 @@ LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, i
 
 static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_m, int n_tiles,
                              cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + (2 * PS_STAGES + 4) * 8 + 16;
+  const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + (2 * PS_STAGES + 5) * 8 + 16;
   static int n_sm = 0;
   if (n_sm == 0) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -973,6 +1021,7 @@ static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out
   p.scale_eps = L.scale_eps;
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
   p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
+  p.wait_limit = g_tc_wait_limit; p.test_skip_kb = g_tc_test_skip_kb;
   CUtensorMap ma, mb;
   int rc;
   if (tokens <= 64) {

@@ -166,6 +166,10 @@ int llmrs_sched_schedule(void* sched, int64_t* ids, int32_t* fields4, int capaci
 int llmrs_sched_on_launched(void* sched, int64_t batch) {
     return guarded([&] { as<Scheduler>(sched, "scheduler")->on_launched(batch); });
 }
+
+int llmrs_sched_cancel(void* sched, int64_t batch) {
+    return guarded([&] { as<Scheduler>(sched, "scheduler")->cancel(batch); });
+}
 namespace {
 void copy_outputs(const std::vector<SchedOutput>& outs, int64_t* out_ids, int32_t* out_fields3, int capacity, int* n_out) {
     *n_out = static_cast<int>(outs.size());

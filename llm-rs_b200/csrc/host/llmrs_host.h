@@ -60,6 +60,7 @@ int llmrs_sched_has_work(void* sched, int* out);
 /* entries: per entry id, and 4 ints: start (-1: the token in flight), n_tokens, sample, pending. *batch: handle, 0 if empty. */
 int llmrs_sched_schedule(void* sched, int64_t* ids, int32_t* fields4, int capacity, int* n, int64_t* batch);
 int llmrs_sched_on_launched(void* sched, int64_t batch);
+int llmrs_sched_cancel(void* sched, int64_t batch);
 /* tokens: one per sampling entry of the batch, in order. outs: per output id, and 3 ints: token (-1 none), finished, reason. */
 int llmrs_sched_on_result(void* sched, int64_t batch, const int32_t* tokens, int n_tokens, int64_t* out_ids,
                           int32_t* out_fields3, int capacity, int* n_out);

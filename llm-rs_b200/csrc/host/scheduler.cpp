@@ -238,6 +238,8 @@ void Scheduler::on_launched(int64_t batch) {
     }
 }
 
+void Scheduler::cancel(int64_t batch) { batches_.erase(batch); }
+
 void Scheduler::on_result(int64_t batch, const int32_t* tokens, int n_tokens, std::vector<SchedOutput>* outs) {
     outs->clear();
     outs->swap(finished_early_);

@@ -66,6 +66,8 @@ public:
     // Decides the next step. Returns a handle for on_launched / on_result (0: nothing to run).
     int64_t schedule(std::vector<SchedEntry>* entries);
     void on_launched(int64_t batch);
+    // The batch was decided but never queued (its pages were gone): forget it; its requests stay as they were.
+    void cancel(int64_t batch);
     // `tokens`: one per entry with `sample`, in the batch's order. batch 0: only what ended without a step.
     void on_result(int64_t batch, const int32_t* tokens, int n_tokens, std::vector<SchedOutput>* outs);
     void abort_all(int reason, std::vector<SchedOutput>* outs);

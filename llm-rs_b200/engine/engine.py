@@ -15,6 +15,7 @@ from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 import torch
 
 from ..sampling import Sampler, SamplingParams
+from ..cache import OutOfPages
 from .runner import ModelRunner, StepEntry
 from .scheduler import Output, Request, Scheduled, Scheduler
 
@@ -59,7 +60,9 @@ class Engine:
         self._inflight = None            # the step that is queued on the GPU and not read back yet
         self._tok_bufs = [None, None]
         self._tok_flip = 0
-        self._steps_since_check = 0
+        self.d2h_bytes = 0               # bytes read back so far: 4 per sampled token and 4 for the error word per step
+        from .. import ops
+        self._error_word = ops.tc_error_flag(self.runner.device)   # written by a kernel whose bounded wait ran out
         # What the steps were made of: steps of decoded tokens only, of prompt portions only, of both;
         # tokens that entered the model as prompt portions and as single decoded tokens.
         self.stats = {"steps": 0, "decode_steps": 0, "prefill_steps": 0, "mixed_steps": 0,
@@ -88,7 +91,33 @@ class Engine:
         """Run one scheduler step. Returns ``(request id, token, finished)`` for every
         request whose token became known or that ended in this call. With ``async_steps``
         the tokens of a step are reported by the NEXT call: the step is queued on the GPU,
-        then the previous step's tokens are read while it runs."""
+        then the previous step's tokens are read while it runs.
+
+        If the step function, the sampler or a kernel fails (a kernel reports through the error word
+        that travels with every step's tokens), every running request ends with ``error_step_failed``,
+        its pages go back, and the exception is raised (llm-scheduler/src/engine.rs:92-99). ``OutOfPages``
+        from a caller who shares the cache with this engine ends nothing: the step is dropped and raised,
+        and the next call schedules again."""
+        try:
+            return self._step()
+        except OutOfPages:
+            raise
+        except Exception:
+            # A step that was queued earlier may still be in flight: its tokens were sampled and are
+            # reported, and the scheduler closes its batch, before everything is aborted.
+            outs: List[Output] = []
+            if self._inflight is not None:
+                flight, self._inflight = self._inflight, None
+                try:
+                    outs += self._collect(flight)
+                except Exception:
+                    pass            # its tokens cannot be read either; abort_all closes its batch
+            outs += self.scheduler.abort_all()
+            for o in outs:
+                self._events.setdefault(o.request_id, []).append(o)
+            raise
+
+    def _step(self) -> List[Tuple[int, Optional[int], bool]]:
         batch = self.scheduler.schedule()
         launched = None
         if batch:
@@ -100,31 +129,25 @@ class Engine:
                                          device_token=src))
             try:
                 logits = self.runner.step(entries, token_source=prev["tokens"] if prev else None)
-                sampled = [s for s in batch if s.sample]
-                tokens = host = event = None
-                if sampled:
-                    rows = [(s.request.params, s.request.request_id, len(s.request.output) + s.request.n_inflight,
-                             s.request.tokens() if s.request.params.repetition_penalty != 1.0 else ())
-                            for s in sampled]
-                    tokens = self.sampler.sample(logits, rows)
-                    host = self._token_buffer(len(sampled))
-                    host.copy_(tokens, non_blocking=True)
-                    event = torch.cuda.Event()
-                    event.record()
-            except Exception:
-                # The step before this one may still be in flight: its tokens were sampled and are
-                # reported, and the scheduler closes its batch, before everything is aborted.
-                outs = []
-                if self._inflight is not None:
-                    flight, self._inflight = self._inflight, None
-                    try:
-                        outs += self._collect(flight)
-                    except Exception:
-                        pass            # its tokens cannot be read either; abort_all closes its batch
-                outs += self.scheduler.abort_all()
-                for o in outs:
-                    self._events.setdefault(o.request_id, []).append(o)
+            except OutOfPages:
+                self.scheduler.cancel(batch)
                 raise
+            sampled = [s for s in batch if s.sample]
+            tokens = None
+            if sampled:
+                rows = [(s.request.params, s.request.request_id, len(s.request.output) + s.request.n_inflight,
+                         s.request.tokens() if s.request.params.repetition_penalty != 1.0 else ())
+                        for s in sampled]
+                tokens = self.sampler.sample(logits, rows)
+            # The step's tokens and, behind them, the kernels' error word: one pinned buffer.
+            n = len(sampled)
+            host = self._token_buffer(n + 1)
+            if n:
+                host[:n].copy_(tokens, non_blocking=True)
+            host[n:].copy_(self._error_word, non_blocking=True)
+            self.d2h_bytes += 4 * (n + 1)
+            event = torch.cuda.Event()
+            event.record()
             self.scheduler.on_launched(batch)
             n_dec = sum(1 for s in batch if len(s.tokens) == 1 and s.sample)
             n_pre = sum(len(s.tokens) for s in batch) - n_dec
@@ -138,14 +161,15 @@ class Engine:
                         "row_of": {s.request.request_id: i for i, s in enumerate(sampled)}}
         outs: List[Output] = []
         if self._inflight is not None:
-            outs += self._collect(self._inflight)
+            flight, self._inflight = self._inflight, launched
+            outs += self._collect(flight)
         self._inflight = launched
         # Read this step's tokens at once when the caller asked for that, or when a request
         # needs its full history on the host for the next step (repetition penalty).
         if launched is not None and (not self.config.async_steps or any(
                 s.request.params.repetition_penalty != 1.0 for s in batch)):
-            outs += self._collect(launched)
             self._inflight = None
+            outs += self._collect(launched)
         if launched is None and self._inflight is None:
             outs += self.scheduler.on_result([], {})    # requests that ended without a step
         for o in outs:
@@ -162,24 +186,21 @@ class Engine:
         return buf[:n]
 
     def _collect(self, flight) -> List[Output]:
-        """Wait for a queued step's tokens and let the scheduler account for them."""
-        sampled = {}
-        if flight["event"] is not None:
-            flight["event"].synchronize()
-            values = flight["host"].tolist()
-            sampled = {rid: values[i] for rid, i in flight["row_of"].items()}
-        self._steps_since_check += 1
-        if self._steps_since_check >= 256:
-            self.check_kernels()
+        """Wait for a queued step's tokens and let the scheduler account for them. The kernels' error
+        word came with the tokens: a kernel that gave up on a bounded wait fails this very step."""
+        flight["event"].synchronize()
+        values = flight["host"].tolist()
+        if values[-1]:
+            self._error_word.zero_()
+            from ..ops import KernelError, tc_error_message
+            raise KernelError(tc_error_message(values[-1]))
+        sampled = {rid: values[i] for rid, i in flight["row_of"].items()}
         return self.scheduler.on_result(flight["batch"], sampled)
 
     def check_kernels(self) -> None:
-        """Raise if a kernel with bounded waits (tcgen05 GEMM or attention) gave up on one since
-        the last check; its step's output would be invalid. Runs every 256 steps and on demand."""
-        from .. import ops
-        self._steps_since_check = 0
-        ops.check_tc_error(self.runner.device)
-        ops.check_attention_error()
+        """Raise if a kernel with bounded waits (tcgen05 product or attention) gave up on one since the
+        last check. ``step`` sees the same word with every step's tokens; this reads it on demand."""
+        self.runner.check_kernels()
 
     # -- conveniences ----------------------------------------------------------------
     def poll(self, request_id: int) -> Output:

@@ -141,6 +141,13 @@ class ModelRunner:
         """The request is finished: its pages and its slot go back."""
         self.manager.release(request_id)
 
+    def check_kernels(self) -> None:
+        """Raise if a kernel with bounded waits (the tcgen05 products and attention) gave up on one since
+        the last check: what the steps since then returned is invalid. Synchronises."""
+        from .. import ops
+        ops.check_tc_error(self.device)
+        ops.check_attention_error()
+
     def live_requests(self) -> List[Hashable]:
         return list(self.manager.requests)
 

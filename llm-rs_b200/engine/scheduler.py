@@ -221,6 +221,12 @@ class Scheduler:
         check(self._lib.llmrs_sched_on_launched(self._handle, batch.handle))
         self._sync()
 
+    def cancel(self, batch: Batch) -> None:
+        """The batch was decided but could not be queued (another user of the cache took its pages):
+        forget it; its requests are scheduled again by the next call."""
+        if batch:
+            check(self._lib.llmrs_sched_cancel(self._handle, batch.handle))
+
     def on_result(self, batch, sampled: Dict[int, int]) -> List[Output]:
         """The step's tokens are on the host: ``sampled`` maps request id -> chosen token for
         the entries with ``sample``. Returns what happened, finished requests freed. An empty

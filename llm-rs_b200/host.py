@@ -49,6 +49,7 @@ def lib() -> ctypes.CDLL:
             "llmrs_sched_has_work": [c_void_p, intp],
             "llmrs_sched_schedule": [c_void_p, i64p, i32p, c_int, intp, i64p],
             "llmrs_sched_on_launched": [c_void_p, c_int64],
+            "llmrs_sched_cancel": [c_void_p, c_int64],
             "llmrs_sched_on_result": [c_void_p, c_int64, i32p, c_int, i64p, i32p, c_int, intp],
             "llmrs_sched_abort_all": [c_void_p, c_int, i64p, i32p, c_int, intp],
             "llmrs_sched_take": [c_void_p, c_int, i64p, c_int, intp],

@@ -213,7 +213,8 @@ def attn_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, tiles:
         _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
         _ptr(cache), _ptr(tiles), n_tiles, _ptr(q_start), _ptr(n_new), _ptr(cached_len), _ptr(block_table),
         block_table.size(1), n_q_heads, n_kv_heads, head_dim, page_size, window, ctypes.c_float(scale),
-        dtype_code(q.dtype), q.size(0), cache.size(0), 1 if prefer_tc else 0, _stream()), "attn_prefill")
+        dtype_code(q.dtype), q.size(0), cache.size(0), 1 if prefer_tc else 0, _ptr(tc_error_flag(q.device)),
+        _stream()), "attn_prefill")
 
 
 def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_splits: int) -> int:
@@ -349,13 +350,45 @@ def tc_error_flag(device) -> torch.Tensor:
     return _tc_flags[dev]
 
 
+TC_ERROR_CODES = {1: "a tcgen05 product kernel gave up waiting on a barrier",
+                  2: "the tcgen05 attention kernel gave up waiting on a barrier",
+                  3: "the tcgen05 attention kernel found its shared memory misaligned"}
+
+
+def tc_error_message(code: int) -> str:
+    return f"{TC_ERROR_CODES.get(code, 'a tcgen05 kernel failed')} (code {code}); the step's output is invalid"
+
+
 def check_tc_error(device) -> None:
-    """Raise if a tcgen05 kernel gave up on a wait since the last check (synchronises)."""
+    """Raise if a tcgen05 kernel (product or attention) gave up on a wait since the last check (synchronises)."""
     flag = tc_error_flag(device)
     code = int(flag.item())
     if code:
         flag.zero_()
-        raise KernelError(f"a tcgen05 kernel gave up waiting on a barrier (code {code}); its output is invalid")
+        raise KernelError(tc_error_message(code))
+
+
+def set_tc_wait_limit(polls: int = 0) -> None:
+    """Polls of a barrier before a wait of the tcgen05 kernels gives up; 0 restores the default (2^22)."""
+    lib = _lib()
+    for name in ("llmrs_tc_set_wait_limit", "llmrs_attention_tc_set_wait_limit"):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = None, [ctypes.c_uint]
+        fn(int(polls))
+
+
+def test_skip_copy(gemm_k_block: int = -1, attention_tile: int = -1) -> None:
+    """For the test of the bounded waits only: the next launches of the tcgen05 product kernels leave out the
+    copy of their k block ``gemm_k_block``, those of the attention kernel the keys of tile ``attention_tile``
+    (-1: every copy is made, the default)."""
+    lib = _lib()
+    for name, v in (("llmrs_tc_test_skip_copy", gemm_k_block), ("llmrs_attention_tc_test_skip_copy", attention_tile)):
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = None, [ctypes.c_int]
+        fn(int(v))
+
+
+test_skip_copy.__test__ = False     # not a test, whatever a collector makes of the name
 
 
 def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
@@ -485,7 +518,11 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 def check_attention_error() -> None:
-    """Raise if an attention kernel gave up on one of its bounded waits since the last check (synchronises)."""
+    """Raise if an attention kernel gave up on one of its bounded waits since the last check (synchronises).
+    Launches through ``attn_prefill`` report into the word that ``check_tc_error`` reads; this also looks at
+    the word inside the library, which launches without a word of the caller's use."""
+    for dev in list(_tc_flags):
+        check_tc_error(dev)
     lib = _lib()
     for name in ("llmrs_attention_tc_error",):
         fn = getattr(lib, name)

@@ -703,3 +703,78 @@ def test_gemm_norm_emission_refusals():
         ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=1, emit=(nw, xw, parts))
     with pytest.raises(ops.KernelError):      # too few rows for the pieces
         ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=4, emit=(nw, xw, parts[:1]))
+
+
+# -- bounded waits ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tokens,features,K,splits,skip", [
+    (8, 256, 256, 1, 1),        # few tokens, one block per tile; every stage is requested before the first wait
+    (8, 256, 1024, 2, 3),       # a cluster of two blocks shares the k range: both give up, both reach the cluster's barriers
+    (16, 128, 1024, 1, 9),      # the ring of six stages has wrapped: the producer is waiting for a free stage
+    (100, 128, 256, None, 2),   # tokens on the rows, one tile per block
+    (300, 512, 512, None, 5)])  # the persistent kernel: copying warp, MMA warp and epilogue warps all leave their loops
+def test_gemm_tcgen05_wait_runs_out_and_the_kernel_returns(tokens, features, K, splits, skip):
+    """A copy that never arrives (the producer leaves it out on request) with a wait limit of 1,024 polls: the
+    kernel returns by itself, the error word is set, nothing is stored where the block gave up; and the next,
+    normal launch gives the right product, so tensor memory was freed and no barrier is left waiting."""
+    ops = _ops()
+    torch.manual_seed(skip)
+    x = (torch.randn(tokens, K, device=DEV) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(features, K, device=DEV) * 0.5).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    ops.check_tc_error(DEV)
+    ops.set_tc_wait_limit(1 << 10)
+    ops.test_skip_copy(gemm_k_block=skip)
+    try:
+        ops.gemm_bf16(x, w, out_dtype=torch.float32, splits=splits)
+        torch.cuda.synchronize()            # the kernel has returned
+        with pytest.raises(ops.KernelError, match="gave up waiting"):
+            ops.check_tc_error(DEV)
+        ops.check_tc_error(DEV)             # reading the word clears it
+    finally:
+        ops.test_skip_copy()
+        ops.set_tc_wait_limit(0)
+    for _ in range(3):                      # enough launches to come by every SM again
+        got = ops.gemm_bf16(x, w, out_dtype=torch.float32, splits=splits).double()
+        assert float((got - want).abs().max()) <= 1e-5 * math.sqrt(K) * float(want.abs().max())
+    ops.check_tc_error(DEV)
+
+
+@pytest.mark.parametrize("skip", [0, 2, 4])
+def test_attention_tcgen05_wait_runs_out_and_the_kernel_returns(skip):
+    """The same for the tcgen05 prefill attention: the keys of one tile never arrive; the blocks that wait for
+    them give up after 1,024 polls, store nothing, and the error word is set. The next launch is right."""
+    ops = _ops()
+    d, nq, nkv, page, lens, new = 128, 4, 2, 16, [0, 200], [700, 520]
+    torch.manual_seed(skip)
+    table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=skip)
+    q = torch.randn(sum(new), nq * d).to(torch.bfloat16)
+    scale = 1 / math.sqrt(d)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, 0, scale)
+    dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+    q_start = torch.tensor(np.cumsum([0] + new[:-1]), dtype=torch.int32, device=DEV)
+    tiles = torch.tensor([(r, off) for r, n in enumerate(new) for off in range(0, n, 64)], dtype=torch.int32, device=DEV)
+    args = (dc, tiles, tiles.size(0), q_start, torch.tensor(new, dtype=torch.int32, device=DEV),
+            torch.tensor(lens, dtype=torch.int32, device=DEV), dt, nq, nkv, d, page, 0, scale)
+    ops.check_tc_error(DEV)
+    ops.set_tc_wait_limit(1 << 10)
+    ops.test_skip_copy(attention_tile=skip)
+    try:
+        out = torch.full((sum(new), nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attn_prefill(dq, out, *args, prefer_tc=True)
+        torch.cuda.synchronize()
+        with pytest.raises(ops.KernelError, match="attention kernel gave up"):
+            ops.check_tc_error(DEV)
+        # Blocks with more than `skip` tiles of keys gave up and stored nothing; the others are right.
+        got = out.double().cpu()
+        written = torch.isfinite(got).all(dim=1)
+        assert not written.all()
+        assert float((got[written] - want[written]).abs().max()) < 2.5e-2 if written.any() else True
+    finally:
+        ops.test_skip_copy()
+        ops.set_tc_wait_limit(0)
+    for _ in range(3):
+        out = torch.full((sum(new), nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.attn_prefill(dq, out, *args, prefer_tc=True)
+        got = out.double().cpu()
+        assert torch.isfinite(got).all() and float((got - want).abs().max()) < 2.5e-2
+    ops.check_attention_error()

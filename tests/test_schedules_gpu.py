@@ -163,3 +163,39 @@ def test_requests_end_at_eos_under_async_steps(models, graphs, tmp_path):
         assert e.requests[rid].output == g
         assert e.finish_reason(rid) == ("stop" if g[-1] == eos else "length")
     assert not e.runner.manager.requests and e.runner.manager.free_pages(0) == 32
+
+
+# -- a kernel that gives up fails the step it is in ---------------------------------------------------
+def test_kernel_error_surfaces_with_the_steps_tokens(models):
+    """The tcgen05 product kernel is made to give up on a wait (its producer leaves out a copy, the limit is
+    1,024 polls) during one decode step of a running engine: that step's call or the next raises, every
+    running request ends with ``error_step_failed``, all pages come back, and the engine serves new requests
+    afterwards with the right tokens."""
+    from llm_rs_b200 import ops
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w = models["D"]
+    rng = np.random.default_rng(41)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in (20, 33)]
+    e = Engine(EngineConfig(model_path=path, block_pool_size=32, page_size=16, dtype="bfloat16", max_requests=4,
+                            max_tokens_per_step=64, prefill_chunk=64, cuda_graphs=False, async_steps=True))
+    ids = [e.add_request(p, SamplingParams(temperature=0.0, max_new_tokens=40, ignore_eos=True)) for p in prompts]
+    for _ in range(4):
+        e.step()
+    assert all(e.requests[i].output for i in ids)
+    ops.set_tc_wait_limit(1 << 10)
+    ops.test_skip_copy(gemm_k_block=1)
+    try:
+        with pytest.raises(ops.KernelError, match="gave up waiting"):
+            for _ in range(3):          # the failing step's tokens are read one call later
+                e.step()
+    finally:
+        ops.test_skip_copy()
+        ops.set_tc_wait_limit(0)
+    torch.cuda.synchronize()
+    ops.tc_error_flag(DEV).zero_()      # steps that were queued behind the failing one set it again
+    assert all(e.finish_reason(i) == "error_step_failed" for i in ids)
+    assert not e.runner.manager.requests and e.runner.manager.free_pages(0) == 32
+    assert not e.has_work()
+    got = e.generate([prompts[0]], SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True))[0]
+    assert P.greedy_gap(cfg, w, prompts[0], got) < 0.05
