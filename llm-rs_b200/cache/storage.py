@@ -1,9 +1,11 @@
 """Device memory of the cache: pages of keys and values per group, state per slot.
 
-One group's pages are one tensor ``[entries, n_pages, n_kv_heads, 2, page_size, head_dim]``
-in the activation type: the keys of one (page, head) are ``page_size * head_dim``
-contiguous elements and its values follow them, so a kernel fetches a tile with one
-straight copy. Fixed-size state is ``[n_slots, *shape]`` float32 per run-order entry
+One group's pages are one tensor ``[entries, n_pages, n_kv_heads, page_size * sum(widths)]`` in the
+activation type, ``widths`` being the group's planes (``CacheNeed.plane_widths``): the rows of one
+(page, head, plane) are ``page_size * width`` contiguous elements and a head's planes follow one
+another, so a kernel fetches a tile with one straight copy. For the usual two planes of equal width
+(keys and values) that is ``[entries, n_pages, n_kv_heads, 2, page_size, head_dim]``, which is the
+view attention gets. Fixed-size state is ``[n_slots, *shape]`` float32 per run-order entry
 that asked for it, zeroed when a request takes the slot.
 """
 from __future__ import annotations
@@ -46,10 +48,11 @@ def plan_groups(needs: Sequence[Tuple[Optional[CacheNeed], Optional[StateNeed]]]
 
 class LayerCache:
     """What a mixer sees of the cache for one run-order entry in one step."""
-    __slots__ = ("kv", "block_table", "page_size", "owns", "state", "group")
+    __slots__ = ("kv", "planes", "block_table", "page_size", "owns", "state", "group")
 
-    def __init__(self, kv, block_table, page_size, owns, state, group):
-        self.kv = kv                    # [n_pages, n_kv_heads, 2, page_size, head_dim] or None
+    def __init__(self, kv, planes, block_table, page_size, owns, state, group):
+        self.kv = kv                    # [n_pages, n_kv_heads, 2, page_size, head_dim] (two equal planes) or None
+        self.planes = planes            # per plane: [n_pages, n_kv_heads, page_size, width] (a view), or None
         self.block_table = block_table  # int32 [requests of the step, pages] or None
         self.page_size = page_size
         self.owns = owns                # False: reads another entry's keys and values, writes none
@@ -63,9 +66,10 @@ class CacheStorage:
         self.page_size, self.n_slots, self.dtype, self.device = page_size, n_slots, dtype, device
         self.run_order = list(run_order)
         self.groups, self.entry_group, self.entry_index = plan_groups(needs, run_order, n_pages)
-        self.kv: List[torch.Tensor] = []
+        self._view_cache: Dict[tuple, tuple] = {}
+        self.kv: List[torch.Tensor] = []      # per group: [entries, pages, heads, page_size * sum(widths)]
         for g in self.groups:
-            shape = (len(g.entries), g.n_pages, g.need.n_kv_heads, 2, page_size, g.need.head_dim)
+            shape = (len(g.entries), g.n_pages, g.need.n_kv_heads, page_size * sum(g.need.plane_widths))
             self.kv.append(torch.zeros(shape, dtype=dtype, device=device))
         self.state: List[Dict[str, torch.Tensor]] = []
         for s, (_, st) in enumerate(needs):
@@ -102,5 +106,22 @@ class CacheStorage:
         src = self.run_order[s].cache_of
         state = self.state[s if src is None else src]
         if g is None:
-            return LayerCache(None, None, self.page_size, src is None, state, None)
-        return LayerCache(self.kv[g][i], block_tables[g], self.page_size, src is None, state, g)
+            return LayerCache(None, None, None, self.page_size, src is None, state, None)
+        kv, planes = self._views(g, i)
+        return LayerCache(kv, planes, block_tables[g], self.page_size, src is None, state, g)
+
+    def _views(self, g: int, i: int):
+        """The views of entry ``i`` of group ``g`` that a mixer gets (made once: they do not change)."""
+        views = self._view_cache.get((g, i))
+        if views is None:
+            flat = self.kv[g][i]                                    # [pages, heads, page_size * sum(widths)]
+            widths = self.groups[g].need.plane_widths
+            planes, at = [], 0
+            for w in widths:
+                planes.append(flat[:, :, at:at + self.page_size * w].unflatten(2, (self.page_size, w)))
+                at += self.page_size * w
+            kv = None
+            if len(widths) == 2 and widths[0] == widths[1]:
+                kv = flat.view(flat.size(0), flat.size(1), 2, self.page_size, widths[0])
+            views = self._view_cache[(g, i)] = (kv, planes)
+        return views

@@ -114,21 +114,32 @@ int llmrs_cm_check_invariants(void* cm) {
 
 int llmrs_pack_step(void* cm, int n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens,
                     const int32_t* n_want, const int32_t* want, const int32_t* device_token, int table_round,
-                    int prefill_tile, int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
-                    int32_t* widths, int32_t* shape8, int64_t* total, int* written) {
+                    int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
+                    int32_t* widths, int32_t* shape4, int64_t* total, int* written) {
     return guarded([&] {
         StepShape s;
         bool ok = pack_step(*as<CacheManager>(cm, "manager"), n_entries, ids, n_tokens, tokens, n_want, want,
-                            device_token, table_round, prefill_tile, out, capacity, offsets, sizes, widths, &s);
-        shape8[0] = s.n_tokens;
-        shape8[1] = s.n_requests;
-        shape8[2] = s.n_want;
-        shape8[3] = s.n_prefill_tiles;
-        shape8[4] = s.n_decode;
-        shape8[5] = s.max_decode_kv_len;
-        shape8[6] = s.long_portions;
-        shape8[7] = 0;
+                            device_token, table_round, out, capacity, offsets, sizes, widths, &s);
+        shape4[0] = s.n_tokens;
+        shape4[1] = s.n_requests;
+        shape4[2] = s.n_want;
+        shape4[3] = 0;
         *total = s.total;
+        *written = ok ? 1 : 0;
+    });
+}
+
+int llmrs_plan_paged_attention(int n_requests, const int32_t* n_new, const int32_t* cached_len, int tile,
+                               int32_t* tiles_out, int64_t tiles_capacity, int32_t* decode_out,
+                               int64_t decode_capacity, int32_t* plan4, int* written) {
+    return guarded([&] {
+        AttentionPlan a;
+        bool ok = plan_paged_attention(n_requests, n_new, cached_len, tile, tiles_out, tiles_capacity, decode_out,
+                                       decode_capacity, &a);
+        plan4[0] = a.n_tiles;
+        plan4[1] = a.n_decode;
+        plan4[2] = a.max_decode_kv_len;
+        plan4[3] = a.long_portions;
         *written = ok ? 1 : 0;
     });
 }

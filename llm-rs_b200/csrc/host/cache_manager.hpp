@@ -96,24 +96,39 @@ private:
 // Where each array of a packed step lies in the step's int32 buffer.
 enum StepArray : int {
     kTokenIds = 0, kPositions, kTokenReq, kQStart, kNNew, kCachedLen, kSlotIds, kWantRows,
-    kPrefillTiles, kDecodeReqs, kPendDst, kPendSrc, kFirstTable  // kFirstTable + g: block table of group g
+    kPendDst, kPendSrc, kFirstTable  // kFirstTable + g: block table of group g
 };
 
 struct StepShape {
-    int n_tokens = 0, n_requests = 0, n_want = 0, n_prefill_tiles = 0, n_decode = 0;
-    int max_decode_kv_len = 0, long_portions = 0;
+    int n_tokens = 0, n_requests = 0, n_want = 0;
     int64_t total = 0;  // int32 elements the packed step takes
 };
 
-// Packs the index arrays of one step (tokens, positions, request rows, per-request
-// lengths, wanted rows, prefill tiles, decode list, pending device tokens, block tables
-// padded to `table_round` pages) into `out`. Every array starts at a multiple of 4
+// Packs the index arrays of one step that every part may read (tokens, positions, request rows,
+// per-request lengths, wanted rows, pending device tokens, block tables padded to `table_round`
+// pages) into `out`. What a mixer plans for itself (tiles, lists, cuts) is not in here: it comes
+// from the mixer's own plan and is appended by the caller. Every array starts at a multiple of 4
 // elements. offsets/sizes have kFirstTable + n_groups entries; widths has n_groups.
 // Returns false, with shape->total set, when `capacity` is too small (nothing is written).
 bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const int32_t* n_tokens,
                const int32_t* tokens, const int32_t* n_want, const int32_t* want,
-               const int32_t* device_token, int table_round, int prefill_tile,
+               const int32_t* device_token, int table_round,
                int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes, int32_t* widths,
                StepShape* shape);
+
+// The plan of paged attention for one step, from the step's per-request numbers alone: requests
+// that bring one token go to the decode list, longer portions are cut into tiles of `tile`
+// queries (request row, offset of the tile's first query).
+struct AttentionPlan {
+    int n_tiles = 0, n_decode = 0;
+    int max_decode_kv_len = 0;   // most keys a decoding request sees (its cached length + 1)
+    int long_portions = 0;       // blocks of 128 queries would be at least half full on average
+};
+
+// tiles_out holds 2 * tiles_capacity ints, decode_out decode_capacity ints. Returns false (and only
+// the counts in *plan) when either is too small.
+bool plan_paged_attention(int n_requests, const int32_t* n_new, const int32_t* cached_len, int tile,
+                          int32_t* tiles_out, int64_t tiles_capacity, int32_t* decode_out,
+                          int64_t decode_capacity, AttentionPlan* plan);
 
 }  // namespace llmrs_host

@@ -39,14 +39,21 @@ int llmrs_cm_table(void* cm, int64_t id, int group, int32_t* out, int capacity, 
 int llmrs_cm_pool_counts(void* cm, int group, int* free_pages, int* capacity);
 int llmrs_cm_check_invariants(void* cm);
 
-/* Packs one step (layout: see StepArray in cache_manager.hpp). shape8 receives n_tokens,
- * n_requests, n_want, n_prefill_tiles, n_decode, max_decode_kv_len, long_portions, 0;
- * *total the int32 elements needed. When capacity < *total nothing is written and
- * *written is 0. */
+/* Packs the index arrays of one step that every part may read (layout: see StepArray in
+ * cache_manager.hpp). shape4 receives n_tokens, n_requests, n_want, 0; *total the int32 elements
+ * needed. When capacity < *total nothing is written and *written is 0. */
 int llmrs_pack_step(void* cm, int n_entries, const int64_t* ids, const int32_t* n_tokens, const int32_t* tokens,
                     const int32_t* n_want, const int32_t* want, const int32_t* device_token, int table_round,
-                    int prefill_tile, int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
-                    int32_t* widths, int32_t* shape8, int64_t* total, int* written);
+                    int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes,
+                    int32_t* widths, int32_t* shape4, int64_t* total, int* written);
+
+/* The plan of paged attention for one step: requests with one new token go to decode_out, longer
+ * portions are cut into tiles of `tile` queries, written to tiles_out as (request row, offset)
+ * pairs. plan4 receives n_tiles, n_decode, max_decode_kv_len, long_portions. When a capacity
+ * (in tiles, in requests) is too small nothing is written and *written is 0. */
+int llmrs_plan_paged_attention(int n_requests, const int32_t* n_new, const int32_t* cached_len, int tile,
+                               int32_t* tiles_out, int64_t tiles_capacity, int32_t* decode_out,
+                               int64_t decode_capacity, int32_t* plan4, int* written);
 
 /* The scheduler (decisions only; see scheduler.hpp). It reads the cache manager `cm`, which must
  * outlive it, and never changes it: after every call that returns `n_release > 0` ids through

@@ -16,30 +16,21 @@ int64_t round_up(int64_t n, int64_t m) { return (n + m - 1) / m * m; }
 
 bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const int32_t* n_tokens,
                const int32_t* tokens, const int32_t* n_want, const int32_t* want,
-               const int32_t* device_token, int table_round, int prefill_tile,
+               const int32_t* device_token, int table_round,
                int32_t* out, int64_t capacity, int64_t* offsets, int64_t* sizes, int32_t* widths,
                StepShape* shape) {
     if (n_entries < 1) throw Failure{kBadArgument, "a step needs at least one entry"};
-    if (table_round < 1 || prefill_tile < 1) throw Failure{kBadArgument, "table_round and prefill_tile must be positive"};
+    if (table_round < 1) throw Failure{kBadArgument, "table_round must be positive"};
     const int G = cm.n_groups();
     const int R = n_entries;
     std::vector<const Record*> recs(R);
-    int64_t T = 0, W = 0, tiles = 0, dec = 0, long_blocks = 0, long_tokens = 0;
-    int max_dec_kv = 0;
+    int64_t T = 0, W = 0;
     for (int r = 0; r < R; ++r) {
         recs[r] = &cm.record(ids[r]);
         int n = n_tokens[r];
         if (n < 1) throw Failure{kBadArgument, "an entry brings no tokens"};
         T += n;
         W += n_want[r];
-        if (n == 1) {
-            ++dec;
-            max_dec_kv = std::max(max_dec_kv, recs[r]->cached_len + 1);
-        } else {
-            tiles += (n + prefill_tile - 1) / prefill_tile;
-            long_blocks += (n + 127) / 128;
-            long_tokens += n;
-        }
     }
     for (int g = 0; g < G; ++g) {
         size_t widest = 0;
@@ -50,8 +41,6 @@ bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const 
     sizes[kTokenIds] = sizes[kPositions] = sizes[kTokenReq] = T;
     sizes[kQStart] = sizes[kNNew] = sizes[kCachedLen] = sizes[kSlotIds] = R;
     sizes[kWantRows] = W;
-    sizes[kPrefillTiles] = 2 * tiles;
-    sizes[kDecodeReqs] = dec;
     sizes[kPendDst] = sizes[kPendSrc] = R;
     for (int g = 0; g < G; ++g) sizes[kFirstTable + g] = static_cast<int64_t>(R) * widths[g];
     int64_t total = 0;
@@ -62,11 +51,6 @@ bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const 
     shape->n_tokens = static_cast<int>(T);
     shape->n_requests = R;
     shape->n_want = static_cast<int>(W);
-    shape->n_prefill_tiles = static_cast<int>(tiles);
-    shape->n_decode = static_cast<int>(dec);
-    shape->max_decode_kv_len = max_dec_kv;
-    // Blocks of 128 queries pay off when the portions fill them at least half on average.
-    shape->long_portions = long_blocks > 0 && long_tokens >= 64 * long_blocks;
     shape->total = total;
     if (total > capacity || out == nullptr) return false;
 
@@ -78,11 +62,9 @@ bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const 
     int32_t* cached = out + offsets[kCachedLen];
     int32_t* slots = out + offsets[kSlotIds];
     int32_t* want_rows = out + offsets[kWantRows];
-    int32_t* tile_list = out + offsets[kPrefillTiles];
-    int32_t* dec_list = out + offsets[kDecodeReqs];
     int32_t* pend_dst = out + offsets[kPendDst];
     int32_t* pend_src = out + offsets[kPendSrc];
-    int64_t at = 0, w_at = 0, t_at = 0, d_at = 0, want_in = 0;
+    int64_t at = 0, w_at = 0, want_in = 0;
     for (int r = 0; r < R; ++r) {
         const Record& rec = *recs[r];
         int n = n_tokens[r];
@@ -101,14 +83,6 @@ bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const 
             want_rows[w_at++] = static_cast<int32_t>(at + w);
         }
         want_in += n_want[r];
-        if (n == 1) {
-            dec_list[d_at++] = r;
-        } else {
-            for (int off = 0; off < n; off += prefill_tile) {
-                tile_list[t_at++] = r;
-                tile_list[t_at++] = off;
-            }
-        }
         if (device_token != nullptr && device_token[r] >= 0) {
             // The entry's single token is still on the device: a kernel copies it in.
             pend_dst[r] = static_cast<int32_t>(at);
@@ -128,6 +102,44 @@ bool pack_step(const CacheManager& cm, int n_entries, const int64_t* ids, const 
             int32_t* row = tab + static_cast<int64_t>(r) * width;
             std::copy(table.begin(), table.end(), row);
             std::fill(row + table.size(), row + width, kReleased);
+        }
+    }
+    return true;
+}
+
+bool plan_paged_attention(int n_requests, const int32_t* n_new, const int32_t* cached_len, int tile,
+                          int32_t* tiles_out, int64_t tiles_capacity, int32_t* decode_out,
+                          int64_t decode_capacity, AttentionPlan* plan) {
+    if (n_requests < 0 || tile < 1) throw Failure{kBadArgument, "attention plan: bad sizes"};
+    int64_t tiles = 0, dec = 0, long_blocks = 0, long_tokens = 0;
+    int max_dec_kv = 0;
+    for (int r = 0; r < n_requests; ++r) {
+        const int n = n_new[r];
+        if (n == 1) {
+            ++dec;
+            max_dec_kv = std::max(max_dec_kv, cached_len[r] + 1);
+        } else if (n > 1) {
+            tiles += (n + tile - 1) / tile;
+            long_blocks += (n + 127) / 128;
+            long_tokens += n;
+        }
+    }
+    plan->n_tiles = static_cast<int>(tiles);
+    plan->n_decode = static_cast<int>(dec);
+    plan->max_decode_kv_len = max_dec_kv;
+    // Blocks of 128 queries pay off when the portions fill them at least half on average.
+    plan->long_portions = long_blocks > 0 && long_tokens >= 64 * long_blocks;
+    if (tiles > tiles_capacity || dec > decode_capacity) return false;
+    int64_t t_at = 0, d_at = 0;
+    for (int r = 0; r < n_requests; ++r) {
+        const int n = n_new[r];
+        if (n == 1) {
+            decode_out[d_at++] = r;
+        } else {
+            for (int off = 0; off < n; off += tile) {
+                tiles_out[t_at++] = r;
+                tiles_out[t_at++] = off;
+            }
         }
     }
     return true;

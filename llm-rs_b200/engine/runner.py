@@ -27,9 +27,8 @@ from ..cache.pool import check
 from ..cache.storage import CacheStorage
 from ..config import load_config
 from ..parts import DecoderModel, ModelSpec, Runtime
+from ..parts.base import Plan, StepInfo
 from ..weights import load_weights
-
-PREFILL_TILE = 64  # queries per entry of the prefill attention kernels' tile list
 
 
 class StepError(RuntimeError):
@@ -48,6 +47,14 @@ class StepEntry:
     device_token: int = -1
 
 
+class PlanView:
+    """A mixer's plan as ``forward`` sees it: ``arrays`` on the device, ``values`` on the host."""
+    __slots__ = ("arrays", "values")
+
+    def __init__(self, arrays, values):
+        self.arrays, self.values = arrays, values
+
+
 class StepContext:
     """Everything a part may read about the current step. Device tensors are int32."""
 
@@ -56,12 +63,11 @@ class StepContext:
         self._scratch_bufs = runner._scratch_bufs
         self.act_dtype = runner.act_dtype
         self.n_tokens = self.n_requests = self.n_want = 0
-        self.n_prefill_tiles = self.n_decode = self.max_decode_kv_len = 0
-        self.long_portions = False
         self.token_ids = self.positions = self.token_req = None
         self.q_start = self.n_new = self.cached_len = self.slot_ids = None
-        self.want_rows = self.prefill_tiles = self.decode_reqs = None
+        self.want_rows = None
         self.block_tables: List[Optional[torch.Tensor]] = []
+        self.plans: Dict[Hashable, PlanView] = {}
         # Host copies, for parts that plan their work on the host.
         self.host_n_new: List[int] = []
         self.host_cached_len: List[int] = []
@@ -71,6 +77,10 @@ class StepContext:
 
     def layer_cache(self, s: int):
         return self._runner.storage.layer_cache(s, self.block_tables)
+
+    def plan(self, key) -> PlanView:
+        """What the mixer with this ``plan_key()`` planned for the step (``Mixer.plan``)."""
+        return self.plans[key]
 
     def scratch(self, name: str, n_floats: int) -> torch.Tensor:
         """Float32 workspace that lives across steps (grown when a step needs more). A step
@@ -95,10 +105,13 @@ class ModelRunner:
         self.page_size = page_size
         self.max_requests = max_requests
         n_pages = max(1, -(-max_tokens // page_size))
-        self.max_positions = min(spec.max_positions, n_pages * page_size)
         self.model = DecoderModel(spec)
-        self.model.bind(tensors, Runtime(self.device, act_dtype, self.max_positions))
         needs = self.model.cache_needs()
+        # A request can grow as far as the model allows and as its pages reach: only a group that keeps
+        # every token bounds it by the pool; a window group gives pages back as it goes, state takes none.
+        keeps_all = any(need is not None and need.kind != "window" for need, _ in needs)
+        self.max_positions = min(spec.max_positions, n_pages * page_size) if keeps_all else spec.max_positions
+        self.model.bind(tensors, Runtime(self.device, act_dtype, self.max_positions))
         self.storage = CacheStorage(needs, spec.run_order, page_size, n_pages, max_requests, act_dtype, self.device)
         self.manager = CacheManager(self.storage.groups, page_size, max_requests)
         self._scratch_bufs: Dict[str, torch.Tensor] = {}
@@ -114,7 +127,14 @@ class ModelRunner:
         # feed-forward, its norms, or the block itself).
         self._graph_safe = all(getattr(part, "graph_safe", True)
                                for b in self.model.blocks for part in [b, *getattr(b, "parts", list)()])
-        # Captured steps by (batch size, wanted rows, table widths), least recently used first; a
+        # Mixers that plan per step, one per plan key, in run order (``Mixer.plan_key`` / ``Mixer.plan``).
+        self._planners: "OrderedDict[Hashable, object]" = OrderedDict()
+        for step in spec.run_order:
+            mixer = getattr(self.model.blocks[step.layer], "mixer", None)
+            key = mixer.plan_key() if mixer is not None and hasattr(mixer, "plan_key") else None
+            if key is not None and key not in self._planners:
+                self._planners[key] = mixer
+        # Captured steps by (batch size, wanted rows, table widths, plans' shapes), least recently used first; a
         # captured step keeps its own logits and workspace, so their number is bounded.
         self._graphs: "OrderedDict[tuple, _DecodeGraph]" = OrderedDict()
         self.max_graphs = 48
@@ -195,10 +215,11 @@ class ModelRunner:
             raise
         return admitted
 
-    def _pack(self, entries: Sequence[StepEntry], table_round: int) -> "_PackedStep":
-        """Pack the step's index arrays into pinned host memory (the host library does it:
-        tokens, positions, request rows, per-request lengths, wanted rows, prefill tiles,
-        decode list, tokens still on the device, block tables padded to ``table_round``)."""
+    def _pack(self, entries: Sequence[StepEntry], table_round: int, for_graph: bool = False) -> "_PackedStep":
+        """Pack the step's index arrays into pinned host memory: the host library writes what every part
+        may read (tokens, positions, request rows, per-request lengths, wanted rows, tokens still on the
+        device, block tables padded to ``table_round``); then every mixer that plans (``Mixer.plan``) is asked
+        once per plan key, and its arrays are appended to the same buffer."""
         R = len(entries)
         G = len(self.manager.groups)
         T = sum(len(e.tokens) for e in entries)
@@ -211,28 +232,55 @@ class ModelRunner:
         offsets = np.empty(host.FIRST_TABLE + G, np.int64)
         sizes = np.empty(host.FIRST_TABLE + G, np.int64)
         widths = np.empty(max(G, 1), np.int32)
-        shape = np.empty(8, np.int32)
+        shape = np.empty(4, np.int32)
         total, written = ctypes.c_int64(), ctypes.c_int()
         flip = self._meta_flip
         self._meta_flip ^= 1
         if self._meta_events[flip] is not None:
             self._meta_events[flip].synchronize()  # the copy that last read this buffer is done
         lib = host.lib()
+        need = 0
         while True:
             buf = self._meta_host[flip]
             cap = 0 if buf is None else buf.numel()
-            check(lib.llmrs_pack_step(
-                self.manager._handle, R, numbers.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data,
-                n_want.ctypes.data, want.ctypes.data, device_token.ctypes.data, table_round, PREFILL_TILE,
-                0 if buf is None else buf.data_ptr(), cap, offsets.ctypes.data, sizes.ctypes.data,
-                widths.ctypes.data, shape.ctypes.data, ctypes.byref(total), ctypes.byref(written)),
-                self.manager._names)
-            if written.value:
-                break
-            self._meta_host[flip] = torch.empty((_round_up(total.value, 4096),), dtype=torch.int32).pin_memory()
+            if cap >= need:
+                check(lib.llmrs_pack_step(
+                    self.manager._handle, R, numbers.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data,
+                    n_want.ctypes.data, want.ctypes.data, device_token.ctypes.data, table_round,
+                    0 if buf is None else buf.data_ptr(), cap, offsets.ctypes.data, sizes.ctypes.data,
+                    widths.ctypes.data, shape.ctypes.data, ctypes.byref(total), ctypes.byref(written)),
+                    self.manager._names)
+                need = total.value
+                if written.value:
+                    # The mixers' plans go behind the common arrays, each array at a multiple of four ints.
+                    host_np = buf.numpy()
+                    off, sz = offsets.tolist(), sizes.tolist()
+                    plans, at = {}, need
+                    if self._planners:
+                        info = StepInfo(
+                            n_tokens=T, n_requests=R, q_start=host_np[off[host.Q_START]:off[host.Q_START] + R],
+                            n_new=host_np[off[host.N_NEW]:off[host.N_NEW] + R],
+                            cached_len=host_np[off[host.CACHED_LEN]:off[host.CACHED_LEN] + R],
+                            slot_ids=host_np[off[host.SLOT_IDS]:off[host.SLOT_IDS] + R],
+                            block_tables=[host_np[off[host.FIRST_TABLE + g]:off[host.FIRST_TABLE + g] + sz[host.FIRST_TABLE + g]]
+                                          .reshape(R, -1) for g in range(G)],
+                            group_keys=[g.need.group_key() for g in self.manager.groups],
+                            page_size=self.page_size, for_graph=for_graph)
+                        for key, mixer in self._planners.items():
+                            plan = mixer.plan(info)
+                            where = {}
+                            for name, arr in plan.arrays.items():
+                                where[name] = (at, int(arr.size))
+                                at += _round_up(max(int(arr.size), 1), 4)
+                            plans[key] = (plan, where)
+                    if at <= cap:
+                        for plan, where in plans.values():
+                            for name, (o, n) in where.items():
+                                host_np[o:o + n] = plan.arrays[name].reshape(-1)
+                        return _PackedStep(buf, flip, at, off, sz, widths[:G].tolist(), shape.tolist(), plans)
+                    need = at
+            self._meta_host[flip] = torch.empty((_round_up(need + 1024, 4096),), dtype=torch.int32).pin_memory()
             self._meta_events[flip] = None
-        return _PackedStep(self._meta_host[flip], flip, int(total.value), offsets.tolist(), sizes.tolist(),
-                           widths[:G].tolist(), shape.tolist())
 
     def _upload(self, packed: "_PackedStep", entries: Sequence[StepEntry],
                 graph: Optional["_DecodeGraph"] = None) -> StepContext:
@@ -253,7 +301,7 @@ class ModelRunner:
         ev = torch.cuda.Event()
         ev.record()
         self._meta_events[packed.flip] = ev
-        T, R, n_want, n_tiles, n_dec, max_dec_kv, long_portions = packed.shape[:7]
+        T, R, n_want = packed.shape[:3]
         host_np = packed.host.numpy()
 
         def host_list(i):
@@ -263,7 +311,7 @@ class ModelRunner:
                           request_ids=[e.request_id for e in entries])
         if graph is not None and graph.ctx is not None:
             graph.ctx.__dict__.update(host_lists)
-            return graph.ctx  # its device views already point into graph.meta
+            return graph.ctx  # its device views already point into graph.meta; its plans' values are the key's
 
         def view(i):
             return dev[offsets[i]:offsets[i] + sizes[i]]
@@ -273,16 +321,10 @@ class ModelRunner:
         ctx.q_start, ctx.n_new = view(host.Q_START), view(host.N_NEW)
         ctx.cached_len, ctx.slot_ids = view(host.CACHED_LEN), view(host.SLOT_IDS)
         ctx.want_rows = view(host.WANT_ROWS)
-        ctx.n_prefill_tiles = n_tiles
-        ctx.long_portions = bool(long_portions)
-        ctx.prefill_tiles = view(host.PREFILL_TILES).view(-1, 2) if n_tiles else view(host.PREFILL_TILES)
-        ctx.n_decode = n_dec
-        ctx.decode_reqs = view(host.DECODE_REQS)
-        ctx.max_decode_kv_len = max_dec_kv
+        for key, (plan, where) in packed.plans.items():
+            arrays = {name: dev[o:o + n].view(plan.arrays[name].shape) for name, (o, n) in where.items()}
+            ctx.plans[key] = PlanView(arrays, dict(plan.values))
         if graph is not None:
-            # Captured launch sizes must hold for every step that replays the graph.
-            if packed.widths:
-                ctx.max_decode_kv_len = max(packed.widths) * self.page_size
             ctx._scratch_bufs = graph.scratch
             graph.ctx = ctx
         ctx.pend_dst, ctx.pend_src = view(host.PEND_DST), view(host.PEND_SRC)
@@ -333,8 +375,11 @@ class ModelRunner:
             ops.scatter_tokens(ctx.token_ids, ctx.pend_dst, token_source, ctx.pend_src)
 
     def _graph_step(self, entries: Sequence[StepEntry], token_source=None) -> Optional[torch.Tensor]:
-        packed = self._pack(entries, GRAPH_TABLE_ROUND)
-        key = (len(entries), tuple(len(e.want) for e in entries), tuple(packed.widths))
+        packed = self._pack(entries, GRAPH_TABLE_ROUND, for_graph=True)
+        # Everything that sizes a captured launch is in the key: the batch, the wanted rows, the tables'
+        # widths, and the shapes and values of the mixers' plans.
+        key = (len(entries), tuple(len(e.want) for e in entries), tuple(packed.widths),
+               tuple((k, plan.signature()) for k, (plan, _) in packed.plans.items()))
         graph = self._graphs.get(key)
         if graph is not None:
             self._graphs.move_to_end(key)
@@ -385,6 +430,7 @@ class _PackedStep:
     sizes: List[int]
     widths: List[int]
     shape: List[int]
+    plans: Dict[Hashable, tuple] = field(default_factory=dict)   # plan key -> (Plan, {array name: (offset, size)})
 
 
 class _DecodeGraph:

@@ -12,8 +12,8 @@ from .csrc import build as _build
 OK, CACHE_ERROR, OUT_OF_PAGES, NO_FREE_SLOT, BAD_ARGUMENT = range(5)
 
 # Order of the arrays in a packed step (StepArray in csrc/host/cache_manager.hpp).
-(TOKEN_IDS, POSITIONS, TOKEN_REQ, Q_START, N_NEW, CACHED_LEN, SLOT_IDS, WANT_ROWS, PREFILL_TILES, DECODE_REQS,
- PEND_DST, PEND_SRC, FIRST_TABLE) = range(13)
+(TOKEN_IDS, POSITIONS, TOKEN_REQ, Q_START, N_NEW, CACHED_LEN, SLOT_IDS, WANT_ROWS, PEND_DST, PEND_SRC,
+ FIRST_TABLE) = range(11)
 
 _configured = False
 
@@ -57,7 +57,9 @@ def lib() -> ctypes.CDLL:
             "llmrs_sched_forget": [c_void_p, c_int64],
             "llmrs_sched_stats": [c_void_p, i64p],
             "llmrs_pack_step": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, i64p, intp],
+                                c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, i64p, intp],
+            "llmrs_plan_paged_attention": [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                           c_void_p, intp],
         }
         for name, argtypes in sigs.items():
             fn = getattr(library, name)
@@ -65,6 +67,26 @@ def lib() -> ctypes.CDLL:
             fn.restype = None if name.endswith("_destroy") else c_int
         _configured = True
     return library
+
+
+def plan_paged_attention(n_new, cached_len, tile: int):
+    """The host library's plan of paged attention for a step (int32 numpy arrays of the step's requests in,
+    ``(tiles [n, 2], decode list, max_decode_kv_len, long_portions)`` out)."""
+    import numpy as np
+    R = int(n_new.shape[0])
+    # Requests that bring one token take no tile: n // tile + 1 bounds a longer portion's tiles.
+    tiles_cap = int(n_new.sum()) // tile + R
+    tiles = np.empty((max(tiles_cap, 1), 2), np.int32)
+    decode = np.empty(max(R, 1), np.int32)
+    plan = np.zeros(4, np.int32)
+    written = c_int()
+    n_new = np.ascontiguousarray(n_new, np.int32)
+    cached_len = np.ascontiguousarray(cached_len, np.int32)
+    rc = lib().llmrs_plan_paged_attention(R, n_new.ctypes.data, cached_len.ctypes.data, tile, tiles.ctypes.data,
+                                          tiles_cap, decode.ctypes.data, R, plan.ctypes.data, byref(written))
+    if rc != 0 or not written.value:
+        raise RuntimeError(f"attention plan failed: {last_error() if rc else 'capacity'}")
+    return tiles[:plan[0]], decode[:plan[1]], int(plan[2]), bool(plan[3])
 
 
 def last_error() -> str:

@@ -7,8 +7,10 @@ from typing import Optional
 
 import torch
 
-from .. import ops
-from .base import Mixer, PositionEncoding, PreNormed, Runtime
+import numpy as np
+
+from .. import host, ops
+from .base import Mixer, Plan, PositionEncoding, PreNormed, Runtime, StepInfo
 from .linear import Linear
 from .registry import build, register
 from .spec import CacheNeed, PartSpec, WeightSpec
@@ -27,6 +29,7 @@ _FUSE_QKV_ROPE = os.environ.get("LLMRS_FUSE_QKV_ROPE", "1") != "0"
 FIXED_KEYS = 192
 CAPACITY_USED = 0.975   # of the blocks the device holds: 256 of 264 ran in one wave, 280 of 280 did not
 MAX_CLUSTER = 16     # splits that the kernel merges itself
+PREFILL_TILE = 64    # queries per entry of the prefill attention kernels' tile list
 
 
 def cut_keys(length: int, units: int, capacity) -> int:
@@ -74,12 +77,16 @@ class GQAttention(Mixer):
 
     The q/k/v weights are concatenated at load so that one product makes all three. The
     output projection may add its result straight into the residual stream.
+
+    ``names`` maps the part's roles (q, k, v, o, q_norm, k_norm) to the tensors' names after the prefix,
+    without ".weight" / ".bias"; an architecture's spec builder gives the names its checkpoints use.
     """
     fuses_residual = True
+    ROLES = ("q", "k", "v", "o", "q_norm", "k_norm")
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, qk_norm: bool = True, qk_norm_eps: float = 1e-6, bias: bool = False,
-                 window: int = 0, scale: Optional[float] = None, split_keys: int = 0, prefix: str = ""):
+                 window: int = 0, scale: Optional[float] = None, split_keys: int = 0, names=None, prefix: str = ""):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
         if head_dim % 16:
@@ -89,48 +96,69 @@ class GQAttention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.split_keys = int(split_keys)   # keys per split of decode attention; 0: chosen per step
         self.prefix = prefix
+        self.names = {role: role for role in self.ROLES}
+        self.names.update(names or {})
+        if set(self.names) != set(self.ROLES):
+            raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
         self.position = build("position", position, prefix=prefix)
         self.q_width, self.kv_width = n_heads * head_dim, n_kv_heads * head_dim
 
     # -- weights ---------------------------------------------------------------------
+    def _name(self, role: str, kind: str = "weight") -> str:
+        return f"{self.prefix}{self.names[role]}.{kind}"
+
     def weight_specs(self):
-        p, H = self.prefix, self.hidden_size
-        specs = [WeightSpec(p + "q_proj.weight", (self.q_width, H)),
-                 WeightSpec(p + "k_proj.weight", (self.kv_width, H)),
-                 WeightSpec(p + "v_proj.weight", (self.kv_width, H)),
-                 WeightSpec(p + "o_proj.weight", (H, self.q_width))]
+        H, nm = self.hidden_size, self._name
+        specs = [WeightSpec(nm("q"), (self.q_width, H)), WeightSpec(nm("k"), (self.kv_width, H)),
+                 WeightSpec(nm("v"), (self.kv_width, H)), WeightSpec(nm("o"), (H, self.q_width))]
         if self.bias:
-            specs += [WeightSpec(p + "q_proj.bias", (self.q_width,), role="bias"),
-                      WeightSpec(p + "k_proj.bias", (self.kv_width,), role="bias"),
-                      WeightSpec(p + "v_proj.bias", (self.kv_width,), role="bias"),
-                      WeightSpec(p + "o_proj.bias", (H,), role="bias", optional=True)]
+            specs += [WeightSpec(nm("q", "bias"), (self.q_width,), role="bias"),
+                      WeightSpec(nm("k", "bias"), (self.kv_width,), role="bias"),
+                      WeightSpec(nm("v", "bias"), (self.kv_width,), role="bias"),
+                      WeightSpec(nm("o", "bias"), (H,), role="bias", optional=True)]
         if self.qk_norm:
-            specs += [WeightSpec(p + "q_norm.weight", (self.head_dim,), role="norm"),
-                      WeightSpec(p + "k_norm.weight", (self.head_dim,), role="norm")]
+            specs += [WeightSpec(nm("q_norm"), (self.head_dim,), role="norm"),
+                      WeightSpec(nm("k_norm"), (self.head_dim,), role="norm")]
         return specs + self.position.weight_specs()
 
     def bind(self, tensors, runtime: Runtime):
-        p = self.prefix
+        nm = self._name
         self.act_dtype = runtime.act_dtype
-        ws = [tensors[p + f"{n}_proj.weight"] for n in "qkv"]
+        ws = [tensors[nm(r)] for r in "qkv"]
         dt = ws[0].dtype if all(w.dtype == ws[0].dtype for w in ws) else torch.float32
         wqkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         bqkv = None
         if self.bias:
-            bqkv = torch.cat([tensors[p + f"{n}_proj.bias"].to(dt) for n in "qkv"], dim=0).contiguous()
+            bqkv = torch.cat([tensors[nm(r, "bias")].to(dt) for r in "qkv"], dim=0).contiguous()
         self.qkv_proj = Linear(wqkv, bqkv, runtime.act_dtype)
         # The query rows alone, for run-order entries that read another entry's cache.
         self.q_proj = Linear(wqkv[: self.q_width], None if bqkv is None else bqkv[: self.q_width], runtime.act_dtype)
-        self.o_proj = Linear(tensors[p + "o_proj.weight"], tensors.get(p + "o_proj.bias"), runtime.act_dtype)
+        self.o_proj = Linear(tensors[nm("o")], tensors.get(nm("o", "bias")), runtime.act_dtype)
         self.q_norm_w = self.k_norm_w = None
         if self.qk_norm:
-            self.q_norm_w = tensors[p + "q_norm.weight"].to(torch.float32).contiguous()
-            self.k_norm_w = tensors[p + "k_norm.weight"].to(torch.float32).contiguous()
+            self.q_norm_w = tensors[nm("q_norm")].to(torch.float32).contiguous()
+            self.k_norm_w = tensors[nm("k_norm")].to(torch.float32).contiguous()
         self.position.bind(tensors, runtime)
 
     # -- cache -----------------------------------------------------------------------
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.n_kv_heads, self.head_dim, self.window)
+
+    # -- the step's plan ---------------------------------------------------------------
+    def plan_key(self):
+        return ("paged_attention", PREFILL_TILE)    # the same for every layer: one plan per step
+
+    def plan(self, step: StepInfo) -> Plan:
+        """Requests that bring one token go to the decode kernel, longer portions are cut into tiles of
+        queries for the prefill kernel (the host library does it). A step that will be replayed from a CUDA
+        graph sizes its decode launch by the block tables' width, which the graph's key holds, instead of the
+        longest request."""
+        tiles, decode, max_kv, long_portions = host.plan_paged_attention(step.n_new, step.cached_len, PREFILL_TILE)
+        if step.for_graph and decode.size and step.block_tables:
+            max_kv = max(t.shape[1] for t in step.block_tables) * step.page_size
+        return Plan(arrays={"prefill_tiles": tiles, "decode_reqs": decode},
+                    values={"n_prefill_tiles": int(tiles.shape[0]), "n_decode": int(decode.size),
+                            "max_decode_kv_len": int(max_kv), "long_portions": int(long_portions)})
 
     def _fuses_rope(self, x, cache, cos_sin) -> bool:
         """True when the q|k|v product can take norms, rotation and cache write as its epilogue."""
@@ -193,18 +221,20 @@ class GQAttention(Mixer):
                                      table, cache.kv if cache.owns else None, nq, nkv, d, self.position.rotary_dim,
                                      cache.page_size, self.qk_norm_eps)
         out = torch.empty((ctx.n_tokens, self.q_width), dtype=q.dtype, device=q.device)
-        if ctx.n_prefill_tiles:
-            ops.attn_prefill(q, out, cache.kv, ctx.prefill_tiles, ctx.n_prefill_tiles, ctx.q_start, ctx.n_new,
+        plan = ctx.plan(self.plan_key())
+        n_tiles, n_decode, max_kv = (plan.values[k] for k in ("n_prefill_tiles", "n_decode", "max_decode_kv_len"))
+        if n_tiles:
+            ops.attn_prefill(q, out, cache.kv, plan.arrays["prefill_tiles"], n_tiles, ctx.q_start, ctx.n_new,
                              ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale,
-                             prefer_tc=ctx.long_portions and _ATTN_TC)
-        if ctx.n_decode:
-            split_keys = self.split_keys or self._choose_split(ctx.n_decode, ctx.max_decode_kv_len, q)
-            max_splits = max(1, -(-ctx.max_decode_kv_len // split_keys))
-            scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(ctx.n_decode, nq, d, max_splits))
+                             prefer_tc=bool(plan.values["long_portions"]) and _ATTN_TC)
+        if n_decode:
+            split_keys = self.split_keys or self._choose_split(n_decode, max_kv, q)
+            max_splits = max(1, -(-max_kv // split_keys))
+            scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(n_decode, nq, d, max_splits))
             # Up to eight splits form a thread-block cluster and merge inside the kernel; more are merged by
             # a second, small kernel. (Merging them in the split kernel's last block,
             # ops.attn_decode(counters=...), measured no faster inside the step and slower at batch 1.)
-            ops.attn_decode(q, out, cache.kv, ctx.decode_reqs, ctx.n_decode, ctx.q_start, ctx.cached_len, table,
+            ops.attn_decode(q, out, cache.kv, plan.arrays["decode_reqs"], n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
                             self.scale)
         if next_norm is not None:

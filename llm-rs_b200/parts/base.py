@@ -10,7 +10,10 @@ Life of a part:  construct -> ``weight_specs()`` tells the loader which tensors 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional
+from typing import TYPE_CHECKING, Dict, List, Optional
+
+if TYPE_CHECKING:
+    import numpy as np
 
 import torch
 
@@ -23,6 +26,46 @@ class Runtime:
     device: torch.device
     act_dtype: torch.dtype          # bfloat16 or float32: type of activations and of the cache
     max_positions: int              # positions 0 .. max_positions-1 can occur
+
+
+@dataclass
+class StepInfo:
+    """What a mixer's ``plan`` may read about a step, on the host, before anything is launched.
+    The arrays are int32 numpy views that are only valid during the call."""
+    n_tokens: int
+    n_requests: int
+    q_start: "np.ndarray"        # per request: index of its first token in the step
+    n_new: "np.ndarray"          # per request: tokens it brings
+    cached_len: "np.ndarray"     # per request: tokens it has cached before the step
+    slot_ids: "np.ndarray"       # per request: its state slot
+    block_tables: List["np.ndarray"]   # per cache group: [requests, width], -1 where a page was released
+    group_keys: List[tuple]      # per cache group: the ``CacheNeed.group_key()`` its entries share
+    page_size: int
+    for_graph: bool              # the step will be captured in a CUDA graph and replayed (see ``Plan``)
+
+    def table_of(self, need: CacheNeed) -> "np.ndarray":
+        """The block table of the group that a mixer with this need writes to."""
+        return self.block_tables[self.group_keys.index(need.group_key())]
+
+
+@dataclass
+class Plan:
+    """What a mixer has planned for a step.
+
+    ``arrays``  int32 numpy arrays; they travel to the device in the same copy as the step's other index
+                arrays and reach ``forward`` as device tensors (``ctx.plan(key).arrays[name]``).
+    ``values``  host integers that size launches (``ctx.plan(key).values[name]``).
+
+    A step of single tokens may be captured in a CUDA graph and replayed for later steps. The graph is chosen by
+    the batch's shape AND by every plan's array sizes and values, so a replayed launch always sees the sizes
+    it was captured with; array CONTENTS are fresh at every replay. With ``StepInfo.for_graph`` a plan should
+    therefore round its values up to what the batch's shape implies (say, a table's width instead of the longest
+    request), or every step captures a graph of its own."""
+    arrays: Dict[str, "np.ndarray"]
+    values: Dict[str, int]
+
+    def signature(self):
+        return (tuple(sorted((k, int(v.size)) for k, v in self.arrays.items())), tuple(sorted(self.values.items())))
 
 
 class Part:
@@ -109,6 +152,18 @@ class Mixer(Part):
 
     def state_need(self) -> Optional[StateNeed]:
         return None
+
+    def plan_key(self):
+        """A hashable name for the plan this mixer wants per step, or None for none. Mixers with equal keys
+        share one plan (it is made once per step, by the first of them in the run order): put into the key
+        whatever the plan depends on."""
+        return None
+
+    def plan(self, step: "StepInfo") -> "Plan":
+        """Host work for one step, done once before anything is launched (see ``Plan``). ``forward`` finds the
+        result under ``ctx.plan(self.plan_key())``. A mixer whose ``forward`` itself works on the host
+        (loops over requests, reads ``ctx.host_*``) sets ``graph_safe = False`` instead."""
+        raise NotImplementedError
 
     def forward(self, x, ctx, cache):
         raise NotImplementedError

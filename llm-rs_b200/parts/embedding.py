@@ -15,7 +15,7 @@ class TokenEmbedding(Part):
     """``h0[t] = table[id_t]``, no scale (llm-core/src/graph/builder.rs:8-14,
     llm-core/src/backends/candle.rs:1238-1261). The result is the float32 residual stream."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "model.embed_tokens.weight", prefix: str = ""):
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "embedding.weight", prefix: str = ""):
         self.vocab_size, self.hidden_size, self.name = vocab_size, hidden_size, prefix + name
 
     def weight_specs(self):
@@ -36,7 +36,7 @@ class LinearHead(Part):
     buffer, used by both. A tied model's folder may still store the head's matrix (a copy of the
     table); it is accepted and not read."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, name: str = "lm_head.weight", tied_to: str = "",
+    def __init__(self, vocab_size: int, hidden_size: int, name: str = "head.weight", tied_to: str = "",
                  prefix: str = ""):
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
         self.name, self.tied_to = prefix + name, tied_to

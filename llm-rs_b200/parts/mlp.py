@@ -23,21 +23,29 @@ class SwiGLU(FeedForward):
     inside the product's epilogue when the tcgen05 kernel runs, else as one kernel. For
     that epilogue the rows alternate 64 of gate and the 64 matching of up (when the
     intermediate size is a multiple of 128); the output may be added straight into the
-    residual stream."""
+    residual stream. ``names`` maps the roles gate, up and down to the tensors' names after the prefix
+    (without ".weight"); an architecture's spec builder gives the names its checkpoints use."""
 
     fuses_residual = True
+    ROLES = ("gate", "up", "down")
 
-    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = ""):
+    def __init__(self, hidden_size: int, intermediate_size: int, names=None, prefix: str = ""):
         self.hidden_size, self.intermediate_size, self.prefix = hidden_size, intermediate_size, prefix
+        self.names = {role: role for role in self.ROLES}
+        self.names.update(names or {})
+        if set(self.names) != set(self.ROLES):
+            raise ValueError(f"names may rename {self.ROLES}, got {sorted(set(self.names) - set(self.ROLES))}")
+
+    def _name(self, role: str) -> str:
+        return f"{self.prefix}{self.names[role]}.weight"
 
     def weight_specs(self):
-        p, H, I = self.prefix, self.hidden_size, self.intermediate_size
-        return [WeightSpec(p + "gate_proj.weight", (I, H)), WeightSpec(p + "up_proj.weight", (I, H)),
-                WeightSpec(p + "down_proj.weight", (H, I))]
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self._name("gate"), (I, H)), WeightSpec(self._name("up"), (I, H)),
+                WeightSpec(self._name("down"), (H, I))]
 
     def bind(self, tensors, runtime: Runtime):
-        p = self.prefix
-        g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        g, u = tensors[self._name("gate")], tensors[self._name("up")]
         dt = g.dtype if g.dtype == u.dtype else torch.float32
         self.block = 0      # columns of gate and up alternate in runs of this many (0: all gate, then all up)
         if dt == torch.bfloat16 and self.intermediate_size % 128 == 0 and self.hidden_size % 8 == 0:
@@ -46,7 +54,7 @@ class SwiGLU(FeedForward):
         else:
             w = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.gate_up = Linear(w, None, runtime.act_dtype)
-        self.down = Linear(tensors[p + "down_proj.weight"], None, runtime.act_dtype)
+        self.down = Linear(tensors[self._name("down")], None, runtime.act_dtype)
 
     def takes_prenormed(self, n_tokens: int) -> bool:
         return bool(self.block) and self.gate_up.tc_enabled() and FUSE_GATE_UP and 0 < n_tokens <= 32

@@ -24,7 +24,9 @@ class LayerSpec:
 
     ``prefix`` is put before every weight name of the layer's parts
     (``model.layers.3.``); the mixer's and the feed-forward's names get their scope
-    after it (``model.layers.3.self_attn.q_proj.weight``).
+    after it (``model.layers.3.self_attn.q_proj.weight``). Scopes and the parts' own tensor names
+    (their ``names`` parameter) come from the architecture's spec builder: the parts' defaults are
+    neutral role names.
     """
     prefix: str
     block: PartSpec
@@ -32,8 +34,8 @@ class LayerSpec:
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
-    mixer_scope: str = "self_attn."
-    feed_forward_scope: str = "mlp."
+    mixer_scope: str = ""
+    feed_forward_scope: str = ""
 
 
 @dataclass(frozen=True)
@@ -97,16 +99,27 @@ class WeightSpec:
 class CacheNeed:
     """What a mixer asks of the paged cache for one run-order entry.
 
-    kind "full": every earlier key stays. kind "window": only the last ``window`` keys
-    are read, pages wholly behind the window are given back.
+    kind "full": every earlier token's rows stay. kind "window": only the last ``window`` tokens'
+    rows are read, pages wholly behind the window are given back.
+
+    A token stores, for each of ``n_kv_heads`` heads, one row per plane; ``planes`` gives the rows'
+    widths. The default () means two planes of ``head_dim`` each: keys and values. A mixer that caches
+    one latent row per token asks for ``n_kv_heads=1, planes=(width,)``; keys and values of different
+    widths are ``planes=(dk, dv)``. Within a page the rows of one (head, plane) are contiguous
+    ([page_size, width]) and a head's planes follow one another.
     """
     kind: str
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    planes: Tuple[int, ...] = ()
+
+    @property
+    def plane_widths(self) -> Tuple[int, ...]:
+        return tuple(self.planes) if self.planes else (self.head_dim, self.head_dim)
 
     def group_key(self) -> Tuple:
-        return (self.kind, self.n_kv_heads, self.head_dim, self.window)
+        return (self.kind, self.n_kv_heads, self.plane_widths, self.window)
 
 
 @dataclass(frozen=True)

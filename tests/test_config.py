@@ -118,3 +118,32 @@ def test_spec_has_no_architecture_constants():
     assert [l.mixer.params["position"].kind for l in spec.layers] == ["rope_half"] * 3 + ["none"]
     assert spec.layers[1].mixer.params["bias"] is True
     assert [s.layer for s in spec.run_order] == [0, 1, 2, 3]
+
+
+def test_parts_take_their_tensor_names_from_the_spec():
+    """The parts know roles; which tensor plays a role is the architecture's data. The same parts with another
+    name map (and other scopes) ask the loader for other tensors."""
+    import dataclasses
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel, PartSpec
+    spec = build_spec(Qwen3Config.from_dict(TINY_A))
+    names = {s.name for s in DecoderModel(spec).weight_specs()}
+    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.layers.1.mlp.down_proj.weight" in names
+    other = []
+    for l in spec.layers:
+        mixer = PartSpec(l.mixer.kind, {**l.mixer.params, "names": {"q": "wq", "k": "wk", "v": "wv", "o": "wo",
+                                                                    "q_norm": "qn", "k_norm": "kn"}})
+        ffn = PartSpec(l.feed_forward.kind, {**l.feed_forward.params, "names": {"gate": "w1", "up": "w3", "down": "w2"}})
+        other.append(dataclasses.replace(l, mixer=mixer, feed_forward=ffn, mixer_scope="attention.",
+                                         feed_forward_scope="feed_forward.", prefix=l.prefix.replace("model.layers", "blocks")))
+    renamed = dataclasses.replace(
+        spec, layers=tuple(other),
+        embedding=PartSpec("token_embedding", {**spec.embedding.params, "name": "tok.weight"}),
+        lm_head=PartSpec("linear_head", {**spec.lm_head.params, "tied_to": "tok.weight"}))
+    names = {s.name for s in DecoderModel(renamed).weight_specs() if s.load}
+    assert {"tok.weight", "blocks.0.attention.wq.weight", "blocks.1.attention.qn.weight",
+            "blocks.1.feed_forward.w2.weight"} <= names
+    assert not any("q_proj" in n or "mlp" in n or "embed_tokens" in n for n in names)
+    with pytest.raises(ValueError, match="names may rename"):
+        DecoderModel(dataclasses.replace(spec, layers=(spec.layers[0], dataclasses.replace(spec.layers[1], mixer=PartSpec(
+            "gqa_attention", {**spec.layers[1].mixer.params, "names": {"query": "x"}})))))

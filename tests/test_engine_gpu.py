@@ -323,7 +323,9 @@ def test_part_rmsnorm_and_swiglu_alone(dtype):
     y = norm.forward(h.clone(), None)
     assert torch.allclose(y.double().cpu(), P.rms_norm(h.double().cpu(), wn.double(), 2e-6), **tol)
 
-    ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200}), prefix="m.")
+    ffn = build("feed_forward", PartSpec("swiglu", {"hidden_size": 72, "intermediate_size": 200, "names": {
+        "gate": "gate_proj", "up": "up_proj", "down": "down_proj"}}), prefix="m.")
+    assert sorted(s.name for s in ffn.weight_specs()) == ["m.down_proj.weight", "m.gate_proj.weight", "m.up_proj.weight"]
     ws = {s.name: (torch.randn(s.shape) * 0.1).to(dtype).to(DEV) for s in ffn.weight_specs()}
     ffn.bind(ws, _runtime(dtype))
     x = torch.randn(5, 72).to(dtype)
@@ -507,6 +509,208 @@ def test_toy_mixer_with_state_plugs_in(models):
         assert n == sum(len(t) for t in reqs.values()) and worst < 1e-4, (worst, where)
     finally:
         unregister("mixer", "toy_running_mean")
+
+
+# -- the same toy kept on the device: CUDA graphs, and a warm-up that must not count twice -----------
+def test_toy_stateful_mixer_under_cuda_graphs(models):
+    """A mixer with per-request state that it updates on the device (nothing of its step is planned on the host):
+    its decode steps are captured in CUDA graphs like anyone's. The step that captures a graph runs the model
+    twice (once to size the workspace, once as the first replay); the state must move once."""
+    import dataclasses
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner, StepEntry
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel, Mixer, PartSpec, StateNeed, WeightSpec, register, unregister
+    from llm_rs_b200.weights import open_model_files
+
+    @register("mixer", "toy_running_mean_device", replace=True)
+    class RunningMeanOnDevice(Mixer):
+        """out_t = W * mean(x_0..x_t) per request; state = (sum of inputs, count). Steps of single tokens touch
+        the device only (index arithmetic on the step's device arrays); longer portions loop on the host, which
+        is fine outside a graph (only steps of single tokens are captured)."""
+
+        def __init__(self, hidden_size, prefix=""):
+            self.hidden_size, self.prefix = hidden_size, prefix
+
+        def weight_specs(self):
+            return [WeightSpec(self.prefix + "mix.weight", (self.hidden_size, self.hidden_size))]
+
+        def state_need(self):
+            return StateNeed({"sum": (self.hidden_size,), "count": (1,)})
+
+        def bind(self, tensors, runtime):
+            self.w = tensors[self.prefix + "mix.weight"].float()
+
+        def forward(self, x, ctx, cache):
+            total, count = cache.state["sum"], cache.state["count"]
+            if ctx.n_tokens == ctx.n_requests:                  # one token per request: request r is row r
+                slots = ctx.slot_ids.long()
+                total.index_add_(0, slots, x.float())
+                count.index_add_(0, slots, torch.ones_like(x[:, :1], dtype=torch.float32))
+                return ((total[slots] / count[slots]) @ self.w.t()).to(x.dtype)
+            out = torch.empty_like(x)
+            for r in range(ctx.n_requests):
+                a, n, slot = ctx.host_q_start[r], ctx.host_n_new[r], ctx.host_slot_ids[r]
+                run = total[slot] + torch.cumsum(x[a:a + n].float(), 0)
+                cnt = count[slot] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)[:, None]
+                out[a:a + n] = ((run / cnt) @ self.w.t()).to(x.dtype)
+                total[slot], count[slot] = run[-1], cnt[-1]
+            return out
+
+    try:
+        path, cfg, w = models["A"]
+        spec = build_spec(Qwen3Config.from_dict(cfg))
+        toy = dataclasses.replace(spec.layers[1], mixer=PartSpec("toy_running_mean_device", {"hidden_size": 64}),
+                                  mixer_scope="toy.")
+        spec = dataclasses.replace(spec, layers=(spec.layers[0], toy))
+        names = [s.name for s in DecoderModel(spec).weight_specs()]
+        f = open_model_files(path)[0]
+        tensors = {n: f.tensor(n).float().to(DEV) for n in names if n in f.names()}
+        mixw = torch.randn(64, 64, generator=torch.Generator().manual_seed(1)) * 0.05
+        tensors["model.layers.1.toy.mix.weight"] = mixw.to(DEV)
+        runner = ModelRunner(spec, tensors, torch.float32, DEV, max_tokens=512, page_size=16, max_requests=4)
+        runner.use_graphs = True
+        assert runner._graph_safe
+
+        def plain(toks):
+            h = P.embedding(w["model.embed_tokens.weight"], toks)
+            h = P.decoder_layer(h, w, 0, cfg, list(range(len(toks))), 0)
+            x = P.rms_norm(h, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+            mean = torch.cumsum(x, 0) / torch.arange(1, len(toks) + 1, dtype=torch.float64)[:, None]
+            h = h + mean @ mixw.double().t()
+            h = h + P.swiglu(P.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"]),
+                             w, "model.layers.1.mlp.")
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
+
+        rng = np.random.default_rng(6)
+        seqs = [rng.integers(0, 256, 40).tolist() for _ in range(3)]
+        refs = [plain(s).numpy() for s in seqs]
+        for r, s in enumerate(seqs):
+            runner.step([StepEntry(r, s[:9 + r], [])])
+        worst = 0.0
+        # Every request decodes every token; the batch's make-up changes, so that graphs of several sizes are
+        # captured, each at a step whose state must not move twice.
+        at = [9, 10, 11]
+        step = 0
+        while min(at) < 40:
+            live = [r for r in range(3) if at[r] < 40 and (step % 4 != r)]
+            if live:
+                rows = runner.step([StepEntry(r, [seqs[r][at[r]]], [0]) for r in live]).cpu().numpy()
+                for k, r in enumerate(live):
+                    worst = max(worst, float(np.abs(rows[k] - refs[r][at[r]]).max()))
+                    at[r] += 1
+            step += 1
+        assert len(runner._graphs) >= 2, "the decode steps were not captured"
+        assert worst < 1e-4, worst
+    finally:
+        unregister("mixer", "toy_running_mean_device")
+
+
+# -- a toy mixer that caches one latent row per token and plans its step on the host ------------------
+def test_toy_latent_cache_mixer_with_a_plan(models):
+    """A mixer that stores ONE row of 24 numbers per token in the paged cache (one head, one plane: neither
+    keys and values nor equal widths) and mixes by a causal mean over the cached rows. Where a token's row goes
+    and which rows a token reads is planned on the host once per step (``plan``) and reaches ``forward`` as
+    device arrays. Registered from this file; storage, cache manager, packer and runner are not touched."""
+    import dataclasses
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import CacheNeed, DecoderModel, Mixer, PartSpec, Plan, WeightSpec, register, unregister
+    from llm_rs_b200.weights import open_model_files
+    L = 24
+
+    @register("mixer", "toy_latent_mean", replace=True)
+    class LatentMean(Mixer):
+        """latent_t = W_in x_t is cached; out_t = W_out mean(latent_0..latent_t)."""
+
+        def __init__(self, hidden_size, latent, prefix=""):
+            self.H, self.L, self.prefix = hidden_size, latent, prefix
+
+        def weight_specs(self):
+            return [WeightSpec(self.prefix + "in.weight", (self.L, self.H)), WeightSpec(self.prefix + "out.weight", (self.H, self.L))]
+
+        def bind(self, tensors, runtime):
+            self.w_in, self.w_out = tensors[self.prefix + "in.weight"].float(), tensors[self.prefix + "out.weight"].float()
+
+        def cache_need(self):
+            return CacheNeed("full", n_kv_heads=1, head_dim=self.L, planes=(self.L,))
+
+        def plan_key(self):
+            return ("toy_latent_mean", self.cache_need().group_key())
+
+        def plan(self, step):
+            # Flat row index (page * page_size + place) of every new token, and of every row each request reads.
+            table, P_ = step.table_of(self.cache_need()), step.page_size
+            write, read, read_start = [], [], [0]
+            for r in range(step.n_requests):
+                c, n = int(step.cached_len[r]), int(step.n_new[r])
+                pos = np.arange(c + n)
+                rows = table[r, pos // P_].astype(np.int64) * P_ + pos % P_
+                write.append(rows[c:])
+                read.append(rows)
+                read_start.append(read_start[-1] + c + n)
+            return Plan(arrays={"write": np.concatenate(write).astype(np.int32), "read": np.concatenate(read).astype(np.int32),
+                                "read_start": np.asarray(read_start, np.int32)},
+                        values={"n_read": read_start[-1]})
+
+        def forward(self, x, ctx, cache):
+            plan = ctx.plan(self.plan_key())
+            rows = cache.planes[0]                         # [pages, 1, page_size, L]: a view into the pool
+            assert cache.kv is None and rows.shape[1:] == (1, cache.page_size, self.L)
+            pages, place = plan.arrays["write"].long() // cache.page_size, plan.arrays["write"].long() % cache.page_size
+            rows[pages, 0, place] = (x.float() @ self.w_in.t()).to(rows.dtype)
+            rd = plan.arrays["read"].long()
+            seen = rows[rd // cache.page_size, 0, rd % cache.page_size].float()      # [n_read, L]
+            out = torch.empty((ctx.n_tokens, self.H), dtype=torch.float32, device=x.device)
+            starts = plan.arrays["read_start"].tolist()
+            for r in range(ctx.n_requests):
+                a, n, c = ctx.host_q_start[r], ctx.host_n_new[r], ctx.host_cached_len[r]
+                mine = seen[starts[r]:starts[r + 1]]
+                mean = torch.cumsum(mine, 0)[c:] / torch.arange(c + 1, c + n + 1, device=x.device)[:, None]
+                out[a:a + n] = mean @ self.w_out.t()
+            return out.to(x.dtype)
+
+        graph_safe = False      # forward reads host lists
+
+    try:
+        path, cfg, w = models["A"]
+        spec = build_spec(Qwen3Config.from_dict(cfg))
+        toy = dataclasses.replace(spec.layers[1], mixer=PartSpec("toy_latent_mean", {"hidden_size": 64, "latent": L}),
+                                  mixer_scope="toy.")
+        spec = dataclasses.replace(spec, layers=(spec.layers[0], toy))
+        names = [s.name for s in DecoderModel(spec).weight_specs()]
+        f = open_model_files(path)[0]
+        tensors = {n: f.tensor(n).float().to(DEV) for n in names if n in f.names()}
+        g = torch.Generator().manual_seed(2)
+        w_in, w_out = torch.randn(L, 64, generator=g) * 0.2, torch.randn(64, L, generator=g) * 0.2
+        tensors["model.layers.1.toy.in.weight"], tensors["model.layers.1.toy.out.weight"] = w_in.to(DEV), w_out.to(DEV)
+
+        def plain(toks):
+            h = P.embedding(w["model.embed_tokens.weight"], toks)
+            h = P.decoder_layer(h, w, 0, cfg, list(range(len(toks))), 0)
+            x = P.rms_norm(h, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+            lat = x @ w_in.double().t()
+            mean = torch.cumsum(lat, 0) / torch.arange(1, len(toks) + 1, dtype=torch.float64)[:, None]
+            h = h + mean @ w_out.double().t()
+            h = h + P.swiglu(P.rms_norm(h, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"]),
+                             w, "model.layers.1.mlp.")
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]), w["model.embed_tokens.weight"])
+
+        rng = np.random.default_rng(12)
+        reqs = {f"r{i}": rng.integers(0, 256, n).tolist() for i, n in enumerate((50, 23, 64, 9, 40))}
+        ref = {r: plain(t).numpy() for r, t in reqs.items()}
+        steps = RU.mixed(reqs, seed=3, max_live=3)
+        runner = ModelRunner(spec, tensors, torch.float32, DEV, max_tokens=RU.live_token_peak(steps), page_size=16,
+                             max_requests=3)
+        assert [g.need.plane_widths for g in runner.storage.groups] == [(16, 16), (L,)]
+        assert runner.storage.kv[1].shape == (1, runner.storage.groups[1].n_pages, 1, 16 * L)
+        got = RU.run_steps(runner, steps)
+        worst, where, n = RU.max_diff(got, ref)
+        assert n == sum(len(t) for t in reqs.values()) and worst < 1e-4, (worst, where)
+        assert all(p.free_pages() == p.capacity for p in runner.manager.pools)
+    finally:
+        unregister("mixer", "toy_latent_mean")
 
 
 # -- a toy feed-forward with routing, defined here ---------------------------------------------------

@@ -199,3 +199,31 @@ def test_kernel_error_surfaces_with_the_steps_tokens(models):
     assert not e.has_work()
     got = e.generate([prompts[0]], SamplingParams(temperature=0.0, max_new_tokens=6, ignore_eos=True))[0]
     assert P.greedy_gap(cfg, w, prompts[0], got) < 0.05
+
+
+# -- a model whose layers all look through a window: the pool does not bound the context --------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_all_window_model_runs_far_beyond_its_pool(models, dtype, tmp_path):
+    """Every layer sees the last 24 keys only, so pages behind the window go back while the request runs: a
+    sequence of 500 tokens runs through a pool of 160, in portions and then token by token."""
+    from llm_rs_b200.config import Qwen3Config
+    from llm_rs_b200.engine import ModelRunner
+    from llm_rs_b200.weights import write_random_model
+    from tiny_configs import TINY_C
+    raw = dict(TINY_C, use_sliding_window=True, sliding_window=24, max_window_layers=0, no_rope_layers=[False] * 4)
+    path = write_random_model(str(tmp_path / "all_window"), Qwen3Config.from_dict(raw), seed=8, sigma=0.05, norm_jitter=0.1)
+    cfg, w = P.load_model_dir(path)
+    assert P.layer_windows(cfg) == [24] * 4
+    toks = np.random.default_rng(3).integers(0, cfg["vocab_size"], 500).tolist()
+    ref = {"a": P.forward(cfg, w, toks).numpy()}
+    runner = ModelRunner.from_model_dir(path, dtype=dtype, max_tokens=160, page_size=16, max_requests=2)
+    assert runner.max_positions == cfg["max_position_embeddings"] > 160
+    steps = RU.portions({"a": toks[:300]}, sizes=(7, 2, 13, 5, 2, 31, 3, 17, 2, 64))
+    steps[-1]["end"] = []
+    steps += [{"entries": [{"id": "a", "tokens": [t], "want": [0]}], "end": []} for t in toks[300:]]
+    steps[-1]["end"] = ["a"]
+    got = RU.run_steps(runner, steps)
+    worst, where, n = RU.max_diff(got, ref)
+    assert n == 500
+    assert worst <= _tol(dtype, ref["a"]), (worst, where)
+    assert runner.manager.free_pages(0) == 10

@@ -12,7 +12,7 @@ from llm_rs_b200.cache import CacheManager, GroupSpec, RELEASED
 from llm_rs_b200.parts import CacheNeed
 
 
-def pack(manager, entries, table_round, tile, capacity=1 << 16):
+def pack(manager, entries, table_round, capacity=1 << 16):
     """entries: (request id, tokens, want, device_token). Returns (arrays by index, shape, widths) or the size needed."""
     R, G = len(entries), len(manager.groups)
     numbers = np.array([manager.record(e[0]).number for e in entries], np.int64)
@@ -23,10 +23,10 @@ def pack(manager, entries, table_round, tile, capacity=1 << 16):
     dev_tok = np.array([e[3] for e in entries], np.int32)
     out = np.full(capacity, 12345, np.int32)
     offsets, sizes = np.zeros(host.FIRST_TABLE + G, np.int64), np.zeros(host.FIRST_TABLE + G, np.int64)
-    widths, shape = np.zeros(max(G, 1), np.int32), np.zeros(8, np.int32)
+    widths, shape = np.zeros(max(G, 1), np.int32), np.zeros(4, np.int32)
     total, written = ctypes.c_int64(), ctypes.c_int()
     rc = host.lib().llmrs_pack_step(manager._handle, R, numbers.ctypes.data, n_tokens.ctypes.data, tokens.ctypes.data,
-                                    n_want.ctypes.data, want.ctypes.data, dev_tok.ctypes.data, table_round, tile,
+                                    n_want.ctypes.data, want.ctypes.data, dev_tok.ctypes.data, table_round,
                                     out.ctypes.data, capacity, offsets.ctypes.data, sizes.ctypes.data,
                                     widths.ctypes.data, shape.ctypes.data, ctypes.byref(total), ctypes.byref(written))
     if rc != 0:
@@ -40,8 +40,8 @@ def pack(manager, entries, table_round, tile, capacity=1 << 16):
     return arrays, shape.tolist(), widths[:G].tolist()
 
 
-def expected(manager, entries, table_round, tile):
-    tok, pos, treq, qs, nn, cl, sl, wr, tiles, dec, pd, ps = ([] for _ in range(12))
+def expected(manager, entries, table_round):
+    tok, pos, treq, qs, nn, cl, sl, wr, pd, ps = ([] for _ in range(10))
     at = 0
     for r, (rid, tokens, want, dev) in enumerate(entries):
         rec = manager.record(rid)
@@ -51,11 +51,6 @@ def expected(manager, entries, table_round, tile):
         treq += [r] * n
         qs.append(at), nn.append(n), cl.append(rec.cached_len), sl.append(rec.slot)
         wr += [at + w for w in want]
-        if n == 1:
-            dec.append(r)
-        else:
-            for off in range(0, n, tile):
-                tiles += [r, off]
         pd.append(at if dev >= 0 else -1), ps.append(dev if dev >= 0 else 0)
         at += n
     tables = []
@@ -63,7 +58,20 @@ def expected(manager, entries, table_round, tile):
         rows = [manager.table(e[0], g) for e in entries]
         width = -(-max(len(t) for t in rows) // table_round) * table_round
         tables.append([p for t in rows for p in t + [RELEASED] * (width - len(t))])
-    return [tok, pos, treq, qs, nn, cl, sl, wr, tiles, dec, pd, ps, *tables]
+    return [tok, pos, treq, qs, nn, cl, sl, wr, pd, ps, *tables]
+
+
+def expected_attention_plan(n_new, cached, tile):
+    tiles, dec = [], []
+    for r, n in enumerate(n_new):
+        if n == 1:
+            dec.append(r)
+        else:
+            tiles += [[r, off] for off in range(0, n, tile)]
+    portions = [n for n in n_new if n > 1]
+    blocks = sum(-(-n // 128) for n in portions)
+    return tiles, dec, max([c + 1 for n, c in zip(n_new, cached) if n == 1], default=0), \
+        bool(blocks and sum(portions) >= 64 * blocks)
 
 
 def _manager(window=0):
@@ -93,31 +101,36 @@ def test_packing_matches_restatement(window):
         for e in entries:
             m.reserve(e[0], len(e[1]))
         tile, table_round = rng.choice([2, 4, 64]), rng.choice([1, 8])
-        arrays, shape, widths = pack(m, entries, table_round, tile)
-        want_arrays = expected(m, entries, table_round, tile)
+        arrays, shape, widths = pack(m, entries, table_round)
+        want_arrays = expected(m, entries, table_round)
+        assert len(arrays) == len(want_arrays)
         for i, (got, exp) in enumerate(zip(arrays, want_arrays)):
             assert got.tolist() == exp, f"array {i} differs in trial {trial}"
         T = sum(len(e[1]) for e in entries)
-        dec_lens = [m.record(e[0]).cached_len + 1 for e in entries if len(e[1]) == 1]
-        assert shape[:6] == [T, len(entries), sum(len(e[2]) for e in entries), len(want_arrays[8]) // 2,
-                             len(want_arrays[9]), max(dec_lens, default=0)]
+        assert shape[:3] == [T, len(entries), sum(len(e[2]) for e in entries)]
+        # The plan of paged attention comes from the per-request numbers that the packing wrote.
+        n_new, cached = arrays[host.N_NEW], arrays[host.CACHED_LEN]
+        tiles, dec, max_kv, long_portions = host.plan_paged_attention(n_new, cached, tile)
+        exp = expected_attention_plan(n_new.tolist(), cached.tolist(), tile)
+        assert (tiles.tolist(), dec.tolist(), max_kv, long_portions) == exp
         for e in entries:
             m.commit(e[0], len(e[1]))
         m.check_invariants()
 
 
 def test_long_portions_flag_and_small_buffer():
+    plan = lambda n_new: host.plan_paged_attention(np.array(n_new, np.int32), np.zeros(len(n_new), np.int32), 64)
+    assert plan([200])[3] is True                 # two blocks of 128, 200 >= 128 tokens
+    assert plan([200, 3])[3] is True              # 203 tokens over three blocks
+    assert plan([3])[3] is False
+    assert plan([1, 1])[0].shape == (0, 2) and plan([1, 1])[1].tolist() == [0, 1]
     m = _manager()
-    m.admit("a"), m.admit("b")
-    m.reserve("a", 200), m.reserve("b", 3)
+    m.admit("a")
+    m.reserve("a", 200)
     big = [("a", list(range(200)), [199], -1)]
-    assert pack(m, big, 8, 64)[1][6] == 1                 # two blocks of 128, 200 >= 128 tokens
-    mixed = big + [("b", [1, 2, 3], [], -1)]
-    assert pack(m, mixed, 8, 64)[1][6] == 1               # 203 tokens over three blocks
-    assert pack(m, [("b", [1, 2, 3], [], -1)], 8, 64)[1][6] == 0
-    need = pack(m, big, 8, 64, capacity=16)               # too small: only the size comes back
-    assert isinstance(need, int) and need > 600
-    arrays, _, _ = pack(m, big, 8, 64, capacity=need)
+    need = pack(m, big, 8, capacity=16)               # too small: only the size comes back
+    assert isinstance(need, int) and need > 400
+    arrays, _, _ = pack(m, big, 8, capacity=need)
     assert arrays[0].tolist() == list(range(200))
 
 
@@ -126,12 +139,12 @@ def test_refusals():
     m.admit("a")
     m.reserve("a", 2)
     with pytest.raises(ValueError, match="wanted place"):
-        pack(m, [("a", [1, 2], [2], -1)], 8, 64)
+        pack(m, [("a", [1, 2], [2], -1)], 8)
     with pytest.raises(ValueError, match="at least one entry"):
-        pack(m, [], 8, 64)
+        pack(m, [], 8)
     with pytest.raises(ValueError, match="not live"):
         m.requests["ghost"] = type(m.record("a"))(m, "ghost", 99, 0)   # a record the library does not know
         try:
-            pack(m, [("ghost", [1], [], -1)], 8, 64)
+            pack(m, [("ghost", [1], [], -1)], 8)
         finally:
             del m.requests["ghost"]
