@@ -17,8 +17,11 @@ A "step" is one decode step of the whole batch. The default is batch 8 at a cont
                  live requests) / time, against the measured HBM copy bandwidth
   points         decode tokens per second at batch 1 and 64
 
-Peaks come from MEASURED_PEAKS.json beside this file when present, else 6.65 TB/s and
-1.59 PFLOP/s. Only N = 1 is supported: the engine is a single-GPU engine.
+The K timed steps run back to back as five runs of K/5 steps with a CUDA event between them: ``value`` and
+``ms_per_step`` are the median run's, ``repeats`` gives the runs' spread and the mean over all K steps.
+Fractions are given against two denominators: the peaks measured on this pool (MEASURED_PEAKS.json beside
+this file when present, else 6.65 TB/s and 1.59 PFLOP/s) and the nominal figures of the part (7.7 TB/s,
+2.25 PFLOP/s dense bf16). Only N = 1 is supported: the engine is a single-GPU engine.
 """
 import argparse
 import json
@@ -48,6 +51,10 @@ WORKLOADS = {
     "stress32b": dict(model="Qwen3-32B shape", cfg=QWEN3_32B, seed=4, requests=16, prompt_lo=8192, prompt_hi=8192,
                       new_tokens=512, temperature=0.0, prefill_chunk=512),
 }
+
+
+NOMINAL = {"hbm_gbs": 7700.0, "bf16_tflops": 2250.0}     # HBM3e of the HGX B200, dense bfloat16
+REPEATS = 5
 
 
 def peaks():
@@ -235,6 +242,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step by itself "
                     "(for a profiler's launch list)")
+    ap.add_argument("--profile", action="store_true", help="instead of the benchmark: time every kernel class of one "
+                    "decode step and of the prefill with CUDA events (eager launches, NVTX ranges) and print a table "
+                    "with bytes, flops and the fraction of the peaks to standard error, the rows as JSON to standard output")
     ap.add_argument("--workload", default="decode", choices=["decode", *WORKLOADS],
                     help="decode: the benchmark contract (default). mixed14b / stress32b: a whole serving run "
                     "through the engine on the layer sizes of Qwen3-14B / Qwen3-32B")
@@ -312,18 +322,26 @@ def main():
             ops.argmax(logits, out)
         torch.cuda.synchronize()
         launches0 = ops.launch_count
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
+        # The steps run back to back; an event after every run of steps // REPEATS steps gives the runs' times.
+        runs = min(REPEATS, steps)
+        marks = [warmup + (steps * r) // runs for r in range(runs + 1)]
+        events = [torch.cuda.Event(enable_timing=True) for _ in marks]
+        events[0].record()
+        at = 1
         for s in range(warmup, warmup + steps):
             logits = runner.step([StepEntry(r, [toks[s][i]], [0]) for i, r in enumerate(ids)])
             ops.argmax(logits, out)
-        end.record()
+            if s + 1 == marks[at]:
+                events[at].record()
+                at += 1
         torch.cuda.synchronize()
         clocks = sampler.stop() if sampler else None
-        ms = start.elapsed_time(end) / steps
+        per_run = [events[r].elapsed_time(events[r + 1]) / (marks[r + 1] - marks[r]) for r in range(runs)]
+        spread = {"runs": runs, "median_ms": round(statistics.median(per_run), 4), "min_ms": round(min(per_run), 4),
+                  "max_ms": round(max(per_run), 4), "mean_ms": round(events[0].elapsed_time(events[-1]) / steps, 4)}
         for rid in ids:
             runner.release(rid)
-        return ms, clocks, ops.launch_count - launches0
+        return statistics.median(per_run), clocks, ops.launch_count - launches0, spread
 
     # Kernels of ours in one captured decode step (a replay launches all of them again).
     def kernels_per_decode_step(batch):
@@ -338,8 +356,35 @@ def main():
             runner.release(rid)
         return n
 
+    if args.profile:
+        from llm_rs_b200.profiling import Profiler
+        runner.use_graphs = False
+        ids = [f"q{i}" for i in range(args.batch)]
+        fill_context(ids, ctx - 8)
+        step = lambda: ops.argmax(runner.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in ids]))
+        for _ in range(3):
+            step()
+        out = {}
+        with Profiler(pk["hbm_gbs"], pk["bf16_tflops"]) as prof:
+            for _ in range(3):
+                step()
+        print(f"[profile] decode step, batch {args.batch}, context {ctx}, {args.layers} layers (3 steps):\n" + prof.report(),
+              file=sys.stderr)
+        out["decode"] = prof.classes()
+        for rid in ids:
+            runner.release(rid)
+        prompt = rng.integers(0, V, args.prefill_tokens).tolist()
+        runner.step([StepEntry("p", prompt, [len(prompt) - 1])])
+        runner.release("p")
+        with Profiler(pk["hbm_gbs"], pk["bf16_tflops"]) as prof:
+            runner.step([StepEntry("p", prompt, [len(prompt) - 1])])
+        print(f"[profile] prefill of {len(prompt)} tokens:\n" + prof.report(), file=sys.stderr)
+        out["prefill"] = prof.classes()
+        print(json.dumps({"profile": out, "peaks": pk, "layers": args.layers, "batch": args.batch, "context": ctx}))
+        return 0
+
     per_step_kernels = kernels_per_decode_step(args.batch)
-    ms, clocks, eager_launches = timed_decode(args.batch, K, W, ClockSampler())
+    ms, clocks, eager_launches, spread = timed_decode(args.batch, K, W, ClockSampler())
     value = args.batch / (ms / 1e3)
     step_bytes = model_bytes_per_decode_step(raw, args.layers, args.batch, ctx)
     achieved = step_bytes / (ms / 1e3) / 1e9
@@ -360,14 +405,16 @@ def main():
         # One replay of a captured step launches every kernel of the step; argmax is launched eagerly.
         "gpu_launches": (per_step_kernels * K if not args.no_graphs else 0) + eager_launches,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"],
+                     "nominal_peak": NOMINAL["hbm_gbs"], "frac_nominal": round(achieved / NOMINAL["hbm_gbs"], 4)},
+        "repeats": spread,
     }
 
     if not args.no_points:
         points = {}
         for b in (1, 64):
             try:
-                ms_b, _, _ = timed_decode(b, max(8, K // 2), W)
+                ms_b, _, _, _ = timed_decode(b, max(10, K // 2), W)
                 points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 2)
             except Exception as e:  # a point that fails must not lose the headline
                 points[f"decode_b{b}"] = None
@@ -379,7 +426,7 @@ def main():
             n_prompt = args.prefill_tokens
             prompt = rng.integers(0, V, n_prompt).tolist()
             times = []
-            for it in range(4):
+            for it in range(REPEATS + 1):        # the first run is warm-up; the median of the others counts
                 start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record()
                 runner.step([StepEntry("p", prompt, [n_prompt - 1])])
@@ -391,8 +438,10 @@ def main():
             pms = statistics.median(times)
             fl = prefill_flops(raw, args.layers, n_prompt)
             result["prefill"] = {"value": round(n_prompt / (pms / 1e3), 1), "tokens": n_prompt,
-                                 "ms": round(pms, 3),
-                                 "frac": round(fl / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"]}
+                                 "ms": round(pms, 3), "min_ms": round(min(times), 3), "max_ms": round(max(times), 3),
+                                 "frac": round(fl / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4), "of": pk["source"],
+                                 "frac_sustained": round(fl / (pms / 1e3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12), 4),
+                                 "frac_nominal": round(fl / (pms / 1e3) / (NOMINAL["bf16_tflops"] * 1e12), 4)}
         except Exception as e:
             result["prefill"] = None
             print(f"[bench] prefill failed: {e}", file=sys.stderr)

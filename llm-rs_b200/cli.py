@@ -47,14 +47,19 @@ def _add_common(p: argparse.ArgumentParser) -> None:
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--seed", type=int, default=0, help="seed of the sampler's draws")
     p.add_argument("--ignore-eos", action="store_true")
+    p.add_argument("--profile", action="store_true", help="time every kernel class with CUDA events (steps launched "
+                   "kernel by kernel instead of from CUDA graphs) and print their shares, bytes, flops and fractions "
+                   "of the device's peaks after the run")
 
 
 def _run(args, max_new_tokens: int, temperature: float, top_p: float, repetition_penalty: float, top_k: int = 0):
     from .engine import Engine, EngineConfig
     from .sampling import SamplingParams
     t0 = time.time()
+    profile = getattr(args, "profile", False)
     engine = Engine(EngineConfig(model_path=args.model_path, block_pool_size=args.block_pool_size,
-                                 page_size=args.page_size, dtype=args.dtype))
+                                 page_size=args.page_size, dtype=args.dtype, cuda_graphs=not profile,
+                                 async_steps=not profile))
     spec = engine.runner.spec
     print(f"Model loaded in {time.time() - t0:.2f}s (vocab_size: {spec.vocab_size}, hidden_dim: {spec.hidden_size})")
     prompt = _prompt_ids(args, spec.vocab_size)
@@ -62,6 +67,10 @@ def _run(args, max_new_tokens: int, temperature: float, top_p: float, repetition
                             repetition_penalty=repetition_penalty, max_new_tokens=max_new_tokens,
                             seed=args.seed, ignore_eos=args.ignore_eos)
     import torch
+    profiler = None
+    if profile:
+        from .profiling import Profiler, device_peaks
+        profiler = Profiler(*device_peaks()).__enter__()
     rid = engine.add_request(prompt, params)
     start = time.time()
     first = last = None
@@ -74,6 +83,9 @@ def _run(args, max_new_tokens: int, temperature: float, top_p: float, repetition
                 first = first or now
                 last = now
                 tokens.append(tok)
+    if profiler is not None:
+        profiler.__exit__(None, None, None)
+        print(profiler.report())
     print("Generated token ids:", ",".join(str(t) for t in tokens))
     print(f"Finish reason: {engine.finish_reason(rid)}")
     if first is not None:

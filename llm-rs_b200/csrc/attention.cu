@@ -23,7 +23,7 @@ int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* c
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
                                 int page_size, int window, float scale, void* out, long long out_stride,
-                                int* counters, int cluster_merge, cudaStream_t stream);
+                                int* counters, int cluster_merge, const L2Prefetch& next, cudaStream_t stream);
 
 bool llmrs_attn_prefill_tc_supported(const void* q, long long q_stride, const void* cache, int d, int page_size,
                                      float scale);
@@ -459,6 +459,7 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
   LLMRS_REQUIRE(n_q_heads % n_kv_heads == 0, "attn_decode: %d query heads are no multiple of %d key heads",
                 n_q_heads, n_kv_heads);
   LLMRS_REQUIRE(d >= 16 && d % 16 == 0 && d <= 1024, "attn_decode: head_dim %d must be a multiple of 16 up to 1024", d);
+  const L2Prefetch next = llmrs_take_next_prefetch();   // for the tensor-core kernel; the others drop it
   if (n_dec == 0) return 0;
   if (dtype == LLMRS_F32)
     return launch_decode<float, 4>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,
@@ -468,11 +469,11 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
     if (counters == nullptr && max_splits <= 16)  // the splits merge inside the kernel, as a cluster
       return llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
                                          table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
-                                         page_size, window, scale, out, out_stride, nullptr, 1, stream);
+                                         page_size, window, scale, out, out_stride, nullptr, 1, next, stream);
     if (counters == nullptr) {
       int rc = llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
                                            table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
-                                           page_size, window, scale, out, out_stride, nullptr, 0, stream);
+                                           page_size, window, scale, out, out_stride, nullptr, 0, next, stream);
       if (rc) return rc;
       dim3 cgrid(n_dec, n_q_heads);
       llmrs_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream, true,
@@ -482,7 +483,7 @@ LLMRS_API int llmrs_attn_decode(const void* q, long long q_stride, void* out, lo
     }
     return llmrs_attn_decode_split_mma(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table,
                                        table_stride, scratch, max_splits, split_keys, n_q_heads, n_kv_heads, d,
-                                       page_size, window, scale, out, out_stride, counters, 0, stream);
+                                       page_size, window, scale, out, out_stride, counters, 0, next, stream);
   }
   if (dtype == LLMRS_BF16)
     return launch_decode<__nv_bfloat16, 8>(q, q_stride, out, out_stride, cache, dec_reqs, n_dec, q_start, cached_len,

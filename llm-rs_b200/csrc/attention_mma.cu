@@ -79,7 +79,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
                              int table_stride, float* __restrict__ part, int max_splits, int split_keys,
                              int n_q_heads, int n_kv_heads, int page_size, int window, float scale,
                              bf16* __restrict__ out, long long out_stride, int* __restrict__ counters,
-                             int cluster_merge) {
+                             int cluster_merge, const L2Prefetch next) {
   constexpr int D = 16 * DCH;
   constexpr int ROW = D + 8;               // 16 bytes of padding: ldmatrix rows fall into distinct banks
   constexpr int CH = D / 8;                // 16-byte chunks per row
@@ -290,6 +290,9 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       mma_bf16_16816(o[2 * nc + 1], pf, b[2], b[3]);
     }
   }
+  // The block's last keys and values are on their way: the weights of the product that follows attention
+  // (see L2Prefetch) can come into the L2 while this block merges its warps and its cluster.
+  if (threadIdx.x == 0) l2_prefetch_slice(next);
   cp_async_wait<0>();
   __syncthreads();
 
@@ -430,7 +433,7 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
                              const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                              float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads,
                              int page_size, int window, float scale, void* out, long long out_stride, int* counters,
-                             int cluster_merge, cudaStream_t stream) {
+                             int cluster_merge, const L2Prefetch& next, cudaStream_t stream) {
   constexpr int D = 16 * DCH;
   const int ng_max = n_q_heads / n_kv_heads < 16 ? n_q_heads / n_kv_heads : 16;
   const size_t smem = dm_ring_bytes(D) + (cluster_merge ? dm_inbox_bytes(ng_max, D, max_splits) : 0);
@@ -461,7 +464,7 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_split_mma_kernel<DCH>, (const bf16*)q, q_stride, (const bf16*)cache,
                                      dec_reqs, q_start, cached_len, block_table, table_stride, scratch, max_splits,
                                      split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out,
-                                     out_stride, counters, cluster_merge);
+                                     out_stride, counters, cluster_merge, next);
   if (e != cudaSuccess) return llmrs_fail("attn_decode_mma launch: %s", cudaGetErrorString(e));
   return llmrs_launch_status("attn_decode_split_mma");
 }
@@ -517,14 +520,14 @@ int llmrs_attn_decode_split_mma(const void* q, long long q_stride, const void* c
                                 const int* q_start, const int* cached_len, const int* block_table, int table_stride,
                                 float* scratch, int max_splits, int split_keys, int n_q_heads, int n_kv_heads, int d,
                                 int page_size, int window, float scale, void* out, long long out_stride,
-                                int* counters, int cluster_merge, cudaStream_t stream) {
+                                int* counters, int cluster_merge, const L2Prefetch& next, cudaStream_t stream) {
   if (cluster_merge && (max_splits < 1 || max_splits > 16))
     return llmrs_fail("attn_decode_mma: a cluster merges at most 16 splits, got %d", max_splits);
 #define LLMRS_DM_CASE(N)                                                                                          \
   case N:                                                                                                          \
     return launch_decode_mma<N>(q, q_stride, cache, dec_reqs, n_dec, q_start, cached_len, block_table, table_stride, \
                                 scratch, max_splits, split_keys, n_q_heads, n_kv_heads, page_size, window, scale, out, \
-                                out_stride, counters, cluster_merge, stream)
+                                out_stride, counters, cluster_merge, next, stream)
   switch (d / 16) {
     LLMRS_DM_CASE(1); LLMRS_DM_CASE(2); LLMRS_DM_CASE(3); LLMRS_DM_CASE(4);
     LLMRS_DM_CASE(5); LLMRS_DM_CASE(6); LLMRS_DM_CASE(7); LLMRS_DM_CASE(8);

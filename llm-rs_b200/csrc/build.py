@@ -27,11 +27,11 @@ LIB_NAME = "libllmrs_b200.so"
 # Fast math stays off: norms, softmax and rotation are checked against float32 references.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
-ABI_VERSION = 3
+ABI_VERSION = 4
 HOST_DIR = os.path.join(CSRC_DIR, "host")
 HOST_LIB_NAME = "libllmrs_b200_host.so"
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
-HOST_ABI_VERSION = 2
+HOST_ABI_VERSION = 3
 
 _lib: Optional[ctypes.CDLL] = None
 _host_lib: Optional[ctypes.CDLL] = None
@@ -236,6 +236,64 @@ def build_host(force: bool = False) -> str:
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
     return os.path.join(d, HOST_LIB_NAME)
+
+
+# -- the engine's C entry points ---------------------------------------------------------
+CAPI_DIR = os.path.join(CSRC_DIR, "capi")
+CAPI_LIB_NAME = "libllmrs_b200_engine.so"
+
+
+def _capi_flags() -> List[str]:
+    """The interpreter a plain C program gets: the library of the Python that builds this, with its module paths."""
+    import sysconfig
+    pylib = sysconfig.get_config_var("INSTSONAME") or sysconfig.get_config_var("LDLIBRARY") or "libpython3.so"
+    libdir = sysconfig.get_config_var("LIBDIR") or ""
+    if libdir and os.path.exists(os.path.join(libdir, pylib)):
+        pylib = os.path.join(libdir, pylib)
+    paths = ":".join(p for p in sys.path if p and os.path.isdir(p))
+    return [*HOST_FLAGS, f'-DLLMRS_PY_LIB="{pylib}"', f'-DLLMRS_PY_PATHS="{paths}"']
+
+
+def _capi_fingerprint() -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(_capi_flags()).encode())
+    for name in sorted(os.listdir(CAPI_DIR)):
+        if name.endswith((".cpp", ".h")):
+            h.update(name.encode())
+            with open(os.path.join(CAPI_DIR, name), "rb") as f:
+                h.update(f.read())
+    return h.hexdigest()
+
+
+def build_engine_api(force: bool = False) -> str:
+    """Make sure the library with the engine's C entry points (``capi/llm_engine.h``) is built; return its path."""
+    fp = _capi_fingerprint()
+    if not force:
+        for d in _build_dirs():
+            if _is_current(d, fp, "capi_stamp.json", CAPI_LIB_NAME):
+                return os.path.join(d, CAPI_LIB_NAME)
+    d = _writable_dir()
+    with open(os.path.join(d, ".capi_lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if force or not _is_current(d, fp, "capi_stamp.json", CAPI_LIB_NAME):
+                cxx = find_cxx()
+                if cxx is None:
+                    raise KernelBuildError("no C++ compiler was found ($CXX, g++, c++, clang++)")
+                tmp = os.path.join(d, f".{CAPI_LIB_NAME}.{os.getpid()}")
+                cmd = [*cxx, *_capi_flags(), "-shared", "-I", CAPI_DIR, os.path.join(CAPI_DIR, "llm_engine.cpp"),
+                       "-o", tmp, "-ldl"]
+                t0 = time.time()
+                r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                if r.returncode != 0:
+                    raise KernelBuildError(f"compiling the engine's C entry points failed:\n{r.stdout}")
+                os.replace(tmp, os.path.join(d, CAPI_LIB_NAME))
+                with open(os.path.join(d, "capi_stamp.json"), "w") as f:
+                    json.dump({"fingerprint": fp}, f)
+                _log(f"built {CAPI_LIB_NAME} in {time.time() - t0:.0f} s")
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+    return os.path.join(d, CAPI_LIB_NAME)
 
 
 def host_library() -> ctypes.CDLL:

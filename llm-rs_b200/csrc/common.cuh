@@ -28,6 +28,31 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // 1: kernels that support it are launched with the programmatic-serialization attribute.
 extern int g_llmrs_pdl;
 
+// Warming the L2 for the kernel that runs next. A decode step is a chain of kernels that each stream some
+// tens of megabytes once; between the end of one kernel's stream and the first bytes of the next the memory
+// system idles (epilogues, barriers, launch). A kernel that was given a hint (llmrs_set_next_prefetch, consumed
+// by the next launch that supports it) asks, when its own last loads are on their way, for the start of the
+// NEXT kernel's weights to be brought into the L2 (126 MB on a B200): every block asks for its slice.
+struct L2Prefetch {
+  const char* ptr;              // 16-byte aligned, or null
+  unsigned long long bytes;     // a multiple of 16
+};
+L2Prefetch llmrs_take_next_prefetch();    // the pending hint (and clears it)
+
+// This block's slice of `pf` (blocks numbered over the whole grid), requested in pieces of 16 KB by the calling thread.
+__device__ __forceinline__ void l2_prefetch_slice(const L2Prefetch& pf) {
+  if (pf.ptr == nullptr || pf.bytes == 0) return;
+  const unsigned long long nb = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+  const unsigned long long b = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+  const unsigned long long chunk = (((pf.bytes + nb - 1) / nb) + 127ull) & ~127ull;
+  const unsigned long long lo = b * chunk;
+  const unsigned long long hi = lo + chunk < pf.bytes ? lo + chunk : pf.bytes;
+  for (unsigned long long a = lo; a < hi; a += 16384ull) {
+    const unsigned int n = (unsigned int)(hi - a < 16384ull ? hi - a : 16384ull);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.ptr + a), "r"(n) : "memory");
+  }
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t llmrs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                 bool pdl, Args... args) {

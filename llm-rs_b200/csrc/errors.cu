@@ -29,5 +29,21 @@ int g_llmrs_pdl = 1;
 // Switch programmatic dependent launch on (1, the default) or off (0) for the kernels that support it.
 LLMRS_API void llmrs_set_pdl(int on) { g_llmrs_pdl = on; }
 
+// The hint for the next launch that can warm the L2 (see L2Prefetch in common.cuh): the start of the weights that
+// the kernel AFTER that launch will stream. One-shot: the launch takes it, and a launch that cannot use it drops it.
+static thread_local L2Prefetch g_next_prefetch = {nullptr, 0};
+LLMRS_API int llmrs_set_next_prefetch(const void* ptr, long long bytes) {
+  LLMRS_REQUIRE(bytes >= 0 && bytes % 16 == 0 && ((uintptr_t)ptr & 15) == 0,
+                "set_next_prefetch: the range must be 16-byte aligned and a multiple of 16 bytes long");
+  g_next_prefetch.ptr = bytes ? (const char*)ptr : nullptr;
+  g_next_prefetch.bytes = ptr ? (unsigned long long)bytes : 0ull;
+  return 0;
+}
+L2Prefetch llmrs_take_next_prefetch() {
+  L2Prefetch p = g_next_prefetch;
+  g_next_prefetch = {nullptr, 0};
+  return p;
+}
+
 // Version of the entry points' signatures; the Python side checks it after loading.
-LLMRS_API int llmrs_abi_version() { return 3; }
+LLMRS_API int llmrs_abi_version() { return 4; }

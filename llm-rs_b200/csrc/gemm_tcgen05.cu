@@ -67,6 +67,7 @@ struct TcParams {
   int a_rows, b_rows;   // valid extents (tokens / features according to the mode)
   int k_blocks;         // ceil(K / 64)
   int* error_flag;
+  L2Prefetch next;      // mode 1: the start of the weights the next kernel streams, to be brought into the L2
   uint32_t wait_limit;  // polls of a barrier before a wait gives up
   int test_skip_kb;     // tests only: the producer leaves out the copy of its k block with this index (-1: none)
   QkvRope qr;           // TC_QKV_ROPE only
@@ -471,6 +472,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // Rows are features, columns tokens. Partial tile -> shared memory -> sum over the
     // cluster's blocks in rank order -> epilogue for the rows this block owns.
     float* red = reinterpret_cast<float*>(tiles);  // [128][BN + 1]; the stages are free (see the join above)
+    // This block's stream is over; what is left is its epilogue: the memory system can serve the next kernel.
+    if (tid == 0) l2_prefetch_slice(p.next);
     constexpr int RS = BN + 1;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 8) {
@@ -1022,6 +1025,7 @@ static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
   p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
   p.wait_limit = g_tc_wait_limit; p.test_skip_kb = g_tc_test_skip_kb;
+  p.next = llmrs_take_next_prefetch();   // used by the few-token kernel; a many-token launch drops it
   CUtensorMap ma, mb;
   int rc;
   if (tokens <= 64) {

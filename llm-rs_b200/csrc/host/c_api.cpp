@@ -34,7 +34,7 @@ T* as(void* handle, const char* what) {
 
 extern "C" {
 
-int llmrs_host_abi_version(void) { return 2; }
+int llmrs_host_abi_version(void) { return 3; }
 const char* llmrs_host_last_error(void) { return g_error.c_str(); }
 
 int llmrs_pool_create(int capacity, void** pool) {

@@ -7,6 +7,7 @@ library is an error (``csrc.build.KernelBuildError``), never a silent fallback.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -153,6 +154,20 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = No
     return out
 
 
+def library_gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` in bfloat16 through the library (cuBLAS via ``torch``): the products of steps with
+    many tokens that this package's own kernel does not take, as the reference's projections are calls into
+    its tensor library (llm-core/src/backends/candle.rs:1276-1340). The only library kernel on the product path
+    (not counted in ``launch_count``, which counts this package's own kernels)."""
+    if out_dtype == torch.float32:
+        y = torch.mm(x, w.t(), out_dtype=torch.float32)
+        if bias is not None:
+            y += bias.to(torch.float32)
+        return y
+    return torch.nn.functional.linear(x, w, bias)
+
+
 def qk_norm_rope_kvwrite(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor],
                          q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
                          cos_sin: Optional[torch.Tensor], positions: torch.Tensor, token_req: torch.Tensor,
@@ -245,7 +260,8 @@ def _lib_ll(name: str):
 def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_reqs: torch.Tensor, n_dec: int,
                 q_start: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor, scratch: torch.Tensor,
                 max_splits: int, split_keys: int, n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
-                window: int, scale: float, counters: Optional[torch.Tensor] = None) -> None:
+                window: int, scale: float, counters: Optional[torch.Tensor] = None,
+                then: Optional[torch.Tensor] = None) -> None:
     """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
     the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace of
     ``attn_decode_scratch_floats`` elements. (bfloat16 with head_dim <= 128 and at most 16 splits: the splits
@@ -253,6 +269,8 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
     one kernel; else a second kernel merges them.) With ``counters`` (int32, at least n_dec * n_q_heads,
     all zero; the call leaves them zero) the tensor-core kernel merges the splits itself instead
     of a second kernel doing it."""
+    if then is not None:
+        hint_next_weights(then, PREFETCH_BYTES_AFTER_ATTENTION)   # the weights of the product after attention
     _need(q, "q", contiguous=False)
     _need(out, "out", q.dtype, contiguous=False)
     _need(cache, "cache", q.dtype)
@@ -391,6 +409,25 @@ def test_skip_copy(gemm_k_block: int = -1, attention_tile: int = -1) -> None:
 test_skip_copy.__test__ = False     # not a test, whatever a collector makes of the name
 
 
+# Bytes of the next kernel's weights that a decode kernel asks into the L2 when its own stream ends
+# (LLMRS_PREFETCH_MB, 0 switches it off).
+PREFETCH_BYTES = int(float(os.environ.get("LLMRS_PREFETCH_MB", "12")) * (1 << 20))
+PREFETCH_BYTES_AFTER_ATTENTION = int(float(os.environ.get("LLMRS_PREFETCH_ATTN_MB", "12")) * (1 << 20))
+
+
+def hint_next_weights(w: Optional[torch.Tensor], limit: Optional[int] = None) -> None:
+    """Tell the next launch of a few-token product or of decode attention which weights the kernel AFTER it
+    will stream: their first ``PREFETCH_BYTES`` are asked into the L2 when that launch's own loads are out.
+    The hint is taken by the next such launch, whichever it is; ``None`` clears it."""
+    fn = _lib().llmrs_set_next_prefetch
+    limit = PREFETCH_BYTES if limit is None else limit
+    if w is None or limit <= 0:
+        fn(ctypes.c_void_p(0), ctypes.c_longlong(0))
+        return
+    n = min(w.numel() * w.element_size(), limit) // 16 * 16
+    _check(fn(ctypes.c_void_p(w.data_ptr()), ctypes.c_longlong(n)), "set_next_prefetch", launches=0)
+
+
 def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     """Blocks of a cluster that share the k range of a skinny product: enough blocks to
     fill the GPU about twice, at least four 64-wide k blocks each."""
@@ -404,13 +441,15 @@ def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     return 1
 
 
-def norm_parts(features: int) -> int:
-    """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per 128 features."""
+def norm_parts(features: int, splits: int = 1) -> int:
+    """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per tile of 128 features
+    (the cluster that shares the tile's k range adds its blocks' shares up in its first block)."""
     return -(-features // 128)
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, epilogue: str = "store",
-              out_dtype: torch.dtype = torch.bfloat16, splits: Optional[int] = None, emit=None, scale=None) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, splits: Optional[int] = None, emit=None, scale=None,
+              then: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ w.T`` for bfloat16 ``x`` [tokens, K] and ``w`` [features, K] on tcgen05 (see csrc/gemm_tcgen05.cu).
 
     epilogue "store": returns [tokens, features] in ``out_dtype``. "residual": ``out`` is the
@@ -418,14 +457,19 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     gate rows and 64 up rows; returns silu(gate) * up, [tokens, features / 2] bfloat16.
 
     A norm spread over two products (at most 64 tokens): ``emit`` = (norm weight float32 [features],
-    xw bfloat16 [tokens, features], parts float32 [norm_parts(features), stride]) makes a
+    xw bfloat16 [tokens, features], parts float32 [norm_parts(features, splits), stride]) makes a
     "residual" epilogue also write xw = (out + product) * weight and the sums of squares of each 128 features;
     ``scale`` = (parts, n_parts, dim, eps) multiplies the product's rows by
     1 / sqrt(sum(parts[:n_parts, token]) / dim + eps).
+
+    ``then`` (at most 64 tokens): the weights that the kernel after this one streams; their start is asked into
+    the L2 when this product's own loads are out (``hint_next_weights``).
     """
     _need(x, "x", torch.bfloat16, contiguous=False)
     _need(w, "w", torch.bfloat16)
     tokens, K = x.shape
+    if then is not None and tokens <= 64:
+        hint_next_weights(then)
     features = w.size(0)
     if w.size(1) != K:
         raise KernelError(f"x has {K} columns, w has {w.size(1)}")
@@ -456,7 +500,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         _need(e_w, "emit weight", torch.float32)
         _need(e_xw, "emit xw", torch.bfloat16)
         _need(e_part, "emit parts", torch.float32)
-        if e_w.numel() != features or e_xw.shape != (tokens, features) or e_part.size(0) < norm_parts(features):
+        if e_w.numel() != features or e_xw.shape != (tokens, features) or e_part.size(0) < norm_parts(features, splits):
             raise KernelError("emit: weight, xw or parts do not fit the product")
         stride = e_part.size(1)
     if scale is not None:

@@ -131,6 +131,7 @@ class GQAttention(Mixer):
         if self.bias:
             bqkv = torch.cat([tensors[nm(r, "bias")].to(dt) for r in "qkv"], dim=0).contiguous()
         self.qkv_proj = Linear(wqkv, bqkv, runtime.act_dtype)
+        self.qkv_proj.warms_next = False
         # The query rows alone, for run-order entries that read another entry's cache.
         self.q_proj = Linear(wqkv[: self.q_width], None if bqkv is None else bqkv[: self.q_width], runtime.act_dtype)
         self.o_proj = Linear(tensors[nm("o")], tensors.get(nm("o", "bias")), runtime.act_dtype)
@@ -139,6 +140,11 @@ class GQAttention(Mixer):
             self.q_norm_w = tensors[nm("q_norm")].to(torch.float32).contiguous()
             self.k_norm_w = tensors[nm("k_norm")].to(torch.float32).contiguous()
         self.position.bind(tensors, runtime)
+
+    def chain(self):
+        # Attention runs between the two: the q|k|v product warms nothing (what follows it reads the cache), the
+        # decode attention kernel warms the L2 for the output projection (see ``forward``).
+        return [self.qkv_proj, self.o_proj]
 
     # -- cache -----------------------------------------------------------------------
     def cache_need(self):
@@ -236,7 +242,7 @@ class GQAttention(Mixer):
             # ops.attn_decode(counters=...), measured no faster inside the step and slower at batch 1.)
             ops.attn_decode(q, out, cache.kv, plan.arrays["decode_reqs"], n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
-                            self.scale)
+                            self.scale, then=self.o_proj.weight if self.o_proj.uses_tc(ctx.n_tokens) else None)
         if next_norm is not None:
             return self.o_proj.forward_into_residual_for_norm(out, residual, *next_norm)
         if residual is not None:

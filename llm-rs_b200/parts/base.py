@@ -77,6 +77,12 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         """Take the tensors named in ``weight_specs`` (already on ``runtime.device``)."""
 
+    def chain(self) -> list:
+        """The part's ``Linear`` products in the order a step runs them (after ``bind``). The model links each
+        to the one that runs after it (``Linear.next_weight``), across parts and layers, so that a decode
+        kernel can warm the L2 for its successor. A part without such products returns []."""
+        return []
+
 
 class PreNormed:
     """The input of a norm whose two halves are spread over the products around it (steps of few

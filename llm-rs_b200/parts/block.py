@@ -33,6 +33,9 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
+    def chain(self):
+        return [lin for part in self.parts() for lin in part.chain()]
+
     def weight_specs(self):
         return [s for part in self.parts() for s in part.weight_specs()]
 

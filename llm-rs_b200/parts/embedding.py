@@ -49,5 +49,8 @@ class LinearHead(Part):
     def bind(self, tensors, runtime: Runtime):
         self.proj = Linear(tensors[self.tied_to or self.name], None, runtime.act_dtype)
 
+    def chain(self):
+        return [self.proj]
+
     def forward(self, x):
         return self.proj.forward(x, out_dtype=torch.float32)

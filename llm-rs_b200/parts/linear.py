@@ -46,6 +46,10 @@ class Linear:
         self.bias = None if bias is None else bias.to(weight.dtype).contiguous()
         self.act_dtype = act_dtype
         n, k = weight.shape
+        # The weights of the product that runs after this one in a step (set by ``DecoderModel.bind``): in
+        # steps of few tokens this product's kernel asks their start into the L2 as its own stream ends.
+        self.next_weight: Optional[torch.Tensor] = None
+        self.warms_next = True      # False: something else runs between this product and the next one
         self.tc_ok = (weight.dtype == torch.bfloat16 and bias is None and weight.is_contiguous()
                       and k % 8 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0)
 
@@ -59,20 +63,15 @@ class Linear:
     def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
         if isinstance(x, PreNormed):     # only when takes_prenormed
-            return ops.gemm_bf16(x.xw, self.weight, out_dtype=out_dtype, scale=x.scale)
+            return ops.gemm_bf16(x.xw, self.weight, out_dtype=out_dtype, scale=x.scale, then=self.next_weight)
         if self.weight.dtype == torch.float32:
             xf = x if x.dtype == torch.float32 else x.to(torch.float32)
             y = ops.gemm_f32(xf, self.weight, self.bias)
             return y if out_dtype == torch.float32 else y.to(out_dtype)
         xb = x if x.dtype == torch.bfloat16 else x.to(torch.bfloat16)
         if self.uses_tc(xb.size(0)) and out_dtype in (torch.float32, torch.bfloat16):
-            return ops.gemm_bf16(xb, self.weight, out_dtype=out_dtype)
-        if out_dtype == torch.float32:
-            y = torch.mm(xb, self.weight.t(), out_dtype=torch.float32)
-            if self.bias is not None:
-                y += self.bias.to(torch.float32)
-            return y
-        return torch.nn.functional.linear(xb, self.weight, self.bias)
+            return ops.gemm_bf16(xb, self.weight, out_dtype=out_dtype, then=self.next_weight)
+        return ops.library_gemm(xb, self.weight, self.bias, out_dtype)
 
     def _splits(self, n_tokens: int) -> int:
         n, k = self.weight.shape
@@ -92,16 +91,17 @@ class Linear:
         (see ``PreNormed``). Only when ``emits_prenormed``."""
         n = self.weight.size(0)
         splits = self._splits(x.size(0))
-        n_parts = ops.norm_parts(n)
+        n_parts = ops.norm_parts(n, splits)
         xw = torch.empty((x.size(0), n), dtype=torch.bfloat16, device=x.device)
         parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
-        ops.gemm_bf16(x, self.weight, out=h, epilogue="residual", splits=splits, emit=(norm_weight, xw, parts))
+        ops.gemm_bf16(x, self.weight, out=h, epilogue="residual", splits=splits, emit=(norm_weight, xw, parts),
+                      then=self.next_weight)
         return PreNormed(xw, parts, n_parts, n, eps)
 
     def forward_into_residual(self, x: torch.Tensor, h: torch.Tensor) -> Optional[torch.Tensor]:
         """``h += x @ weight.T`` inside the product's epilogue when the tcgen05 kernel runs
         (returns None); otherwise the product is returned for the caller to add."""
         if x.dtype == torch.bfloat16 and self.uses_tc(x.size(0)) and h.is_contiguous():
-            ops.gemm_bf16(x, self.weight, out=h, epilogue="residual")
+            ops.gemm_bf16(x, self.weight, out=h, epilogue="residual", then=self.next_weight)
             return None
         return self.forward(x)

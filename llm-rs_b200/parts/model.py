@@ -36,6 +36,11 @@ class DecoderModel:
         self.runtime = runtime
         for part in self.parts():
             part.bind(tensors, runtime)
+        # Every product learns which weights are streamed after its own (see ``Part.chain``).
+        order = [lin for step in self.spec.run_order for lin in getattr(self.blocks[step.layer], "chain", list)()]
+        order += getattr(self.lm_head, "chain", list)()
+        for lin, after in zip(order, order[1:]):
+            lin.next_weight = after.weight if lin.warms_next and after.weight.dtype == torch.bfloat16 else None
 
     def cache_needs(self) -> List[Tuple[Optional[CacheNeed], Optional[StateNeed]]]:
         """Per run-order entry: the pages and the state its mixer wants. An entry that

@@ -654,7 +654,7 @@ def test_gemm_norm_spread_over_two_products(tokens, features, K, splits, consume
     eps = 3e-5
     h = h0.to(DEV).clone()
     xw = torch.full((tokens, features), float("nan"), dtype=torch.bfloat16, device=DEV)
-    n_parts = ops.norm_parts(features)
+    n_parts = ops.norm_parts(features, splits)
     parts = torch.full((n_parts, 64), float("nan"), dtype=torch.float32, device=DEV)
     ops.gemm_bf16(x.to(DEV), w.to(DEV), out=h, epilogue="residual", splits=splits, emit=(nw.to(DEV), xw, parts))
     torch.cuda.synchronize()
