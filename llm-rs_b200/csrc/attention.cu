@@ -93,7 +93,7 @@ attn_prefill_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__
       const int key = kb + kk;
       float kf = 0.f, vf = 0.f;
       if (key < kv_hi) {
-        const int page = table[key / page_size];
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
         const size_t base = kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, d) + (size_t)(key % page_size) * d + cc;
         kf = to_float(cache[base]);
         vf = to_float(cache[base + (size_t)page_size * d]);
@@ -266,7 +266,7 @@ attn_decode_split_kernel(const T* __restrict__ q, long long q_stride, const T* _
     const int kk = kbase + kslot;
     const bool live = kk < nk;
     const int key = k_begin + (live ? kk : 0);
-    const int page = table[key / page_size];
+    const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
     const T* kr = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, d) + (size_t)(key % page_size) * d;
     float dot[DC_HG];
 #pragma unroll
@@ -333,7 +333,7 @@ attn_decode_split_kernel(const T* __restrict__ q, long long q_stride, const T* _
   if (my_sub < n_sub) {
     for (int kk = my_sub; kk < nk; kk += n_sub) {
       const int key = k_begin + kk;
-      const int page = table[key / page_size];
+      const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 3, key);
       const T* vr = cache + kv_tile_offset(page, kvh, 1, n_kv_heads, page_size, d) + (size_t)(key % page_size) * d + col;
       float vf[4];
       if constexpr (sizeof(T) == 2) {

@@ -131,7 +131,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       if ((i >> 5) != pages_base) {
         pages_base = i >> 5;
         const int ti = tile_first + warp + ((pages_base << 5) + lane) * DM_WARPS;
-        my_pages = ti <= tile_last ? table[(ti * DM_TILE) / page_size] : 0;
+        my_pages = ti <= tile_last ? LLMRS_CHECKED_PAGE(table[(ti * DM_TILE) / page_size], 4, ti * DM_TILE) : 0;
       }
       const int page = __shfl_sync(0xffffffffu, my_pages, i & 31);
       const bf16* kbase = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) +
@@ -167,7 +167,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       const bool valid = key >= k_begin && key < k_end;
       const bf16* src = cache;
       if (valid) {
-        const int page = table[key / page_size];
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 4, key);
         src = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) + (size_t)(key % page_size) * D + ch * 8;
       }
       cp_async_16(Ks + row * ROW + ch * 8, src, valid ? 16 : 0);
@@ -580,7 +580,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
       const bool valid = key >= key_floor && key < kv_hi;
       const bf16* src = cache;
       if (valid) {
-        const int page = table[key / page_size];
+        const int page = LLMRS_CHECKED_PAGE(table[key / page_size], 4, key);
         src = cache + kv_tile_offset(page, kvh, 0, n_kv_heads, page_size, D) + (size_t)(key % page_size) * D + ch * 8;
       }
       cp_async_16(Ks + row * ROW + ch * 8, src, valid ? 16 : 0);

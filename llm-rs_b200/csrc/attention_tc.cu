@@ -268,11 +268,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     // the block may see (past the end, or before the window) is filled from the page of the newest key
     // instead: whatever a slot holds must be finite (it meets a probability of zero), and shared memory
     // that no copy ever wrote need not be.
-    const int spare_page = table[(kv_hi - 1) / page_size];
+    const int spare_page = LLMRS_CHECKED_PAGE(table[(kv_hi - 1) / page_size], 6, kv_hi - 1);
     auto page_of = [&](int t) {
       const int key = kv_lo + t * AT_BK + box_rows * i;
       if (lane >= n_boxes || t >= n_tiles) return -1;
-      return (key < kv_hi && key + box_rows - 1 >= key_floor) ? table[key / page_size] : spare_page;
+      return (key < kv_hi && key + box_rows - 1 >= key_floor) ? LLMRS_CHECKED_PAGE(table[key / page_size], 6, key) : spare_page;
     };
     auto load_tile = [&](int t, int page) {
       copies = t + 1;

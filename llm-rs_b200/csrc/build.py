@@ -23,14 +23,28 @@ import time
 from typing import List, Optional
 
 CSRC_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_NAME = "libllmrs_b200.so"
+# Two build variants, chosen by the environment at import (each has its own library beside the normal one):
+#   LLMRS_DEBUG_KERNELS=1  the kernels check the indices they are about to use (page ids, positions, token
+#                          ids); a bad one is recorded in a word that ``ops.debug_take()`` reads and its
+#                          access is skipped: no trap, no fault. For hunting a wrong table or position
+#                          where a memory checker cannot be run.
+#   LLMRS_HOST_SANITIZE=1  the C++ host library built with AddressSanitizer and UndefinedBehaviorSanitizer
+#                          (run Python with the sanitizer's runtime preloaded; tests/test_host_sanitized.py).
+DEBUG_KERNELS = os.environ.get("LLMRS_DEBUG_KERNELS", "0") == "1"
+HOST_SANITIZE = os.environ.get("LLMRS_HOST_SANITIZE", "0") == "1"
+_VARIANT = "_debug" if DEBUG_KERNELS else ""
+LIB_NAME = f"libllmrs_b200{_VARIANT}.so"
+STAMP_NAME = f"stamp{_VARIANT}.json"
 # Fast math stays off: norms, softmax and rotation are checked against float32 references.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC"]
+              "-Xcompiler", "-fPIC"] + (["-DLLMRS_DEBUG_CHECKS"] if DEBUG_KERNELS else [])
 ABI_VERSION = 4
 HOST_DIR = os.path.join(CSRC_DIR, "host")
-HOST_LIB_NAME = "libllmrs_b200_host.so"
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall"]
+HOST_LIB_NAME = "libllmrs_b200_host_san.so" if HOST_SANITIZE else "libllmrs_b200_host.so"
+HOST_STAMP_NAME = "host_san_stamp.json" if HOST_SANITIZE else "host_stamp.json"
+HOST_FLAGS = ["-std=c++17", "-fPIC", "-Wall"] + (
+    ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+    if HOST_SANITIZE else ["-O2"])
 HOST_ABI_VERSION = 3
 
 _lib: Optional[ctypes.CDLL] = None
@@ -79,7 +93,7 @@ def _build_dirs() -> List[str]:
     return dirs
 
 
-def _is_current(build_dir: str, fp: str, stamp_name: str = "stamp.json", lib_name: str = LIB_NAME) -> bool:
+def _is_current(build_dir: str, fp: str, stamp_name: str = STAMP_NAME, lib_name: str = LIB_NAME) -> bool:
     stamp = os.path.join(build_dir, stamp_name)
     lib = os.path.join(build_dir, lib_name)
     if not (os.path.isfile(stamp) and os.path.isfile(lib)):
@@ -116,7 +130,7 @@ def _compile(build_dir: str, fp: str) -> None:
     t0 = time.time()
     procs = []
     for name in srcs:
-        obj = os.path.join(build_dir, name[:-3] + ".o")
+        obj = os.path.join(build_dir, name[:-3] + _VARIANT + ".o")
         cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, name), "-o", obj]
         procs.append((name, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     pending = list(procs)
@@ -142,7 +156,7 @@ def _compile(build_dir: str, fp: str) -> None:
     if r.returncode != 0:
         raise KernelBuildError(f"linking the kernel library failed:\n{r.stdout}")
     os.replace(lib_tmp, os.path.join(build_dir, LIB_NAME))
-    with open(os.path.join(build_dir, "stamp.json"), "w") as f:
+    with open(os.path.join(build_dir, STAMP_NAME), "w") as f:
         json.dump({"fingerprint": fp, "flags": NVCC_FLAGS, "sources": srcs}, f)
     _log(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
 
@@ -215,7 +229,7 @@ def _compile_host(build_dir: str, fp: str) -> None:
     if r.returncode != 0:
         raise KernelBuildError(f"compiling the host library failed:\n{r.stdout}")
     os.replace(lib_tmp, os.path.join(build_dir, HOST_LIB_NAME))
-    with open(os.path.join(build_dir, "host_stamp.json"), "w") as f:
+    with open(os.path.join(build_dir, HOST_STAMP_NAME), "w") as f:
         json.dump({"fingerprint": fp, "flags": HOST_FLAGS, "sources": host_sources()}, f)
     _log(f"built {HOST_LIB_NAME} in {time.time() - t0:.0f} s")
 
@@ -225,13 +239,13 @@ def build_host(force: bool = False) -> str:
     fp = _host_fingerprint()
     if not force:
         for d in _build_dirs():
-            if _is_current(d, fp, "host_stamp.json", HOST_LIB_NAME):
+            if _is_current(d, fp, HOST_STAMP_NAME, HOST_LIB_NAME):
                 return os.path.join(d, HOST_LIB_NAME)
     d = _writable_dir()
     with open(os.path.join(d, ".host_lock"), "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
-            if force or not _is_current(d, fp, "host_stamp.json", HOST_LIB_NAME):
+            if force or not _is_current(d, fp, HOST_STAMP_NAME, HOST_LIB_NAME):
                 _compile_host(d, fp)
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

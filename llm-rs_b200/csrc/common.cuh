@@ -73,6 +73,37 @@ inline cudaError_t llmrs_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block,
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ---- the debug build (-DLLMRS_DEBUG_CHECKS; LLMRS_DEBUG_KERNELS=1 at import) ---------------------------
+// Where a memory checker cannot be run, the kernels check the indices they are about to use themselves: a page
+// id taken from a block table (the realistic fault is -1, a page that a window has released), a token id. A bad
+// one is recorded (the first one with its values, and how many there were) and replaced by one that stays inside
+// the buffer; nothing traps. llmrs_debug_take() reads and clears the record of every file of the library.
+//   codes: 1 token id (embedding), 2 page for a cache write, 3/4 page read by the generic / mma.sync attention,
+//          5 page in the q|k|v epilogue, 6 page read by the tcgen05 attention
+#ifdef LLMRS_DEBUG_CHECKS
+static __device__ int g_llmrs_debug[4];   // code, value, where, count (one record per file of the library)
+struct LlmrsDebugReader { explicit LlmrsDebugReader(int (*read)(int*)); };   // errors.cu keeps the list
+static int llmrs_debug_read_file(int* out4) {
+  const int zero[4] = {0, 0, 0, 0};
+  if (cudaMemcpyFromSymbol(out4, g_llmrs_debug, sizeof(zero)) != cudaSuccess) return -1;
+  if (out4[3]) cudaMemcpyToSymbol(g_llmrs_debug, zero, sizeof(zero));
+  return 0;
+}
+static LlmrsDebugReader g_llmrs_debug_reader(&llmrs_debug_read_file);
+__device__ __forceinline__ int llmrs_checked(int value, int lo, int hi, int code, int where, int fallback) {
+  if (value >= lo && value < hi) return value;
+  if (atomicAdd(&g_llmrs_debug[3], 1) == 0) {
+    g_llmrs_debug[0] = code;
+    g_llmrs_debug[1] = value;
+    g_llmrs_debug[2] = where;
+  }
+  return fallback;
+}
+#define LLMRS_CHECKED_PAGE(page, code, where) llmrs_checked((page), 0, 0x7fffffff, (code), (where), 0)
+#else
+#define LLMRS_CHECKED_PAGE(page, code, where) (page)
+#endif
+
 #define LLMRS_REQUIRE(cond, ...)                     \
   do {                                               \
     if (!(cond)) return llmrs_fail(__VA_ARGS__);     \

@@ -15,6 +15,9 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
   const int t = blockIdx.x;
   int id = ids[t];
   // Ids are checked on the host; clamp all the same so that a bad id reads inside the table.
+#ifdef LLMRS_DEBUG_CHECKS
+  id = llmrs_checked(id, 0, vocab, 1, t, 0);
+#endif
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   const TW* row = table + (size_t)id * hidden;
   float* o = out + (size_t)t * hidden;

@@ -45,5 +45,30 @@ L2Prefetch llmrs_take_next_prefetch() {
   return p;
 }
 
+// The debug build's records (see common.cuh): every file of the library that checks indices registers its reader.
+static int (*g_debug_readers[32])(int*);
+static int g_n_debug_readers = 0;
+#ifdef LLMRS_DEBUG_CHECKS
+LlmrsDebugReader::LlmrsDebugReader(int (*read)(int*)) {
+  if (g_n_debug_readers < 32) g_debug_readers[g_n_debug_readers++] = read;
+}
+#endif
+// out4 receives code, value, where and the number of failed checks since the last call (all files together; the
+// first record found wins). Returns 1 in a debug build, 0 in a normal one (nothing is checked), -1 on a CUDA error.
+LLMRS_API int llmrs_debug_take(int* out4) {
+  out4[0] = out4[1] = out4[2] = out4[3] = 0;
+#ifdef LLMRS_DEBUG_CHECKS
+  for (int i = 0; i < g_n_debug_readers; ++i) {
+    int r[4] = {0, 0, 0, 0};
+    if (g_debug_readers[i](r) != 0) return -1;
+    if (r[3] && !out4[3]) { out4[0] = r[0]; out4[1] = r[1]; out4[2] = r[2]; }
+    out4[3] += r[3];
+  }
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 // Version of the entry points' signatures; the Python side checks it after loading.
 LLMRS_API int llmrs_abi_version() { return 4; }

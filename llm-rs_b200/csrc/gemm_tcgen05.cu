@@ -224,7 +224,8 @@ __device__ __forceinline__ void qkv_fetch_tokens(const QkvRope& g, int rank, int
   page = 0;
   if (j < n_tok) {
     pos = g.positions[t0 + j];
-    if (head >= g.n_q_heads) page = g.block_table[(size_t)g.token_req[t0 + j] * g.table_stride + pos / g.page_size];
+    if (head >= g.n_q_heads)
+      page = LLMRS_CHECKED_PAGE(g.block_table[(size_t)g.token_req[t0 + j] * g.table_stride + pos / g.page_size], 5, t0 + j);
   }
 }
 

@@ -50,7 +50,7 @@ __global__ void qk_norm_rope_kvwrite_kernel(
     if (kind == 0) {
       dst = q + (size_t)t * q_stride + (size_t)head * d;
     } else {
-      const int page = block_table[(size_t)token_req[t] * table_stride + pos / page_size];
+      const int page = LLMRS_CHECKED_PAGE(block_table[(size_t)token_req[t] * table_stride + pos / page_size], 2, t);
       dst = cache + kv_tile_offset(page, head, kind - 1, n_kv_heads, page_size, d) + (size_t)(pos % page_size) * d;
     }
     if (kind == 2) {
@@ -110,7 +110,7 @@ qk_norm_rope_kvwrite_d128_kernel(__nv_bfloat16* __restrict__ q, long long q_stri
   if (first - sub >= n_heads_total) return;
   for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
   const int pos = positions[t];
-  const size_t page_base = k ? (size_t)block_table[(size_t)token_req[t] * table_stride + pos / page_size] : 0;
+  const size_t page_base = k ? (size_t)LLMRS_CHECKED_PAGE(block_table[(size_t)token_req[t] * table_stride + pos / page_size], 2, t) : 0;
 
   const __nv_bfloat16* src[D128_PASSES];
   __nv_bfloat16* dst[D128_PASSES];

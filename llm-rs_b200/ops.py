@@ -428,6 +428,20 @@ def hint_next_weights(w: Optional[torch.Tensor], limit: Optional[int] = None) ->
     _check(fn(ctypes.c_void_p(w.data_ptr()), ctypes.c_longlong(n)), "set_next_prefetch", launches=0)
 
 
+def debug_take():
+    """The debug build's record (``LLMRS_DEBUG_KERNELS=1``): ``(code, value, where, count)`` of the index checks
+    that failed since the last call, or None when nothing failed. Raises in a normal build, which checks nothing.
+    Synchronises."""
+    out = (ctypes.c_int * 4)()
+    torch.cuda.synchronize()
+    rc = _lib().llmrs_debug_take(out)
+    if rc == 0:
+        raise KernelError("this is not the debug build of the kernel library (set LLMRS_DEBUG_KERNELS=1 before import)")
+    if rc < 0:
+        raise KernelError("reading the debug record failed")
+    return tuple(out) if out[3] else None
+
+
 def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     """Blocks of a cluster that share the k range of a skinny product: enough blocks to
     fill the GPU about twice, at least four 64-wide k blocks each."""
