@@ -20,8 +20,9 @@
 // a larger page, and half of the head; the boxes of a tile are issued by as many lanes side by
 // side, since one copy costs its issuer some 80 cycles), so the softmax threads never wait for
 // issue work and the copies never delay an MMA. K and V go through a ring of three stages. The
-// roles meet at mbarriers only. Two blocks share an SM: while one does its softmax the other's
-// MMAs run. Blocks with the longest rows of keys are scheduled first.
+// roles meet at mbarriers only. A block holds all 512 columns of tensor memory (S twice, O, Q), so one
+// block runs per SM; S of the next tile is computed while the softmax of this one runs. Blocks with the
+// longest rows of keys are scheduled first.
 //
 // Same contract and math as attn_prefill_kernel in attention.cu (scores, softmax and the
 // weighted sum accumulate in float32; llm-core/src/backends/candle.rs:1587-1640). Every
