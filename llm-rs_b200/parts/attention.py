@@ -89,8 +89,9 @@ class GQAttention(Mixer):
                  window: int = 0, scale: Optional[float] = None, split_keys: int = 0, names=None, prefix: str = ""):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads are no multiple of {n_kv_heads} key/value heads")
-        if head_dim % 16:
-            raise ValueError(f"head_dim {head_dim} must be a multiple of 16 for the attention kernels")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples of 16 "
+                             f"from 16 to 256")
         self.hidden_size, self.n_heads, self.n_kv_heads, self.head_dim = hidden_size, n_heads, n_kv_heads, head_dim
         self.qk_norm, self.qk_norm_eps, self.bias, self.window = qk_norm, float(qk_norm_eps), bias, int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)

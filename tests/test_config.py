@@ -147,3 +147,14 @@ def test_parts_take_their_tensor_names_from_the_spec():
     with pytest.raises(ValueError, match="names may rename"):
         DecoderModel(dataclasses.replace(spec, layers=(spec.layers[0], dataclasses.replace(spec.layers[1], mixer=PartSpec(
             "gqa_attention", {**spec.layers[1].mixer.params, "names": {"query": "x"}})))))
+
+
+@pytest.mark.parametrize("head_dim", [8, 24, 272, 512])
+def test_head_sizes_the_kernels_do_not_take_are_refused_when_the_model_is_built(head_dim):
+    """Head sizes come in steps of 16 up to 256; anything else is refused with a clear error when the model is put
+    together, not by a kernel at the first step."""
+    from llm_rs_b200.models.qwen3 import build_spec
+    from llm_rs_b200.parts import DecoderModel
+    spec = build_spec(Qwen3Config.from_dict({**TINY_A, "head_dim": head_dim}))
+    with pytest.raises(ValueError, match=f"head_dim {head_dim} is not supported"):
+        DecoderModel(spec)

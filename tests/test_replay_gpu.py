@@ -25,7 +25,8 @@ TOL_F32 = 1e-4
 TOL_BF16_REL = 0.02
 
 LENGTHS = {"A": [5, 17, 33, 64, 100, 161], "B": [1, 9, 40, 77, 128, 200], "C": [3, 30, 48, 65, 97, 150],
-           "D": [40, 130, 300, 520, 257], "E": [40, 130, 300, 520, 257]}
+           "D": [40, 130, 300, 520, 257], "E": [40, 130, 300, 520, 257], "F": [2, 19, 70, 131, 260],
+           "G": [4, 31, 66, 129, 200]}
 MODES = ["whole", "tail", "portions", "mixed"]
 
 

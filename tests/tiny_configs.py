@@ -35,9 +35,28 @@ TINY_D = dict(
     tie_word_embeddings=False, attention_bias=False, max_position_embeddings=2048, hidden_act="silu",
     eos_token_id=519)
 
+# Heads wider than 128 elements and no power of two (the bfloat16 engine then takes its generic attention
+# kernels), one key head for three query heads, pages of 4 keys, a width and a vocabulary that are odd multiples.
+TINY_F = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=72, num_attention_heads=3, num_key_value_heads=1, head_dim=160,
+    intermediate_size=200, vocab_size=291, rope_theta=20000.0, rms_norm_eps=2e-6,
+    tie_word_embeddings=True, attention_bias=False, max_position_embeddings=700, hidden_act="silu",
+    eos_token_id=[7])
+
+# Sizes that are multiples of nothing useful: a width of 70, a feed-forward width of 150, a prime vocabulary, five
+# heads that each have their own key head (no grouping): no vectorised or tensor-core fast path applies as it stands.
+TINY_G = dict(
+    architectures=["Qwen3ForCausalLM"], model_type="qwen3",
+    num_hidden_layers=2, hidden_size=70, num_attention_heads=5, num_key_value_heads=5, head_dim=16,
+    intermediate_size=150, vocab_size=257, rope_theta=10000.0, rms_norm_eps=1e-5,
+    tie_word_embeddings=False, attention_bias=True, max_position_embeddings=300, hidden_act="silu",
+    eos_token_id=3)
+
 # name -> (config.json, seed, sigma of matrices, page size); E is D with pages of 64 keys
 TINY = {"A": (TINY_A, 0, 0.02, 16), "B": (TINY_B, 1, 0.03, 8), "C": (TINY_C, 5, 0.05, 16),
-        "D": (TINY_D, 6, 0.04, 16), "E": (TINY_D, 6, 0.04, 64)}
+        "D": (TINY_D, 6, 0.04, 16), "E": (TINY_D, 6, 0.04, 64), "F": (TINY_F, 9, 0.05, 4),
+        "G": (TINY_G, 10, 0.05, 16)}
 
 
 def write_tiny_model(name: str, folder: str, sigma_scale: float = 1.0, norm_dtype=None) -> str:
