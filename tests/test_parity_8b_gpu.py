@@ -91,19 +91,24 @@ def _replay(runner, steps, ref):
     return worst, where, n
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
 @pytest.mark.parametrize("mode", MODES)
-def test_engine_at_qwen3_8b_layer_sizes_matches_plain(setup, mode, dtype):
+def test_engine_at_qwen3_8b_layer_sizes_matches_plain(setup, mode, dtype, graphs):
+    """``graphs``: steps of single tokens are captured in CUDA graphs and replayed (the way the engine decodes)."""
     from llm_rs_b200.engine import ModelRunner
     spec, t16, reqs, wanted, ref = setup
+    if graphs and mode in ("whole", "portions"):
+        pytest.skip("no step of single tokens in this mode")
     steps = RU.want_only(_steps(mode, reqs), wanted)
     tensors = t16 if dtype == "bfloat16" else {k: v.float() for k, v in t16.items()}
     runner = ModelRunner(spec, tensors, getattr(torch, dtype), DEV, max_tokens=RU.live_token_peak(steps),
                          page_size=16, max_requests=4)
+    runner.use_graphs = graphs
     free = runner.manager.free_pages(0)
     worst, where, n = _replay(runner, steps, ref)
     assert n == sum(len(w) for w in wanted.values())
     assert runner.manager.free_pages(0) == free, "pages were lost"
+    assert bool(runner._graphs) == graphs
     scale = max(float(rows.abs().max()) for _, rows in ref.values())
     tol = 1e-4 if dtype == "float32" else 0.02 * scale
     assert worst <= tol, (f"{LAYERS} of {LAYERS_OF} layers, {mode}, {dtype}: max |diff| {worst:.3e} at {where} "
