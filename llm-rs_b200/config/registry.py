@@ -40,6 +40,10 @@ def register_architecture(entry: ArchitectureEntry, *, replace: bool = False) ->
     _ARCHITECTURES[entry.name] = entry
 
 
+def unregister_architecture(name: str) -> None:
+    _ARCHITECTURES.pop(name, None)
+
+
 def architecture_names() -> List[str]:
     return sorted(_ARCHITECTURES)
 

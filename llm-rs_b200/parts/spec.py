@@ -33,7 +33,7 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: PartSpec
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec] = None     # a block with one norm for both branches has none
     mixer_scope: str = ""
     feed_forward_scope: str = ""
 
