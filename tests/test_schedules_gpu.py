@@ -227,3 +227,48 @@ def test_all_window_model_runs_far_beyond_its_pool(models, dtype, tmp_path):
     assert n == 500
     assert worst <= _tol(dtype, ref["a"]), (worst, where)
     assert runner.manager.free_pages(0) == 10
+
+
+# -- random workloads through the whole engine ------------------------------------------------------
+@pytest.mark.parametrize("name,seed", [("A", 0), ("A", 1), ("C", 2), ("C", 3), ("D", 4)])
+def test_random_workloads_through_the_engine(models, name, seed):
+    """Requests of random lengths arrive while others run, in a pool so small that the scheduler preempts, with
+    CUDA graphs and queued steps on: every request still gets exactly the greedy tokens of the plain
+    implementation (float32), whatever was batched with it, preempted around it or recomputed."""
+    from llm_rs_b200.engine import Engine, EngineConfig
+    from llm_rs_b200.sampling import SamplingParams
+    path, cfg, w = models[name]
+    rng = np.random.default_rng(1000 + seed)
+    n_req = 10
+    prompts = [rng.integers(0, cfg["vocab_size"], int(rng.integers(1, 70))).tolist() for _ in range(n_req)]
+    new = [int(rng.integers(1, 18)) for _ in range(n_req)]
+    arrive = sorted(int(rng.integers(0, 25)) for _ in range(n_req))      # the engine step at which each is submitted
+    e = Engine(EngineConfig(model_path=path, block_pool_size=12, page_size=16, dtype="float32", max_requests=4,
+                            max_tokens_per_step=int(rng.choice([24, 40, 64])), prefill_chunk=int(rng.choice([8, 16, 32])),
+                            cuda_graphs=True, async_steps=True))
+    ids, step = {}, 0
+    while len(ids) < n_req or e.has_work():
+        for i in range(n_req):
+            if i not in ids and arrive[i] <= step:
+                ids[i] = e.add_request(prompts[i], SamplingParams(temperature=0.0, max_new_tokens=new[i], ignore_eos=True))
+        e.step()
+        step += 1
+        assert step < 3000
+        e.runner.manager.check_invariants()
+    for i in range(n_req):
+        got = e.requests[ids[i]].output
+        assert len(got) == new[i], (i, e.finish_reason(ids[i]))
+        assert P.greedy_gap(cfg, w, prompts[i], got) < 1e-4, (name, seed, i)
+    assert not e.runner.manager.requests
+    assert all(e.runner.manager.free_pages(g) == 12 for g in range(len(e.runner.manager.groups)))
+    _PREEMPTIONS.append(e.scheduler.stats["preemptions"])
+
+
+_PREEMPTIONS = []
+
+
+def test_random_workloads_did_preempt():
+    """The pools above are meant to be too small: at least one of the runs must have preempted."""
+    if not _PREEMPTIONS:
+        pytest.skip("the random workloads did not run in this session")
+    assert sum(_PREEMPTIONS) >= 1, _PREEMPTIONS
