@@ -117,3 +117,26 @@ def test_trace_run_program(models, tmp_path, dtype):
         assert k == data.shape[0]
     scale = max(float(np.abs(r).max()) for r in ref.values())
     assert worst <= (TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale), worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [11, 12, 13])
+@pytest.mark.parametrize("name", ["C", "D", "E", "F"])
+def test_mixed_replay_with_other_cuts(models, name, seed, dtype):
+    """The mixed trace again with other seeds, portion sizes from 2 to 300 tokens (longer than C's window, long
+    enough for the tcgen05 attention of D and E), other tail lengths and two or three live requests."""
+    from llm_rs_b200.engine import ModelRunner
+    path, cfg, reqs, ref = models[name]
+    rng = np.random.default_rng(seed)
+    sizes = tuple(int(x) for x in rng.choice([2, 3, 7, 16, 31, 33, 64, 65, 128, 129, 200, 300], size=6, replace=False))
+    steps = RU.mixed(reqs, seed=seed, max_live=int(rng.integers(2, 5)), decode_tail=int(rng.integers(1, 40)), sizes=sizes)
+    runner = ModelRunner.from_model_dir(path, dtype=getattr(torch, dtype), max_tokens=RU.live_token_peak(steps),
+                                        page_size=TINY[name][3], max_requests=4)
+    runner.use_graphs = bool(seed % 2)
+    got = RU.run_steps(runner, steps)
+    worst, where, n = RU.max_diff(got, ref)
+    assert n == sum(len(t) for t in reqs.values())
+    scale = max(float(np.abs(r).max()) for r in ref.values())
+    tol = TOL_F32 if dtype == "float32" else TOL_BF16_REL * scale
+    assert worst <= tol, f"{name} seed {seed} sizes {sizes} {dtype}: max |diff| {worst:.3e} at {where} (tolerance {tol:.3e})"
+    assert all(p.free_pages() == p.capacity for p in runner.manager.pools)
