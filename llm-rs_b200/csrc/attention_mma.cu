@@ -71,7 +71,12 @@ __host__ __device__ inline size_t dm_inbox_bytes(int ng, int d, int splits) {
   return (size_t)splits * (2 * ng + dm_share(ng, d, splits)) * 4;
 }
 
-template <int DCH>
+// SWAP (at most 8 query heads per key head, the usual case): the keys are the 16 rows of the MMA and the heads its
+// 8 columns (S^T = K Q^T, O^T = V^T P^T), so a tile of 16 keys takes one MMA per 16 elements of the head where the
+// other orientation (heads on the 16 rows, most of them padding) takes two; P goes from the accumulators' layout
+// to the operand's by a transposing register move (movmatrix). The legacy tensor path is slow enough on this part
+// that the MMAs of a tile are a large part of a warp's time per tile.
+template <int DCH, bool SWAP>
 __global__ void __launch_bounds__(DM_THREADS)
 attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ cache,
                              const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
@@ -181,6 +186,12 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   const float sl2 = scale * LOG2E;
 
+  // Accumulators of the swapped orientation: O^T per 16 elements of the head (rows) and the heads 2tq, 2tq+1
+  // (columns); the running maximum and sum of those two heads (the same in the eight lanes that share tq).
+  float ot[DCH][4];
+#pragma unroll
+  for (int n = 0; n < DCH; ++n) ot[n][0] = ot[n][1] = ot[n][2] = ot[n][3] = 0.f;
+  float m_h[2] = {-INFINITY, -INFINITY}, l_h[2] = {0.f, 0.f};
   // The first tiles are requested before the wait on the preceding kernels (they overlap
   // those kernels' tails), except a tile that holds the newest key, which this step writes.
   const int new_tile = (kv_len - 1) / DM_TILE;
@@ -195,6 +206,89 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
     if (s < n_my && tile_first + warp + s * DM_WARPS >= new_tile) load_tile(s, s);
     cp_async_commit();
   }
+  if constexpr (SWAP) {
+    // Q^T as B fragments (k = element of the head, n = head): lane (gq, tq) holds elements 2tq, 2tq+1 (and +8) of
+    // head gq for every 16 elements; heads beyond the group are zero.
+    uint32_t qb[DCH][2];
+    {
+      const bf16* qh = q + (size_t)q_start[req] * q_stride + (size_t)(kvh * G + g0 + gq) * D;
+#pragma unroll
+      for (int kc = 0; kc < DCH; ++kc) {
+        qb[kc][0] = gq < ng ? *reinterpret_cast<const uint32_t*>(qh + kc * 16 + tq * 2) : 0u;
+        qb[kc][1] = gq < ng ? *reinterpret_cast<const uint32_t*>(qh + kc * 16 + tq * 2 + 8) : 0u;
+      }
+    }
+    for (int i = 0; i < n_my; ++i) {
+      cp_async_wait<DM_STAGES - 2>();
+      __syncwarp();
+      if (i + DM_STAGES - 1 < n_my) load_tile(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
+      cp_async_commit();
+
+      const bf16* Ks = wbase + (size_t)(i % DM_STAGES) * 2 * TILE_ELEMS;
+      const bf16* Vs = Ks + TILE_ELEMS;
+      const int key0 = (tile_first + warp + i * DM_WARPS) * DM_TILE;
+      const int j = lane >> 3;
+
+      // S^T: 16 keys (rows) x 8 heads (columns). s[0], s[1]: key gq, heads 2tq, 2tq+1; s[2], s[3]: key gq + 8.
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int kc = 0; kc < DCH; ++kc) {
+        uint32_t a[4];
+        // matrix j: keys (j%2)*8.., elements of the head kc*16 + (j/2)*8..
+        ldmatrix_x4(a, Ks + ((j & 1) * 8 + (lane & 7)) * ROW + kc * 16 + (j >> 1) * 8);
+        mma_bf16_16816(sc, a, qb[kc][0], qb[kc][1]);
+      }
+      const bool edge = key0 < k_begin || key0 + DM_TILE > k_end;
+      if (edge) {
+        const bool seen_lo = key0 + gq >= k_begin && key0 + gq < k_end;
+        const bool seen_hi = key0 + gq + 8 >= k_begin && key0 + gq + 8 < k_end;
+        sc[0] = seen_lo ? sc[0] : -INFINITY; sc[1] = seen_lo ? sc[1] : -INFINITY;
+        sc[2] = seen_hi ? sc[2] : -INFINITY; sc[3] = seen_hi ? sc[3] : -INFINITY;
+      }
+      float corr[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {       // this lane's two heads; the keys of a head are spread over gq
+        float mx = fmaxf(sc[h], sc[2 + h]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        const float m_new = fmaxf(m_h[h], mx * sl2);
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        corr[h] = ex2(m_h[h] - m_use);
+        m_h[h] = m_new;
+        const float p0 = ex2(fmaf(sc[h], sl2, -m_use)), p1 = ex2(fmaf(sc[2 + h], sl2, -m_use));
+        sc[h] = p0;
+        sc[2 + h] = p1;
+        float sum = p0 + p1;
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 8);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+        l_h[h] = l_h[h] * corr[h] + sum;
+      }
+      // P^T as B fragments (k = key, n = head): the accumulators hold (key gq, heads 2tq..), the operand wants
+      // (keys 2tq.., head gq): one transposing move per 8 keys.
+      uint32_t pb0, pb1;
+      {
+        const uint32_t lo = pack_bf16(sc[0], sc[1]), hi = pack_bf16(sc[2], sc[3]);
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb0) : "r"(lo));
+        asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(pb1) : "r"(hi));
+      }
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
+#pragma unroll
+        for (int n = 0; n < DCH; ++n) {
+          ot[n][0] *= corr[0]; ot[n][1] *= corr[1]; ot[n][2] *= corr[0]; ot[n][3] *= corr[1];
+        }
+      }
+      // O^T += V^T P^T: rows are 16 elements of the head, the A fragments are 8x8 blocks of V read transposed.
+#pragma unroll
+      for (int nc = 0; nc < DCH; ++nc) {
+        uint32_t a[4];
+        // matrix j: keys (j/2)*8.., elements of the head nc*16 + (j%2)*8..
+        ldmatrix_x4_trans(a, Vs + ((j >> 1) * 8 + (lane & 7)) * ROW + nc * 16 + (j & 1) * 8);
+        mma_bf16_16816(ot[nc], a, pb0, pb1);
+      }
+    }
+  } else {
   // Query rows as A fragments: row gq is head g0+gq, row gq+8 is head g0+gq+8; absent heads are zero.
   uint32_t qf[DCH][4];
   {
@@ -290,6 +384,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       mma_bf16_16816(o[2 * nc + 1], pf, b[2], b[3]);
     }
   }
+  }
   // The block's last keys and values are on their way: the weights of the product that follows attention
   // (see L2Prefetch) can come into the L2 while this block merges its warps and its cluster.
   if (threadIdx.x == 0) l2_prefetch_slice(next);
@@ -300,16 +395,30 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   float* Om = reinterpret_cast<float*>(smem_raw);           // [warps][16][D]
   float* Mm = Om + DM_WARPS * 16 * D;                       // [warps][16]
   float* Lm = Mm + DM_WARPS * 16;
+  if constexpr (SWAP) {
+    // Rows of Om are heads (2tq, 2tq+1 of this lane), columns elements of the head (gq and gq + 8 of every 16).
 #pragma unroll
-  for (int n = 0; n < 2 * DCH; ++n) {
-    const int col = n * 8 + tq * 2;
-    float* r0 = Om + ((size_t)warp * 16 + gq) * D + col;
-    float* r1 = Om + ((size_t)warp * 16 + gq + 8) * D + col;
-    r0[0] = o[n][0]; r0[1] = o[n][1]; r1[0] = o[n][2]; r1[1] = o[n][3];
-  }
-  if (tq == 0) {
-    Mm[warp * 16 + gq] = m_row[0]; Mm[warp * 16 + gq + 8] = m_row[1];
-    Lm[warp * 16 + gq] = l_row[0]; Lm[warp * 16 + gq + 8] = l_row[1];
+    for (int n = 0; n < DCH; ++n) {
+      float* h0 = Om + ((size_t)warp * 16 + tq * 2) * D + n * 16 + gq;
+      float* h1 = h0 + D;
+      h0[0] = ot[n][0]; h1[0] = ot[n][1]; h0[8] = ot[n][2]; h1[8] = ot[n][3];
+    }
+    if (gq == 0) {
+      Mm[warp * 16 + tq * 2] = m_h[0]; Mm[warp * 16 + tq * 2 + 1] = m_h[1];
+      Lm[warp * 16 + tq * 2] = l_h[0]; Lm[warp * 16 + tq * 2 + 1] = l_h[1];
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < 2 * DCH; ++n) {
+      const int col = n * 8 + tq * 2;
+      float* r0 = Om + ((size_t)warp * 16 + gq) * D + col;
+      float* r1 = Om + ((size_t)warp * 16 + gq + 8) * D + col;
+      r0[0] = o[n][0]; r0[1] = o[n][1]; r1[0] = o[n][2]; r1[1] = o[n][3];
+    }
+    if (tq == 0) {
+      Mm[warp * 16 + gq] = m_row[0]; Mm[warp * 16 + gq + 8] = m_row[1];
+      Lm[warp * 16 + gq] = l_row[0]; Lm[warp * 16 + gq + 8] = l_row[1];
+    }
   }
   __syncthreads();
   const int S = (int)gridDim.z;
@@ -418,10 +527,14 @@ static int decode_mma_allow(size_t smem) {
   static std::mutex mutex;
   std::lock_guard<std::mutex> lock(mutex);
   if (smem > allowed) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>,
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH, false>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
-    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH, false>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<DCH, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
     if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
     allowed = smem;
   }
@@ -461,7 +574,9 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   }
   cfg.attrs = attr;
   cfg.numAttrs = n_attr;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_split_mma_kernel<DCH>, (const bf16*)q, q_stride, (const bf16*)cache,
+  // At most eight query heads per key head: the keys take the MMA's rows (see the kernel).
+  auto kernel = G <= 8 ? attn_decode_split_mma_kernel<DCH, true> : attn_decode_split_mma_kernel<DCH, false>;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (const bf16*)cache,
                                      dec_reqs, q_start, cached_len, block_table, table_stride, scratch, max_splits,
                                      split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out,
                                      out_stride, counters, cluster_merge, next);
@@ -487,7 +602,8 @@ static int decode_mma_capacity(int cluster, int ng, int* blocks) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  e = cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH>, &cfg);
+  e = ng <= 8 ? cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH, true>, &cfg)
+              : cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH, false>, &cfg);
   if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: occupancy of clusters of %d: %s", cluster, cudaGetErrorString(e));
   *blocks = n * cluster;
   return 0;

@@ -213,7 +213,7 @@ def _run_attention(q, cache, table, lens, new, nq, nkv, d, page, window, scale, 
 
 SHAPES = [  # nq, nkv, d, page
     (4, 2, 16, 16), (6, 3, 48, 8), (8, 1, 64, 16), (5, 5, 80, 4), (32, 8, 128, 16), (3, 1, 96, 32), (40, 2, 32, 16),
-    (2, 1, 160, 16), (4, 2, 256, 16)]
+    (2, 1, 160, 16), (4, 2, 256, 16), (7, 1, 32, 8), (18, 2, 64, 16)]
 
 
 @pytest.mark.parametrize("impl", ["auto", "generic", "auto-two-kernels"])
