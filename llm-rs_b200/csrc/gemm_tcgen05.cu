@@ -179,6 +179,22 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, float (&v)[8]) {
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 32 consecutive float32 columns of this thread's lane.
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -645,13 +661,164 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 constexpr int PS_BN = 256, PS_STAGES = 4, PS_THREADS = 192;
 constexpr uint32_t PS_A_BYTES = TC_BM * TC_BK * 2, PS_B_BYTES = PS_BN * TC_BK * 2, PS_STAGE_BYTES = PS_A_BYTES + PS_B_BYTES;
 
+// The residual stream's old values for the epilogue warps of the many-token kernels. In tensor memory a lane owns a
+// token's row, and rows of h lie kilobytes apart: loaded by the lanes themselves, a tile's 8,192 values per warp came
+// in at the latency of 32 round trips to memory (30 us a tile, longer than the tile's MMAs). Instead TMA brings
+// pieces of 32 rows x 32 columns (128-byte swizzle, so that a lane reads its row without bank conflicts) into two
+// buffers per warp, two pieces ahead of their use and across tiles.
+constexpr uint32_t HF_PIECE_BYTES = 32 * 32 * 4;
+struct HFeed {
+  uint32_t buf0 = 0;            // the warp's first buffer in shared memory (the second lies HF_PIECE_BYTES on)
+  uint32_t bar0 = 0;            // its first barrier (the second 8 bytes on)
+  long long issued = 0, taken = 0;   // pieces requested / used
+};
+__device__ __forceinline__ void hfeed_request(const CUtensorMap* map_h, HFeed& hf, int col, int row, bool leader_lane) {
+  if (leader_lane) {
+    const uint32_t b = (uint32_t)(hf.issued & 1);
+    // The lanes' reads of the buffer (generic proxy) come before the copy into it (async proxy).
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_expect_tx(hf.bar0 + 8 * b, HF_PIECE_BYTES);
+    tma_load_2d(hf.buf0 + HF_PIECE_BYTES * b, map_h, hf.bar0 + 8 * b, col, row);
+  }
+  ++hf.issued;
+}
+// The first two pieces of a tile (before its loop; later pieces are requested as earlier ones are used).
+__device__ __forceinline__ void hfeed_start(const CUtensorMap* map_h, HFeed& hf, int tn, int tok0, bool leader_lane) {
+  hfeed_request(map_h, hf, tn * 256, tok0, leader_lane);
+  hfeed_request(map_h, hf, tn * 256 + 32, tok0, leader_lane);
+}
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// The factor a norm spread over two products still owes this token's row (see TcParams), 1 without one.
+__device__ __forceinline__ float ps_row_scale(const TcParams& p, int tok, bool t_ok) {
+  if (!p.scale_part || !t_ok) return 1.f;
+  float ss = 0.f;
+  for (int q = 0; q < p.scale_parts; ++q) ss += __ldcg(p.scale_part + (size_t)q * p.part_stride + tok);
+  return 1.0f / sqrtf(ss / (float)p.scale_dim + p.scale_eps);
+}
+
+// The epilogue of one tile of 256 columns whose rows are tokens, for one warp: `taddr` its 32 lanes of tensor memory
+// at the tile's first column, `tok0` the token of lane 0 (lane l owns token tok0 + l), `tn` the tile's index along the
+// features. TC_RESIDUAL: `hf` feeds the old values of h; the first two pieces of this tile have been requested, and
+// those of the warp's next tile (next_tn, next_tok0; next_tn < 0: none) are requested here. All 32 lanes walk it
+// together (tcgen05.ld is warp-wide) whether their token exists or not. False: a wait ran out.
+__device__ __forceinline__ bool ps_epilogue_tile(const TcParams& p, const CUtensorMap* map_h, HFeed& hf, uint32_t taddr,
+                                                 int tok0, int lane, int tn, int next_tn, int next_tok0,
+                                                 bool leader_lane, volatile int* abort_flag) {
+  const int tok = tok0 + lane;
+  const bool t_ok = tok < p.a_rows;
+  const float inv = ps_row_scale(p, tok, t_ok);
+  if (p.epilogue == TC_SILU_MUL) {
+    // Columns come in groups of 128: 64 gate columns, then the 64 up columns of the same features.
+#pragma unroll 1
+    for (int g = 0; g < PS_BN / 128; ++g) {
+#pragma unroll 1
+      for (int c = 0; c < 64; c += 8) {
+        float gv[8], uv[8];
+        tc_ld8(taddr + g * 128 + c, gv);
+        tc_ld8(taddr + g * 128 + 64 + c, uv);
+        const int f = (tn * PS_BN + g * 128) / 2 + c;
+        if (t_ok && f < p.b_rows / 2) {
+          uint4 pk;
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            h2[e] = __floats2bfloat162_rn(silu_f(gv[2 * e] * inv) * (uv[2 * e] * inv),
+                                          silu_f(gv[2 * e + 1] * inv) * (uv[2 * e + 1] * inv));
+          *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
+        }
+        __syncwarp();
+      }
+    }
+  } else if (p.epilogue == TC_RESIDUAL) {
+    // h += y, 32 columns at a time. With emit_w the same pass writes the input of the norm that follows,
+    // (h + y) * w in bfloat16, and adds up the squares of the lane's row.
+    float* hrow = (float*)p.out + (size_t)tok * p.ldo;
+    float ss = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < PS_BN; c += 32) {
+      float v[32];
+      tc_ld32(taddr + c, v);
+      const uint32_t b = (uint32_t)(hf.taken & 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(hf.bar0 + 8 * b, (uint32_t)(hf.taken >> 1) & 1, p.wait_limit, abort_flag)))
+        return false;
+      const uint32_t row_addr = hf.buf0 + HF_PIECE_BYTES * b + (uint32_t)lane * 128;
+      float4 hv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hv[j] = ld_shared_f4(row_addr + (uint32_t)((j ^ (lane & 7)) << 4));
+      ++hf.taken;
+      __syncwarp();   // every lane has read the buffer: the piece after next may land in it
+      if (c + 64 < PS_BN) hfeed_request(map_h, hf, tn * PS_BN + c + 64, tok0, leader_lane);
+      else if (next_tn >= 0) hfeed_request(map_h, hf, next_tn * PS_BN + c + 64 - PS_BN, next_tok0, leader_lane);
+      const int f = tn * PS_BN + c;
+      if (t_ok) {
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          if (f + 4 * j >= p.b_rows) break;     // features come in eights
+          float n[8];
+          n[0] = hv[j].x + v[4 * j] * inv; n[1] = hv[j].y + v[4 * j + 1] * inv;
+          n[2] = hv[j].z + v[4 * j + 2] * inv; n[3] = hv[j].w + v[4 * j + 3] * inv;
+          n[4] = hv[j + 1].x + v[4 * j + 4] * inv; n[5] = hv[j + 1].y + v[4 * j + 5] * inv;
+          n[6] = hv[j + 1].z + v[4 * j + 6] * inv; n[7] = hv[j + 1].w + v[4 * j + 7] * inv;
+          float4* dst = reinterpret_cast<float4*>(hrow + f + 4 * j);
+          dst[0] = make_float4(n[0], n[1], n[2], n[3]);
+          dst[1] = make_float4(n[4], n[5], n[6], n[7]);
+          if (p.emit_w) {
+            const float4 w0 = *reinterpret_cast<const float4*>(p.emit_w + f + 4 * j);
+            const float4 w1 = *reinterpret_cast<const float4*>(p.emit_w + f + 4 * j + 4);
+            uint4 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+            h2[0] = __floats2bfloat162_rn(n[0] * w0.x, n[1] * w0.y);
+            h2[1] = __floats2bfloat162_rn(n[2] * w0.z, n[3] * w0.w);
+            h2[2] = __floats2bfloat162_rn(n[4] * w1.x, n[5] * w1.y);
+            h2[3] = __floats2bfloat162_rn(n[6] * w1.z, n[7] * w1.w);
+            *reinterpret_cast<uint4*>(p.emit_xw + (size_t)tok * p.emit_ld + f + 4 * j) = pk;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += n[e] * n[e];
+          }
+        }
+      }
+      __syncwarp();
+    }
+    if (p.emit_w && t_ok) p.emit_part[(size_t)tn * p.part_stride + tok] = ss;
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < PS_BN; c += 8) {
+      float v[8];
+      tc_ld8(taddr + c, v);
+      const int f = tn * PS_BN + c;
+      if (!t_ok || f >= p.b_rows) {
+        // nothing to store for this thread; stay with the warp for the next tcgen05.ld
+      } else if (p.out_dtype == LLMRS_F32) {
+        float4* op = reinterpret_cast<float4*>((float*)p.out + (size_t)tok * p.ldo + f);
+        op[0] = make_float4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        op[1] = make_float4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+      } else {
+        uint4 pk;
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
+      }
+      __syncwarp();
+    }
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(PS_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          const TcParams p, int n_m, int n_tiles) {
+                          const __grid_constant__ CUtensorMap map_h, const TcParams p, int n_m, int n_tiles) {
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + (size_t)PS_STAGES * PS_STAGE_BYTES);   // full[4], empty[4], acc_full[2], acc_empty[2], drain
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PS_STAGES + 5);
+  unsigned char* h_pieces = tiles + (size_t)PS_STAGES * PS_STAGE_BYTES;   // two pieces of h per epilogue warp (HFeed)
+  // full[4], empty[4], acc_full[2], acc_empty[2], drain, then the epilogue warps' two barriers each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(h_pieces + 8 * HF_PIECE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PS_STAGES + 5 + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   pdl_launch_dependents();
@@ -663,6 +830,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     mbar_init(acc_empty0, 128);
     mbar_init(acc_empty0 + 8, 128);
     mbar_init(drain_bar, 1);
+    for (int s = 0; s < 8; ++s) mbar_init(drain_bar + 8 + 8 * s, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -679,6 +847,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
   pdl_wait();   // x is what an earlier kernel wrote; the epilogue writes what earlier kernels read
   const int nkb = p.k_blocks;
   long long copies = 0;   // warp 0: stages whose copies it has requested
+  HFeed hf;               // epilogue warps: their pieces of the residual stream
 
   if (warp == 0) {
     // Copies: the whole warp walks the loop, one elected lane issues.
@@ -738,7 +907,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     // Epilogue: thread = one token row of the tile; a warp reaches the 32 lanes of tensor memory
     // that its index modulo 4 names.
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
+    const bool leader = tc_elect_one();
+    hf.buf0 = tc_smem(h_pieces) + (uint32_t)(warp - 2) * 2 * HF_PIECE_BYTES;
+    hf.bar0 = drain_bar + 8 + (uint32_t)(warp - 2) * 16;
+    if (p.epilogue == TC_RESIDUAL && (int)blockIdx.x < n_tiles)
+      hfeed_start(&map_h, hf, blockIdx.x / n_m, (blockIdx.x % n_m) * TC_BM + quarter * 32, leader);
     int lt = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++lt) {
@@ -747,57 +920,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * PS_BN;
-      const int tok = tm * TC_BM + row;
-      const bool t_ok = tok < p.a_rows;
-      if (p.epilogue == TC_SILU_MUL) {
-        // Columns come in groups of 128: 64 gate columns, then the 64 up columns of the same features.
-#pragma unroll 1
-        for (int g = 0; g < PS_BN / 128; ++g) {
-#pragma unroll 1
-          for (int c = 0; c < 64; c += 8) {
-            float gv[8], uv[8];
-            tc_ld8(taddr + g * 128 + c, gv);
-            tc_ld8(taddr + g * 128 + 64 + c, uv);
-            const int f = (tn * PS_BN + g * 128) / 2 + c;
-            if (t_ok && f < p.b_rows / 2) {
-              uint4 pk;
-              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                h2[e] = __floats2bfloat162_rn(silu_f(gv[2 * e]) * uv[2 * e], silu_f(gv[2 * e + 1]) * uv[2 * e + 1]);
-              *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
-            }
-            __syncwarp();
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < PS_BN; c += 8) {
-          float v[8];
-          tc_ld8(taddr + c, v);
-          const int f = tn * PS_BN + c;
-          if (!t_ok || f >= p.b_rows) {
-            // nothing to store for this thread; stay with the warp for the next tcgen05.ld
-          } else if (p.epilogue == TC_RESIDUAL) {
-            float4* hp = reinterpret_cast<float4*>((float*)p.out + (size_t)tok * p.ldo + f);
-            float4 x0 = hp[0], x1 = hp[1];
-            x0.x += v[0]; x0.y += v[1]; x0.z += v[2]; x0.w += v[3];
-            x1.x += v[4]; x1.y += v[5]; x1.z += v[6]; x1.w += v[7];
-            hp[0] = x0; hp[1] = x1;
-          } else if (p.out_dtype == LLMRS_F32) {
-            float4* op = reinterpret_cast<float4*>((float*)p.out + (size_t)tok * p.ldo + f);
-            op[0] = make_float4(v[0], v[1], v[2], v[3]);
-            op[1] = make_float4(v[4], v[5], v[6], v[7]);
-          } else {
-            uint4 pk;
-            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-            *reinterpret_cast<uint4*>((bf16*)p.out + (size_t)tok * p.ldo + f) = pk;
-          }
-          __syncwarp();
-        }
-      }
+      const int t_next = t + (int)gridDim.x;
+      const bool more = t_next < n_tiles && p.epilogue == TC_RESIDUAL;
+      ok = ps_epilogue_tile(p, &map_h, hf, taddr, tm * TC_BM + quarter * 32, lane, tn, more ? t_next / n_m : -1,
+                            more ? (t_next % n_m) * TC_BM + quarter * 32 : 0, leader, abort_flag);
+      if (!ok) break;
       tc_fence_before();
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
     }
@@ -815,11 +942,249 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
       for (long long i = copies > PS_STAGES ? copies - PS_STAGES : 0; i < copies; ++i)
         if (i != p.test_skip_kb) mbar_drain(full0 + 8 * (int)(i % PS_STAGES), (uint32_t)(i / PS_STAGES) & 1, p.wait_limit);
       if (p.error_flag) atomicExch(p.error_flag, 1);
+    } else if (warp >= 2) {
+      for (long long i = hf.taken; i < hf.issued; ++i) mbar_drain(hf.bar0 + 8 * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1, p.wait_limit);
     }
     __syncthreads();
   }
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// ---- the persistent kernel for many tokens on pairs of SMs (cta_group::2) ------------------------
+// A thread-block cluster of two blocks owns a tile of 256 tokens x 256 features. Each block copies its 128 token
+// rows of x and ITS HALF (128 feature rows) of the weight tile; one thread of the pair's first block (the leader)
+// issues tcgen05.mma.cta_group::2, M = 256, N = 256, which reads A from each block's own shared memory and B from
+// both, and leaves each block's 128 rows of the result in that block's tensor memory. Against the one-block
+// kernel an SM reads half the B operand from its shared memory per flop and holds 32 KB instead of 48 KB a
+// stage. The roles of a block: warp 0 copies (TMA), warp 1 issues the MMAs (leader only), warps 2-5 run the
+// epilogue of the block's own rows. Barriers:
+//   full[s]      (leader's) both blocks' copies of a stage have landed: each block's TMA completes its bytes on
+//                the leader's barrier (cp.async.bulk.tensor ... .cta_group::2 allows a barrier in the peer block)
+//   empty[s]     (each block's own) the MMAs that read the stage are done: tcgen05.commit, multicast to both blocks
+//   acc_full[b]  (each block's own) the tile in accumulator buffer b is complete: tcgen05.commit, multicast
+//   acc_empty[b] (leader's) both blocks' epilogues have read buffer b: one arrival per epilogue warp
+// Every wait is bounded as in the other kernels; a block that gave up still meets its peer at the cluster barrier
+// before tensor memory is freed.
+constexpr int PR_STAGES = 6, PR_THREADS = 192;
+constexpr uint32_t PR_HALF_BYTES = TC_BM * TC_BK * 2, PR_STAGE_BYTES = 2 * PR_HALF_BYTES;   // A rows + half of B
+
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  return remote;
+}
+// A copy into this block's shared memory whose bytes are counted by a barrier that may lie in the pair's other block.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// One arrival, in both blocks of the pair, on the barrier at this offset of shared memory, when every MMA issued
+// so far by this thread has finished.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(both) : "memory");
+}
+// The same on this block's barrier alone.
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Bounded wait on a barrier that threads of the other block arrive on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t limit, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < limit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (it > 128) {
+      __nanosleep(64);
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+// Instruction descriptor of the pair's MMA: bf16 x bf16 -> f32, both K-major, M = 256 over the two blocks, N = n.
+__host__ __device__ constexpr uint32_t tc_instr_desc_pair(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+// ACC_BUFS accumulator buffers of 256 columns: 2 (all 512 columns; the epilogue of a tile runs under the MMAs of the
+// next) or 1.
+template <int ACC_BUFS>
+__global__ void __launch_bounds__(PR_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_h, const TcParams p, int n_m, int n_tiles, int* tmem_seen) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  unsigned char* h_pieces = tiles + (size_t)PR_STAGES * PR_STAGE_BYTES;   // two pieces of h per epilogue warp (HFeed)
+  // full[S], empty[S], acc_full[2], acc_empty[2], drain, then the epilogue warps' two barriers each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(h_pieces + 8 * HF_PIECE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * PR_STAGES + 5 + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_rank();        // 0: the leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + PR_STAGES), acc_full0 = tc_smem(bars + 2 * PR_STAGES),
+                 acc_empty0 = acc_full0 + 16, drain_bar = acc_full0 + 32;
+  constexpr uint32_t COLS = ACC_BUFS * PS_BN;
+  if (tid == 0) {
+    for (int s = 0; s < 2 * PR_STAGES + 2; ++s) mbar_init(full0 + 8 * s, 1);
+    mbar_init(acc_empty0, 8);        // one arrival from each of the four epilogue warps of both blocks
+    mbar_init(acc_empty0 + 8, 8);
+    mbar_init(drain_bar, 1);
+    for (int s = 0; s < 8; ++s) mbar_init(drain_bar + 8 + 8 * s, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    // Both blocks of the pair allocate (the same columns in each block's tensor memory).
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_smem(tmem_slot)), "r"(COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync_all();   // the peer's barriers exist before anything is sent to them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (tmem_seen && tid == 0) tmem_seen[blockIdx.x] = (int)tmem_base;   // tests: what each block was given
+  pdl_wait();   // x is what an earlier kernel wrote; the epilogue writes what earlier kernels read
+  const int nkb = p.k_blocks;
+  long long copies = 0;   // warp 0: stages whose copies it has requested
+  HFeed hf;               // epilogue warps: their pieces of the residual stream
+
+  if (warp == 0) {
+    // Copies: the whole warp walks the loop, one elected lane issues. The leader announces the bytes of both blocks.
+    const bool leader_lane = tc_elect_one();
+    long long it = 0;
+    bool ok = true;
+    for (int t = pair; t < n_tiles && ok; t += n_pairs) {
+      const int tm = t % n_m, tn = t / n_m;
+      for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int s = (int)(it % PR_STAGES);
+        if (it >= PR_STAGES) {
+          ok = __all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, (uint32_t)((it / PR_STAGES) - 1) & 1, p.wait_limit, abort_flag));
+          if (!ok) break;
+        }
+        if (leader_lane && it != p.test_skip_kb) {
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * PR_STAGE_BYTES);
+          const uint32_t dst = tc_smem(tiles + (size_t)s * PR_STAGE_BYTES);
+          const uint32_t bar = map_to_rank(full0 + 8 * s, 0u);
+          tma_load_2d_pair(dst, &map_a, bar, kb * TC_BK, tm * 2 * TC_BM + (int)rank * TC_BM);
+          tma_load_2d_pair(dst + PR_HALF_BYTES, &map_b, bar, kb * TC_BK, tn * PS_BN + (int)rank * (PS_BN / 2));
+        }
+        __syncwarp();
+      }
+    }
+    copies = it;
+  } else if (warp == 1) {
+    if (rank == 0) {
+      // MMAs of the pair: operands computed by the whole warp, issued by one elected lane of the leader.
+      constexpr uint32_t idesc = tc_instr_desc_pair(PS_BN);
+      const bool leader_lane = tc_elect_one();
+      long long it = 0;
+      int lt = 0;
+      bool ok = true;
+      for (int t = pair; t < n_tiles && ok; t += n_pairs, ++lt) {
+        const int buf = lt % ACC_BUFS;
+        if (lt >= ACC_BUFS) {   // both epilogues have read the tile that lay in this buffer
+          ok = __all_sync(0xffffffffu, mbar_wait_cluster(acc_empty0 + 8 * buf, (uint32_t)((lt / ACC_BUFS) - 1) & 1, p.wait_limit, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t d_addr = tmem_base + (uint32_t)buf * PS_BN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = (int)(it % PR_STAGES);
+          ok = __all_sync(0xffffffffu, mbar_wait_cluster(full0 + 8 * s, (uint32_t)(it / PR_STAGES) & 1, p.wait_limit, abort_flag));
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = tc_smem(tiles + (size_t)s * PR_STAGE_BYTES);
+          const uint64_t a_desc = tc_smem_desc(a_addr), b_desc = tc_smem_desc(a_addr + PR_HALF_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)
+            if (leader_lane) tc_mma_pair(d_addr, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          if (leader_lane) tc_commit_pair(empty0 + 8 * s);
+          __syncwarp();
+        }
+        if (leader_lane && ok) tc_commit_pair(acc_full0 + 8 * buf);
+        __syncwarp();
+      }
+    }
+  } else {
+    // Epilogue of this block's 128 token rows: thread = one row; a warp reaches the 32 lanes of tensor memory
+    // that its index modulo 4 names.
+    const int quarter = warp & 3;
+    const bool leader_lane = tc_elect_one();
+    const int row0 = (int)rank * TC_BM + quarter * 32;   // the warp's first row of a tile
+    hf.buf0 = tc_smem(h_pieces) + (uint32_t)(warp - 2) * 2 * HF_PIECE_BYTES;
+    hf.bar0 = drain_bar + 8 + (uint32_t)(warp - 2) * 16;
+    if (p.epilogue == TC_RESIDUAL && pair < n_tiles)
+      hfeed_start(&map_h, hf, pair / n_m, (pair % n_m) * 2 * TC_BM + row0, leader_lane);
+    int lt = 0;
+    bool ok = true;
+    for (int t = pair; t < n_tiles && ok; t += n_pairs, ++lt) {
+      const int tm = t % n_m, tn = t / n_m, buf = lt % ACC_BUFS;
+      ok = __all_sync(0xffffffffu, mbar_wait(acc_full0 + 8 * buf, (uint32_t)(lt / ACC_BUFS) & 1, p.wait_limit, abort_flag));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * PS_BN;
+      const int t_next = t + n_pairs;
+      const bool more = t_next < n_tiles && p.epilogue == TC_RESIDUAL;
+      ok = ps_epilogue_tile(p, &map_h, hf, taddr, tm * 2 * TC_BM + row0, lane, tn, more ? t_next / n_m : -1,
+                            more ? (t_next % n_m) * 2 * TC_BM + row0 : 0, leader_lane, abort_flag);
+      if (!ok) break;
+      tc_fence_before();
+      __syncwarp();   // the warp has read its lanes of the buffer
+      if (lane == 0) mbar_arrive_cluster(map_to_rank(acc_empty0 + 8 * buf, 0u));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // The block gave up. The MMAs that were issued must be done before tensor memory is freed, and the copies that
+    // were requested must have landed (the leader's barriers count both blocks' bytes; the peer stays until the
+    // cluster barrier below).
+    if (rank == 0 && warp == 1) {
+      if (tc_elect_one()) tc_commit_pair_local(drain_bar);
+      __syncwarp();
+      mbar_drain(drain_bar, 0, p.wait_limit);
+    } else if (rank == 0 && tid == 0) {
+      for (long long i = copies > PR_STAGES ? copies - PR_STAGES : 0; i < copies; ++i)
+        if (i != p.test_skip_kb) mbar_drain(full0 + 8 * (int)(i % PR_STAGES), (uint32_t)(i / PR_STAGES) & 1, p.wait_limit);
+    } else if (warp >= 2) {
+      for (long long i = hf.taken; i < hf.issued; ++i) mbar_drain(hf.bar0 + 8 * (uint32_t)(i & 1), (uint32_t)(i >> 1) & 1, p.wait_limit);
+    }
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    __syncthreads();
+  }
+  // Neither block may free tensor memory or leave while the other still computes into it or signals its barriers.
+  tc_fence_before();
+  cluster_sync_all();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(COLS) : "memory");
   }
 }
 
@@ -863,6 +1228,23 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return llmrs_fail("gemm_bf16: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+// Tensor map of the float32 residual stream [rows, cols] with row stride ld (elements) for the pieces of 32 x 32 that
+// the many-token kernels' epilogue warps fetch (see HFeed).
+static int make_map_h(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return llmrs_fail("gemm_bf16: cuTensorMapEncodeTiled is not available from this driver");
+  LLMRS_REQUIRE(((uintptr_t)base & 15) == 0 && ld % 4 == 0, "gemm_bf16: the residual stream must be 16-byte aligned, rows too");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return llmrs_fail("gemm_bf16: cuTensorMapEncodeTiled (residual stream) failed with code %d", (int)r);
   return 0;
 }
 
@@ -940,9 +1322,9 @@ LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, i
                         splits, error_flag, &qr, &nl, stream);
 }
 
-static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, int n_m, int n_tiles,
-                             cudaStream_t stream) {
-  const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + (2 * PS_STAGES + 5) * 8 + 16;
+static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mh, const TcParams& p,
+                             int n_m, int n_tiles, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)PS_STAGES * PS_STAGE_BYTES + 8 * HF_PIECE_BYTES + (2 * PS_STAGES + 5 + 8) * 8 + 16;
   static int n_sm = 0;
   if (n_sm == 0) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -965,9 +1347,89 @@ static int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const
     cfg.numAttrs = 1;
   }
   cfg.attrs = attr;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel, ma, mb, p, n_m, n_tiles);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_persistent_kernel, ma, mb, mh, p, n_m, n_tiles);
   if (e != cudaSuccess) return llmrs_fail("gemm_bf16 launch: %s", cudaGetErrorString(e));
   return llmrs_launch_status("gemm_bf16");
+}
+
+// Many tokens on pairs of SMs (gemm_tc_pair_kernel): as many clusters of two blocks as the device holds at a time.
+static int g_tc_pairs = 1;
+
+// 0: steps of many tokens stay on the one-block kernel (1, the default: the kernel on pairs of SMs from 129 tokens).
+LLMRS_API void llmrs_tc_use_pairs(int on) { g_tc_pairs = on ? 1 : 0; }
+
+template <int ACC_BUFS>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mh, const TcParams& p, int n_m,
+                       int n_tiles, int* tmem_seen, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)PR_STAGES * PR_STAGE_BYTES + 8 * HF_PIECE_BYTES + (2 * PR_STAGES + 5 + 8) * 8 + 16;
+  static int max_pairs = 0;
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (max_pairs == 0) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<ACC_BUFS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return llmrs_fail("gemm_bf16: shared memory %zu: %s", smem, cudaGetErrorString(e));
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2);
+      q.blockDim = dim3(PR_THREADS);
+      q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension;
+      qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.attrs = qa;
+      q.numAttrs = 1;
+      int n = 0;
+      e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<ACC_BUFS>, &q);
+      if (e != cudaSuccess || n <= 0) return llmrs_fail("gemm_bf16: no room for a pair of blocks: %s", cudaGetErrorString(e));
+      max_pairs = n;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * (n_tiles < max_pairs ? n_tiles : max_pairs));
+  cfg.blockDim = dim3(PR_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.numAttrs = 1;
+  if (g_llmrs_pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cfg.attrs = attr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<ACC_BUFS>, ma, mb, mh, p, n_m, n_tiles, tmem_seen);
+  if (e != cudaSuccess) return llmrs_fail("gemm_bf16 launch (pairs): %s", cudaGetErrorString(e));
+  return llmrs_launch_status("gemm_bf16");
+}
+
+// The kernel on pairs of SMs by itself, for tests and measurements: acc_buffers accumulator tiles in tensor memory
+// (1 or 2); tmem_seen (or null) receives, per block, the tensor-memory address the block was given.
+LLMRS_API int llmrs_gemm_bf16_pairs(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
+                                    int features, int K, int epilogue, int out_dtype, int acc_buffers, int* tmem_seen,
+                                    int* error_flag, cudaStream_t stream) {
+  LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16_pairs: unknown epilogue %d", epilogue);
+  LLMRS_REQUIRE(acc_buffers == 1 || acc_buffers == 2, "gemm_bf16_pairs: 1 or 2 accumulator buffers");
+  LLMRS_REQUIRE(tokens > 0 && features > 0 && K > 0, "gemm_bf16_pairs: bad sizes");
+  LLMRS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && features % 8 == 0 && ldo % 8 == 0,
+                "gemm_bf16_pairs: K, features and the row strides must be multiples of 8");
+  LLMRS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16_pairs: operands must be 16-byte aligned");
+  LLMRS_REQUIRE(epilogue != TC_SILU_MUL || features % 256 == 0,
+                "gemm_bf16_pairs: SiLU*up needs features in groups of 256, got %d", features);
+  TcParams p = {};
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype; p.epilogue = epilogue;
+  p.k_blocks = (K + TC_BK - 1) / TC_BK; p.error_flag = error_flag;
+  p.wait_limit = g_tc_wait_limit; p.test_skip_kb = g_tc_test_skip_kb;
+  p.a_rows = tokens; p.b_rows = features;
+  CUtensorMap ma, mb, mh = {};
+  int rc;
+  if ((rc = make_map(&ma, x, tokens, K, ldx, TC_BM))) return rc;
+  if ((rc = make_map(&mb, w, features, K, K, PS_BN / 2))) return rc;
+  if (epilogue == TC_RESIDUAL && (rc = make_map_h(&mh, out, tokens, features, ldo))) return rc;
+  const int n_m = (tokens + 2 * TC_BM - 1) / (2 * TC_BM), n_n = (features + PS_BN - 1) / PS_BN;
+  if (acc_buffers == 1) return launch_pair<1>(ma, mb, mh, p, n_m, n_m * n_n, tmem_seen, stream);
+  return launch_pair<2>(ma, mb, mh, p, n_m, n_m * n_n, tmem_seen, stream);
 }
 
 // y = x W^T for bfloat16 x [tokens, K] (row stride ldx) and W [features, K] (dense).
@@ -983,20 +1445,21 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
                         nullptr, stream);
 }
 
-// llmrs_gemm_bf16 for at most 64 tokens as one half of a norm that is spread over two products:
-// with emit_w (TC_RESIDUAL, splits >= 2) it also writes emit_xw[tokens, emit_ld] = (h + y) * emit_w in
-// bfloat16 and emit_part[ceil(features / 128), part_stride], its clusters' sums of squares per
-// token; with scale_part it multiplies the rows of y by 1 / sqrt(sum of the scale_parts entries of the
-// row's token / scale_dim + scale_eps) before its epilogue.
+// llmrs_gemm_bf16 as one half of a norm that is spread over two products: with emit_w (TC_RESIDUAL; at most 64
+// tokens: splits >= 2) it also writes emit_xw[tokens, emit_ld] = (h + y) * emit_w in bfloat16 and
+// emit_part[pieces, part_stride], the sums of squares per token of each piece of the features (128 wide for at
+// most 64 tokens, 256 wide for more); with scale_part it multiplies the rows of y by 1 / sqrt(sum of the
+// scale_parts entries of the row's token / scale_dim + scale_eps) before its epilogue.
 LLMRS_API int llmrs_gemm_bf16_norm(const void* x, long long ldx, const void* w, void* out, long long ldo, int tokens,
                                    int features, int K, int epilogue, int out_dtype, int splits, const float* emit_w,
                                    void* emit_xw, long long emit_ld, float* emit_part, const float* scale_part,
                                    int part_stride, int scale_parts, int scale_dim, float scale_eps,
                                    int* error_flag, cudaStream_t stream) {
   LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
-  LLMRS_REQUIRE(tokens <= 64, "gemm_bf16_norm: takes at most 64 tokens, got %d", tokens);
-  LLMRS_REQUIRE(!emit_w || (epilogue == TC_RESIDUAL && splits >= 2 && emit_xw && emit_part && part_stride >= tokens),
-                "gemm_bf16_norm: the next norm's input is written by a residual epilogue with 2 or more splits");
+  LLMRS_REQUIRE(!emit_w || (epilogue == TC_RESIDUAL && emit_xw && emit_part && part_stride >= tokens),
+                "gemm_bf16_norm: the next norm's input is written by a residual epilogue");
+  LLMRS_REQUIRE(!emit_w || tokens > 64 || splits >= 2, "gemm_bf16_norm: at most 64 tokens emit with 2 or more splits");
+  LLMRS_REQUIRE(tokens <= 64 || features >= 256, "gemm_bf16_norm: more than 64 tokens need at least 256 features");
   LLMRS_REQUIRE(!scale_part || (scale_parts > 0 && scale_dim > 0 && part_stride >= tokens),
                 "gemm_bf16_norm: bad description of the row scales");
   NormLink nl;
@@ -1049,6 +1512,14 @@ static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out
   if ((rc = make_map(&mb, w, features, K, K, bn))) return rc;
   p.a_rows = tokens; p.b_rows = features;
   dim3 grid((tokens + TC_BM - 1) / TC_BM, (features + bn - 1) / bn, 1);
-  if (bn == 256) return launch_persistent(ma, mb, p, grid.x, grid.x * grid.y, stream);
+  CUtensorMap mh = {};
+  if (bn == 256 && epilogue == TC_RESIDUAL && (rc = make_map_h(&mh, out, tokens, features, ldo))) return rc;
+  if (bn == 256 && g_tc_pairs && tokens > TC_BM) {
+    // Tiles of 256 tokens on pairs of SMs; each block copies its half of a weight tile.
+    if ((rc = make_map(&mb, w, features, K, K, PS_BN / 2))) return rc;
+    const int n_m = (tokens + 2 * TC_BM - 1) / (2 * TC_BM);
+    return launch_pair<2>(ma, mb, mh, p, n_m, n_m * (int)grid.y, nullptr, stream);
+  }
+  if (bn == 256) return launch_persistent(ma, mb, mh, p, grid.x, grid.x * grid.y, stream);
   return launch_tc<128, 6, 0>(ma, mb, p, grid, 1, stream);
 }

@@ -455,10 +455,55 @@ def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     return 1
 
 
-def norm_parts(features: int, splits: int = 1) -> int:
-    """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per tile of 128 features
-    (the cluster that shares the tile's k range adds its blocks' shares up in its first block)."""
-    return -(-features // 128)
+def norm_parts(features: int, splits: int = 1, tokens: int = 1) -> int:
+    """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per tile of features, 128
+    wide for at most 64 tokens (the cluster that shares the tile's k range adds its blocks' shares up in its first
+    block), 256 wide for more."""
+    return -(-features // (128 if tokens <= 64 else 256))
+
+
+def gemm_bf16_pairs(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, epilogue: str = "store",
+                    out_dtype: torch.dtype = torch.bfloat16, acc_buffers: int = 2,
+                    tmem_seen: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``gemm_bf16`` for many tokens through the kernel that runs a tile of 256 x 256 on a pair of SMs
+    (tcgen05.mma.cta_group::2; ``gemm_tc_pair_kernel`` in csrc/gemm_tcgen05.cu), called by itself. ``gemm_bf16``
+    takes the same kernel from 129 tokens on (``use_tc_pairs``). ``acc_buffers``: accumulator tiles a block holds in
+    tensor memory; ``tmem_seen`` (int32, one entry per block) receives the address each block was given."""
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    _need(w, "w", torch.bfloat16)
+    tokens, K = x.shape
+    features = w.size(0)
+    if w.size(1) != K:
+        raise KernelError(f"x has {K} columns, w has {w.size(1)}")
+    epi = EPILOGUE[epilogue]
+    if epilogue == "residual":
+        _need(out, "out", torch.float32)
+        if out.shape != (tokens, features):
+            raise KernelError(f"residual stream is {tuple(out.shape)}, product is {(tokens, features)}")
+        odt = torch.float32
+    else:
+        width = features // 2 if epilogue == "silu_mul" else features
+        odt = torch.bfloat16 if epilogue == "silu_mul" else out_dtype
+        if out is None:
+            out = torch.empty((tokens, width), dtype=odt, device=x.device)
+        _need(out, "out", odt)
+    if tmem_seen is not None:
+        _need(tmem_seen, "tmem_seen", torch.int32)
+        if tmem_seen.numel() < 2 * torch.cuda.get_device_properties(x.device).multi_processor_count:
+            raise KernelError("tmem_seen needs an entry per block (two per SM)")
+    _check(_lib().llmrs_gemm_bf16_pairs(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
+                                        ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
+                                        acc_buffers, _ptr(tmem_seen), _ptr(tc_error_flag(x.device)), _stream()),
+           "gemm_bf16_pairs")
+    return out
+
+
+def use_tc_pairs(on: bool) -> None:
+    """Whether ``gemm_bf16`` sends steps of more than 128 tokens to the kernel on pairs of SMs (the default) or keeps
+    them on the one-block persistent kernel."""
+    fn = _lib().llmrs_tc_use_pairs
+    fn.restype, fn.argtypes = None, [ctypes.c_int]
+    fn(1 if on else 0)
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, epilogue: str = "store",
@@ -470,9 +515,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     float32 residual stream and gets the product added. "silu_mul": ``w`` alternates 64
     gate rows and 64 up rows; returns silu(gate) * up, [tokens, features / 2] bfloat16.
 
-    A norm spread over two products (at most 64 tokens): ``emit`` = (norm weight float32 [features],
-    xw bfloat16 [tokens, features], parts float32 [norm_parts(features, splits), stride]) makes a
-    "residual" epilogue also write xw = (out + product) * weight and the sums of squares of each 128 features;
+    A norm spread over two products: ``emit`` = (norm weight float32 [features], xw bfloat16 [tokens, features],
+    parts float32 [norm_parts(features, splits, tokens), stride >= tokens]) makes a "residual" epilogue also write
+    xw = (out + product) * weight and the sums of squares of each piece of the features;
     ``scale`` = (parts, n_parts, dim, eps) multiplies the product's rows by
     1 / sqrt(sum(parts[:n_parts, token]) / dim + eps).
 
@@ -514,7 +559,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
         _need(e_w, "emit weight", torch.float32)
         _need(e_xw, "emit xw", torch.bfloat16)
         _need(e_part, "emit parts", torch.float32)
-        if e_w.numel() != features or e_xw.shape != (tokens, features) or e_part.size(0) < norm_parts(features, splits):
+        if e_w.numel() != features or e_xw.shape != (tokens, features) or e_part.size(0) < norm_parts(features, splits, tokens):
             raise KernelError("emit: weight, xw or parts do not fit the product")
         stride = e_part.size(1)
     if scale is not None:

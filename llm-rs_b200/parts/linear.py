@@ -5,7 +5,11 @@ tcgen05 kernel (``csrc/gemm_tcgen05.cu``: weights fill the 128 rows of the MMA, 
 is shared by a thread-block cluster) with the residual sum or SiLU*up fused into its
 epilogue; larger steps go through the library product (cuBLAS via ``torch``), as the
 reference's projections go through its tensor library
-(llm-core/src/backends/candle.rs:1276-1340). float32 weights, the whole float32 path and
+(llm-core/src/backends/candle.rs:1276-1340), except the gate|up product with its SiLU*up
+epilogue (``parts/mlp.py``), which runs this package's kernel for many tokens (tiles of
+256 x 256 on pairs of SMs, tcgen05.mma.cta_group::2) at every size. ``LLMRS_TC_MANY_TOKENS=n``
+sends every product of steps of n tokens or more to that kernel, with the residual sum and the
+norms spread over its epilogues as in decode steps. float32 weights, the whole float32 path and
 tensors that the model folder stores in 32-bit, go through this package's own FFMA
 kernel: true 32-bit, no reduced-precision tensor-core mode.
 """
@@ -23,8 +27,13 @@ from .base import PreNormed
 # steps: up to 16 tokens the kernel with its fused epilogues is ahead of the library product plus the separate
 # kernels, from 17 to 32 tokens it is 3-4 % behind, at 64 tokens far behind.)
 TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "16"))
-# Also for larger steps (prefill) when set; by default those stay with the library product.
-TC_PREFILL = os.environ.get("LLMRS_TC_PREFILL", "0") == "1"
+# Steps with at least this many tokens take the tcgen05 kernel for many tokens for every product; 0 (the default)
+# keeps all but gate|up on the library product. (Prefill of 2,048 tokens at Qwen3-8B sizes, 36 layers, timed over
+# seconds under the power cap: 24.9 ms with the library's q|k|v, o and down products and the norm kernels, 25.6 ms
+# with this package's kernel and no norm kernels, 26.0 ms with it and the norm kernels; launched alone in a burst
+# the kernel is level with the library for q|k|v (72 us), 4 us behind for o (53 against 49, residual sum and the
+# next norm's input included, which cost the library path 14 us more) and 13 us behind for down (145 against 132).)
+TC_MANY_TOKENS = int(os.environ.get("LLMRS_TC_MANY_TOKENS", "0"))
 
 
 _SM_COUNT = {}
@@ -58,7 +67,9 @@ class Linear:
         return self.tc_ok and TC_MAX_TOKENS > 0
 
     def uses_tc(self, n_tokens: int) -> bool:
-        return self.tc_ok and n_tokens > 0 and (n_tokens <= TC_MAX_TOKENS or (TC_PREFILL and TC_MAX_TOKENS > 0))
+        if not self.tc_enabled() or n_tokens <= 0:
+            return False
+        return n_tokens <= TC_MAX_TOKENS or 0 < TC_MANY_TOKENS <= n_tokens
 
     def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
@@ -78,12 +89,14 @@ class Linear:
         return ops.tc_splits(n_tokens, n, k, _sm_count(self.weight.device))
 
     def takes_prenormed(self, n_tokens: int) -> bool:
-        """True when ``forward`` accepts a ``PreNormed`` (the tcgen05 kernel for few tokens scales its rows)."""
-        return self.uses_tc(n_tokens) and n_tokens <= 64
+        """True when ``forward`` accepts a ``PreNormed`` (the tcgen05 kernels scale their rows)."""
+        return self.uses_tc(n_tokens) and (n_tokens <= 64 or self.weight.size(0) >= 256)
 
     def emits_prenormed(self, n_tokens: int) -> bool:
         """True when ``forward_into_residual`` can also write the input of the norm that follows."""
-        return self.uses_tc(n_tokens) and n_tokens <= 64 and self._splits(n_tokens) >= 2
+        if not self.uses_tc(n_tokens):
+            return False
+        return self._splits(n_tokens) >= 2 if n_tokens <= 64 else self.weight.size(0) >= 256
 
     def forward_into_residual_for_norm(self, x: torch.Tensor, h: torch.Tensor, norm_weight: torch.Tensor,
                                        eps: float) -> PreNormed:
@@ -91,9 +104,9 @@ class Linear:
         (see ``PreNormed``). Only when ``emits_prenormed``."""
         n = self.weight.size(0)
         splits = self._splits(x.size(0))
-        n_parts = ops.norm_parts(n, splits)
+        n_parts = ops.norm_parts(n, splits, x.size(0))
         xw = torch.empty((x.size(0), n), dtype=torch.bfloat16, device=x.device)
-        parts = torch.empty((n_parts, 64), dtype=torch.float32, device=x.device)
+        parts = torch.empty((n_parts, max(64, x.size(0))), dtype=torch.float32, device=x.device)
         ops.gemm_bf16(x, self.weight, out=h, epilogue="residual", splits=splits, emit=(norm_weight, xw, parts),
                       then=self.next_weight)
         return PreNormed(xw, parts, n_parts, n, eps)

@@ -60,7 +60,9 @@ class SwiGLU(FeedForward):
         return [self.gate_up, self.down]
 
     def takes_prenormed(self, n_tokens: int) -> bool:
-        return bool(self.block) and self.gate_up.tc_enabled() and FUSE_GATE_UP and 0 < n_tokens <= 32
+        if not (self.block and self.gate_up.tc_enabled() and FUSE_GATE_UP):
+            return False
+        return 0 < n_tokens <= 32 or (n_tokens > 64 and self.gate_up.uses_tc(n_tokens))
 
     def emits_prenormed(self, n_tokens: int) -> bool:
         return self.down.emits_prenormed(n_tokens)
@@ -73,8 +75,8 @@ class SwiGLU(FeedForward):
                 return self.down.forward_into_residual_for_norm(act, residual, *next_norm)
             return self.down.forward_into_residual(act, residual) if residual is not None else self.down.forward(act)
         # With interleaved weights the product and SiLU(gate) * up are one kernel at every number of
-        # tokens: for many tokens the persistent tcgen05 kernel with this epilogue is level with the
-        # library product followed by the SiLU kernel, or ahead of it (2,048 tokens: 295 against 315 us).
+        # tokens: for many tokens the persistent tcgen05 kernel on pairs of SMs with this epilogue is ahead of
+        # the library product followed by the SiLU kernel (2,048 tokens: 261 against 271 + 20 us).
         # (From 33 to 64 tokens the few-token kernel's widest tile is behind the library product followed by the
         # SiLU kernel: 10.53 against 10.38 ms a step at 64 tokens.)
         if (self.block and x.dtype == torch.bfloat16 and self.gate_up.tc_enabled() and FUSE_GATE_UP

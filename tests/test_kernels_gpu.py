@@ -474,11 +474,85 @@ def test_gemm_tcgen05_few_tokens(tokens, features, K, epilogue, out_dtype, split
     (130, 1024, 512, "silu_mul", torch.bfloat16), (515, 768, 320, "store", torch.bfloat16),
     (1100, 10496, 192, "store", torch.bfloat16), (2048, 12288, 128, "silu_mul", torch.bfloat16),
     (1500, 8200, 72, "residual", torch.float32)])
-def test_gemm_tcgen05_many_tokens(tokens, features, K, epilogue, out_dtype):
-    """Tokens on the 128 rows of the MMA; with 256 features or more the persistent kernel, whose blocks
-    walk several tiles each (the last three cases give every block two to four tiles, so that both
-    accumulator buffers and the ring of stages wrap, with a ragged edge in tokens, features and k)."""
-    _tc_case(tokens, features, K, epilogue, out_dtype, None)
+@pytest.mark.parametrize("pairs", [True, False])
+def test_gemm_tcgen05_many_tokens(tokens, features, K, epilogue, out_dtype, pairs):
+    """Tokens on the rows of the MMA; with 256 features or more a persistent kernel, whose blocks walk several
+    tiles each (the last three cases give every block two to four tiles, so that both accumulator buffers and the
+    ring of stages wrap, with a ragged edge in tokens, features and k): from 129 tokens tiles of 256 x 256 on pairs
+    of SMs (``pairs``), else tiles of 128 x 256 on one."""
+    ops = _ops()
+    ops.use_tc_pairs(pairs)
+    try:
+        _tc_case(tokens, features, K, epilogue, out_dtype, None)
+    finally:
+        ops.use_tc_pairs(True)
+
+
+def test_gemm_on_pairs_of_sms_alone():
+    """The kernel on pairs of SMs called by itself, with one and with two accumulator buffers; both blocks of
+    every pair are given the same columns of tensor memory (the pair's MMA writes one address in both)."""
+    ops = _ops()
+    torch.manual_seed(5)
+    for tokens, features, K, bufs in [(256, 256, 64, 1), (300, 520, 200, 1), (1000, 1288, 1032, 2), (2048, 4096, 512, 2)]:
+        x = (torch.randn(tokens, K, device=DEV) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(features, K, device=DEV) * 0.5).to(torch.bfloat16)
+        seen = torch.full((2 * torch.cuda.get_device_properties(DEV).multi_processor_count,), -1, dtype=torch.int32, device=DEV)
+        got = ops.gemm_bf16_pairs(x, w, out_dtype=torch.float32, acc_buffers=bufs, tmem_seen=seen).double()
+        ops.check_tc_error(DEV)
+        want = x.double() @ w.double().t()
+        assert float((got - want).abs().max()) <= 1e-5 * math.sqrt(K) * float(want.abs().max())
+        used = seen[seen >= 0].cpu().tolist()
+        n_tiles = -(-tokens // 256) * -(-features // 256)
+        assert len(used) == 2 * min(n_tiles, len(used) // 2) and len(used) % 2 == 0
+        assert all(a == b for a, b in zip(used[0::2], used[1::2])), "the blocks of a pair were given different columns"
+
+
+@pytest.mark.parametrize("pairs", [True, False])
+@pytest.mark.parametrize("tokens,features,K,consumer", [
+    (300, 512, 256, "store"), (1000, 1288, 520, "silu_mul"), (257, 4096, 128, "store"), (129, 256, 64, "silu_mul")])
+def test_gemm_norm_spread_over_two_products_many_tokens(tokens, features, K, consumer, pairs):
+    """The same for many tokens: the residual epilogue of the persistent kernels turns its 32 x 32 pieces round in
+    shared memory, writes h, h * weight and the rows' sums of squares per tile of 256 features; the products after
+    it scale their rows. Against rmsnorm(h + x W^T) W2^T in float64."""
+    ops = _ops()
+    ops.use_tc_pairs(pairs)
+    try:
+        torch.manual_seed(tokens + features)
+        x = (torch.randn(tokens, K) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(features, K) * 0.05).to(torch.bfloat16)
+        h0 = torch.randn(tokens, features) * torch.linspace(0.2, 3.0, tokens)[:, None]   # rows of different size
+        nw = 1 + 0.2 * torch.randn(features)
+        eps = 3e-5
+        h = h0.to(DEV).clone()
+        xw = torch.full((tokens, features), float("nan"), dtype=torch.bfloat16, device=DEV)
+        n_parts = ops.norm_parts(features, 1, tokens)
+        assert n_parts == -(-features // 256)
+        parts = torch.full((n_parts, tokens + 3), float("nan"), dtype=torch.float32, device=DEV)
+        ops.gemm_bf16(x.to(DEV), w.to(DEV), out=h, epilogue="residual", emit=(nw.to(DEV), xw, parts))
+        torch.cuda.synchronize()
+        ops.check_tc_error(DEV)
+        want_h = h0.double() + x.double() @ w.double().t()
+        assert float((h.double().cpu() - want_h).abs().max()) < 1e-3
+        assert bool(torch.isnan(parts[:, tokens:]).all()), "a sum was written beyond the tokens"
+        ss = parts[:, :tokens].double().cpu().sum(0)
+        assert float(((ss - (want_h ** 2).sum(-1)) / (want_h ** 2).sum(-1)).abs().max()) < 1e-4
+        assert float((xw.double().cpu() - want_h * nw.double()).abs().max()) < 2e-2 * float((want_h * nw.double()).abs().max())
+        normed = want_h / torch.sqrt((want_h ** 2).mean(-1, keepdim=True) + eps) * nw.double()
+        scale = (parts, n_parts, features, eps)
+        if consumer == "store":
+            w2 = (torch.randn(264, features) * 0.05).to(torch.bfloat16)
+            got = ops.gemm_bf16(xw, w2.to(DEV), out_dtype=torch.float32, scale=scale)
+            want = normed @ w2.double().t()
+        else:
+            g, u = (torch.randn(256, features) * 0.05).to(torch.bfloat16), (torch.randn(256, features) * 0.05).to(torch.bfloat16)
+            got = ops.gemm_bf16(xw, ops.interleave_gate_up(g, u).to(DEV), epilogue="silu_mul", scale=scale)
+            a, b = normed @ g.double().t(), normed @ u.double().t()
+            want = a * torch.sigmoid(a) * b
+        torch.cuda.synchronize()
+        ops.check_tc_error(DEV)
+        assert float((got.double().cpu() - want).abs().max()) < 2e-2 * float(want.abs().max())
+    finally:
+        ops.use_tc_pairs(True)
 
 
 def test_gemm_tcgen05_strided_input_and_refusals():
@@ -711,7 +785,9 @@ def test_gemm_norm_emission_refusals():
     (8, 256, 1024, 2, 3),       # a cluster of two blocks shares the k range: both give up, both reach the cluster's barriers
     (16, 128, 1024, 1, 9),      # the ring of six stages has wrapped: the producer is waiting for a free stage
     (100, 128, 256, None, 2),   # tokens on the rows, one tile per block
-    (300, 512, 512, None, 5)])  # the persistent kernel: copying warp, MMA warp and epilogue warps all leave their loops
+    (300, 512, 512, None, 5),   # the kernel on pairs of SMs: both blocks' copying, MMA and epilogue warps leave their loops
+    (300, 512, 1024, None, 13), # the same after the ring of six stages has wrapped
+    (100, 512, 512, None, 5)])  # the persistent kernel on single SMs (at most 128 tokens)
 def test_gemm_tcgen05_wait_runs_out_and_the_kernel_returns(tokens, features, K, splits, skip):
     """A copy that never arrives (the producer leaves it out on request) with a wait limit of 1,024 polls: the
     kernel returns by itself, the error word is set, nothing is stored where the block gave up; and the next,

@@ -116,3 +116,29 @@ def test_engine_at_qwen3_8b_layer_sizes_matches_plain(setup, mode, dtype, graphs
     from llm_rs_b200 import ops
     ops.check_tc_error(torch.device(DEV))
     ops.check_attention_error()
+
+
+@pytest.mark.parametrize("mode", ["whole", "mixed"])
+def test_every_product_of_large_steps_on_this_packages_kernel(setup, mode, monkeypatch):
+    """Steps of 256 tokens or more with all their products on the tcgen05 kernel for many tokens (off by default
+    for all but gate|up): the residual sums and the norms are then spread over the products' epilogues as in decode
+    steps, and no norm kernel runs between the layers' products."""
+    from llm_rs_b200 import ops
+    from llm_rs_b200.engine import ModelRunner
+    from llm_rs_b200.parts import linear
+    monkeypatch.setattr(linear, "TC_MANY_TOKENS", 256)
+    spec, t16, reqs, wanted, ref = setup
+    steps = RU.want_only(_steps(mode, reqs), wanted)
+    runner = ModelRunner(spec, t16, torch.bfloat16, DEV, max_tokens=RU.live_token_peak(steps), page_size=16,
+                         max_requests=4)
+    norms = []
+    real = ops.add_rmsnorm
+    monkeypatch.setattr(ops, "add_rmsnorm", lambda *a, **k: (norms.append(a[0].size(0)), real(*a, **k))[1])
+    worst, where, n = _replay(runner, steps, ref)
+    scale = max(float(rows.abs().max()) for _, rows in ref.values())
+    assert worst <= 0.02 * scale, f"{mode}: max |diff| {worst:.3e} at {where} (largest logit {scale:.3f})"
+    ops.check_tc_error(torch.device(DEV))
+    if mode == "whole":      # in a large step only the first layer's input norm and the final norm are kernels
+        large = sum(1 for st in steps if sum(len(e["tokens"]) for e in st["entries"]) >= 256)
+        assert 0 < large < len(steps)
+        assert len(norms) == 2 * large + (2 * LAYERS + 1) * (len(steps) - large), (len(norms), large, len(steps))
