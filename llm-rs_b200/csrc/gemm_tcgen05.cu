@@ -217,33 +217,17 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t ran
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-// Sum over the cluster's blocks, in rank order, of the float at `local_addr` in each block's shared memory.
-// All loads are issued before the first is used: one round trip through the cluster instead of one per block.
-__device__ __forceinline__ float cluster_sum_f32(uint32_t local_addr, int splits) {
-  float v[8];
-#pragma unroll
-  for (int r = 0; r < 8; ++r) v[r] = r < splits ? ld_cluster_f32(local_addr, (uint32_t)r) : 0.f;
-  float acc = 0.f;
-#pragma unroll
-  for (int r = 0; r < 8; ++r) acc += v[r];
-  return acc;
+// Four consecutive floats at `local_addr` (16-byte aligned) of the shared memory of block `rank` of the cluster.
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
-
-// The q|k|v epilogue's look-ups for a warp's tokens, one token per lane: the warp's i-th token is
-// rank + splits * (ewarp + 4 * i); lane i fetches its position and (for key and value heads) its page.
-__device__ __forceinline__ void qkv_fetch_tokens(const QkvRope& g, int rank, int splits, int ewarp, int lane, int n_tok,
-                                                 int t0, int head, int& pos, int& page) {
-  const int j = rank + splits * (ewarp + (TC_THREADS / 32) * lane);
-  pos = 0;
-  page = 0;
-  if (j < n_tok) {
-    pos = g.positions[t0 + j];
-    if (head >= g.n_q_heads)
-      page = LLMRS_CHECKED_PAGE(g.block_table[(size_t)g.token_req[t0 + j] * g.table_stride + pos / g.page_size], 5, t0 + j);
-  }
-}
 
 // ---- the kernel ----------------------------------------------------------------------------
 // MODE 0: rows of the tile are tokens (A = x), columns features (B = W); one block per tile.
@@ -272,7 +256,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   // Row scales of a product that follows a norm spread over two products (see TcParams).
   __shared__ float inv_s[64], inv_part[64];
-  __shared__ float ss_ranks[8 * 64];   // in the cluster's first block: every block's sums of squares per token
   const bool scaled = MODE == 1 && p.scale_part != nullptr;
 
   const uint32_t full0 = tc_smem(bars), empty0 = tc_smem(bars + STAGES), accum_bar = tc_smem(bars + 2 * STAGES);
@@ -298,18 +281,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Mode 1: the items of the epilogue are dealt out so that warps 2 and 3, which have nothing to do while
-  // the product runs, own the first ones, and they fetch what those items need from global memory (the
-  // residual's old values, positions, rotation, page) under the product instead of after it.
+  // Mode 1, the epilogue's work: the tokens of the tile are dealt out over the blocks of the cluster (block `rank`
+  // owns tokens rank, rank + splits, ...), and an item is a token of the block and a quad q: features 4q..4q+3 and
+  // 64+4q..64+4q+3 of the tile's 128, i.e. four of the pairs (i, i + 64) that SiLU*up and the rotation combine.
+  // Thread etid takes items etid, etid + 128, ...: warps 2 and 3, which have nothing to do while the product runs,
+  // own the first ones and fetch what those need from global memory (the residual's old values, the next norm's
+  // weight, position, page, rotation) under the product instead of after it.
   const int etid = MODE == 1 ? ((tid + 64) & (TC_THREADS - 1)) : tid;
-  const int ewarp = etid >> 5;
   const uint32_t rank = (MODE == 1 && splits > 1) ? cluster_rank() : 0u;
-  const int per = 64 / splits;                 // feature pairs (i, i + 64) owned by this block
   const int n_tok = MODE == 1 ? min(BN, p.b_rows - tile_b * BN) : 0;
+  const int n_mine = n_tok > (int)rank ? (n_tok - 1 - (int)rank) / splits + 1 : 0;   // tokens this block owns
+  const int n_items = n_mine * 16;
   bool pf = false;
-  float pf_h_lo = 0.f, pf_h_hi = 0.f, pf_w_lo = 0.f, pf_w_hi = 0.f;
+  float4 pf_a = make_float4(0.f, 0.f, 0.f, 0.f), pf_b = pf_a, pf_c = pf_a, pf_d = pf_a;   // residual: h lo/hi, w lo/hi; q|k|v: rotation
   int pf_pos = 0, pf_page = 0;
-  float2 pf_cs0 = make_float2(1.f, 0.f), pf_cs1 = make_float2(1.f, 0.f);
 
   int issued = 0;                      // thread 0: k blocks whose copies it has requested
   const int skip = p.test_skip_kb;     // -1 outside the test of the bounded waits
@@ -361,23 +346,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (leader) tc_commit(accum_bar);
   } else if (MODE == 1 && warp >= 2) {
     pdl_wait();
-    if (p.epilogue == TC_RESIDUAL) {
-      if (etid < per * n_tok) {
-        const int pr = etid % per, j = etid / per;
-        const int f_lo = tile_a * TC_BM + (int)rank * per + pr, f_hi = f_lo + 64;
-        const float* h = (const float*)p.out + (size_t)(tile_b * BN + j) * p.ldo;
-        if (f_lo < p.a_rows) { pf_h_lo = h[f_lo]; if (p.emit_w) pf_w_lo = p.emit_w[f_lo]; }
-        if (f_hi < p.a_rows) { pf_h_hi = h[f_hi]; if (p.emit_w) pf_w_hi = p.emit_w[f_hi]; }
+    if (etid < n_items) {      // the thread's first item
+      const int j = (int)rank + splits * (etid >> 4), q = etid & 15, t = tile_b * BN + j;
+      if (p.epilogue == TC_RESIDUAL) {
+        const int f_lo = tile_a * TC_BM + 4 * q, f_hi = f_lo + 64;
+        const float* h = (const float*)p.out + (size_t)t * p.ldo;
+        if (f_lo < p.a_rows) { pf_a = *reinterpret_cast<const float4*>(h + f_lo); if (p.emit_w) pf_c = *reinterpret_cast<const float4*>(p.emit_w + f_lo); }
+        if (f_hi < p.a_rows) { pf_b = *reinterpret_cast<const float4*>(h + f_hi); if (p.emit_w) pf_d = *reinterpret_cast<const float4*>(p.emit_w + f_hi); }
+        pf = true;
+      } else if (p.epilogue == TC_QKV_ROPE) {
+        const QkvRope& g = p.qr;
+        pf_pos = g.positions[t];
+        if (tile_a >= g.n_q_heads)
+          pf_page = LLMRS_CHECKED_PAGE(g.block_table[(size_t)g.token_req[t] * g.table_stride + pf_pos / g.page_size], 5, t);
+        if (g.cos_sin && tile_a < g.n_q_heads + g.n_kv_heads) {
+          const float4* cs = reinterpret_cast<const float4*>(g.cos_sin + ((size_t)pf_pos * 64 + 4 * q) * 2);
+          pf_a = cs[0];
+          pf_b = cs[1];
+        }
         pf = true;
       }
-    } else if (p.epilogue == TC_QKV_ROPE) {
-      qkv_fetch_tokens(p.qr, (int)rank, splits, ewarp, lane, n_tok, tile_b * BN, tile_a, pf_pos, pf_page);
-      if (p.qr.cos_sin && tile_a < p.qr.n_q_heads + p.qr.n_kv_heads) {   // the rotation of the warp's first token
-        const int pos0 = __shfl_sync(0xffffffffu, pf_pos, 0);
-        pf_cs0 = *reinterpret_cast<const float2*>(p.qr.cos_sin + ((size_t)pos0 * 64 + lane) * 2);
-        pf_cs1 = *reinterpret_cast<const float2*>(p.qr.cos_sin + ((size_t)pos0 * 64 + lane + 32) * 2);
-      }
-      pf = true;
     }
     if (p.scale_part) {
       // While the product runs: the row scales 1/sqrt(sum of the pieces / dim + eps) of this
@@ -486,12 +474,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_before();
     __syncthreads();
   } else {
-    // Rows are features, columns tokens. Partial tile -> shared memory -> sum over the
-    // cluster's blocks in rank order -> epilogue for the rows this block owns.
-    float* red = reinterpret_cast<float*>(tiles);  // [128][BN + 1]; the stages are free (see the join above)
+    // Rows are features, columns tokens. Partial tile -> shared memory, token-major -> every block sums, over the
+    // cluster's blocks in rank order, the tokens it owns -> epilogue. A thread's item is 2 x 4 neighbouring features of
+    // one token: 16-byte loads, through the cluster too, and all of an item's loads are issued before the first is used.
+    // [BN tokens][RT]; the stages are free (see the join above).
+    float* red = reinterpret_cast<float*>(tiles);
     // This block's stream is over; what is left is its epilogue: the memory system can serve the next kernel.
     if (tid == 0) l2_prefetch_slice(p.next);
-    constexpr int RS = BN + 1;
+    constexpr int RT = TC_BM + 4;     // a token's row: 16-byte aligned, and neighbouring tokens four banks apart
 #pragma unroll 1
     for (int c = 0; c < BN; c += 8) {
       float v[8];
@@ -502,149 +492,170 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int e = 0; e < 8; ++e) v[e] = 0.f;
       }
 #pragma unroll
-      for (int e = 0; e < 8; ++e) red[row * RS + c + e] = v[e];
+      for (int e = 0; e < 8; ++e) red[(c + e) * RT + row] = v[e];
     }
     tc_fence_before();
     if (splits > 1) cluster_sync_all(); else __syncthreads();
 
     const uint32_t red_addr = tc_smem(red);
-    if (p.epilogue == TC_QKV_ROPE) {
-      // The tile is one head. A block of the cluster takes every splits-th token, a warp one token at a
-      // time: lane l holds features l, l + 32, l + 64, l + 96, i.e. the rotation's pairs (l, l + 64) and
-      // (l + 32, l + 96), and the head's sum of squares is one warp reduction.
-      const QkvRope& g = p.qr;
-      const int head = tile_a;
-      const int kind = head < g.n_q_heads ? 0 : head < g.n_q_heads + g.n_kv_heads ? 1 : 2;
-      const int hidx = kind == 0 ? head : kind == 1 ? head - g.n_q_heads : head - g.n_q_heads - g.n_kv_heads;
-      const bool cs_fetched = pf;
-      if (!pf) qkv_fetch_tokens(g, (int)rank, splits, ewarp, lane, n_tok, tile_b * BN, head, pf_pos, pf_page);
-      int it = 0;
-      for (int j = (int)rank + splits * ewarp; j < n_tok; j += splits * (TC_THREADS / 32), ++it) {
-        // Global loads first (they only need the position), then the sums over the cluster.
-        const int pos = __shfl_sync(0xffffffffu, pf_pos, it & 31);
-        const int page = __shfl_sync(0xffffffffu, pf_page, it & 31);
-        float2 cs0 = pf_cs0, cs1 = pf_cs1;
-        if (kind != 2 && g.cos_sin && !(cs_fetched && it == 0)) {
-          cs0 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane) * 2);
-          cs1 = *reinterpret_cast<const float2*>(g.cos_sin + ((size_t)pos * 64 + lane + 32) * 2);
-        }
-        float x[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int f = lane + 32 * q;
-          float acc = 0.f;
-          if (splits > 1) {
-            acc = cluster_sum_f32(red_addr + (uint32_t)(f * RS + j) * 4, splits);
-          } else {
-            acc = red[f * RS + j];
+    const QkvRope& g = p.qr;
+    // q|k|v: the tile is one head.
+    const int kind = tile_a < g.n_q_heads ? 0 : tile_a < g.n_q_heads + g.n_kv_heads ? 1 : 2;
+    const int hidx = kind == 0 ? tile_a : kind == 1 ? tile_a - g.n_q_heads : tile_a - g.n_q_heads - g.n_kv_heads;
+    for (int base = 0; base < n_items; base += TC_THREADS) {   // every thread walks the loop (warp shuffles below)
+      const int it = base + etid;
+      const bool live = it < n_items;
+      const bool fetched = pf && base == 0;
+      const int q = it & 15;
+      const int j = (int)rank + splits * (live ? it >> 4 : 0);      // a thread without an item works on the block's first token, stores nothing
+      const int t = tile_b * BN + j;
+      const int f_lo = tile_a * TC_BM + 4 * q, f_hi = f_lo + 64;     // features come in eights: a quad is whole or absent
+      const bool lo_ok = live && f_lo < p.a_rows, hi_ok = live && f_hi < p.a_rows;
+      // What the item needs from global memory is asked for before the sums over the cluster, so that the
+      // latencies overlap.
+      float4 ga = pf_a, gb = pf_b, gc = pf_c, gd = pf_d;
+      int pos = pf_pos, page = pf_page;
+      if (!fetched) {
+        if (p.epilogue == TC_RESIDUAL) {
+          const float* h = (const float*)p.out + (size_t)t * p.ldo;
+          if (lo_ok) { ga = *reinterpret_cast<const float4*>(h + f_lo); if (p.emit_w) gc = *reinterpret_cast<const float4*>(p.emit_w + f_lo); }
+          if (hi_ok) { gb = *reinterpret_cast<const float4*>(h + f_hi); if (p.emit_w) gd = *reinterpret_cast<const float4*>(p.emit_w + f_hi); }
+        } else if (p.epilogue == TC_QKV_ROPE && live) {
+          pos = g.positions[t];
+          if (kind != 0)
+            page = LLMRS_CHECKED_PAGE(g.block_table[(size_t)g.token_req[t] * g.table_stride + pos / g.page_size], 5, t);
+          if (g.cos_sin && kind != 2) {
+            const float4* cs = reinterpret_cast<const float4*>(g.cos_sin + ((size_t)pos * 64 + 4 * q) * 2);
+            ga = cs[0];
+            gb = cs[1];
           }
-          x[q] = scaled ? acc * inv_s[j] : acc;
         }
-        const int t = tile_b * BN + j;
+      }
+      float lo[4], hi[4];
+      {
+        const uint32_t a_lo = red_addr + (uint32_t)(j * RT + 4 * q) * 4, a_hi = a_lo + 64 * 4;
+        float4 sl, sh;
+        if (splits > 1) {
+          float4 vl[8], vh[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r)
+            if (r < splits) {
+              vl[r] = ld_cluster_f32x4(a_lo, (uint32_t)r);
+              vh[r] = ld_cluster_f32x4(a_hi, (uint32_t)r);
+            }
+          sl = vl[0];
+          sh = vh[0];
+#pragma unroll
+          for (int r = 1; r < 8; ++r)
+            if (r < splits) {       // in rank order
+              sl.x += vl[r].x; sl.y += vl[r].y; sl.z += vl[r].z; sl.w += vl[r].w;
+              sh.x += vh[r].x; sh.y += vh[r].y; sh.z += vh[r].z; sh.w += vh[r].w;
+            }
+        } else {
+          sl = *reinterpret_cast<const float4*>(red + j * RT + 4 * q);
+          sh = *reinterpret_cast<const float4*>(red + j * RT + 4 * q + 64);
+        }
+        const float sc = scaled ? inv_s[j] : 1.f;
+        lo[0] = sl.x * sc; lo[1] = sl.y * sc; lo[2] = sl.z * sc; lo[3] = sl.w * sc;
+        hi[0] = sh.x * sc; hi[1] = sh.y * sc; hi[2] = sh.z * sc; hi[3] = sh.w * sc;
+      }
+      if (p.epilogue == TC_SILU_MUL) {
+        // The tile's first 64 rows are gate rows, the other 64 the up rows of the same features.
+        const int f = tile_a * (TC_BM / 2) + 4 * q;
+        if (live && f < p.a_rows / 2) {
+          uint2 pk;
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+          h2[0] = __floats2bfloat162_rn(silu_f(lo[0]) * hi[0], silu_f(lo[1]) * hi[1]);
+          h2[1] = __floats2bfloat162_rn(silu_f(lo[2]) * hi[2], silu_f(lo[3]) * hi[3]);
+          *reinterpret_cast<uint2*>((bf16*)p.out + (size_t)t * p.ldo + f) = pk;
+        }
+      } else if (p.epilogue == TC_RESIDUAL) {
+        float* h = (float*)p.out + (size_t)t * p.ldo;
+        const float4 n_lo = make_float4(ga.x + lo[0], ga.y + lo[1], ga.z + lo[2], ga.w + lo[3]);
+        const float4 n_hi = make_float4(gb.x + hi[0], gb.y + hi[1], gb.z + hi[2], gb.w + hi[3]);
+        if (lo_ok) *reinterpret_cast<float4*>(h + f_lo) = n_lo;
+        if (hi_ok) *reinterpret_cast<float4*>(h + f_hi) = n_hi;
+        if (p.emit_w) {
+          // The norm that follows: its input times its weight, and the sum of squares of the token's 128 features
+          // of this tile (the 16 threads of a token sit side by side in a warp).
+          float ss = 0.f;
+          if (lo_ok) {
+            uint2 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+            h2[0] = __floats2bfloat162_rn(n_lo.x * gc.x, n_lo.y * gc.y);
+            h2[1] = __floats2bfloat162_rn(n_lo.z * gc.z, n_lo.w * gc.w);
+            *reinterpret_cast<uint2*>(p.emit_xw + (size_t)t * p.emit_ld + f_lo) = pk;
+            ss += n_lo.x * n_lo.x + n_lo.y * n_lo.y + n_lo.z * n_lo.z + n_lo.w * n_lo.w;
+          }
+          if (hi_ok) {
+            uint2 pk;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+            h2[0] = __floats2bfloat162_rn(n_hi.x * gd.x, n_hi.y * gd.y);
+            h2[1] = __floats2bfloat162_rn(n_hi.z * gd.z, n_hi.w * gd.w);
+            *reinterpret_cast<uint2*>(p.emit_xw + (size_t)t * p.emit_ld + f_hi) = pk;
+            ss += n_hi.x * n_hi.x + n_hi.y * n_hi.y + n_hi.z * n_hi.z + n_hi.w * n_hi.w;
+          }
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+          if (live && q == 0) p.emit_part[(size_t)tile_a * p.part_stride + t] = ss;
+        }
+      } else if (p.epilogue == TC_QKV_ROPE) {
         if (kind != 2) {
           const float* w = kind == 0 ? g.q_norm_w : g.k_norm_w;
           if (w) {
-            float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+            float ss = lo[0] * lo[0] + lo[1] * lo[1] + lo[2] * lo[2] + lo[3] * lo[3] +
+                       hi[0] * hi[0] + hi[1] * hi[1] + hi[2] * hi[2] + hi[3] * hi[3];
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             const float inv = 1.0f / sqrtf(ss / 128.0f + g.eps);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) x[q] *= inv * w[lane + 32 * q];
+            const float4 w_lo = *reinterpret_cast<const float4*>(w + 4 * q), w_hi = *reinterpret_cast<const float4*>(w + 64 + 4 * q);
+            lo[0] *= inv * w_lo.x; lo[1] *= inv * w_lo.y; lo[2] *= inv * w_lo.z; lo[3] *= inv * w_lo.w;
+            hi[0] *= inv * w_hi.x; hi[1] *= inv * w_hi.y; hi[2] *= inv * w_hi.z; hi[3] *= inv * w_hi.w;
           }
           if (g.cos_sin) {
-            const float a0 = x[0] * cs0.x - x[2] * cs0.y, b0 = x[2] * cs0.x + x[0] * cs0.y;
-            const float a1 = x[1] * cs1.x - x[3] * cs1.y, b1 = x[3] * cs1.x + x[1] * cs1.y;
-            x[0] = a0; x[2] = b0; x[1] = a1; x[3] = b1;
+            // (cos, sin) of the pairs 4q..4q+3: feature i turns with feature i + 64.
+            const float c[4] = {ga.x, ga.z, gb.x, gb.z}, sn[4] = {ga.y, ga.w, gb.y, gb.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float a0 = lo[e] * c[e] - hi[e] * sn[e], b0 = hi[e] * c[e] + lo[e] * sn[e];
+              lo[e] = a0;
+              hi[e] = b0;
+            }
           }
         }
-        bf16* dst;
-        if (kind == 0) {
-          dst = g.q_out + (size_t)t * g.ldq + (size_t)hidx * 128;
-        } else {
-          dst = g.cache + kv_tile_offset(page, hidx, kind - 1, g.n_kv_heads, g.page_size, 128) +
-                (size_t)(pos % g.page_size) * 128;
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) dst[lane + 32 * q] = __float2bfloat16_rn(x[q]);
-      }
-    } else
-    for (int base = 0; base < per * n_tok; base += TC_THREADS) {   // every thread walks the loop (warp shuffles below)
-      const int idx = base + etid;
-      const bool live = idx < per * n_tok;
-      const bool fetched = pf && base == 0;
-      const int pr = idx % per, j = live ? idx / per : 0;
-      const int i_lo = (int)rank * per + pr, i_hi = i_lo + 64;
-      const int t = tile_b * BN + j;
-      const int f_lo = tile_a * TC_BM + i_lo, f_hi = f_lo + 64;
-      // The residual's old values (and the next norm's weight) are asked for before the sums over the
-      // cluster, so that the two latencies overlap.
-      float h_lo = 0.f, h_hi = 0.f, w_lo = 0.f, w_hi = 0.f;
-      if (p.epilogue == TC_RESIDUAL && live) {
-        const float* h = (const float*)p.out + (size_t)t * p.ldo;
-        if (f_lo < p.a_rows) {
-          h_lo = fetched ? pf_h_lo : h[f_lo];
-          if (p.emit_w) w_lo = fetched ? pf_w_lo : p.emit_w[f_lo];
-        }
-        if (f_hi < p.a_rows) {
-          h_hi = fetched ? pf_h_hi : h[f_hi];
-          if (p.emit_w) w_hi = fetched ? pf_w_hi : p.emit_w[f_hi];
-        }
-      }
-      float lo = 0.f, hi = 0.f;
-      if (live) {
-        if (splits > 1) {
-          float vlo[8], vhi[8];
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {   // all loads first: one round trip through the cluster, not one per block
-            vlo[r] = r < splits ? ld_cluster_f32(red_addr + (uint32_t)(i_lo * RS + j) * 4, (uint32_t)r) : 0.f;
-            vhi[r] = r < splits ? ld_cluster_f32(red_addr + (uint32_t)(i_hi * RS + j) * 4, (uint32_t)r) : 0.f;
+        if (live) {
+          bf16* dst;
+          if (kind == 0) {
+            dst = g.q_out + (size_t)t * g.ldq + (size_t)hidx * 128;
+          } else {
+            dst = g.cache + kv_tile_offset(page, hidx, kind - 1, g.n_kv_heads, g.page_size, 128) +
+                  (size_t)(pos % g.page_size) * 128;
           }
-#pragma unroll
-          for (int r = 0; r < 8; ++r) { lo += vlo[r]; hi += vhi[r]; }
-        } else {
-          lo = red[i_lo * RS + j];
-          hi = red[i_hi * RS + j];
-        }
-        if (scaled) {
-          lo *= inv_s[j];
-          hi *= inv_s[j];
-        }
-      }
-      if (p.epilogue == TC_SILU_MUL) {
-        const int f = tile_a * (TC_BM / 2) + i_lo;
-        if (live && f < p.a_rows / 2) ((bf16*)p.out)[(size_t)t * p.ldo + f] = __float2bfloat16_rn(silu_f(lo) * hi);
-      } else if (p.epilogue == TC_RESIDUAL) {
-        float* h = (float*)p.out + (size_t)t * p.ldo;
-        float n_lo = 0.f, n_hi = 0.f;
-        if (live && f_lo < p.a_rows) { n_lo = h_lo + lo; h[f_lo] = n_lo; }
-        if (live && f_hi < p.a_rows) { n_hi = h_hi + hi; h[f_hi] = n_hi; }
-        if (p.emit_w) {
-          // The norm that follows: its input times its weight, and this block's share of the sum of
-          // squares per token (the `per` threads of a token sit side by side in a warp).
-          if (live && f_lo < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_lo] = __float2bfloat16_rn(n_lo * w_lo);
-          if (live && f_hi < p.a_rows) p.emit_xw[(size_t)t * p.emit_ld + f_hi] = __float2bfloat16_rn(n_hi * w_hi);
-          float ss = n_lo * n_lo + n_hi * n_hi;
-          for (int o = per >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-          if (live && pr == 0) st_cluster_f32(tc_smem(ss_ranks + (int)rank * 64 + j), 0u, ss);
+          uint2 pl, ph;
+          __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&pl);
+          __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ph);
+          l2[0] = __floats2bfloat162_rn(lo[0], lo[1]); l2[1] = __floats2bfloat162_rn(lo[2], lo[3]);
+          h2[0] = __floats2bfloat162_rn(hi[0], hi[1]); h2[1] = __floats2bfloat162_rn(hi[2], hi[3]);
+          *reinterpret_cast<uint2*>(dst + 4 * q) = pl;
+          *reinterpret_cast<uint2*>(dst + 64 + 4 * q) = ph;
         }
       } else if (p.out_dtype == LLMRS_F32) {
         float* o = (float*)p.out + (size_t)t * p.ldo;
-        if (live && f_lo < p.a_rows) o[f_lo] = lo;
-        if (live && f_hi < p.a_rows) o[f_hi] = hi;
+        if (lo_ok) *reinterpret_cast<float4*>(o + f_lo) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+        if (hi_ok) *reinterpret_cast<float4*>(o + f_hi) = make_float4(hi[0], hi[1], hi[2], hi[3]);
       } else {
         bf16* o = (bf16*)p.out + (size_t)t * p.ldo;
-        if (live && f_lo < p.a_rows) o[f_lo] = __float2bfloat16_rn(lo);
-        if (live && f_hi < p.a_rows) o[f_hi] = __float2bfloat16_rn(hi);
+        uint2 pl, ph;
+        __nv_bfloat162* l2 = reinterpret_cast<__nv_bfloat162*>(&pl);
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&ph);
+        l2[0] = __floats2bfloat162_rn(lo[0], lo[1]); l2[1] = __floats2bfloat162_rn(lo[2], lo[3]);
+        h2[0] = __floats2bfloat162_rn(hi[0], hi[1]); h2[1] = __floats2bfloat162_rn(hi[2], hi[3]);
+        if (lo_ok) *reinterpret_cast<uint2*>(o + f_lo) = pl;
+        if (hi_ok) *reinterpret_cast<uint2*>(o + f_hi) = ph;
       }
     }
     // No block may leave while another still reads its shared memory.
     if (splits > 1) cluster_sync_all(); else __syncthreads();
-    if (p.emit_w && p.epilogue == TC_RESIDUAL && rank == 0 && tid < n_tok) {
-      // The cluster's sums of squares, added in the order of its blocks: one piece per tile of features.
-      float ss = 0.f;
-      for (int r = 0; r < splits; ++r) ss += ss_ranks[r * 64 + tid];
-      p.emit_part[(size_t)tile_a * p.part_stride + tile_b * BN + tid] = ss;
-    }
   }
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
@@ -1310,6 +1321,9 @@ LLMRS_API int llmrs_gemm_qkv_rope(const void* x, long long ldx, const void* w, i
   LLMRS_REQUIRE(tokens > 0 && tokens <= 64, "gemm_qkv_rope: takes 1 to 64 tokens, got %d", tokens);
   LLMRS_REQUIRE(n_q_heads > 0 && n_kv_heads > 0 && page_size > 0 && table_stride > 0, "gemm_qkv_rope: bad sizes");
   LLMRS_REQUIRE(q_out && cache && positions && token_req && block_table, "gemm_qkv_rope: missing argument");
+  LLMRS_REQUIRE(((uintptr_t)q_out & 15) == 0 && ldq % 8 == 0 && ((uintptr_t)cache & 15) == 0 && ((uintptr_t)cos_sin & 15) == 0 &&
+                    ((uintptr_t)q_norm_w & 15) == 0 && ((uintptr_t)k_norm_w & 15) == 0,
+                "gemm_qkv_rope: q_out, the cache, the rotation table and the norm weights must be 16-byte aligned");
   QkvRope qr;
   qr.q_out = (__nv_bfloat16*)q_out; qr.ldq = ldq; qr.cache = (__nv_bfloat16*)cache; qr.q_norm_w = q_norm_w;
   qr.k_norm_w = k_norm_w; qr.cos_sin = cos_sin; qr.positions = positions; qr.token_req = token_req;
@@ -1445,8 +1459,7 @@ LLMRS_API int llmrs_gemm_bf16(const void* x, long long ldx, const void* w, void*
                         nullptr, stream);
 }
 
-// llmrs_gemm_bf16 as one half of a norm that is spread over two products: with emit_w (TC_RESIDUAL; at most 64
-// tokens: splits >= 2) it also writes emit_xw[tokens, emit_ld] = (h + y) * emit_w in bfloat16 and
+// llmrs_gemm_bf16 as one half of a norm that is spread over two products: with emit_w (TC_RESIDUAL) it also writes emit_xw[tokens, emit_ld] = (h + y) * emit_w in bfloat16 and
 // emit_part[pieces, part_stride], the sums of squares per token of each piece of the features (128 wide for at
 // most 64 tokens, 256 wide for more); with scale_part it multiplies the rows of y by 1 / sqrt(sum of the
 // scale_parts entries of the row's token / scale_dim + scale_eps) before its epilogue.
@@ -1458,7 +1471,8 @@ LLMRS_API int llmrs_gemm_bf16_norm(const void* x, long long ldx, const void* w, 
   LLMRS_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_bf16: unknown epilogue %d", epilogue);
   LLMRS_REQUIRE(!emit_w || (epilogue == TC_RESIDUAL && emit_xw && emit_part && part_stride >= tokens),
                 "gemm_bf16_norm: the next norm's input is written by a residual epilogue");
-  LLMRS_REQUIRE(!emit_w || tokens > 64 || splits >= 2, "gemm_bf16_norm: at most 64 tokens emit with 2 or more splits");
+  LLMRS_REQUIRE(!emit_w || (((uintptr_t)emit_w & 15) == 0 && ((uintptr_t)emit_xw & 15) == 0 && emit_ld % 8 == 0),
+                "gemm_bf16_norm: the norm's weight and input must be 16-byte aligned, rows too");
   LLMRS_REQUIRE(tokens <= 64 || features >= 256, "gemm_bf16_norm: more than 64 tokens need at least 256 features");
   LLMRS_REQUIRE(!scale_part || (scale_parts > 0 && scale_dim > 0 && part_stride >= tokens),
                 "gemm_bf16_norm: bad description of the row scales");
@@ -1477,6 +1491,7 @@ static int gemm_bf16_impl(const void* x, long long ldx, const void* w, void* out
   LLMRS_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16: operands must be 16-byte aligned");
   LLMRS_REQUIRE(features % 8 == 0 && ldo % 8 == 0, "gemm_bf16: features %d and the output row stride %lld must be "
                 "multiples of 8", features, ldo);
+  LLMRS_REQUIRE(((uintptr_t)out & 15) == 0, "gemm_bf16: the output must be 16-byte aligned");
   LLMRS_REQUIRE(epilogue != TC_SILU_MUL || features % 128 == 0,
                 "gemm_bf16: SiLU*up needs features in groups of 128, got %d", features);
   TcParams p;

@@ -26,6 +26,9 @@ _FUSE_QKV_ROPE = os.environ.get("LLMRS_FUSE_QKV_ROPE", "1") != "0"
 
 # A decode attention block's fixed cost (start, merge of its warps and of the cluster) in keys' worth of
 # streaming; see GQAttention._choose_split.
+# The q|k|v product with norms, rotation and cache write in its epilogue is taken up to this many tokens; above, the
+# library product and the rotation kernel are ahead (at 64 tokens 16 + 5 us against 24).
+QKV_TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_QKV_MAX_TOKENS", "32"))
 FIXED_KEYS = 192
 CAPACITY_USED = 0.975   # of the blocks the device holds: 256 of 264 ran in one wave, 280 of 280 did not
 MAX_CLUSTER = 16     # splits that the kernel merges itself
@@ -135,6 +138,7 @@ class GQAttention(Mixer):
         self.qkv_proj.warms_next = False
         # The query rows alone, for run-order entries that read another entry's cache.
         self.q_proj = Linear(wqkv[: self.q_width], None if bqkv is None else bqkv[: self.q_width], runtime.act_dtype)
+        self.qkv_proj.tc_max_tokens = self.q_proj.tc_max_tokens = QKV_TC_MAX_TOKENS
         self.o_proj = Linear(tensors[nm("o")], tensors.get(nm("o", "bias")), runtime.act_dtype)
         self.q_norm_w = self.k_norm_w = None
         if self.qk_norm:
@@ -241,9 +245,13 @@ class GQAttention(Mixer):
             # Up to eight splits form a thread-block cluster and merge inside the kernel; more are merged by
             # a second, small kernel. (Merging them in the split kernel's last block,
             # ops.attn_decode(counters=...), measured no faster inside the step and slower at batch 1.)
+            # The kernel asks the start of o_proj's weights into the L2 as its blocks finish their streams; when its
+            # blocks run in several waves the first to finish would ask long before the kernel ends, and the keys and
+            # values still streaming would push the weights out again.
+            one_wave = n_decode * nkv * max_splits <= 2 * _sm_count(q.device)
             ops.attn_decode(q, out, cache.kv, plan.arrays["decode_reqs"], n_decode, ctx.q_start, ctx.cached_len, table,
-                            scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window,
-                            self.scale, then=self.o_proj.weight if self.o_proj.uses_tc(ctx.n_tokens) else None)
+                            scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window, self.scale,
+                            then=self.o_proj.weight if one_wave and self.o_proj.uses_tc(ctx.n_tokens) else None)
         if next_norm is not None:
             return self.o_proj.forward_into_residual_for_norm(out, residual, *next_norm)
         if residual is not None:

@@ -1,6 +1,6 @@
 """Matrix products of the parts.
 
-bfloat16 weights: steps of up to ``TC_MAX_TOKENS`` tokens (decoding) run this package's
+bfloat16 weights: steps of up to ``TC_MAX_TOKENS`` tokens (decoding, 64 at most) run this package's
 tcgen05 kernel (``csrc/gemm_tcgen05.cu``: weights fill the 128 rows of the MMA, the k range
 is shared by a thread-block cluster) with the residual sum or SiLU*up fused into its
 epilogue; larger steps go through the library product (cuBLAS via ``torch``), as the
@@ -23,10 +23,11 @@ import torch
 from .. import ops
 from .base import PreNormed
 
-# Steps with at most this many tokens take the tcgen05 kernel; 0 switches it off. (Measured inside decode
-# steps: up to 16 tokens the kernel with its fused epilogues is ahead of the library product plus the separate
-# kernels, from 17 to 32 tokens it is 3-4 % behind, at 64 tokens far behind.)
-TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "16"))
+# Steps with at most this many tokens take the tcgen05 kernel for few tokens; 0 switches the tcgen05 products off.
+# (Measured inside decode steps at Qwen3-8B sizes: with its fused epilogues the kernel is ahead of the library product
+# plus the separate kernels at every number of tokens it takes, 4.08 -> 3.58 ms a step at 32 tokens; a product may set
+# a lower limit of its own, ``Linear.tc_max_tokens``.)
+TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "64"))
 # Steps with at least this many tokens take the tcgen05 kernel for many tokens for every product; 0 (the default)
 # keeps all but gate|up on the library product. (Prefill of 2,048 tokens at Qwen3-8B sizes, 36 layers, timed over
 # seconds under the power cap: 24.9 ms with the library's q|k|v, o and down products and the norm kernels, 25.6 ms
@@ -59,6 +60,7 @@ class Linear:
         # steps of few tokens this product's kernel asks their start into the L2 as its own stream ends.
         self.next_weight: Optional[torch.Tensor] = None
         self.warms_next = True      # False: something else runs between this product and the next one
+        self.tc_max_tokens: Optional[int] = None    # a limit of this product's own below TC_MAX_TOKENS
         self.tc_ok = (weight.dtype == torch.bfloat16 and bias is None and weight.is_contiguous()
                       and k % 8 == 0 and n % 8 == 0 and weight.data_ptr() % 16 == 0)
 
@@ -69,7 +71,8 @@ class Linear:
     def uses_tc(self, n_tokens: int) -> bool:
         if not self.tc_enabled() or n_tokens <= 0:
             return False
-        return n_tokens <= TC_MAX_TOKENS or 0 < TC_MANY_TOKENS <= n_tokens
+        few = TC_MAX_TOKENS if self.tc_max_tokens is None else min(TC_MAX_TOKENS, self.tc_max_tokens)
+        return n_tokens <= few or 0 < TC_MANY_TOKENS <= n_tokens
 
     def forward(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or self.act_dtype
@@ -94,9 +97,7 @@ class Linear:
 
     def emits_prenormed(self, n_tokens: int) -> bool:
         """True when ``forward_into_residual`` can also write the input of the norm that follows."""
-        if not self.uses_tc(n_tokens):
-            return False
-        return self._splits(n_tokens) >= 2 if n_tokens <= 64 else self.weight.size(0) >= 256
+        return self.uses_tc(n_tokens) and (n_tokens <= 64 or self.weight.size(0) >= 256)
 
     def forward_into_residual_for_norm(self, x: torch.Tensor, h: torch.Tensor, norm_weight: torch.Tensor,
                                        eps: float) -> PreNormed:

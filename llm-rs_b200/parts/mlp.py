@@ -62,7 +62,7 @@ class SwiGLU(FeedForward):
     def takes_prenormed(self, n_tokens: int) -> bool:
         if not (self.block and self.gate_up.tc_enabled() and FUSE_GATE_UP):
             return False
-        return 0 < n_tokens <= 32 or (n_tokens > 64 and self.gate_up.uses_tc(n_tokens))
+        return 0 < n_tokens <= 64 or self.gate_up.uses_tc(n_tokens)
 
     def emits_prenormed(self, n_tokens: int) -> bool:
         return self.down.emits_prenormed(n_tokens)
@@ -75,12 +75,9 @@ class SwiGLU(FeedForward):
                 return self.down.forward_into_residual_for_norm(act, residual, *next_norm)
             return self.down.forward_into_residual(act, residual) if residual is not None else self.down.forward(act)
         # With interleaved weights the product and SiLU(gate) * up are one kernel at every number of
-        # tokens: for many tokens the persistent tcgen05 kernel on pairs of SMs with this epilogue is ahead of
-        # the library product followed by the SiLU kernel (2,048 tokens: 261 against 271 + 20 us).
-        # (From 33 to 64 tokens the few-token kernel's widest tile is behind the library product followed by the
-        # SiLU kernel: 10.53 against 10.38 ms a step at 64 tokens.)
-        if (self.block and x.dtype == torch.bfloat16 and self.gate_up.tc_enabled() and FUSE_GATE_UP
-                and not 32 < x.size(0) <= 64):
+        # tokens: for few tokens the cluster kernel (40 against 44 us for the library product and the SiLU kernel at
+        # 64 tokens), for many the persistent tcgen05 kernel on pairs of SMs (2,048 tokens: 261 against 271 + 20 us).
+        if self.block and x.dtype == torch.bfloat16 and self.gate_up.tc_enabled() and FUSE_GATE_UP:
             act = ops.gemm_bf16(x, self.gate_up.weight, epilogue="silu_mul", then=self.gate_up.next_weight)
         else:
             act = ops.silu_mul(self.gate_up.forward(x), block=self.block)

@@ -714,7 +714,7 @@ def test_gemm_qkv_rope_epilogue(tokens, nq, nkv, K, page, rope, norm):
 
 @pytest.mark.parametrize("tokens,features,K,splits,consumer", [
     (8, 256, 512, 2, "store"), (1, 384, 256, 4, "silu_mul"), (19, 200, 1024, 8, "store"), (32, 512, 512, 2, "qkv_rope"),
-    (64, 136, 256, 2, "silu_mul")])
+    (64, 136, 256, 2, "silu_mul"), (5, 264, 128, 1, "store"), (33, 128, 512, 4, "qkv_rope")])
 def test_gemm_norm_spread_over_two_products(tokens, features, K, splits, consumer):
     """A residual epilogue that also writes the next norm's input (h * weight and sums of squares in
     pieces), and the products that take it and scale their rows, against
@@ -773,8 +773,9 @@ def test_gemm_norm_emission_refusals():
     w = torch.zeros(256, 256, dtype=torch.bfloat16, device=DEV)
     h = torch.zeros(8, 256, device=DEV)
     nw, xw, parts = torch.ones(256, device=DEV), torch.empty(8, 256, dtype=torch.bfloat16, device=DEV), torch.empty(8, 64, device=DEV)
-    with pytest.raises(ops.KernelError):      # one split: the sums of squares would need 64 threads a token
-        ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=1, emit=(nw, xw, parts))
+    with pytest.raises(ops.KernelError):      # a row stride of the norm's input that is no multiple of 8
+        ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=2,
+                      emit=(nw, torch.empty(8, 260, dtype=torch.bfloat16, device=DEV)[:, :256], parts))
     with pytest.raises(ops.KernelError):      # too few rows for the pieces
         ops.gemm_bf16(x, w, out=h, epilogue="residual", splits=4, emit=(nw, xw, parts[:1]))
 
