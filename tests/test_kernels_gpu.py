@@ -468,6 +468,25 @@ def test_gemm_tcgen05_few_tokens(tokens, features, K, epilogue, out_dtype, split
     _tc_case(tokens, features, K, epilogue, out_dtype, splits)
 
 
+def test_gemm_tcgen05_few_tokens_random_shapes():
+    """Random token counts, widths (multiples of 8, ragged against the tiles of 128 features and 64 of k), cluster
+    sizes and epilogues: every item of the epilogue's division by tokens and quads, with and without a partner
+    feature 64 further on, must land where the plain product says."""
+    rng = np.random.default_rng(11)
+    for _ in range(48):
+        tokens = int(rng.integers(1, 65))
+        K = int(rng.integers(1, 40)) * 8
+        epilogue = ["store", "store", "residual", "silu_mul"][int(rng.integers(0, 4))]
+        features = int(rng.integers(1, 6)) * 128 if epilogue == "silu_mul" else int(rng.integers(1, 80)) * 8
+        k_blocks = -(-K // 64)
+        splits = int(rng.choice([s for s in (1, 2, 4, 8) if s <= max(1, k_blocks)]))
+        out_dtype = torch.float32 if rng.integers(0, 2) else torch.bfloat16
+        try:
+            _tc_case(tokens, features, K, epilogue, out_dtype, splits)
+        except AssertionError as e:
+            raise AssertionError(f"tokens {tokens} features {features} K {K} {epilogue} {out_dtype} splits {splits}: {e}")
+
+
 @pytest.mark.parametrize("tokens,features,K,epilogue,out_dtype", [
     (65, 128, 64, "store", torch.float32), (128, 256, 512, "store", torch.bfloat16),
     (300, 392, 1000, "store", torch.float32), (200, 512, 4096, "residual", torch.float32),
