@@ -179,8 +179,8 @@ LLMRS_API int llmrs_attn_prefill(const void* q, long long q_stride, void* out, l
   const size_t smem = (size_t)(PF_BQ * d + PF_BK * (d + 1) + PF_BK * d + PF_BQ * PF_BK) * sizeof(float);
   dim3 grid(n_tiles, n_q_heads, PF_TILE / PF_BQ);
   cudaError_t e;
-  // (The tcgen05 kernel keeps the tile index in gridDim.y.)
-  if (dtype == LLMRS_BF16 && prefer_tc && !g_generic_only && n_tiles <= 65535 &&
+  // (The tcgen05 kernel notes the list's 128-row tiles in shared memory: at most 8,192 entries.)
+  if (dtype == LLMRS_BF16 && prefer_tc && !g_generic_only && n_tiles <= 8192 &&
       llmrs_attn_prefill_tc_supported(q, q_stride, cache, d, page_size, scale))
     return llmrs_attn_prefill_tc(q, q_stride, n_tokens, out, out_stride, cache,
                                  (long long)n_pages * n_kv_heads * 2 * page_size, tiles, n_tiles, q_start, n_new,

@@ -41,6 +41,7 @@ namespace {
 
 constexpr int AT_BQ = 128, AT_BK = 128, AT_D = 128, AT_THREADS = 128, AT_STAGES = 3;
 constexpr uint32_t AT_WAIT_LIMIT = 1u << 22;
+constexpr int AT_MAX_LIST = 8192;    // entries of the tile list that a launch takes (a block notes its 128-row tiles in shared memory)
 constexpr float AT_LOG2E = 1.4426950408889634f;
 constexpr uint32_t K_BYTES = AT_BK * AT_D * 2, V_BYTES = K_BYTES, STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr uint32_t HALF_BYTES = AT_BK * 128;   // one half of head_dim of a K or V tile: [128 keys][64 dims]
@@ -198,7 +199,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                        bf16* __restrict__ out, long long out_stride, const int* __restrict__ tiles,
                        const int* __restrict__ q_start, const int* __restrict__ n_new,
                        const int* __restrict__ cached_len, const int* __restrict__ block_table, int table_stride,
-                       int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale,
+                       int n_list, int persistent, int n_q_heads, int n_kv_heads, int page_size, int box_rows, int window, float scale,
                        int* __restrict__ error_flag, uint32_t wait_limit, int test_skip_tile) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* base = smem_raw;           // 1024-byte aligned (checked below): the swizzle pattern needs it
@@ -206,26 +207,63 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   uint64_t* bars = reinterpret_cast<uint64_t*>(KV + AT_STAGES * STAGE_BYTES);   // kfull[3], kfree[3], vfull[3], vfree[3], s[2], p[2], o[2], q, drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * AT_STAGES + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_valid_slot = reinterpret_cast<int*>(tmem_slot + 2);
+  uint16_t* valid = reinterpret_cast<uint16_t*>(tmem_slot + 4);     // AT_MAX_LIST entries: the list's 128-row tiles
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // Later tiles of a prompt see more keys: run them first, for every head, so that the long blocks
-  // do not end the kernel alone (blocks start in the order of blockIdx.x, then blockIdx.y).
-  const int tile = gridDim.y - 1 - blockIdx.y, head = blockIdx.x;
-  const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
-  if (q_off % AT_BQ != 0) return;           // the list names tiles of 64 queries; a block takes two
   if ((sm(base) & 1023u) != 0) {            // never seen; without the alignment the operands would be garbage
     if (threadIdx.x == 0) atomicExch(error_flag ? error_flag : &g_attn_tc_error, 3);
     return;
   }
-  const int kvh = head / (n_q_heads / n_kv_heads);
-  const int rows = min(AT_BQ, n_new[req] - q_off);
-  const int tok0 = q_start[req] + q_off;
-  const int pos0 = cached_len[req] + q_off;
-  const int kv_hi = pos0 + rows;
-  const int key_floor = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int kv_lo = (key_floor / AT_BK) * AT_BK;
-  const int n_tiles = (kv_hi - kv_lo + AT_BK - 1) / AT_BK;
-  const int* table = block_table + (size_t)req * table_stride;
+  // The work: an item is 128 query rows of one request and one query head: those entries of the list of 64-query
+  // tiles whose offset is a multiple of 128 (warp 0 notes them in shared memory first), times the heads. Items are
+  // numbered so that later tiles of a prompt, which see more keys, come first, for every head; block b of G walks
+  // the numbering like a snake (b, 2G-1-b, 2G+b, 4G-1-b, ...), which gives every block about the same number of
+  // key tiles, and keeps tensor memory, barriers and the ring of stages from one item to the next: the copies of an
+  // item's first keys run under the end of the item before.
+  // With a block per item (persistent == 0) the block's number names an entry and a head, and the block of an entry
+  // that starts no 128-row tile leaves at once.
+  if (!persistent && tiles[2 * (n_list - 1 - (int)blockIdx.x / n_q_heads) + 1] % AT_BQ != 0) return;
+  if (persistent && warp == 0) {
+    int n = 0;
+    for (int e0 = 0; e0 < n_list; e0 += 32) {
+      const int e = e0 + lane;
+      const bool is_item = e < n_list && tiles[2 * e + 1] % AT_BQ == 0;
+      const unsigned m = __ballot_sync(0xffffffffu, is_item);
+      if (is_item) valid[n + __popc(m & ((1u << lane) - 1u))] = (uint16_t)e;
+      n += __popc(m);
+    }
+    if (lane == 0) *n_valid_slot = n;
+  }
+  __syncthreads();
+  const int n_valid = persistent ? *n_valid_slot : n_list;
+  struct Item {
+    int rows, tok0, pos0, kv_hi, key_floor, kv_lo, n_tiles, head, kvh;
+    const int* table;
+  };
+  const int n_lin = n_valid * n_q_heads;
+  auto item_index = [&](int r) {    // the block's r-th item, or -1 when it has no more
+    if (!persistent) return r == 0 ? (int)blockIdx.x : -1;
+    const int G = (int)gridDim.x, b = (int)blockIdx.x;
+    const int L = (r & 1) ? (r + 1) * G - 1 - b : r * G + b;
+    return L < n_lin ? L : -1;
+  };
+  auto item_at = [&](int L, Item& it) {
+    const int e = n_valid - 1 - L / n_q_heads, tile = persistent ? (int)valid[e] : e;
+    const int req = tiles[2 * tile], q_off = tiles[2 * tile + 1];
+    it.head = L % n_q_heads;
+    it.kvh = it.head / (n_q_heads / n_kv_heads);
+    it.rows = min(AT_BQ, n_new[req] - q_off);
+    it.tok0 = q_start[req] + q_off;
+    it.pos0 = cached_len[req] + q_off;
+    it.kv_hi = it.pos0 + it.rows;
+    it.key_floor = window > 0 ? max(0, it.pos0 - window + 1) : 0;
+    it.kv_lo = (it.key_floor / AT_BK) * AT_BK;
+    it.n_tiles = (it.kv_hi - it.kv_lo + AT_BK - 1) / AT_BK;
+    it.table = block_table + (size_t)req * table_stride;
+    return true;
+  };
+  if (item_index(0) < 0) return;     // more blocks than items
 
   const uint32_t bar_kfull = sm(bars), bar_kfree = sm(bars + AT_STAGES), bar_vfull = sm(bars + 2 * AT_STAGES),
                  bar_vfree = sm(bars + 3 * AT_STAGES), bar_s = sm(bars + 4 * AT_STAGES), bar_p = bar_s + 16,
@@ -252,52 +290,61 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t idesc_s = instr_desc(AT_BK, 0), idesc_pv = instr_desc(AT_D, 1);
 
-  int copies = 0;   // copying warps: tiles whose copies the warp has requested
+  int copies = 0;   // copying warps: tiles (counted over the block's items) whose copies the warp has requested
   auto wait_all = [&](uint32_t bar, uint32_t parity) {
     return __all_sync(0xffffffffu, bar_wait(bar, parity, wait_limit, abort_flag));
   };
+  // Every role walks the block's items in the same order and counts their key tiles on: `g0` is the number of
+  // tiles of the items before, and tile t of an item uses the stage (g0 + t) % 3 and the barriers' phases of g0 + t.
   if (warp >= 5) {
     // ---- the copying warps: warp 5 brings K, warp 6 V; one box per lane, and a lane's box of tile t
-    // is the same part of every tile. K of a tile is wanted two tiles before its V.
+    // is the same part of every tile.
     const int which = warp - 5;
     const int per_half = AT_BK / box_rows;            // boxes per half of the head: 8 or 2
     const int n_boxes = 2 * per_half;
     const int h = lane / per_half, i = lane % per_half;
     const uint32_t box_bytes = (uint32_t)box_rows * 128;
     const uint32_t bar_full = which ? bar_vfull : bar_kfull, bar_free = which ? bar_vfree : bar_kfree;
-    // Page of this lane's box of tile t, or -1 (the lane copies nothing). A box whose keys no query of
-    // the block may see (past the end, or before the window) is filled from the page of the newest key
-    // instead: whatever a slot holds must be finite (it meets a probability of zero), and shared memory
-    // that no copy ever wrote need not be.
-    const int spare_page = LLMRS_CHECKED_PAGE(table[(kv_hi - 1) / page_size], 6, kv_hi - 1);
-    auto page_of = [&](int t) {
-      const int key = kv_lo + t * AT_BK + box_rows * i;
-      if (lane >= n_boxes || t >= n_tiles) return -1;
-      return (key < kv_hi && key + box_rows - 1 >= key_floor) ? LLMRS_CHECKED_PAGE(table[key / page_size], 6, key) : spare_page;
-    };
-    auto load_tile = [&](int t, int page) {
-      copies = t + 1;
-      if (which == 0 && t == test_skip_tile) return;  // tests only: K of this tile never arrives
-      const int st = t % AT_STAGES;
-      const unsigned live = __ballot_sync(0xffffffffu, page >= 0);
-      const uint32_t bar = bar_full + 8 * st;
-      if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * box_bytes);
-      __syncwarp();
-      if (page >= 0) {
-        const int key = kv_lo + t * AT_BK + box_rows * i;
-        const int row = ((page * n_kv_heads + kvh) * 2 + which) * page_size + key % page_size;
-        tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * HALF_BYTES + i * box_bytes, &map_kv, bar, h * 64, row);
+    int g0 = 0;
+    bool ok = true;
+    for (int r = 0; ok; ++r) {
+      const int L = item_index(r);
+      if (L < 0) break;
+      Item it;
+      item_at(L, it);
+      // Page of this lane's box of tile t, or -1 (the lane copies nothing). A box whose keys no query of
+      // the item may see (past the end, or before the window) is filled from the page of the newest key
+      // instead: whatever a slot holds must be finite (it meets a probability of zero), and shared memory
+      // that no copy ever wrote need not be.
+      const int spare_page = LLMRS_CHECKED_PAGE(it.table[(it.kv_hi - 1) / page_size], 6, it.kv_hi - 1);
+      auto page_of = [&](int t) {
+        const int key = it.kv_lo + t * AT_BK + box_rows * i;
+        if (lane >= n_boxes || t >= it.n_tiles) return -1;
+        return (key < it.kv_hi && key + box_rows - 1 >= it.key_floor) ? LLMRS_CHECKED_PAGE(it.table[key / page_size], 6, key)
+                                                                     : spare_page;
+      };
+      int page = page_of(0);                          // looked up one tile ahead of its copy
+      for (int t = 0; t < it.n_tiles; ++t) {
+        const int g = g0 + t, st = g % AT_STAGES;
+        const int next = page_of(t + 1);
+        // The stage is free once the MMAs that read the tile three before are done.
+        if (g >= AT_STAGES && !wait_all(bar_free + 8 * st, ((g / AT_STAGES) - 1) & 1)) { ok = false; break; }
+        copies = g + 1;
+        if (!(which == 0 && g == test_skip_tile)) {   // tests only: K of this tile never arrives
+          const unsigned live = __ballot_sync(0xffffffffu, page >= 0);
+          const uint32_t bar = bar_full + 8 * st;
+          if (lane == 0) bar_expect(bar, (uint32_t)__popc(live) * box_bytes);
+          __syncwarp();
+          if (page >= 0) {
+            const int key = it.kv_lo + t * AT_BK + box_rows * i;
+            const int row = ((page * n_kv_heads + it.kvh) * 2 + which) * page_size + key % page_size;
+            tma_2d(sm(KV) + st * STAGE_BYTES + which * K_BYTES + h * HALF_BYTES + i * box_bytes, &map_kv, bar, h * 64, row);
+          }
+          __syncwarp();
+        }
+        page = next;
       }
-      __syncwarp();
-    };
-    for (int t = 0; t < n_tiles && t < AT_STAGES; ++t) load_tile(t, page_of(t));
-    int page = page_of(AT_STAGES);                    // looked up one tile ahead of its copy
-    for (int j = 0; j + AT_STAGES < n_tiles; ++j) {
-      const int next = page_of(j + AT_STAGES + 1);
-      // The slot of tile j is free once the MMAs that read it are done.
-      if (!wait_all(bar_free + 8 * (j % AT_STAGES), (j / AT_STAGES) & 1)) break;
-      load_tile(j + AT_STAGES, page);
-      page = next;
+      g0 += it.n_tiles;
     }
   } else if (warp == 4) {
     // ---- the MMA warp: all lanes walk the loop together; lane 0 issues -------------------------
@@ -306,9 +353,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     // wants them. Issued from a divergent branch (`if (lane == 0)`) an MMA of this size costs its
     // thread some 120 cycles instead of the 32 to 64 that the tensor cores need for it.
     const bool leader = elect_one();
-    auto issue_s = [&](int t) {     // S_t = Q K_t^T into S buffer t % 2; Q is read from tensor memory
-      const uint32_t kbuf = sm(KV) + (t % AT_STAGES) * STAGE_BYTES;
-      const uint32_t s_col = tmem + S_COL + (t & 1) * AT_BK;
+    auto issue_s = [&](int g) {     // S of the tile with running number g = Q K^T into S buffer g % 2; Q is read from tensor memory
+      const uint32_t kbuf = sm(KV) + (g % AT_STAGES) * STAGE_BYTES;
+      const uint32_t s_col = tmem + S_COL + (g & 1) * AT_BK;
 #pragma unroll
       for (int kk = 0; kk < AT_D / 16; ++kk) {
         const uint32_t half = kk / 4;   // head_dim 0-63 or 64-127: each half is its own swizzled tile
@@ -316,181 +363,205 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         if (leader) mma_ts(s_col, tmem + Q_COL + kk * 8, bd, idesc_s, kk > 0 ? 1u : 0u);
       }
       if (leader) {
-        commit(bar_s + 8 * (t & 1));
-        commit(bar_kfree + 8 * (t % AT_STAGES));   // the slot of K may be refilled
+        commit(bar_s + 8 * (g & 1));
+        commit(bar_kfree + 8 * (g % AT_STAGES));   // the slot of K may be refilled
       }
       __syncwarp();
     };
-    // S runs one tile ahead of the softmax: S of tiles 0 and 1 now, S of tile j+2 as soon as P of
-    // tile j (which lies over S of tile j) has been used.
-    bool ok = wait_all(bar_q, 0) && wait_all(bar_kfull, 0);
-    if (ok) {
-      fence_after();
-      issue_s(0);
-    }
-    if (ok && n_tiles > 1) {
-      ok = wait_all(bar_kfull + 8, 0);
+    int g0 = 0, n_done = 0;
+    bool ok = true;
+    for (int r = 0; ok; ++r) {
+      const int L = item_index(r);
+      if (L < 0) break;
+      Item it;
+      item_at(L, it);
+      const int n_tiles = it.n_tiles;
+      // S runs one tile ahead of the softmax: S of tiles 0 and 1 now (the item's queries are in tensor memory,
+      // which also says that the softmax threads are done with the item before), S of tile j+2 as soon as P of
+      // tile j (which lies over S of tile j) has been used.
+      ok = wait_all(bar_q, n_done & 1) && wait_all(bar_kfull + 8 * (g0 % AT_STAGES), (g0 / AT_STAGES) & 1);
       if (ok) {
         fence_after();
-        issue_s(1);
+        issue_s(g0);
       }
-    }
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int st = j % AT_STAGES;
-      // K of tile j+2 has landed long before P of tile j is there: look before the wait that matters.
-      if (j + 2 < n_tiles) {
-        ok = wait_all(bar_kfull + 8 * ((j + 2) % AT_STAGES), ((j + 2) / AT_STAGES) & 1);
+      if (ok && n_tiles > 1) {
+        ok = wait_all(bar_kfull + 8 * ((g0 + 1) % AT_STAGES), ((g0 + 1) / AT_STAGES) & 1);
+        if (ok) {
+          fence_after();
+          issue_s(g0 + 1);
+        }
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int g = g0 + j, st = g % AT_STAGES;
+        // K of tile j+2 has landed long before P of tile j is there: look before the wait that matters.
+        if (j + 2 < n_tiles) {
+          ok = wait_all(bar_kfull + 8 * ((g + 2) % AT_STAGES), ((g + 2) / AT_STAGES) & 1);
+          if (!ok) break;
+        }
+        // O += P V of tile j: its V has landed, and P is written.
+        ok = wait_all(bar_vfull + 8 * st, (g / AT_STAGES) & 1) && wait_all(bar_p + 8 * (g & 1), (g >> 1) & 1);
         if (!ok) break;
-      }
-      // O += P V of tile j: its V has landed, and P is written.
-      ok = wait_all(bar_vfull + 8 * st, (j / AT_STAGES) & 1) && wait_all(bar_p + 8 * (j & 1), (j >> 1) & 1);
-      if (!ok) break;
-      fence_after();
-      {
-        const uint32_t vbuf = sm(KV) + st * STAGE_BYTES + K_BYTES;
-        const uint32_t p_col = tmem + S_COL + (j & 1) * AT_BK;
+        fence_after();
+        {
+          const uint32_t vbuf = sm(KV) + st * STAGE_BYTES + K_BYTES;
+          const uint32_t p_col = tmem + S_COL + (g & 1) * AT_BK;
 #pragma unroll
-        for (int kk = 0; kk < AT_BK / 16; ++kk) {
-          const uint64_t bd = smem_desc(vbuf + kk * 2048, HALF_BYTES, 1024);
-          if (leader) mma_ts(tmem + O_COL, p_col + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < AT_BK / 16; ++kk) {
+            const uint64_t bd = smem_desc(vbuf + kk * 2048, HALF_BYTES, 1024);
+            if (leader) mma_ts(tmem + O_COL, p_col + kk * 8, bd, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          if (leader) {
+            commit(bar_vfree + 8 * st);  // the slot of V may be refilled
+            commit(bar_o + 8 * (g & 1)); // O holds the item's tiles 0..j
+          }
         }
-        if (leader) {
-          commit(bar_vfree + 8 * st);  // the slot of V may be refilled
-          commit(bar_o + 8 * (j & 1)); // O holds tiles 0..j
-        }
+        __syncwarp();
+        // S of tile j+2 goes over P of tile j: the tensor cores run MMAs in the order of issue.
+        if (j + 2 < n_tiles) issue_s(g + 2);
       }
-      __syncwarp();
-      // S of tile j+2 goes over P of tile j: the tensor cores run MMAs in the order of issue.
-      if (j + 2 < n_tiles) issue_s(j + 2);
+      g0 += n_tiles;
+      ++n_done;
     }
   } else {
     // ---- softmax threads ------------------------------------------------------------------
     const int row = tid;                      // this thread's query row = its lane of tensor memory
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    // The query row goes into tensor memory (two bfloat16 per column), where Q K^T reads it as its
-    // A operand: shared memory then only has to feed K.
-    {
-      const uint4* qrow = reinterpret_cast<const uint4*>(q + (size_t)(tok0 + row) * q_stride + (size_t)head * AT_D);
-#pragma unroll
-      for (int hlf = 0; hlf < 2; ++hlf) {
-        uint32_t r[32];
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const uint4 v = row < rows ? qrow[hlf * 8 + c] : make_uint4(0u, 0u, 0u, 0u);
-          r[4 * c] = v.x; r[4 * c + 1] = v.y; r[4 * c + 2] = v.z; r[4 * c + 3] = v.w;
-        }
-        tmem_st32u(lane_addr + Q_COL + hlf * 32, r);
-      }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      fence_before();
-      bar_arrive(bar_q);
-    }
-    const int my_pos = pos0 + row;
     const float sl2 = scale * AT_LOG2E;
-    float m_ref = -INFINITY, l_sum = 0.f;
+    int g0 = 0;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      const int kb = kv_lo + j * AT_BK;
-      const uint32_t s_addr = lane_addr + S_COL + (j & 1) * AT_BK;
-      ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * (j & 1), (j >> 1) & 1, wait_limit, abort_flag));
-      if (!ok) break;
-      fence_after();
-      // This thread's 128 scores -> probabilities.
-      float s[AT_BK];
+    for (int r = 0; ok; ++r) {
+      const int L = item_index(r);
+      if (L < 0) break;
+      Item it;
+      item_at(L, it);
+      const int n_tiles = it.n_tiles, pos0 = it.pos0, rows = it.rows;
+      // The query row goes into tensor memory (two bfloat16 per column), where Q K^T reads it as its
+      // A operand: shared memory then only has to feed K. (Every MMA of the item before is done: this thread
+      // has waited for its last O.)
+      {
+        const uint4* qrow = reinterpret_cast<const uint4*>(q + (size_t)(it.tok0 + row) * q_stride + (size_t)it.head * AT_D);
 #pragma unroll
-      for (int c = 0; c < AT_BK; c += 32) {
-        float t0[32];
-        tmem_ld32(s_addr + c, t0);
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          uint32_t rr[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) s[c + e] = t0[e];
-      }
-      const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window);
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < AT_BK; ++c) {
-          const int key = kb + c;
-          const bool seen = key <= my_pos && (window <= 0 || key > my_pos - window);
-          s[c] = seen ? s[c] : -INFINITY;
+          for (int c = 0; c < 8; ++c) {
+            const uint4 v = row < rows ? qrow[hlf * 8 + c] : make_uint4(0u, 0u, 0u, 0u);
+            rr[4 * c] = v.x; rr[4 * c + 1] = v.y; rr[4 * c + 2] = v.z; rr[4 * c + 3] = v.w;
+          }
+          tmem_st32u(lane_addr + Q_COL + hlf * 32, rr);
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        fence_before();
+        bar_arrive(bar_q);
       }
-      // Four running maxima (and sums below): a chain of 128 dependent operations would be the
-      // longest thing this thread does.
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < AT_BK; c += 4) {
-        mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
-        mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // The reference maximum moves only when the row's maximum outgrew it by a factor 256.
-      const float m_tile = mx * sl2;
-      float factor = 1.f;
-      bool moved = false;
-      if (m_tile > m_ref + 8.f) {   // also the first tile with a visible key (m_ref = -inf)
-        factor = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_tile);
-        m_ref = m_tile;
-        moved = j > 0;
-        l_sum *= factor;
-      }
-      const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      // P goes over S (all of this thread's S is in registers by now), 64 keys at a time.
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c0 = 0; c0 < AT_BK / 2; c0 += 32) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float p0 = ex2(fmaf(s[2 * (c0 + c)], sl2, -m_use));
-          const float p1 = ex2(fmaf(s[2 * (c0 + c) + 1], sl2, -m_use));
-          sum4[c & 3] += p0 + p1;
-          const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-          pk[c] = *reinterpret_cast<const uint32_t*>(&h2);
-        }
-        tmem_st32u(s_addr + c0, pk);
-      }
-      l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      // Where a row's reference moved, O is rescaled (rare after the first tiles; the loads and
-      // stores of tensor memory are warp-wide, so the warp decides together), once O += P V of the
-      // tile before is done (S of tile j implies O += P V of tile j-2 only).
-      if (__any_sync(0xffffffffu, moved)) {
-        ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, wait_limit, abort_flag));
+      const int my_pos = pos0 + row;
+      float m_ref = -INFINITY, l_sum = 0.f;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int g = g0 + j;
+        const int kb = it.kv_lo + j * AT_BK;
+        const uint32_t s_addr = lane_addr + S_COL + (g & 1) * AT_BK;
+        ok = __all_sync(0xffffffffu, bar_wait(bar_s + 8 * (g & 1), (g >> 1) & 1, wait_limit, abort_flag));
         if (!ok) break;
         fence_after();
+        // This thread's 128 scores -> probabilities.
+        float s[AT_BK];
+#pragma unroll
+        for (int c = 0; c < AT_BK; c += 32) {
+          float t0[32];
+          tmem_ld32(s_addr + c, t0);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) s[c + e] = t0[e];
+        }
+        const bool need_mask = kb + AT_BK - 1 > pos0 || (window > 0 && kb <= pos0 + AT_BQ - 1 - window);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < AT_BK; ++c) {
+            const int key = kb + c;
+            const bool seen = key <= my_pos && (window <= 0 || key > my_pos - window);
+            s[c] = seen ? s[c] : -INFINITY;
+          }
+        }
+        // Four running maxima (and sums below): a chain of 128 dependent operations would be the
+        // longest thing this thread does.
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < AT_BK; c += 4) {
+          mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+          mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // The reference maximum moves only when the row's maximum outgrew it by a factor 256.
+        const float m_tile = mx * sl2;
+        float factor = 1.f;
+        bool moved = false;
+        if (m_tile > m_ref + 8.f) {   // also the first tile with a visible key (m_ref = -inf)
+          factor = m_ref == -INFINITY ? 0.f : ex2(m_ref - m_tile);
+          m_ref = m_tile;
+          moved = j > 0;
+          l_sum *= factor;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        // P goes over S (all of this thread's S is in registers by now), 64 keys at a time.
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c0 = 0; c0 < AT_BK / 2; c0 += 32) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const float p0 = ex2(fmaf(s[2 * (c0 + c)], sl2, -m_use));
+            const float p1 = ex2(fmaf(s[2 * (c0 + c) + 1], sl2, -m_use));
+            sum4[c & 3] += p0 + p1;
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+            pk[c] = *reinterpret_cast<const uint32_t*>(&h2);
+          }
+          tmem_st32u(s_addr + c0, pk);
+        }
+        l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        // Where a row's reference moved, O is rescaled (rare after the first tiles; the loads and
+        // stores of tensor memory are warp-wide, so the warp decides together), once O += P V of the
+        // tile before is done (S of tile j implies O += P V of tile j-2 only).
+        if (__any_sync(0xffffffffu, moved)) {
+          ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((g - 1) & 1), ((g - 1) >> 1) & 1, wait_limit, abort_flag));
+          if (!ok) break;
+          fence_after();
+#pragma unroll 1
+          for (int c = 0; c < AT_D; c += 32) {
+            float o[32];
+            tmem_ld32(lane_addr + O_COL + c, o);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] *= factor;
+            tmem_st32(lane_addr + O_COL + c, o);
+          }
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        fence_before();
+        bar_arrive(bar_p + 8 * (g & 1));
+      }
+      const int g_last = g0 + n_tiles - 1;
+      if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * (g_last & 1), (g_last >> 1) & 1, wait_limit, abort_flag));
+      fence_after();
+      if (ok) {
+        // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
+        const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+        bf16* orow = out + (size_t)(it.tok0 + row) * out_stride + (size_t)it.head * AT_D;
 #pragma unroll 1
         for (int c = 0; c < AT_D; c += 32) {
           float o[32];
           tmem_ld32(lane_addr + O_COL + c, o);
+          if (row < rows) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] *= factor;
-          tmem_st32(lane_addr + O_COL + c, o);
-        }
-      }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      fence_before();
-      bar_arrive(bar_p + 8 * (j & 1));
-    }
-    if (ok) ok = __all_sync(0xffffffffu, bar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, wait_limit, abort_flag));
-    fence_after();
-    if (ok) {
-      // Every thread reads its row of O (the load is warp-wide); rows past the portion's end are not stored.
-      const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-      bf16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * AT_D;
-#pragma unroll 1
-      for (int c = 0; c < AT_D; c += 32) {
-        float o[32];
-        tmem_ld32(lane_addr + O_COL + c, o);
-        if (row < rows) {
+            for (int e = 0; e < 32; e += 8) {
+              uint4 pk;
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 pk;
-            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) h2[q] = __floats2bfloat162_rn(o[e + 2 * q] * inv, o[e + 2 * q + 1] * inv);
-            *reinterpret_cast<uint4*>(orow + c + e) = pk;
+              for (int q8 = 0; q8 < 4; ++q8) h2[q8] = __floats2bfloat162_rn(o[e + 2 * q8] * inv, o[e + 2 * q8 + 1] * inv);
+              *reinterpret_cast<uint4*>(orow + c + e) = pk;
+            }
           }
+          __syncwarp();
         }
-        __syncwarp();
       }
+      g0 += n_tiles;
     }
   }
   fence_before();
@@ -588,17 +659,33 @@ int llmrs_attn_prefill_tc(const void* q, long long q_stride, int n_tokens, void*
   // One copy per page and half of the head; a page of a multiple of 64 keys is copied 64 keys at a time.
   const int box_rows = page_size % 64 == 0 ? 64 : 16;
   if ((rc = make_map(&map_kv, cache, cache_rows, AT_D, AT_D, box_rows))) return rc;
-  const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 8) * 8 + 8;
+  const size_t smem = AT_STAGES * STAGE_BYTES + (4 * AT_STAGES + 8) * 8 + 16 + 2 * AT_MAX_LIST;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llmrs_fail("attn_prefill_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid(n_q_heads, n_tiles);
+  // A block holds all of tensor memory, so an SM runs one at a time. With up to 16 items per SM one block per SM
+  // walks its share of them, and an item's start runs under the end of the item before (one prompt of 1,024 /
+  // 2,048 / 4,096 / 8,192 tokens: 27 / 62 / 173 / 589 us against 30 / 69 / 183 / 595 with a block per item). With
+  // more, a block per item, which the hardware hands out longest first: fixed shares then lose more than the
+  // starts cost (32,768 tokens: 8.8 against 8.55 ms).
+  static int n_sm = 0;
+  if (n_sm == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    if (n_sm <= 0) n_sm = 1;
+  }
+  // (About every second entry of the list starts a 128-row tile; a block that finds no item leaves at once.)
+  const long long n_lin = (long long)n_q_heads * n_tiles, n_items = (long long)n_q_heads * ((n_tiles + 1) / 2);
+  const int persistent = n_items > n_sm && n_items <= 16LL * n_sm ? 1 : 0;
+  dim3 grid((unsigned)(persistent ? n_sm : n_lin));
   attn_prefill_tc_kernel<<<grid, AT_THREADS + 96, smem, stream>>>(map_kv, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                                                               tiles, q_start, n_new, cached_len, block_table,
-                                                              table_stride, n_q_heads, n_kv_heads, page_size, box_rows,
-                                                              window, scale, error_flag, g_wait_limit, g_test_skip_tile);
+                                                              table_stride, n_tiles, persistent, n_q_heads, n_kv_heads, page_size,
+                                                              box_rows, window, scale, error_flag, g_wait_limit,
+                                                              g_test_skip_tile);
   return llmrs_launch_status("attn_prefill_tc");
 }
