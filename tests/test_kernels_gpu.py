@@ -601,11 +601,15 @@ def test_silu_mul_interleaved_layout(dtype):
     ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 16, 0), ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 32, 37),
     ([1000], [1000], 4, 1, 16, 0), ([0, 500], [1100, 700], 8, 8, 16, 200), ([5], [257], 6, 3, 48, 129),
     ([70, 0, 129, 300], [150, 65, 2, 130], 8, 2, 64, 0), ([0, 500], [1100, 700], 8, 8, 64, 200),
-    ([5], [257], 6, 3, 128, 129), ([1000], [1000], 4, 1, 64, 0), ([0], [1], 2, 1, 64, 0)])
+    ([5], [257], 6, 3, 128, 129), ([1000], [1000], 4, 1, 64, 0), ([0], [1], 2, 1, 64, 0),
+    ([100, 0, 900, 5], [1500, 700, 129, 3], 16, 4, 16, 0), ([100, 0, 900, 5], [1500, 700, 129, 3], 16, 2, 64, 300),
+    ([0], [2048], 12, 4, 16, 0)])
 def test_attention_prefill_tcgen05(lens, new, nq, nkv, page, window):
     """Blocks of 128 queries on tcgen05 against the plain attention: partial blocks, several requests,
     earlier context, windows that start inside a tile, pages larger than a 16-key box, and pages of a
-    multiple of 64 keys (which are copied 64 keys at a time)."""
+    multiple of 64 keys (which are copied 64 keys at a time). The last three cases have more 128-row items than
+    the device has SMs: one block per SM then walks several items, of different requests and lengths, and
+    carries barriers' phases, stages and tensor memory from one to the next."""
     ops = _ops()
     d = 128
     torch.manual_seed(len(lens) * 31 + window)
@@ -835,12 +839,14 @@ def test_gemm_tcgen05_wait_runs_out_and_the_kernel_returns(tokens, features, K, 
     ops.check_tc_error(DEV)
 
 
-@pytest.mark.parametrize("skip", [0, 2, 4])
-def test_attention_tcgen05_wait_runs_out_and_the_kernel_returns(skip):
+@pytest.mark.parametrize("skip,nq", [(0, 4), (2, 4), (4, 4), (3, 32), (9, 32)])
+def test_attention_tcgen05_wait_runs_out_and_the_kernel_returns(skip, nq):
     """The same for the tcgen05 prefill attention: the keys of one tile never arrive; the blocks that wait for
-    them give up after 1,024 polls, store nothing, and the error word is set. The next launch is right."""
+    them give up after 1,024 polls, store nothing, and the error word is set. The next launch is right. With 32
+    heads there are more items than SMs and a block walks several: the tile that never arrives is then counted
+    over a block's items, so some blocks give up in their first item and some in a later one."""
     ops = _ops()
-    d, nq, nkv, page, lens, new = 128, 4, 2, 16, [0, 200], [700, 520]
+    d, nkv, page, lens, new = 128, 2, 16, [0, 200], [700, 520]
     torch.manual_seed(skip)
     table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=skip)
     q = torch.randn(sum(new), nq * d).to(torch.bfloat16)
