@@ -50,19 +50,21 @@ def _cost_library(x, w, *a, **k):
 
 def _cost_attn_decode(q, out, cache, dec_reqs, n_dec, q_start, cached_len, block_table, scratch, max_splits, split_keys,
                       n_q_heads, n_kv_heads, head_dim, page_size, window, scale, **k):
-    lens = (cached_len[dec_reqs[:n_dec].long()] + 1).clamp(max=window if window > 0 else 1 << 30)
-    keys = int(lens.sum())
-    return (f"{n_dec} requests", keys * 2 * n_kv_heads * head_dim * cache.element_size() + _nbytes(q, out),
-            4.0 * keys * n_q_heads * head_dim)
+    # The keys are counted on the device and read when the report is made: a read here would make the host wait for
+    # the device, and the next launch's preparation on the host would then show up as that kernel's time.
+    keys = (cached_len[dec_reqs[:n_dec].long()] + 1).clamp(max=window if window > 0 else 1 << 30).sum()
+    per_key, fixed = 2 * n_kv_heads * head_dim * cache.element_size(), _nbytes(q, out)
+    return (f"{n_dec} requests", lambda: int(keys) * per_key + fixed, lambda: 4.0 * int(keys) * n_q_heads * head_dim)
 
 
 def _cost_attn_prefill(q, out, cache, tiles, n_tiles, q_start, n_new, cached_len, block_table, n_q_heads, n_kv_heads,
                        head_dim, page_size, window, scale, **k):
     n, c = n_new.double(), cached_len.double()
-    pairs = float((n * c + n * (n + 1) / 2).sum())      # (query, key) pairs a causal portion sees
-    keys = float((n + c).sum())
-    return (f"{int(n.sum())} tokens", int(keys * 2 * n_kv_heads * head_dim * cache.element_size()) + _nbytes(q, out),
-            4.0 * pairs * n_q_heads * head_dim)
+    pairs = (n * c + n * (n + 1) / 2).sum()             # (query, key) pairs a causal portion sees
+    keys, tokens = (n + c).sum(), int(q.size(0))
+    per_key, fixed = 2 * n_kv_heads * head_dim * cache.element_size(), _nbytes(q, out)
+    return (f"{tokens} tokens", lambda: int(float(keys) * per_key) + fixed,
+            lambda: 4.0 * float(pairs) * n_q_heads * head_dim)
 
 
 def _cost_rows(*tensors_from):
@@ -103,7 +105,7 @@ class Profiler:
     def __init__(self, hbm_gbs: float, tflops: float, nvtx: bool = True):
         self.hbm_gbs, self.tflops, self.nvtx = float(hbm_gbs), float(tflops), nvtx
         self._saved: Dict[str, Callable] = {}
-        self._calls: List[Tuple[str, int, float, torch.cuda.Event, torch.cuda.Event]] = []
+        self._calls: List[tuple] = []      # (class, bytes, flops, start event, end event); bytes and flops may be callables
 
     def __enter__(self):
         for name, cost in WRAPPED.items():
@@ -134,7 +136,7 @@ class Profiler:
                 end.record()
                 if self.nvtx:
                     torch.cuda.nvtx.range_pop()
-                self._calls.append((cls, int(nbytes), float(flops), start, end))
+                self._calls.append((cls, nbytes, flops, start, end))
         return timed
 
     def classes(self) -> List[dict]:
@@ -146,8 +148,8 @@ class Profiler:
             a = agg.setdefault(cls, [0, 0.0, 0.0, 0.0])
             a[0] += 1
             a[1] += start.elapsed_time(end) * 1e3
-            a[2] += nbytes
-            a[3] += flops
+            a[2] += int(nbytes() if callable(nbytes) else nbytes)      # (counted on the device: see _cost_attn_decode)
+            a[3] += float(flops() if callable(flops) else flops)
         total = sum(a[1] for a in agg.values()) or 1.0
         rows = []
         for cls, (n, us, nbytes, flops) in agg.items():
@@ -163,7 +165,8 @@ class Profiler:
         rows = self.classes()
         lines = [f"{'share':>6} {'us total':>10} {'calls':>6} {'us each':>9} {'MB each':>9} {'GFLOP each':>11} "
                  f"{'GB/s':>8} {'TFLOP/s':>8} {'of peak':>8}  kernel class",
-                 f"(peaks: {self.hbm_gbs:.0f} GB/s, {self.tflops:.0f} TFLOP/s; serialised launches, CUDA events)"]
+                 f"(peaks: {self.hbm_gbs:.0f} GB/s, {self.tflops:.0f} TFLOP/s; serialised launches, CUDA events: where the "
+                 f"device waited for the host to prepare a launch, that wait counts, so kernels of tens of us read high)"]
         for r in rows:
             lines.append(f"{100 * r['share']:5.1f}% {r['us_total']:10.1f} {r['calls']:6d} {r['us_each']:9.2f} "
                          f"{r['bytes_each'] / 1e6:9.2f} {r['flops_each'] / 1e9:11.3f} {r['gb_s']:8.1f} {r['tflop_s']:8.2f} "
