@@ -35,7 +35,16 @@ def _lib():
     return _build.library()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current CUDA stream's handle. (``torch.cuda.current_stream()`` builds a Python object every time: some
+    7 us a call, 1.2 ms of the 6 ms the host needs to issue the 290 launches of a prefill step; the raw handle is
+    asked for directly where this torch offers it.)"""
+    if _raw_stream is not None and _raw_device is not None:
+        return ctypes.c_void_p(_raw_stream(_raw_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -442,6 +451,17 @@ def debug_take():
     return tuple(out) if out[3] else None
 
 
+_SM_COUNT = {}
+
+
+def sm_count(device) -> int:
+    """SMs of the device (looked up once: the properties call costs microseconds, and products ask every time)."""
+    n = _SM_COUNT.get(device)
+    if n is None:
+        n = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
 def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
     """Blocks of a cluster that share the k range of a skinny product: enough blocks to
     fill the GPU about twice, at least four 64-wide k blocks each."""
@@ -489,7 +509,7 @@ def gemm_bf16_pairs(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor
         _need(out, "out", odt)
     if tmem_seen is not None:
         _need(tmem_seen, "tmem_seen", torch.int32)
-        if tmem_seen.numel() < 2 * torch.cuda.get_device_properties(x.device).multi_processor_count:
+        if tmem_seen.numel() < 2 * sm_count(x.device):
             raise KernelError("tmem_seen needs an entry per block (two per SM)")
     _check(_lib().llmrs_gemm_bf16_pairs(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
                                         ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
@@ -545,7 +565,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
             out = torch.empty((tokens, width), dtype=odt, device=x.device)
         _need(out, "out", odt)
     if splits is None:
-        splits = tc_splits(tokens, features, K, torch.cuda.get_device_properties(x.device).multi_processor_count)
+        splits = tc_splits(tokens, features, K, sm_count(x.device))
     if emit is None and scale is None:
         _check(_lib().llmrs_gemm_bf16(_ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), _ptr(out),
                                       ctypes.c_longlong(out.stride(0)), tokens, features, K, epi, dtype_code(odt),
@@ -603,7 +623,7 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache: 
     for name, t in (("positions", positions), ("token_req", token_req), ("block_table", block_table)):
         _need(t, name, torch.int32)
     if splits is None:
-        splits = tc_splits(tokens, features, K, torch.cuda.get_device_properties(x.device).multi_processor_count)
+        splits = tc_splits(tokens, features, K, sm_count(x.device))
     _check(_lib().llmrs_gemm_qkv_rope(
         _ptr(x), ctypes.c_longlong(_row_stride(x, "x")), _ptr(w), tokens, K, splits, _ptr(q_out),
         ctypes.c_longlong(q_out.stride(0)), _ptr(cache), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos_sin),
