@@ -71,9 +71,9 @@ struct TcParams {
   uint32_t wait_limit;  // polls of a barrier before a wait gives up
   int test_skip_kb;     // tests only: the producer leaves out the copy of its k block with this index (-1: none)
   QkvRope qr;           // TC_QKV_ROPE only
-  // A norm that is spread over two products (few tokens). The product BEFORE the norm (TC_RESIDUAL) also
-  // writes emit_xw = (h + product) * emit_w in bfloat16, the norm's input times its weight, and each of
-  // its clusters leaves the sum of squares of the 128 features of h it wrote in emit_part[tile][token]. The
+  // A norm that is spread over two products. The product BEFORE the norm (TC_RESIDUAL) also writes
+  // emit_xw = (h + product) * emit_w in bfloat16, the norm's input times its weight, and leaves the sum of
+  // squares of the features of h that a tile holds (128, or 256 with many tokens) in emit_part[tile][token]. The
   // product AFTER the norm takes emit_xw as its x and multiplies its rows by 1/sqrt(sum / scale_dim +
   // scale_eps), sum being the scale_parts entries of scale_part for the row's token, added in order.
   const float* emit_w;

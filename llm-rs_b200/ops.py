@@ -477,8 +477,8 @@ def tc_splits(tokens: int, features: int, K: int, sms: int = 148) -> int:
 
 def norm_parts(features: int, splits: int = 1, tokens: int = 1) -> int:
     """Rows of the sums of squares that a residual epilogue with ``emit`` writes: one per tile of features, 128
-    wide for at most 64 tokens (the cluster that shares the tile's k range adds its blocks' shares up in its first
-    block), 256 wide for more."""
+    wide for at most 64 tokens (the block of the cluster that owns a token writes the token's sum), 256 wide for
+    more."""
     return -(-features // (128 if tokens <= 64 else 256))
 
 
