@@ -59,8 +59,9 @@ constexpr int DM_WARPS = 4, DM_THREADS = DM_WARPS * 32, DM_STAGES = 3, DM_TILE =
 // Shared memory of the decode kernel: the warps' rings of tiles (re-used for their merge), and behind them,
 // when the splits merge as a cluster, what the other blocks send: per sender the maximum and the sum of each
 // of the ng heads, and this block's share of the ng * d outputs (dealt out in runs of 32 over the blocks).
-__host__ __device__ constexpr size_t dm_ring_bytes(int d) {
-  const size_t pipe = (size_t)DM_WARPS * DM_STAGES * 2 * DM_TILE * (d + 8) * 2;
+constexpr int DM_STAGES_LIGHT = 2;   // the ring of the kernel of which three blocks fit an SM (see the kernel)
+__host__ __device__ constexpr size_t dm_ring_bytes(int d, int stages = DM_STAGES) {
+  const size_t pipe = (size_t)DM_WARPS * stages * 2 * DM_TILE * (d + 8) * 2;
   const size_t merge = (size_t)(DM_WARPS * 16 * d + 2 * DM_WARPS * 16 + 16 * (d + 2)) * 4;
   return ((pipe > merge ? pipe : merge) + 15) / 16 * 16;
 }
@@ -76,7 +77,11 @@ __host__ __device__ inline size_t dm_inbox_bytes(int ng, int d, int splits) {
 // other orientation (heads on the 16 rows, most of them padding) takes two; P goes from the accumulators' layout
 // to the operand's by a transposing register move (movmatrix). The legacy tensor path is slow enough on this part
 // that the MMAs of a tile are a large part of a warp's time per tile.
-template <int DCH, bool SWAP>
+// STAGES: tiles of a warp's ring. Three: two tiles on their way while one is used, two blocks an SM. Two (head_dim
+// 128, keys on the MMA's rows only): one tile on its way, three blocks an SM: slower when either fits the step's
+// blocks in one wave (4.13 against 3.58 ms a step at 32 requests with contexts of 512), faster when only it does
+// (40 requests: 4.07 against 4.97 ms), so the caller asks for it per launch (llmrs_attn_decode_next_ring).
+template <int DCH, bool SWAP, int STAGES = DM_STAGES>
 __global__ void __launch_bounds__(DM_THREADS)
 attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, const bf16* __restrict__ cache,
                              const int* __restrict__ dec_reqs, const int* __restrict__ q_start,
@@ -121,7 +126,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   const int n_tiles = tile_last - tile_first + 1;
   const int n_my = n_tiles > warp ? (n_tiles - warp + DM_WARPS - 1) / DM_WARPS : 0;
 
-  bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * DM_STAGES * 2 * TILE_ELEMS;
+  bf16* wbase = reinterpret_cast<bf16*>(smem_raw) + (size_t)warp * STAGES * 2 * TILE_ELEMS;
 
   // When a page holds whole 16-key tiles, a tile is one contiguous run of rows in one
   // page: lane j keeps the page of the warp's j-th tile (of the current 32), so the
@@ -196,13 +201,13 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   // those kernels' tails), except a tile that holds the newest key, which this step writes.
   const int new_tile = (kv_len - 1) / DM_TILE;
 #pragma unroll
-  for (int s = 0; s < DM_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < n_my && tile_first + warp + s * DM_WARPS < new_tile) load_tile(s, s);
     cp_async_commit();
   }
   pdl_wait();
 #pragma unroll
-  for (int s = 0; s < DM_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < n_my && tile_first + warp + s * DM_WARPS >= new_tile) load_tile(s, s);
     cp_async_commit();
   }
@@ -219,12 +224,12 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       }
     }
     for (int i = 0; i < n_my; ++i) {
-      cp_async_wait<DM_STAGES - 2>();
+      cp_async_wait<STAGES - 2>();
       __syncwarp();
-      if (i + DM_STAGES - 1 < n_my) load_tile(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
+      if (i + STAGES - 1 < n_my) load_tile(i + STAGES - 1, (i + STAGES - 1) % STAGES);
       cp_async_commit();
 
-      const bf16* Ks = wbase + (size_t)(i % DM_STAGES) * 2 * TILE_ELEMS;
+      const bf16* Ks = wbase + (size_t)(i % STAGES) * 2 * TILE_ELEMS;
       const bf16* Vs = Ks + TILE_ELEMS;
       const int key0 = (tile_first + warp + i * DM_WARPS) * DM_TILE;
       const int j = lane >> 3;
@@ -302,16 +307,16 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
       qf[kc][3] = gq + 8 < ng ? *reinterpret_cast<const uint32_t*>(qt + (size_t)(gq + 8) * D + col + 8) : 0u;
     }
   }
-  // The ring was filled with 2 * (DM_STAGES - 1) groups: tile s (s < DM_STAGES - 1) lies in group
-  // s or DM_STAGES - 1 + s, tile i >= DM_STAGES - 1 in group DM_STAGES - 1 + i. Leaving the newest
-  // DM_STAGES - 2 groups pending at iteration i still covers tile i.
+  // The ring was filled with 2 * (STAGES - 1) groups: tile s (s < STAGES - 1) lies in group
+  // s or STAGES - 1 + s, tile i >= STAGES - 1 in group STAGES - 1 + i. Leaving the newest
+  // STAGES - 2 groups pending at iteration i still covers tile i.
   for (int i = 0; i < n_my; ++i) {
-    cp_async_wait<DM_STAGES - 2>();
+    cp_async_wait<STAGES - 2>();
     __syncwarp();
-    if (i + DM_STAGES - 1 < n_my) load_tile(i + DM_STAGES - 1, (i + DM_STAGES - 1) % DM_STAGES);
+    if (i + STAGES - 1 < n_my) load_tile(i + STAGES - 1, (i + STAGES - 1) % STAGES);
     cp_async_commit();
 
-    const bf16* Ks = wbase + (size_t)(i % DM_STAGES) * 2 * TILE_ELEMS;
+    const bf16* Ks = wbase + (size_t)(i % STAGES) * 2 * TILE_ELEMS;
     const bf16* Vs = Ks + TILE_ELEMS;
     const int key0 = (tile_first + warp + i * DM_WARPS) * DM_TILE;
 
@@ -423,7 +428,7 @@ attn_decode_split_mma_kernel(const bf16* __restrict__ q, long long q_stride, con
   __syncthreads();
   const int S = (int)gridDim.z;
   const int share = dm_share(ng, D, S);
-  float* inbox_ml = reinterpret_cast<float*>(smem_raw + dm_ring_bytes(D));   // [S][ng][2]
+  float* inbox_ml = reinterpret_cast<float*>(smem_raw + dm_ring_bytes(D, STAGES));   // [S][ng][2]
   float* inbox_o = inbox_ml + (size_t)S * ng * 2;                            // [S][share]
   if (cluster_merge) dm_cluster_wait();   // every block of the cluster runs
   for (int i = threadIdx.x; i < ng * D; i += DM_THREADS) {
@@ -541,6 +546,28 @@ static int decode_mma_allow(size_t smem) {
   return 0;
 }
 
+// The same for the kernel with the ring of two tiles (head_dim 128, keys on the MMA's rows).
+static int decode_mma_allow_light(size_t smem) {
+  static size_t allowed = 0;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (smem > allowed) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<8, true, DM_STAGES_LIGHT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
+    e = cudaFuncSetAttribute(attn_decode_split_mma_kernel<8, true, DM_STAGES_LIGHT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: clusters of 16: %s", cudaGetErrorString(e));
+    allowed = smem;
+  }
+  return 0;
+}
+static bool decode_mma_light_applies(int dch, int n_q_heads, int n_kv_heads) { return dch == 8 && n_q_heads / n_kv_heads <= 8; }
+
+// The ring of the NEXT launch of the tensor-core decode kernel: 2 asks for the kernel with the ring of two tiles where
+// it exists (head_dim 128, at most 8 query heads per key head), anything else for the usual one. One launch takes it.
+static int g_next_ring = 0;
+LLMRS_API void llmrs_attn_decode_next_ring(int stages) { g_next_ring = stages; }
+
 template <int DCH>
 static int launch_decode_mma(const void* q, long long q_stride, const void* cache, const int* dec_reqs, int n_dec,
                              const int* q_start, const int* cached_len, const int* block_table, int table_stride,
@@ -549,8 +576,10 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
                              int cluster_merge, const L2Prefetch& next, cudaStream_t stream) {
   constexpr int D = 16 * DCH;
   const int ng_max = n_q_heads / n_kv_heads < 16 ? n_q_heads / n_kv_heads : 16;
-  const size_t smem = dm_ring_bytes(D) + (cluster_merge ? dm_inbox_bytes(ng_max, D, max_splits) : 0);
-  if (int rc = decode_mma_allow<DCH>(smem)) return rc;
+  const bool light = g_next_ring == DM_STAGES_LIGHT && decode_mma_light_applies(DCH, n_q_heads, n_kv_heads);
+  g_next_ring = 0;
+  const size_t smem = dm_ring_bytes(D, light ? DM_STAGES_LIGHT : DM_STAGES) + (cluster_merge ? dm_inbox_bytes(ng_max, D, max_splits) : 0);
+  if (int rc = light ? decode_mma_allow_light(smem) : decode_mma_allow<DCH>(smem)) return rc;
   const int G = n_q_heads / n_kv_heads;
   dim3 grid(n_dec, n_kv_heads * ((G + 15) / 16), max_splits);
   cudaLaunchConfig_t cfg = {};
@@ -576,6 +605,9 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
   cfg.numAttrs = n_attr;
   // At most eight query heads per key head: the keys take the MMA's rows (see the kernel).
   auto kernel = G <= 8 ? attn_decode_split_mma_kernel<DCH, true> : attn_decode_split_mma_kernel<DCH, false>;
+  if constexpr (DCH == 8) {
+    if (light) kernel = attn_decode_split_mma_kernel<8, true, DM_STAGES_LIGHT>;
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, (const bf16*)q, q_stride, (const bf16*)cache,
                                      dec_reqs, q_start, cached_len, block_table, table_stride, scratch, max_splits,
                                      split_keys, n_q_heads, n_kv_heads, page_size, window, scale, (bf16*)out,
@@ -585,10 +617,10 @@ static int launch_decode_mma(const void* q, long long q_stride, const void* cach
 }
 
 template <int DCH>
-static int decode_mma_capacity(int cluster, int ng, int* blocks) {
+static int decode_mma_capacity(int cluster, int ng, int* blocks, bool light = false) {
   constexpr int D = 16 * DCH;
-  const size_t smem = dm_ring_bytes(D) + (cluster > 1 ? dm_inbox_bytes(ng, D, cluster) : 0);
-  if (int rc = decode_mma_allow<DCH>(smem)) return rc;
+  const size_t smem = dm_ring_bytes(D, light ? DM_STAGES_LIGHT : DM_STAGES) + (cluster > 1 ? dm_inbox_bytes(ng, D, cluster) : 0);
+  if (int rc = light ? decode_mma_allow_light(smem) : decode_mma_allow<DCH>(smem)) return rc;
   cudaError_t e;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(64, 8, cluster);
@@ -602,6 +634,14 @@ static int decode_mma_capacity(int cluster, int ng, int* blocks) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
+  if constexpr (DCH == 8) {
+    if (light) {
+      e = cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<8, true, DM_STAGES_LIGHT>, &cfg);
+      if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: occupancy of clusters of %d: %s", cluster, cudaGetErrorString(e));
+      *blocks = n * cluster;
+      return 0;
+    }
+  }
   e = ng <= 8 ? cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH, true>, &cfg)
               : cudaOccupancyMaxActiveClusters(&n, attn_decode_split_mma_kernel<DCH, false>, &cfg);
   if (e != cudaSuccess) return llmrs_fail("attn_decode_mma: occupancy of clusters of %d: %s", cluster, cudaGetErrorString(e));
@@ -625,6 +665,16 @@ LLMRS_API int llmrs_attn_decode_capacity(int d, int cluster, int ng, int* blocks
     case 7: return decode_mma_capacity<7>(cluster, ng, blocks);
     default: return decode_mma_capacity<8>(cluster, ng, blocks);
   }
+}
+
+// The same for the kernel with the ring of two tiles; *blocks = 0 where that kernel does not exist (head_dim other than
+// 128, more than 8 query heads per key head).
+LLMRS_API int llmrs_attn_decode_capacity_light(int d, int cluster, int ng, int* blocks) {
+  if (cluster < 1 || cluster > 16 || ng < 1 || ng > 16 || d % 16 || d < 16 || d > 128)
+    return llmrs_fail("attn_decode_capacity: head_dim %d, clusters of %d, %d heads", d, cluster, ng);
+  *blocks = 0;
+  if (!decode_mma_light_applies(d / 16, ng, 1)) return 0;
+  return decode_mma_capacity<8>(cluster, ng, blocks, true);
 }
 
 // The split step of decode attention on the tensor cores (bfloat16, head_dim <= 128).

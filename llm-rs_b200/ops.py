@@ -248,14 +248,15 @@ def attn_decode_scratch_floats(n_dec: int, n_q_heads: int, head_dim: int, max_sp
 _decode_capacity = {}
 
 
-def attn_decode_capacity(head_dim: int, cluster: int, heads: int = 4, device=None) -> int:
+def attn_decode_capacity(head_dim: int, cluster: int, heads: int = 4, device=None, light: bool = False) -> int:
     """Blocks of the tensor-core decode attention kernel that the device holds at a time when they come in
-    thread-block clusters of ``cluster`` (1 to 16) and serve ``heads`` query heads per key head (at most 16)."""
-    key = (head_dim, cluster, heads, device)
+    thread-block clusters of ``cluster`` (1 to 16) and serve ``heads`` query heads per key head (at most 16).
+    ``light``: of the kernel with the ring of two tiles (``attn_decode(ring=2)``); 0 where it does not exist."""
+    key = (head_dim, cluster, heads, device, light)
     if key not in _decode_capacity:
         blocks = ctypes.c_int()
-        _check(_lib().llmrs_attn_decode_capacity(head_dim, cluster, heads, ctypes.byref(blocks)), "attn_decode_capacity",
-               launches=0)
+        fn = _lib().llmrs_attn_decode_capacity_light if light else _lib().llmrs_attn_decode_capacity
+        _check(fn(head_dim, cluster, heads, ctypes.byref(blocks)), "attn_decode_capacity", launches=0)
         _decode_capacity[key] = blocks.value
     return _decode_capacity[key]
 
@@ -270,14 +271,16 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
                 q_start: torch.Tensor, cached_len: torch.Tensor, block_table: torch.Tensor, scratch: torch.Tensor,
                 max_splits: int, split_keys: int, n_q_heads: int, n_kv_heads: int, head_dim: int, page_size: int,
                 window: int, scale: float, counters: Optional[torch.Tensor] = None,
-                then: Optional[torch.Tensor] = None) -> None:
+                then: Optional[torch.Tensor] = None, ring: int = 0) -> None:
     """Attention of single new tokens (``dec_reqs``: int32 request rows) over the paged cache,
     the keys cut into splits of ``split_keys`` and merged; ``scratch`` is float32 workspace of
     ``attn_decode_scratch_floats`` elements. (bfloat16 with head_dim <= 128 and at most 16 splits: the splits
     of a request and key head run as one thread-block cluster and merge through distributed shared memory,
     one kernel; else a second kernel merges them.) With ``counters`` (int32, at least n_dec * n_q_heads,
     all zero; the call leaves them zero) the tensor-core kernel merges the splits itself instead
-    of a second kernel doing it."""
+    of a second kernel doing it. ``ring`` = 2 asks for the tensor-core kernel with a ring of two tiles per warp, of
+    which three blocks fit an SM instead of two (head_dim 128, at most 8 query heads per key head; elsewhere it
+    changes nothing): for steps whose blocks then fit one wave and otherwise do not."""
     if then is not None:
         hint_next_weights(then, PREFETCH_BYTES_AFTER_ATTENTION)   # the weights of the product after attention
     _need(q, "q", contiguous=False)
@@ -294,6 +297,10 @@ def attn_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, dec_req
         _need(counters, "counters", torch.int32)
         if counters.numel() < n_dec * n_q_heads:
             raise KernelError(f"attn_decode counters hold {counters.numel()} ints, {n_dec * n_q_heads} needed")
+    if ring:
+        fn = _lib().llmrs_attn_decode_next_ring
+        fn.restype = None
+        fn(int(ring))
     _check(_lib().llmrs_attn_decode(
         _ptr(q), ctypes.c_longlong(_row_stride(q, "q")), _ptr(out), ctypes.c_longlong(_row_stride(out, "out")),
         _ptr(cache), _ptr(dec_reqs), n_dec, _ptr(q_start), _ptr(cached_len), _ptr(block_table), block_table.size(1),

@@ -35,7 +35,33 @@ MAX_CLUSTER = 16     # splits that the kernel merges itself
 PREFILL_TILE = 64    # queries per entry of the prefill attention kernels' tile list
 
 
+# A block of the kernel with the ring of two tiles (three blocks an SM) takes about this much longer than one of the
+# usual kernel (two blocks an SM, two tiles on their way per warp): it pays only where it saves a wave.
+LIGHT_COST = 1.3
+# LLMRS_ATTN_LIGHT=0 never takes that kernel.
+_ATTN_LIGHT = os.environ.get("LLMRS_ATTN_LIGHT", "1") != "0"
+
+
+def cut_keys_and_ring(length: int, units: int, capacity, capacity_light=None):
+    """``cut_keys`` for both kernels: (keys per split, ring) with ring 2 where the kernel with the ring of two tiles,
+    of which the device holds ``capacity_light(cluster)`` blocks (0: no such kernel), comes out cheaper."""
+    keys, cost, waves = _cut(length, units, capacity)
+    if capacity_light is not None and cost is not None and waves > 1 and capacity_light(1) > 0:
+        # Only where the usual kernel's blocks need more than one wave at every cut and the light kernel's fit one:
+        # one wave of the usual kernel beats one of the light one (batch 8: 3.66 against 3.70 ms a step), and so do
+        # its several waves the light kernel's several (batch 64, context 4,096: 9.75 against 9.93 ms).
+        keys2, cost2, waves2 = _cut(length, units, capacity_light)
+        if cost2 is not None and waves2 == 1 and cost2 * LIGHT_COST < cost:
+            return keys2, 2
+    return keys, 3
+
+
 def cut_keys(length: int, units: int, capacity) -> int:
+    """Keys per split for the usual kernel (see ``_cut``)."""
+    return _cut(length, units, capacity)[0]
+
+
+def _cut(length: int, units: int, capacity):
     """Keys per split for the tensor-core decode attention kernel: ``length`` keys at most per request,
     ``units`` (request, key head group) pairs, ``capacity(cluster)`` the blocks the device holds at a time in
     thread-block clusters of that size.
@@ -43,21 +69,23 @@ def cut_keys(length: int, units: int, capacity) -> int:
     Up to ``MAX_CLUSTER`` splits merge inside the kernel as a cluster, and the cluster's size decides how many
     blocks are held (on a B200 284 in clusters of 4, 264 in clusters of 8, ...). A step whose blocks need a
     second wave that stays nearly empty loses more than longer splits cost, so: the cut with the least
-    waves x (keys per split + a block's fixed cost); the fewest splits among equals."""
-    best_keys, best_cost, best_real = 0, None, 0
+    waves x (keys per split + a block's fixed cost); the fewest splits among equals. Returns the keys per split,
+    that cost and the waves (cost None: the cut for the merging kernel)."""
+    best_keys, best_cost, best_real, best_waves = 0, None, 0, 0
     for splits in range(1, MAX_CLUSTER + 1):
         keys = max(-(-(-(-length // splits)) // 64) * 64, 128)
         real = -(-length // keys)
         # (a wave that fills every slot was measured slow: the neighbouring kernels' blocks hold some)
         held = max(1, int(CAPACITY_USED * capacity(real)))
-        cost = -(-(real * units) // held) * (keys + FIXED_KEYS)
+        waves = -(-(real * units) // held)
+        cost = waves * (keys + FIXED_KEYS)
         if best_cost is None or cost < best_cost:
-            best_keys, best_cost, best_real = keys, cost, real
+            best_keys, best_cost, best_real, best_waves = keys, cost, real, waves
     if best_real == MAX_CLUSTER and best_keys > 1024 and 2 * MAX_CLUSTER * units <= capacity(1):
         # Few requests with long contexts: more, shorter splits and a second kernel that merges them.
         splits = min(64, capacity(1) // units)
-        return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048)
-    return best_keys
+        return min(max(-(-(-(-length // splits)) // 64) * 64, 128), 2048), None, 0
+    return best_keys, best_cost, best_waves
 
 
 def _sm_count(device) -> int:
@@ -181,9 +209,9 @@ class GQAttention(Mixer):
             return type(self.position).apply_unfused is PositionEncoding.apply_unfused
         return self.position.rotary_dim == 128 and cos_sin.dtype == torch.float32
 
-    def _choose_split(self, n_decode: int, max_kv_len: int, q: torch.Tensor) -> int:
-        """Keys per split of decode attention. The choice changes results by rounding only (every split is
-        merged in float32)."""
+    def _choose_split(self, n_decode: int, max_kv_len: int, q: torch.Tensor):
+        """(Keys per split of decode attention, ring of the kernel: see ``ops.attn_decode``). The choice changes
+        results by rounding only (every split is merged in float32)."""
         sms = _sm_count(q.device)
         groups = self.n_kv_heads * (-(-(self.n_heads // self.n_kv_heads) // 16))
         units = max(1, n_decode * groups)
@@ -192,8 +220,11 @@ class GQAttention(Mixer):
         if q.dtype != torch.bfloat16 or self.head_dim > 128:
             # The generic kernel: enough blocks to fill the GPU about twice.
             keys = -(-length // max(1, (2 * sms) // units))
-            return min(max(-(-keys // 64) * 64, 128), 1024)
-        return cut_keys(length, units, lambda cluster: ops.attn_decode_capacity(self.head_dim, cluster, heads, q.device))
+            return min(max(-(-keys // 64) * 64, 128), 1024), 3
+        return cut_keys_and_ring(
+            length, units, lambda cluster: ops.attn_decode_capacity(self.head_dim, cluster, heads, q.device),
+            (lambda cluster: ops.attn_decode_capacity(self.head_dim, cluster, heads, q.device, light=True))
+            if _ATTN_LIGHT else None)
 
     def takes_prenormed(self, n_tokens: int) -> bool:
         return self.qkv_proj.takes_prenormed(n_tokens) and self.q_proj.takes_prenormed(n_tokens)
@@ -239,7 +270,7 @@ class GQAttention(Mixer):
                              ctx.cached_len, table, nq, nkv, d, cache.page_size, self.window, self.scale,
                              prefer_tc=bool(plan.values["long_portions"]) and _ATTN_TC)
         if n_decode:
-            split_keys = self.split_keys or self._choose_split(n_decode, max_kv, q)
+            split_keys, ring = (self.split_keys, 3) if self.split_keys else self._choose_split(n_decode, max_kv, q)
             max_splits = max(1, -(-max_kv // split_keys))
             scratch = ctx.scratch("attn_decode", ops.attn_decode_scratch_floats(n_decode, nq, d, max_splits))
             # Up to eight splits form a thread-block cluster and merge inside the kernel; more are merged by
@@ -251,7 +282,8 @@ class GQAttention(Mixer):
             one_wave = n_decode * nkv * max_splits <= 2 * _sm_count(q.device)
             ops.attn_decode(q, out, cache.kv, plan.arrays["decode_reqs"], n_decode, ctx.q_start, ctx.cached_len, table,
                             scratch, max_splits, split_keys, nq, nkv, d, cache.page_size, self.window, self.scale,
-                            then=self.o_proj.weight if one_wave and self.o_proj.uses_tc(ctx.n_tokens) else None)
+                            then=self.o_proj.weight if one_wave and self.o_proj.uses_tc(ctx.n_tokens) else None,
+                            ring=ring if ring == 2 else 0)
         if next_norm is not None:
             return self.o_proj.forward_into_residual_for_norm(out, residual, *next_norm)
         if residual is not None:

@@ -360,9 +360,13 @@ def test_decode_attention_split_choice():
     assert all(128 <= held[s] <= 2 * 148 for s in held)
     for length in (100, 4096, 5000, 32768):
         for n in range(1, 41):
-            keys = att._choose_split(n, length, q)
+            keys, ring = att._choose_split(n, length, q)
             splits = -(-length // keys)
-            assert keys % 64 == 0 and keys >= 128
+            assert keys % 64 == 0 and keys >= 128 and ring in (2, 3)
+            if ring == 2:       # the kernel of which three blocks fit an SM: only where it saves a wave
+                light = int(CAPACITY_USED * ops.attn_decode_capacity(128, splits, 4, DEV, light=True))
+                assert light > held[splits] and -(-(splits * n * 8) // light) < -(-(splits * n * 8) // held[splits])
+                continue
             costs = {}
             for s in range(1, MAX_CLUSTER + 1):
                 k = max(-(-(-(-length // s)) // 64) * 64, 128)

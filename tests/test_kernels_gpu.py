@@ -263,6 +263,35 @@ def test_decode_attention_merged_by_large_clusters(nq, nkv, d, split_keys, lens)
     assert torch.allclose(got, want, atol=2.5e-2, rtol=2e-2), float((got - want).abs().max())
 
 
+@pytest.mark.parametrize("nq,nkv,lens,split_keys", [
+    (32, 8, [511, 300, 17, 0, 512], 512), (8, 2, [1000, 999], 256), (5, 1, [70], 128), (16, 1, [200, 90], 128)])
+def test_decode_attention_with_the_ring_of_two_tiles(nq, nkv, lens, split_keys):
+    """The kernel of which three blocks fit an SM (one tile on its way per warp instead of two), asked for per launch:
+    same results, and the request is used up by one launch. With 16 query heads per key head there is no such kernel
+    and the usual one runs."""
+    ops = _ops()
+    d, page = 128, 16
+    new = [1] * len(lens)
+    torch.manual_seed(nq + len(lens))
+    table, cache = _paged_setup(lens, new, nkv, d, page, torch.bfloat16, seed=5)
+    q = (torch.randn(len(lens), nq * d) * 1.5).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    want = _attention_reference(q, cache, table, lens, new, nq, nkv, d, page, 0, scale)
+    assert (ops.attn_decode_capacity(d, 1, nq // nkv, DEV, light=True) > ops.attn_decode_capacity(d, 1, nq // nkv, DEV)) == (nq // nkv <= 8)
+    dq, dc, dt = q.to(DEV), cache.to(DEV), table.to(DEV)
+    q_start = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    cached = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    dec = torch.arange(len(lens), dtype=torch.int32, device=DEV)
+    max_splits = -(-(max(lens) + 1) // split_keys)
+    for ring in (2, 0):
+        out = torch.full((len(lens), nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+        scratch = torch.full((ops.attn_decode_scratch_floats(len(lens), nq, d, max_splits),), float("nan"), device=DEV)
+        ops.attn_decode(dq, out, dc, dec, len(lens), q_start, cached, dt, scratch, max_splits, split_keys, nq, nkv, d, page,
+                        0, scale, ring=ring)
+        torch.cuda.synchronize()
+        assert torch.allclose(out.double().cpu(), want, atol=2.5e-2, rtol=2e-2), (ring, float((out.double().cpu() - want).abs().max()))
+
+
 def test_capacity_query_between_two_large_cluster_launches():
     """The capacity query (how many blocks the device holds in clusters of a size) sets the same kernel's
     shared-memory limit as the launcher: asked about small clusters between two launches with clusters of 16

@@ -2,7 +2,7 @@
 holds in thread-block clusters of each size: no GPU needed."""
 import pytest
 
-from llm_rs_b200.parts.attention import CAPACITY_USED, FIXED_KEYS, MAX_CLUSTER, cut_keys
+from llm_rs_b200.parts.attention import CAPACITY_USED, FIXED_KEYS, LIGHT_COST, MAX_CLUSTER, cut_keys, cut_keys_and_ring
 
 # Blocks of the decode kernel (heads of 128, 4 query heads per key head) that a B200 holds in clusters of 1..16.
 B200 = [296, 296, 279, 284, 280, 270, 259, 264, 270, 260, 231, 252, 221, 196, 210, 224]
@@ -60,3 +60,28 @@ def test_every_cut_is_the_cheapest_of_its_kind(length, units):
             real = splits_of(length, k)
             costs.append(-(-(real * units) // int(CAPACITY_USED * held(real))) * (k + FIXED_KEYS))
         assert -(-(splits * units) // int(CAPACITY_USED * held(splits))) * (keys + FIXED_KEYS) == min(costs)
+
+
+# The same for the kernel with the ring of two tiles per warp, of which three blocks fit an SM.
+B200_LIGHT = [444, 444, 420, 424, 420, 408, 392, 400, 396, 390, 352, 372, 338, 294, 315, 336]
+
+
+def held_light(cluster):
+    return B200_LIGHT[cluster - 1]
+
+
+@pytest.mark.parametrize("requests,ring", [(8, 3), (32, 3), (36, 3), (38, 2), (40, 2), (48, 2), (54, 2), (56, 3), (64, 3)])
+def test_the_light_kernel_is_taken_where_it_saves_a_wave(requests, ring):
+    """Contexts of 512 keys, eight key heads a request: up to 36 requests one wave of the usual kernel holds the
+    step's blocks; from 38 to 54 only the kernel with three blocks an SM does; from 56 on neither."""
+    keys, got = cut_keys_and_ring(512, requests * 8, held, held_light)
+    assert got == ring and keys % 64 == 0
+    if ring == 3:
+        assert keys == cut_keys(512, requests * 8, held)
+
+
+def test_without_a_light_kernel_nothing_changes():
+    for units in (8, 64, 320, 384, 1000):
+        assert cut_keys_and_ring(4096, units, held, lambda cluster: 0) == (cut_keys(4096, units, held), 3)
+        assert cut_keys_and_ring(4096, units, held) == (cut_keys(4096, units, held), 3)
+    assert LIGHT_COST > 1
