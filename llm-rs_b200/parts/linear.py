@@ -33,7 +33,8 @@ TC_MAX_TOKENS = int(os.environ.get("LLMRS_TC_MAX_TOKENS", "64"))
 # seconds under the power cap: 24.9 ms with the library's q|k|v, o and down products and the norm kernels, 25.6 ms
 # with this package's kernel and no norm kernels, 26.0 ms with it and the norm kernels; launched alone in a burst
 # the kernel is level with the library for q|k|v (72 us), 4 us behind for o (53 against 49, residual sum and the
-# next norm's input included, which cost the library path 14 us more) and 13 us behind for down (145 against 132).)
+# next norm's input included, which cost the library path 14 us more) and 13 us behind for down (145 against 132);
+# with o alone, o and down, or all three on it the step took 25.5-25.8, 25.8-26.1 and 25.5-25.9 ms against 25.1.)
 TC_MANY_TOKENS = int(os.environ.get("LLMRS_TC_MANY_TOKENS", "0"))
 
 
